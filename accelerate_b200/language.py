@@ -1,0 +1,724 @@
+"""Host-side mirror of the reference's array-language interface for the hot path.
+
+The reference's front end (``Data.Array.Accelerate.Language`` /
+``Data.Array.Accelerate.Prelude``) is a Haskell EDSL whose terms go through
+sharing recovery and fusion (``Data/Array/Accelerate/Trafo.hs:63-85``) before
+a backend sees them.  No Haskell toolchain exists where this backend is built
+and tested, so this module provides the same operators with the same argument
+order and meaning in Python, and produces the *post-fusion* form directly:
+
+* producers (``generate``/``map``/``zipWith``/``backpermute``/``fill`` ...) stay
+  *delayed* (an extent expression plus an index function) and are embedded into
+  their consumer, as ``Trafo/Fusion.hs:161-216`` arranges;
+* consumers (``fold*``, ``scan*``, ``permute``, ``stencil*``) become manifest
+  nodes of the program text handed to the backend.
+
+The result of building a term is the S-expression program text that both the
+B200 backend (``accelerate_b200.backend``) and the CPU oracle accept.
+"""
+from __future__ import annotations
+
+import itertools
+import numpy as np
+
+# ----------------------------------------------------------------------------
+# Types.  Scalars are strings; tuples are Python tuples of types.
+# ``Int`` is 64-bit (Array/Data.hs:380-384); ``Bool`` is a Word8 tag.
+# ----------------------------------------------------------------------------
+SCALARS = ("i8", "i16", "i32", "i64", "u8", "u16", "u32", "u64", "f32", "f64")
+NP_OF = {
+    "i8": np.int8, "i16": np.int16, "i32": np.int32, "i64": np.int64,
+    "u8": np.uint8, "u16": np.uint16, "u32": np.uint32, "u64": np.uint64,
+    "f32": np.float32, "f64": np.float64,
+}
+TY_OF_NP = {np.dtype(v): k for k, v in NP_OF.items()}
+TY_OF_NP[np.dtype(np.bool_)] = "u8"
+INT, BOOL = "i64", "u8"
+
+
+def is_float(t):
+    return t in ("f32", "f64")
+
+
+def is_scalar(t):
+    return isinstance(t, str)
+
+
+def ty_sx(t):
+    if is_scalar(t):
+        return t
+    return "(tup" + "".join(" " + ty_sx(c) for c in t) + ")"
+
+
+def flatten_ty(t):
+    if is_scalar(t):
+        return [t]
+    out = []
+    for c in t:
+        out += flatten_ty(c)
+    return out
+
+
+def shape_ty(rank):
+    return tuple([INT] * rank)
+
+
+_counter = itertools.count()
+
+
+def _fresh(prefix):
+    return f"{prefix}{next(_counter)}"
+
+
+def reset_names():
+    """Restart name generation (makes program text deterministic per trace)."""
+    global _counter
+    _counter = itertools.count()
+
+
+# ----------------------------------------------------------------------------
+# Scalar expressions (AST.hs:524-645 OpenExp; primitives AST.hs:661-753)
+# ----------------------------------------------------------------------------
+def _lit(t, v):
+    if is_float(t):
+        f = float(np.float32(v)) if t == "f32" else float(v)
+        if f != f:
+            s = "nan"
+        elif f in (float("inf"), float("-inf")):
+            s = "inf" if f > 0 else "-inf"
+        else:
+            s = f.hex()
+        return f"(const {t} {s})"
+    return f"(const {t} {int(NP_OF[t](v))})"
+
+
+class Exp:
+    """A typed scalar expression.  ``deps`` are the manifest arrays it reads."""
+
+    __slots__ = ("ty", "sx", "deps", "parts")
+    __array_priority__ = 1000
+
+    def __init__(self, ty, sx, deps=frozenset(), parts=None):
+        self.ty, self.sx, self.deps, self.parts = ty, sx, frozenset(deps), parts
+
+    # -- tuples ------------------------------------------------------------
+    def __getitem__(self, i):
+        if is_scalar(self.ty):
+            raise TypeError("projection from a scalar expression")
+        if self.parts is not None:
+            return self.parts[i]
+        return Exp(self.ty[i], f"(prj {i} {self.sx})", self.deps)
+
+    def __len__(self):
+        if is_scalar(self.ty):
+            raise TypeError("scalar expression has no length")
+        return len(self.ty)
+
+    def __iter__(self):
+        return (self[i] for i in range(len(self)))
+
+    # -- arithmetic --------------------------------------------------------
+    def _bin(self, op, other, swap=False, result=None):
+        o = lift(other, self.ty)
+        a, b = (o, self) if swap else (self, o)
+        if a.ty != b.ty:
+            raise TypeError(f"{op}: operand types differ: {a.ty} vs {b.ty}")
+        return Exp(result or a.ty, f"(prim {op} {a.ty} {a.sx} {b.sx})", a.deps | b.deps)
+
+    def _un(self, op, result=None):
+        return Exp(result or self.ty, f"(prim {op} {self.ty} {self.sx})", self.deps)
+
+    def __add__(self, o): return self._bin("add", o)
+    def __radd__(self, o): return self._bin("add", o, True)
+    def __sub__(self, o): return self._bin("sub", o)
+    def __rsub__(self, o): return self._bin("sub", o, True)
+    def __mul__(self, o): return self._bin("mul", o)
+    def __rmul__(self, o): return self._bin("mul", o, True)
+    def __neg__(self): return self._un("neg")
+    def __abs__(self): return self._un("abs")
+    def __truediv__(self, o): return self._bin("fdiv", o)
+    def __rtruediv__(self, o): return self._bin("fdiv", o, True)
+    def __floordiv__(self, o): return self._bin("idiv", o)      # Haskell `div`
+    def __mod__(self, o): return self._bin("mod", o)            # Haskell `mod`
+    def __and__(self, o): return self._bin("band", o)
+    def __or__(self, o): return self._bin("bor", o)
+    def __xor__(self, o): return self._bin("bxor", o)
+    def __invert__(self): return self._un("bnot")
+    def __lshift__(self, o): return _shift("shl", self, o)
+    def __rshift__(self, o): return _shift("shr", self, o)
+    def __pow__(self, o): return self._bin("fpow", o)
+    def __lt__(self, o): return self._bin("lt", o, result=BOOL)
+    def __gt__(self, o): return self._bin("gt", o, result=BOOL)
+    def __le__(self, o): return self._bin("le", o, result=BOOL)
+    def __ge__(self, o): return self._bin("ge", o, result=BOOL)
+    def eq(self, o): return self._bin("eq", o, result=BOOL)
+    def ne(self, o): return self._bin("ne", o, result=BOOL)
+    __hash__ = object.__hash__
+
+    def __bool__(self):
+        raise TypeError("an embedded expression has no Python truth value; use cond()")
+
+
+def _shift(op, a, n):
+    n = lift(n, INT)
+    return Exp(a.ty, f"(prim {op} {a.ty} {a.sx} {n.sx})", a.deps | n.deps)
+
+
+def constant(v, ty=None):
+    """``constant`` (Smart.hs): embed a host value."""
+    if isinstance(v, Exp):
+        return v
+    if isinstance(v, tuple):
+        tys = ty if ty is not None else [None] * len(v)
+        return tup(*[constant(x, t) for x, t in zip(v, tys)])
+    if ty is None:
+        if isinstance(v, (bool, np.bool_)):
+            ty = BOOL
+        elif isinstance(v, (int, np.integer)) and not isinstance(v, np.generic):
+            ty = INT
+        elif isinstance(v, float):
+            ty = "f64"
+        else:
+            ty = TY_OF_NP[np.dtype(type(v))]
+    return Exp(ty, _lit(ty, v))
+
+
+def lift(v, ty):
+    """Embed ``v`` at type ``ty`` unless it is an expression already."""
+    if isinstance(v, Exp):
+        return v
+    if isinstance(v, tuple):
+        return tup(*[lift(x, t) for x, t in zip(v, ty)])
+    return Exp(ty, _lit(ty, v))
+
+
+def tup(*xs):
+    xs = [x if isinstance(x, Exp) else constant(x) for x in xs]
+    deps = frozenset().union(*[x.deps for x in xs]) if xs else frozenset()
+    return Exp(tuple(x.ty for x in xs), "(tup" + "".join(" " + x.sx for x in xs) + ")", deps, parts=list(xs))
+
+
+def index(*ix):
+    """``Z :. i :. j`` — outermost first, innermost last."""
+    return tup(*[lift(i, INT) for i in ix])
+
+
+index0 = index()
+
+
+def let_(e, body):
+    """Explicit sharing of a scalar sub-expression."""
+    v = _fresh("v")
+    r = body(Exp(e.ty, f"(var {v})", e.deps))
+    return Exp(r.ty, f"(let {v} {e.sx} {r.sx})", e.deps | r.deps)
+
+
+def cond(c, t, e):
+    t = t if isinstance(t, Exp) else constant(t)
+    e = lift(e, t.ty)
+    if t.ty != e.ty:
+        raise TypeError("cond: branch types differ")
+    return Exp(t.ty, f"(cond {c.sx} {t.sx} {e.sx})", c.deps | t.deps | e.deps)
+
+
+def while_(p, f, x):
+    x = x if isinstance(x, Exp) else constant(x)
+    pv, fv = _fresh("v"), _fresh("v")
+    pe = p(Exp(x.ty, f"(var {pv})"))
+    fe = f(Exp(x.ty, f"(var {fv})"))
+    sx = (f"(while (lam (({pv} {ty_sx(x.ty)})) {pe.sx}) (lam (({fv} {ty_sx(x.ty)})) {fe.sx}) {x.sx})")
+    return Exp(x.ty, sx, x.deps | pe.deps | fe.deps)
+
+
+def _prim1(op):
+    def f(x):
+        return x._un(op)
+    f.__name__ = op
+    return f
+
+
+for _n in ("sin cos tan asin acos atan sinh cosh tanh asinh acosh atanh exp sqrt log recip").split():
+    globals()[_n] = _prim1(_n)
+signum = _prim1("sig")
+
+
+def is_nan(x): return x._un("isnan", BOOL)
+def is_infinite(x): return x._un("isinf", BOOL)
+def pop_count(x): return x._un("popcount", INT)
+def count_leading_zeros(x): return x._un("clz", INT)
+def count_trailing_zeros(x): return x._un("ctz", INT)
+def quot(a, b): return a._bin("quot", b)
+def rem(a, b): return a._bin("rem", b)
+def div(a, b): return a._bin("idiv", b)
+def mod(a, b): return a._bin("mod", b)
+def atan2(a, b): return a._bin("atan2", b)
+def log_base(b, x): return b._bin("logbase", x)
+def rotate_l(a, n): return _shift("rotl", a, n)
+def rotate_r(a, n): return _shift("rotr", a, n)
+
+
+def max_(a, b):
+    a = a if isinstance(a, Exp) else lift(a, b.ty)
+    return a._bin("max", b)
+
+
+def min_(a, b):
+    a = a if isinstance(a, Exp) else lift(a, b.ty)
+    return a._bin("min", b)
+
+
+def land(a, b): return Exp(BOOL, f"(prim land u8 {a.sx} {b.sx})", a.deps | b.deps)
+def lor(a, b): return Exp(BOOL, f"(prim lor u8 {a.sx} {b.sx})", a.deps | b.deps)
+def lnot(a): return Exp(BOOL, f"(prim lnot u8 {a.sx})", a.deps)
+
+
+def _conv(op, x, to):
+    return Exp(to, f"(prim {op} {x.ty} {to} {x.sx})", x.deps)
+
+
+def from_integral(x, to): return _conv("fromintegral", x, to)
+def to_floating(x, to): return _conv("tofloating", x, to)
+def truncate(x, to=INT): return _conv("truncate", x, to)
+def round_(x, to=INT): return _conv("round", x, to)
+def floor(x, to=INT): return _conv("floor", x, to)
+def ceiling(x, to=INT): return _conv("ceiling", x, to)
+def min_bound(t): return Exp(t, f"(minbound {t})")
+def max_bound(t): return Exp(t, f"(maxbound {t})")
+def pi(t): return Exp(t, f"(pi {t})")
+def bitcast(x, to): return Exp(to, f"(coerce {x.ty} {to} {x.sx})", x.deps)
+def undef(t): return Exp(t, f"(undef {ty_sx(t)})")
+
+
+def Just_(ix):
+    """``Just_ ix`` as the PrimMaybe encoding (tag, ix)  (AST.hs:201-202)."""
+    ix = ix if isinstance(ix, Exp) else index(*ix)
+    return tup(Exp(BOOL, "(const u8 1)"), ix)
+
+
+def Nothing_(rank):
+    return tup(Exp(BOOL, "(const u8 0)"), undef(shape_ty(rank)))
+
+
+def shape_size(sh): return Exp(INT, f"(shapesize {sh.sx})", sh.deps)
+def to_index(sh, ix): return Exp(INT, f"(toindex {sh.sx} {ix.sx})", sh.deps | ix.deps)
+def from_index(sh, i):
+    i = lift(i, INT)
+    return Exp(sh.ty, f"(fromindex {sh.sx} {i.sx})", sh.deps | i.deps)
+
+
+def _lam(params, body):
+    ps = " ".join(f"({n} {ty_sx(t)})" for n, t in params)
+    return f"(lam ({ps}) {body.sx})"
+
+
+def _fun(f, *tys):
+    """Reify a Python function over expressions as ``(lam ...)`` text."""
+    names = [_fresh("v") for _ in tys]
+    args = [Exp(t, f"(var {n})") for n, t in zip(names, tys)]
+    body = f(*args)
+    if not isinstance(body, Exp):
+        body = tup(*body) if isinstance(body, tuple) else constant(body)
+    return _lam(list(zip(names, tys)), body), body
+
+
+# ----------------------------------------------------------------------------
+# Arrays
+# ----------------------------------------------------------------------------
+class Node:
+    """A manifest array (program input or an executed node)."""
+
+    def __init__(self, kind, rank, elt, sx=None, deps=(), nouts=1, data=None):
+        self.kind, self.rank, self.elt, self.sx = kind, rank, elt, sx
+        self.deps = list(deps)
+        self.nouts = nouts
+        self.names = [_fresh("a") for _ in range(nouts)]
+        self.data = data        # inputs: (shape, [leaf ndarrays]) or None for a parameter
+        self.out_ranks = [rank]
+        self.out_elts = [elt]
+
+
+class Acc:
+    """An array term: manifest (``node``) or delayed (``extent`` + ``fn``)."""
+
+    def __init__(self, rank, elt, node=None, out=0, extent=None, fn=None):
+        self.rank, self.elt, self.node, self.out = rank, elt, node, out
+        self._extent, self._fn = extent, fn
+
+    @property
+    def manifest(self):
+        return self.node is not None
+
+    @property
+    def name(self):
+        return self.node.names[self.out]
+
+    # shape / indexing -----------------------------------------------------
+    @property
+    def shape(self):
+        if self.manifest:
+            return Exp(shape_ty(self.rank), f"(shape {self.name})", {self.node})
+        return self._extent
+
+    def size(self):
+        return shape_size(self.shape)
+
+    def __getitem__(self, ix):
+        """``arr ! ix``"""
+        if not isinstance(ix, Exp):
+            ix = index(*ix) if isinstance(ix, tuple) else index(ix)
+        if self.manifest:
+            return Exp(self.elt, f"(index {self.name} {ix.sx})", ix.deps | {self.node})
+        return self._fn(ix)
+
+    def linear(self, i):
+        """``arr !! i``"""
+        i = lift(i, INT)
+        if self.manifest:
+            return Exp(self.elt, f"(lindex {self.name} {i.sx})", i.deps | {self.node})
+        return self._fn(from_index(self.shape, i))
+
+    def operand(self):
+        """Text of this array as a consumer's operand, plus its dependencies."""
+        if self.manifest:
+            return f"(manifest {self.name})", {self.node}
+        lam, body = _fun(self._fn, shape_ty(self.rank))
+        return f"(delayed {self._extent.sx} {lam})", body.deps | self._extent.deps
+
+
+def use(a, elt=None):
+    """``use``: embed host array(s).  A tuple/list of equal-shape ndarrays is an
+    array of tuples in struct-of-arrays form (Array/Data.hs:95-98)."""
+    if isinstance(a, Acc):
+        return a
+    if isinstance(a, (tuple, list)):
+        leaves = [np.ascontiguousarray(x) for x in a]
+        if elt is None:
+            elt = tuple(TY_OF_NP[x.dtype] for x in leaves)
+    else:
+        a = np.ascontiguousarray(a)
+        leaves = [a.view(np.uint8) if a.dtype == np.bool_ else a]
+        elt = elt or TY_OF_NP[a.dtype]
+    sh = tuple(int(d) for d in leaves[0].shape)
+    node = Node("in", len(sh), elt, data=(sh, leaves))
+    return Acc(len(sh), elt, node=node)
+
+
+def param(rank, elt):
+    """An array parameter of a program (bound at run time)."""
+    return Acc(rank, elt, node=Node("in", rank, elt))
+
+
+def _mk(kind, rank, elt, sx, deps, nouts=1, ranks=None, elts=None):
+    node = Node(kind, rank, elt, sx=sx, deps=[d for d in deps], nouts=nouts)
+    if ranks:
+        node.out_ranks, node.out_elts = ranks, elts
+    return node
+
+
+def _shape_exp(sh, rank=None):
+    if isinstance(sh, Exp):
+        return sh
+    if isinstance(sh, int):
+        sh = (sh,)
+    return index(*sh)
+
+
+def intersect(a, b):
+    """Shape.hs:81-91"""
+    if a.sx == b.sx:
+        return a
+    return tup(*[min_(x, y) for x, y in zip(a, b)])
+
+
+# producers (stay delayed) ----------------------------------------------------
+def generate(sh, f, elt=None):
+    sh = _shape_exp(sh)
+    rank = len(sh.ty)
+    if elt is None:
+        probe = f(Exp(shape_ty(rank), "(var _probe)"))
+        probe = probe if isinstance(probe, Exp) else (tup(*probe) if isinstance(probe, tuple) else constant(probe))
+        elt = probe.ty
+
+    def fn(ix):
+        r = f(ix)
+        return r if isinstance(r, Exp) else (tup(*r) if isinstance(r, tuple) else lift(r, elt))
+    return Acc(rank, elt, extent=sh, fn=fn)
+
+
+def fill(sh, v):
+    v = v if isinstance(v, Exp) else constant(v)
+    return generate(sh, lambda ix: v, v.ty)
+
+
+def map_(f, a):
+    a = use(a)
+    return generate(a.shape, lambda ix: f(a[ix]))
+
+
+def zipWith(f, a, b):
+    a, b = use(a), use(b)
+    return generate(intersect(a.shape, b.shape), lambda ix: f(a[ix], b[ix]))
+
+
+def zip_(a, b):
+    return zipWith(lambda x, y: tup(x, y), a, b)
+
+
+def backpermute(sh, p, a):
+    a = use(a)
+
+    def fn(ix):
+        j = p(ix)
+        return a[j if isinstance(j, Exp) else index(*j)]
+    return generate(_shape_exp(sh), fn, a.elt)
+
+
+def enumFromN(sh, x):
+    sh = _shape_exp(sh)
+    x = x if isinstance(x, Exp) else constant(x)
+    return generate(sh, lambda ix: x + from_integral(to_index(sh, ix), x.ty) if x.ty != INT else x + to_index(sh, ix), x.ty)
+
+
+def reshape(sh, a):
+    a = compute(use(a))
+    sh = _shape_exp(sh)
+    node = _mk("reshape", len(sh.ty), a.elt, f"(reshape {sh.sx} {a.name})", sh.deps | {a.node})
+    return Acc(len(sh.ty), a.elt, node=node)
+
+
+def compute(a):
+    """Force a delayed array to be materialised (``compute``, Prelude.hs:2177)."""
+    a = use(a)
+    if a.manifest:
+        return a
+    lam, body = _fun(a._fn, shape_ty(a.rank))
+    sx = f"(generate {ty_sx(a.elt)} {a._extent.sx} {lam})"
+    node = _mk("generate", a.rank, a.elt, sx, body.deps | a._extent.deps)
+    return Acc(a.rank, a.elt, node=node)
+
+
+def unit(e):
+    e = e if isinstance(e, Exp) else constant(e)
+    return generate(index0, lambda ix: e, e.ty)
+
+
+def the(a):
+    return use(a)[index0]
+
+
+# consumers (manifest nodes) -------------------------------------------------
+def _fold_like(kind, f, z, a, seg=None):
+    a = use(a)
+    lam, fb = _fun(f, a.elt, a.elt)
+    op, deps = a.operand()
+    deps = deps | fb.deps
+    zs = ""
+    if z is not None:
+        z = lift(z, a.elt)
+        zs = " " + z.sx
+        deps = deps | z.deps
+    extra = ""
+    if seg is not None:
+        sop, sdeps = seg.operand()
+        extra = " " + sop
+        deps = deps | sdeps
+    return f"({kind} {ty_sx(a.elt)} {lam}{zs} {op}{extra})", deps, a
+
+
+def fold(f, z, a):
+    """``fold`` (Language.hs:523): reduce the innermost dimension."""
+    sx, deps, a = _fold_like("fold", f, z, a)
+    return Acc(a.rank - 1, a.elt, node=_mk("fold", a.rank - 1, a.elt, sx, deps))
+
+
+def fold1(f, a):
+    """``fold1`` (Language.hs:541)."""
+    return fold(f, None, a)
+
+
+def foldSeg_(f, z, a, offsets):
+    """``foldSeg'`` (Language.hs:561): the descriptor holds segment OFFSETS."""
+    offsets = use(offsets)
+    sx, deps, a = _fold_like("foldseg", f, z, a, seg=offsets)
+    return Acc(a.rank, a.elt, node=_mk("foldseg", a.rank, a.elt, sx, deps))
+
+
+def fold1Seg_(f, a, offsets):
+    return foldSeg_(f, None, a, offsets)
+
+
+def foldSeg(f, z, a, lengths):
+    """``foldSeg`` (Prelude.hs:710-717): lengths are turned into offsets with
+    ``scanl (+) 0``."""
+    lengths = use(lengths)
+    return foldSeg_(f, z, a, scanl(lambda x, y: x + y, lift(0, lengths.elt), lengths))
+
+
+def fold1Seg(f, a, lengths):
+    """``fold1Seg`` (Prelude.hs:737-743)."""
+    lengths = use(lengths)
+    return fold1Seg_(f, a, scanl(lambda x, y: x + y, lift(0, lengths.elt), lengths))
+
+
+def _scan(kind, f, z, a):
+    sx, deps, a = _fold_like(kind, f, z, a)
+    return Acc(a.rank, a.elt, node=_mk(kind, a.rank, a.elt, sx, deps))
+
+
+def scanl(f, z, a): return _scan("scanl", f, z, a)      # Language.hs:607
+def scanl1(f, a): return _scan("scanl", f, None, a)     # Language.hs:660
+def scanr(f, z, a): return _scan("scanr", f, z, a)      # Language.hs:673
+def scanr1(f, a): return _scan("scanr", f, None, a)     # Language.hs:690
+
+
+def _scan_prime(kind, f, z, a):
+    sx, deps, a = _fold_like(kind, f, z, a)
+    node = _mk(kind, a.rank, a.elt, sx, deps, nouts=2, ranks=[a.rank, a.rank - 1], elts=[a.elt, a.elt])
+    return Acc(a.rank, a.elt, node=node, out=0), Acc(a.rank - 1, a.elt, node=node, out=1)
+
+
+def scanl_prime(f, z, a): return _scan_prime("scanl'", f, z, a)   # scanl', Language.hs:640
+def scanr_prime(f, z, a): return _scan_prime("scanr'", f, z, a)   # scanr', Language.hs:683
+
+
+def permute(f, defaults, p, a):
+    """``permute`` (Language.hs:792): ``f new old``; ``p`` returns ``Just_ ix`` /
+    ``Nothing_``.  The defaults are always manifest (Fusion.hs:213)."""
+    a = use(a)
+    defaults = compute(use(defaults))
+    lam, fb = _fun(f, a.elt, a.elt)
+
+    def pf(ix):
+        r = p(ix)
+        return r
+    plam, pb = _fun(pf, shape_ty(a.rank))
+    op, deps = a.operand()
+    deps = deps | fb.deps | pb.deps | {defaults.node}
+    sx = f"(permute {ty_sx(a.elt)} {lam} {defaults.name} {plam} {op})"
+    return Acc(defaults.rank, a.elt, node=_mk("permute", defaults.rank, a.elt, sx, deps))
+
+
+def scatter(to, defaults, xs):
+    """``scatter`` (Prelude.hs): ``permute const``, unique targets assumed."""
+    to, xs = use(to), use(xs)
+    return permute(lambda new, old: new, defaults, lambda ix: Just_(index(to[ix])), xs)
+
+
+class Boundary:
+    def __init__(self, kind, value=None):
+        self.kind, self.value = kind, value
+
+
+clamp, mirror, wrap = Boundary("clamp"), Boundary("mirror"), Boundary("wrap")
+
+
+def function(f):
+    """``function`` boundary (Language.hs:1060-1070)."""
+    return Boundary("function", f)
+
+
+def constant_boundary(v):
+    """``AST.Constant`` boundary (AST.hs:480-485)."""
+    return Boundary("constant", v)
+
+
+def _stencil_arg(extent, elt):
+    """Nested-tuple type of a neighbourhood: outermost dimension outermost."""
+    t = elt
+    for e in reversed(extent):
+        t = tuple([t] * e)
+    return t
+
+
+def _nest(e, depth):
+    """Turn an expression of nested-tuple type into nested Python tuples."""
+    if depth == 0:
+        return e
+    return tuple(_nest(e[i], depth - 1) for i in range(len(e.ty)))
+
+
+def _boundary_sx(b, rank, elt):
+    if b.kind in ("clamp", "mirror", "wrap"):
+        return b.kind, frozenset()
+    if b.kind == "constant":
+        v = lift(b.value, elt)
+        return f"(constant {v.sx})", v.deps
+    lam, body = _fun(lambda ix: lift(b.value(ix), elt), shape_ty(rank))
+    return f"(function {lam})", body.deps
+
+
+def stencil(f, boundary, a, extent=None):
+    """``stencil`` (Language.hs:956).  ``extent`` gives the neighbourhood size
+    per dimension (3/5/7/9; default 3 everywhere); ``f`` receives nested Python
+    tuples, outermost dimension outermost, offsets -r..+r."""
+    a = use(a)
+    extent = tuple(extent or [3] * a.rank)
+    st = _stencil_arg(extent, a.elt)
+    lam, fb = _fun(lambda s: f(_nest(s, a.rank)), st)
+    bsx, bdeps = _boundary_sx(boundary, a.rank, a.elt)
+    op, deps = a.operand()
+    relt = fb.ty
+    sx = f"(stencil {ty_sx(relt)} (stencilr {' '.join(str(e) for e in extent)}) {lam} {bsx} {op})"
+    return Acc(a.rank, relt, node=_mk("stencil", a.rank, relt, sx, deps | fb.deps | bdeps))
+
+
+def stencil2(f, b1, a1, b2, a2, extent1=None, extent2=None):
+    """``stencil2`` (Language.hs:975); result extent is the intersection."""
+    a1, a2 = use(a1), use(a2)
+    e1 = tuple(extent1 or [3] * a1.rank)
+    e2 = tuple(extent2 or [3] * a2.rank)
+    lam, fb = _fun(lambda s, t: f(_nest(s, a1.rank), _nest(t, a2.rank)), _stencil_arg(e1, a1.elt), _stencil_arg(e2, a2.elt))
+    s1, d1 = _boundary_sx(b1, a1.rank, a1.elt)
+    s2, d2 = _boundary_sx(b2, a2.rank, a2.elt)
+    o1, dd1 = a1.operand()
+    o2, dd2 = a2.operand()
+    relt = fb.ty
+    sx = (f"(stencil2 {ty_sx(relt)} (stencilr {' '.join(str(e) for e in e1)}) (stencilr {' '.join(str(e) for e in e2)}) "
+          f"{lam} {s1} {o1} {s2} {o2})")
+    return Acc(a1.rank, relt, node=_mk("stencil2", a1.rank, relt, sx, fb.deps | d1 | d2 | dd1 | dd2))
+
+
+# derived operations (Prelude.hs:826-884) --------------------------------------
+def sum_(a): a = use(a); return fold(lambda x, y: x + y, lift(0, a.elt), a)
+def product(a): a = use(a); return fold(lambda x, y: x * y, lift(1, a.elt), a)
+def maximum(a): return fold1(max_, a)
+def minimum(a): return fold1(min_, a)
+
+
+# ----------------------------------------------------------------------------
+# Program assembly
+# ----------------------------------------------------------------------------
+class Program:
+    """Program text plus the description of its inputs and outputs."""
+
+    def __init__(self, text, inputs, outputs):
+        self.text = text
+        self.inputs = inputs          # list of Node (kind "in")
+        self.outputs = outputs        # list of (rank, elt)
+
+
+def build_program(results):
+    """Collect every node the results depend on, in dependency order."""
+    results = [compute(use(r)) for r in (results if isinstance(results, (list, tuple)) else [results])]
+    order, seen = [], set()
+
+    def visit(n):
+        if id(n) in seen:
+            return
+        seen.add(id(n))
+        for d in n.deps:
+            visit(d)
+        order.append(n)
+    for r in results:
+        visit(r.node)
+    inputs = [n for n in order if n.kind == "in"]
+    lines = ["(program"]
+    for n in inputs:
+        lines.append(f"  (in {n.names[0]} (array {n.rank} {ty_sx(n.elt)}))")
+    for n in order:
+        if n.kind == "in":
+            continue
+        lhs = n.names[0] if n.nouts == 1 else "(" + " ".join(n.names) + ")"
+        lines.append(f"  (let {lhs} {n.sx})")
+    lines.append("  (out " + " ".join(r.name for r in results) + "))")
+    return Program("\n".join(lines), inputs, [(r.rank, r.elt) for r in results])
