@@ -1,0 +1,280 @@
+"""``run`` / ``runN`` on a B200 through the C-ABI library (``libaccb200.so``).
+
+Mirrors the reference backend interface (``Interpreter.hs:93-126``): ``run``
+evaluates a closed array term, ``runN`` turns a function over arrays into a
+function over host arrays that is compiled once and reused.  There is no CPU
+fallback: without the built library or without a GPU every entry point raises.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+
+import numpy as np
+
+from . import language as L
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+_LIB_PATH = os.path.join(_HERE, "libaccb200.so")
+_lib = None
+
+ERRORS = {1: "parse", 2: "type", 3: "compile", 4: "cuda", 5: "bounds", 6: "unsupported", 7: "argument", 8: "timeout"}
+
+
+class B200Error(RuntimeError):
+    """Failure reported by the backend (the Haskell wrapper would throw the
+    corresponding ``boundsError`` / ``internalError``, Error.hs:77-85)."""
+
+    def __init__(self, code, message):
+        super().__init__(f"[{ERRORS.get(code, code)}] {message}")
+        self.code = code
+
+
+def lib():
+    """The loaded C-ABI library; raises if it has not been built."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(_LIB_PATH):
+            raise B200Error(4, f"{_LIB_PATH} is missing: build it with `python -m accelerate_b200.build` (no CPU fallback exists)")
+        l = ctypes.CDLL(_LIB_PATH)
+        vp, cp, i64p, u64p = ctypes.c_void_p, ctypes.c_char_p, ctypes.POINTER(ctypes.c_int64), ctypes.POINTER(ctypes.c_uint64)
+        l.b200_last_error.restype = cp
+        l.b200_ctx_create.argtypes = [ctypes.c_int, ctypes.c_uint32, ctypes.POINTER(vp)]
+        l.b200_ctx_destroy.argtypes = [vp]
+        l.b200_ctx_destroy.restype = None
+        l.b200_array_new.argtypes = [vp, cp, ctypes.c_int, i64p, u64p]
+        l.b200_array_wrap.argtypes = [vp, cp, ctypes.c_int, i64p, ctypes.POINTER(vp), u64p]
+        l.b200_array_upload.argtypes = [vp, ctypes.c_uint64, ctypes.c_int, vp, ctypes.c_size_t]
+        l.b200_array_download.argtypes = [vp, ctypes.c_uint64, ctypes.c_int, vp, ctypes.c_size_t]
+        l.b200_array_free.argtypes = [vp, ctypes.c_uint64]
+        l.b200_array_rank.argtypes = [vp, ctypes.c_uint64, ctypes.POINTER(ctypes.c_int)]
+        l.b200_array_shape.argtypes = [vp, ctypes.c_uint64, i64p]
+        l.b200_array_num_leaves.argtypes = [vp, ctypes.c_uint64, ctypes.POINTER(ctypes.c_int)]
+        l.b200_array_leaf_type.argtypes = [vp, ctypes.c_uint64, ctypes.c_int, ctypes.POINTER(cp)]
+        l.b200_array_devptr.argtypes = [vp, ctypes.c_uint64, ctypes.c_int, ctypes.POINTER(vp)]
+        l.b200_program_load.argtypes = [vp, cp, ctypes.c_size_t, ctypes.POINTER(vp)]
+        l.b200_program_free.argtypes = [vp]
+        l.b200_program_free.restype = None
+        l.b200_program_num_inputs.argtypes = [vp, ctypes.POINTER(ctypes.c_int)]
+        l.b200_program_num_outputs.argtypes = [vp, ctypes.POINTER(ctypes.c_int)]
+        l.b200_program_run.argtypes = [vp, u64p, ctypes.c_int, u64p, ctypes.c_int]
+        l.b200_sync.argtypes = [vp]
+        l.b200_stats.argtypes = [vp, i64p]
+        l.b200_ctx_stream.argtypes = [vp, ctypes.POINTER(vp)]
+        l.b200_compile_check.argtypes = [cp, ctypes.c_size_t, ctypes.c_char_p, ctypes.c_size_t]
+        l.b200_kernel_source.argtypes = [cp, ctypes.c_size_t, ctypes.c_int, ctypes.c_char_p, ctypes.c_size_t]
+        _lib = l
+    return _lib
+
+
+def _check(rc):
+    if rc != 0:
+        raise B200Error(rc, lib().b200_last_error().decode(errors="replace"))
+
+
+def compile_check(text):
+    """NVRTC-compile every kernel of ``text`` for sm_100a; needs no GPU."""
+    log = ctypes.create_string_buffer(1 << 16)
+    b = text.encode()
+    rc = lib().b200_compile_check(b, len(b), log, len(log))
+    if rc != 0:
+        raise B200Error(rc, log.value.decode(errors="replace"))
+    return log.value.decode()
+
+
+def kernel_source(text, node=0):
+    buf = ctypes.create_string_buffer(1 << 20)
+    b = text.encode()
+    _check(lib().b200_kernel_source(b, len(b), node, buf, len(buf)))
+    return buf.value.decode()
+
+
+class DeviceArray:
+    """A device-resident array (struct-of-arrays) owned by a context."""
+
+    def __init__(self, ctx, ident, elt=None):
+        self.ctx, self.id = ctx, ident
+        l = lib()
+        r = ctypes.c_int()
+        _check(l.b200_array_rank(ctx.h, ident, ctypes.byref(r)))
+        sh = (ctypes.c_int64 * max(1, r.value))()
+        _check(l.b200_array_shape(ctx.h, ident, sh))
+        self.shape = tuple(int(sh[i]) for i in range(r.value))
+        n = ctypes.c_int()
+        _check(l.b200_array_num_leaves(ctx.h, ident, ctypes.byref(n)))
+        self.leaf_types = []
+        for k in range(n.value):
+            s = ctypes.c_char_p()
+            _check(l.b200_array_leaf_type(ctx.h, ident, k, ctypes.byref(s)))
+            self.leaf_types.append(s.value.decode())
+        self.elt = elt if elt is not None else (self.leaf_types[0] if n.value == 1 else tuple(self.leaf_types))
+
+    def devptr(self, leaf=0):
+        p = ctypes.c_void_p()
+        _check(lib().b200_array_devptr(self.ctx.h, self.id, leaf, ctypes.byref(p)))
+        return p.value or 0
+
+    def upload(self, leaves):
+        for k, a in enumerate(leaves):
+            a = np.ascontiguousarray(a)
+            _check(lib().b200_array_upload(self.ctx.h, self.id, k, a.ctypes.data, a.nbytes))
+        return self
+
+    def download(self, out=None):
+        """Host copy: an ndarray (scalar elements) or a tuple of ndarrays."""
+        res = []
+        for k, t in enumerate(self.leaf_types):
+            a = out[k] if out is not None else np.empty(self.shape, dtype=L.NP_OF[t])
+            _check(lib().b200_array_download(self.ctx.h, self.id, k, a.ctypes.data, a.nbytes))
+            res.append(a)
+        return res[0] if L.is_scalar(self.elt) else tuple(res)
+
+    def free(self):
+        if self.id is not None and self.ctx.h:
+            lib().b200_array_free(self.ctx.h, self.id)
+            self.id = None
+
+    def __del__(self):
+        try:
+            self.free()
+        except Exception:
+            pass
+
+
+class Context:
+    """A backend handle: one GPU, one stream, a kernel cache."""
+
+    def __init__(self, device=0):
+        self.h = ctypes.c_void_p()
+        _check(lib().b200_ctx_create(device, 0, ctypes.byref(self.h)))
+        self.device = device
+        self._programs = {}
+
+    def close(self):
+        if self.h:
+            for p in self._programs.values():
+                lib().b200_program_free(p)
+            self._programs = {}
+            lib().b200_ctx_destroy(self.h)
+            self.h = ctypes.c_void_p()
+
+    # arrays ---------------------------------------------------------------
+    def array(self, elt, shape):
+        ident = ctypes.c_uint64()
+        sh = (ctypes.c_int64 * max(1, len(shape)))(*shape)
+        _check(lib().b200_array_new(self.h, L.ty_sx(elt).encode(), len(shape), sh, ctypes.byref(ident)))
+        return DeviceArray(self, ident.value, elt)
+
+    def from_host(self, a, elt=None):
+        """Upload an ndarray, or a tuple of equal-shape ndarrays (array of tuples)."""
+        leaves = [np.ascontiguousarray(x) for x in (a if isinstance(a, (tuple, list)) else [a])]
+        leaves = [x.view(np.uint8) if x.dtype == np.bool_ else x for x in leaves]
+        if elt is None:
+            elt = tuple(L.TY_OF_NP[x.dtype] for x in leaves) if isinstance(a, (tuple, list)) else L.TY_OF_NP[leaves[0].dtype]
+        return self.array(elt, leaves[0].shape).upload(leaves)
+
+    def wrap(self, elt, shape, ptrs):
+        """Adopt caller-owned device memory (one pointer per leaf)."""
+        ident = ctypes.c_uint64()
+        sh = (ctypes.c_int64 * max(1, len(shape)))(*shape)
+        arr = (ctypes.c_void_p * len(ptrs))(*ptrs)
+        _check(lib().b200_array_wrap(self.h, L.ty_sx(elt).encode(), len(shape), sh, arr, ctypes.byref(ident)))
+        return DeviceArray(self, ident.value, elt)
+
+    # programs ---------------------------------------------------------------
+    def load(self, text):
+        p = self._programs.get(text)
+        if p is None:
+            p = ctypes.c_void_p()
+            b = text.encode()
+            _check(lib().b200_program_load(self.h, b, len(b), ctypes.byref(p)))
+            self._programs[text] = p
+        return p
+
+    def execute(self, text, inputs, n_out):
+        """Run program ``text`` on device arrays; returns device arrays."""
+        p = self.load(text)
+        ins = (ctypes.c_uint64 * max(1, len(inputs)))(*[a.id for a in inputs])
+        outs = (ctypes.c_uint64 * max(1, n_out))()
+        _check(lib().b200_program_run(p, ins, len(inputs), outs, n_out))
+        return [DeviceArray(self, outs[k]) for k in range(n_out)]
+
+    def sync(self):
+        _check(lib().b200_sync(self.h))
+
+    def stats(self):
+        out = (ctypes.c_int64 * 8)()
+        _check(lib().b200_stats(self.h, out))
+        keys = ["launches", "h2d_bytes", "d2h_bytes", "compiled", "mem_hits", "disk_hits", "allocated_bytes", "runs"]
+        return dict(zip(keys, [int(v) for v in out]))
+
+    def stream(self):
+        s = ctypes.c_void_p()
+        _check(lib().b200_ctx_stream(self.h, ctypes.byref(s)))
+        return s.value or 0
+
+
+_default = None
+
+
+def default_context():
+    global _default
+    if _default is None:
+        dev = int(os.environ.get("LOCAL_RANK", "0")) if "ACCELERATE_B200_DEVICE" not in os.environ else int(os.environ["ACCELERATE_B200_DEVICE"])
+        _default = Context(dev)
+    return _default
+
+
+def run_program(prog, host_inputs, ctx=None):
+    """Upload, execute, download.  ``host_inputs``: list of ``(shape, [leaves])``."""
+    ctx = ctx or default_context()
+    ins = []
+    for n, (shape, leaves) in zip(prog.inputs, host_inputs):
+        ins.append(ctx.array(n.elt, shape).upload(leaves))
+    outs = ctx.execute(prog.text, ins, len(prog.outputs))
+    res = []
+    for o, (_, elt) in zip(outs, prog.outputs):
+        o.elt = elt
+        res.append(o.download())
+    return res
+
+
+def run(acc, ctx=None):
+    """``run :: Arrays a => Acc a -> a`` (Interpreter.hs:93)."""
+    single = not isinstance(acc, (list, tuple))
+    prog = L.build_program(acc)
+    res = run_program(prog, [n.data for n in prog.inputs], ctx)
+    return res[0] if single else res
+
+
+def runN(f, ctx=None):
+    """``runN`` (Interpreter.hs:110-126): the program is built and loaded on the
+    first call for given argument types and reused afterwards."""
+    cache = {}
+
+    def go(*arrays):
+        arrays = [a if isinstance(a, (tuple, list)) else np.ascontiguousarray(a) for a in arrays]
+        sig = tuple((tuple(x.dtype.str for x in a), a[0].ndim) if isinstance(a, (tuple, list)) else (a.dtype.str, a.ndim) for a in arrays)
+        ent = cache.get(sig)
+        if ent is None:
+            L.reset_names()
+            params = []
+            for a in arrays:
+                if isinstance(a, (tuple, list)):
+                    params.append(L.param(a[0].ndim, tuple(L.TY_OF_NP[x.dtype] for x in a)))
+                else:
+                    params.append(L.param(a.ndim, L.TY_OF_NP[a.dtype]))
+            res = f(*params)
+            single = not isinstance(res, (list, tuple))
+            prog = L.build_program(res)
+            order = [params.index(next(q for q in params if q.node is n)) for n in prog.inputs]
+            ent = cache[sig] = (prog, order, single)
+        prog, order, single = ent
+        host = []
+        for k in order:
+            a = arrays[k]
+            leaves = list(a) if isinstance(a, (tuple, list)) else [a]
+            host.append((tuple(leaves[0].shape), leaves))
+        out = run_program(prog, host, ctx)
+        return out[0] if single else out
+    return go

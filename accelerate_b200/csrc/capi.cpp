@@ -1,0 +1,350 @@
+// extern "C" surface of the backend (declared in include/accelerate_b200.h).
+#include <cstring>
+#include <string>
+
+#include "../../include/accelerate_b200.h"
+#include "runtime.hpp"
+
+using namespace accb200;
+
+struct b200_ctx { Ctx c; };
+struct b200_program { Program p; };
+
+namespace {
+thread_local std::string g_error;
+
+int fail(const Error& e) {
+  g_error = e.what();
+  return e.code;
+}
+int fail_std(const std::exception& e) {
+  g_error = e.what();
+  return B200_ERR_ARG;
+}
+#define B200_TRY try {
+#define B200_END                     \
+  return B200_OK;                    \
+  }                                  \
+  catch (const Error& e) { return fail(e); } \
+  catch (const std::exception& e) { return fail_std(e); }
+
+DevArrayP lookup(Ctx& c, uint64_t id) {
+  auto it = c.arrays.find(id);
+  if (it == c.arrays.end()) throw Error(B200_ERR_ARG, "unknown array id " + std::to_string(id));
+  return it->second;
+}
+Type parse_type_text(const char* s) {
+  Sx x = parse_sexp(s, strlen(s));
+  return parse_type(x);
+}
+void build_nodes(Program& p) {
+  p.nodes.resize(p.ir->nodes.size());
+  for (size_t i = 0; i < p.ir->nodes.size(); ++i) {
+    if (p.ir->nodes[i].kind == N_RESHAPE) continue;
+    p.nodes[i].glue = build_glue(p.ir->nodes[i], p.ir->arrays);
+    p.nodes[i].has_glue = true;
+  }
+}
+}  // namespace
+
+extern "C" {
+
+const char* b200_last_error(void) { return g_error.c_str(); }
+
+int b200_ctx_create(int device, uint32_t flags, b200_ctx** out) {
+  (void)flags;
+  B200_TRY
+  if (!out) throw Error(B200_ERR_ARG, "null output pointer");
+  int ndev = 0;
+  cudaError_t e = cudaGetDeviceCount(&ndev);
+  if (e != cudaSuccess || ndev == 0)
+    throw Error(B200_ERR_CUDA, std::string("no CUDA device available (") + cudaGetErrorString(e) + "); this backend has no CPU fallback");
+  if (device < 0 || device >= ndev) throw Error(B200_ERR_ARG, "device index out of range");
+  auto h = std::make_unique<b200_ctx>();
+  Ctx& c = h->c;
+  c.device = device;
+  c.check(cudaSetDevice(device), "cudaSetDevice");
+  c.check(cudaFree(nullptr), "context creation");
+  c.drv.load();
+  cudaDeviceProp prop;
+  c.check(cudaGetDeviceProperties(&prop, device), "cudaGetDeviceProperties");
+  if (prop.major != 10) throw Error(B200_ERR_CUDA, "this backend is built for sm_100a (B200) only; found compute capability " +
+                                                    std::to_string(prop.major) + "." + std::to_string(prop.minor));
+  c.sm_count = prop.multiProcessorCount;
+  c.check(cudaStreamCreateWithFlags(&c.stream, cudaStreamNonBlocking), "cudaStreamCreate");
+  // keep freed blocks in the stream-ordered pool instead of returning them to the driver
+  cudaMemPool_t pool;
+  c.check(cudaDeviceGetDefaultMemPool(&pool, device), "cudaDeviceGetDefaultMemPool");
+  uint64_t threshold = ~0ull;
+  c.check(cudaMemPoolSetAttribute(pool, cudaMemPoolAttrReleaseThreshold, &threshold), "cudaMemPoolSetAttribute");
+  c.check(cudaMalloc((void**)&c.d_words, 64), "cudaMalloc");
+  c.check(cudaMemset(c.d_words, 0, 64), "cudaMemset");
+  if (const char* s = getenv("ACCELERATE_B200_SPIN_LIMIT")) c.spin_limit = atoll(s);
+  *out = h.release();
+  B200_END
+}
+
+void b200_ctx_destroy(b200_ctx* ctx) {
+  if (!ctx) return;
+  Ctx& c = ctx->c;
+  cudaSetDevice(c.device);
+  cudaStreamSynchronize(c.stream);
+  {
+    std::lock_guard<std::mutex> g(c.mu);
+    c.arrays.clear();
+    for (auto& k : c.kernels)
+      if (k.second.module) c.drv.ModuleUnload(k.second.module);
+    c.kernels.clear();
+    if (c.scan_scratch) cudaFreeAsync(c.scan_scratch, c.stream);
+  }
+  cudaStreamSynchronize(c.stream);
+  cudaFree(c.d_words);
+  cudaStreamDestroy(c.stream);
+  delete ctx;
+}
+
+int b200_array_new(b200_ctx* ctx, const char* elt_type, int rank, const int64_t* shape, uint64_t* id) {
+  B200_TRY
+  if (!ctx || !elt_type || !id || rank < 0 || (rank > 0 && !shape)) throw Error(B200_ERR_ARG, "bad argument");
+  Ctx& c = ctx->c;
+  std::lock_guard<std::mutex> g(c.mu);
+  c.check(cudaSetDevice(c.device), "cudaSetDevice");
+  DevArrayP a = c.new_array(parse_type_text(elt_type), std::vector<int64_t>(shape, shape + rank));
+  *id = c.next_id++;
+  c.arrays[*id] = a;
+  B200_END
+}
+
+int b200_array_wrap(b200_ctx* ctx, const char* elt_type, int rank, const int64_t* shape, void* const* leaf_ptrs, uint64_t* id) {
+  B200_TRY
+  if (!ctx || !elt_type || !id || rank < 0 || (rank > 0 && !shape) || !leaf_ptrs) throw Error(B200_ERR_ARG, "bad argument");
+  Ctx& c = ctx->c;
+  std::lock_guard<std::mutex> g(c.mu);
+  auto a = std::make_shared<DevArray>();
+  a->elt = parse_type_text(elt_type);
+  a->leaf_ty = a->elt.leaves();
+  a->shape.assign(shape, shape + rank);
+  const int64_t n = a->size();
+  for (size_t l = 0; l < a->leaf_ty.size(); ++l) {
+    auto b = std::make_shared<Buffer>();
+    b->ctx = &c;
+    b->ptr = leaf_ptrs[l];
+    b->bytes = (size_t)n * ty_bytes[a->leaf_ty[l]];
+    b->owned = false;
+    a->leaf.push_back(b);
+  }
+  *id = c.next_id++;
+  c.arrays[*id] = a;
+  B200_END
+}
+
+int b200_array_upload(b200_ctx* ctx, uint64_t id, int leaf, const void* host, size_t bytes) {
+  B200_TRY
+  if (!ctx) throw Error(B200_ERR_ARG, "null context");
+  Ctx& c = ctx->c;
+  std::lock_guard<std::mutex> g(c.mu);
+  c.check(cudaSetDevice(c.device), "cudaSetDevice");
+  DevArrayP a = lookup(c, id);
+  if (leaf < 0 || (size_t)leaf >= a->leaf.size()) throw Error(B200_ERR_ARG, "leaf index out of range");
+  if (bytes != a->leaf[leaf]->bytes) throw Error(B200_ERR_ARG, "upload size does not match the array");
+  if (bytes) {
+    if (!host) throw Error(B200_ERR_ARG, "null host pointer");
+    c.check(cudaMemcpyAsync(a->leaf[leaf]->ptr, host, bytes, cudaMemcpyHostToDevice, c.stream), "cudaMemcpyAsync(H2D)");
+    // the caller's buffer may be reused or collected as soon as we return
+    c.check(cudaStreamSynchronize(c.stream), "cudaStreamSynchronize");
+    c.h2d += (long long)bytes;
+  }
+  B200_END
+}
+
+static int check_device_status(Ctx& c) {
+  int words[4] = {0, 0, 0, 0};
+  c.check(cudaMemcpyAsync(words, c.d_words, 4, cudaMemcpyDeviceToHost, c.stream), "cudaMemcpyAsync");
+  c.check(cudaStreamSynchronize(c.stream), "cudaStreamSynchronize");
+  if (words[0] != 0) {
+    c.check(cudaMemsetAsync(c.d_words, 0, 16, c.stream), "cudaMemsetAsync");  // also re-arms the ticket counters
+    if (words[0] == 1001) throw Error(B200_ERR_BOUNDS, "empty segment");
+    throw Error(B200_ERR_TIMEOUT, "a device-side wait exceeded its limit (status " + std::to_string(words[0]) + "); results are incomplete");
+  }
+  return 0;
+}
+
+int b200_array_download(b200_ctx* ctx, uint64_t id, int leaf, void* host, size_t bytes) {
+  B200_TRY
+  if (!ctx) throw Error(B200_ERR_ARG, "null context");
+  Ctx& c = ctx->c;
+  std::lock_guard<std::mutex> g(c.mu);
+  c.check(cudaSetDevice(c.device), "cudaSetDevice");
+  DevArrayP a = lookup(c, id);
+  if (leaf < 0 || (size_t)leaf >= a->leaf.size()) throw Error(B200_ERR_ARG, "leaf index out of range");
+  if (bytes != a->leaf[leaf]->bytes) throw Error(B200_ERR_ARG, "download size does not match the array");
+  if (bytes) {
+    if (!host) throw Error(B200_ERR_ARG, "null host pointer");
+    c.check(cudaMemcpyAsync(host, a->leaf[leaf]->ptr, bytes, cudaMemcpyDeviceToHost, c.stream), "cudaMemcpyAsync(D2H)");
+    c.d2h += (long long)bytes;
+  }
+  check_device_status(c);
+  B200_END
+}
+
+int b200_array_free(b200_ctx* ctx, uint64_t id) {
+  B200_TRY
+  if (!ctx) throw Error(B200_ERR_ARG, "null context");
+  Ctx& c = ctx->c;
+  std::lock_guard<std::mutex> g(c.mu);
+  if (!c.arrays.erase(id)) throw Error(B200_ERR_ARG, "unknown array id " + std::to_string(id));
+  B200_END
+}
+
+int b200_array_rank(b200_ctx* ctx, uint64_t id, int* rank) {
+  B200_TRY
+  std::lock_guard<std::mutex> g(ctx->c.mu);
+  *rank = (int)lookup(ctx->c, id)->shape.size();
+  B200_END
+}
+int b200_array_shape(b200_ctx* ctx, uint64_t id, int64_t* shape) {
+  B200_TRY
+  std::lock_guard<std::mutex> g(ctx->c.mu);
+  DevArrayP a = lookup(ctx->c, id);
+  for (size_t d = 0; d < a->shape.size(); ++d) shape[d] = a->shape[d];
+  B200_END
+}
+int b200_array_num_leaves(b200_ctx* ctx, uint64_t id, int* n) {
+  B200_TRY
+  std::lock_guard<std::mutex> g(ctx->c.mu);
+  *n = (int)lookup(ctx->c, id)->leaf.size();
+  B200_END
+}
+int b200_array_leaf_type(b200_ctx* ctx, uint64_t id, int leaf, const char** name) {
+  B200_TRY
+  std::lock_guard<std::mutex> g(ctx->c.mu);
+  DevArrayP a = lookup(ctx->c, id);
+  if (leaf < 0 || (size_t)leaf >= a->leaf_ty.size()) throw Error(B200_ERR_ARG, "leaf index out of range");
+  *name = ty_name[a->leaf_ty[leaf]];
+  B200_END
+}
+int b200_array_devptr(b200_ctx* ctx, uint64_t id, int leaf, void** ptr) {
+  B200_TRY
+  std::lock_guard<std::mutex> g(ctx->c.mu);
+  DevArrayP a = lookup(ctx->c, id);
+  if (leaf < 0 || (size_t)leaf >= a->leaf.size()) throw Error(B200_ERR_ARG, "leaf index out of range");
+  *ptr = a->leaf[leaf]->ptr;
+  B200_END
+}
+
+int b200_program_load(b200_ctx* ctx, const char* text, size_t len, b200_program** out) {
+  B200_TRY
+  if (!ctx || !text || !out) throw Error(B200_ERR_ARG, "bad argument");
+  auto h = std::make_unique<b200_program>();
+  h->p.ctx = &ctx->c;
+  h->p.ir = parse_program(text, len);
+  build_nodes(h->p);
+  *out = h.release();
+  B200_END
+}
+void b200_program_free(b200_program* prog) { delete prog; }
+int b200_program_num_inputs(b200_program* prog, int* n) {
+  B200_TRY
+  *n = (int)prog->p.ir->inputs.size();
+  B200_END
+}
+int b200_program_num_outputs(b200_program* prog, int* n) {
+  B200_TRY
+  *n = (int)prog->p.ir->outputs.size();
+  B200_END
+}
+
+int b200_program_run(b200_program* prog, const uint64_t* in_ids, int n_in, uint64_t* out_ids, int n_out) {
+  B200_TRY
+  if (!prog) throw Error(B200_ERR_ARG, "null program");
+  Ctx& c = *prog->p.ctx;
+  std::lock_guard<std::mutex> g(c.mu);
+  c.check(cudaSetDevice(c.device), "cudaSetDevice");
+  std::vector<DevArrayP> ins, outs;
+  for (int k = 0; k < n_in; ++k) ins.push_back(lookup(c, in_ids[k]));
+  prog->p.run(ins, outs);
+  if ((int)outs.size() != n_out) throw Error(B200_ERR_ARG, "program yields " + std::to_string(outs.size()) + " arrays");
+  for (int k = 0; k < n_out; ++k) {
+    out_ids[k] = c.next_id++;
+    c.arrays[out_ids[k]] = outs[k];
+  }
+  B200_END
+}
+
+int b200_sync(b200_ctx* ctx) {
+  B200_TRY
+  if (!ctx) throw Error(B200_ERR_ARG, "null context");
+  Ctx& c = ctx->c;
+  std::lock_guard<std::mutex> g(c.mu);
+  c.check(cudaSetDevice(c.device), "cudaSetDevice");
+  check_device_status(c);
+  B200_END
+}
+
+int b200_stats(b200_ctx* ctx, int64_t out[8]) {
+  B200_TRY
+  Ctx& c = ctx->c;
+  out[0] = c.launches;
+  out[1] = c.h2d;
+  out[2] = c.d2h;
+  out[3] = c.cstats.compiled;
+  out[4] = c.mem_hits;
+  out[5] = c.cstats.disk_hits;
+  out[6] = c.allocated;
+  out[7] = c.runs;
+  B200_END
+}
+
+int b200_ctx_stream(b200_ctx* ctx, void** stream) {
+  B200_TRY
+  *stream = (void*)ctx->c.stream;
+  B200_END
+}
+
+int b200_compile_check(const char* text, size_t len, char* log, size_t log_len) {
+  std::string msg;
+  int rc = B200_OK;
+  try {
+    Program p;
+    p.ir = parse_program(text, len);
+    build_nodes(p);
+    for (size_t i = 0; i < p.ir->nodes.size(); ++i) {
+      if (!p.nodes[i].has_glue) continue;
+      for (auto& v : default_variants(p.ir->nodes[i], p.nodes[i].glue)) {
+        std::string src = assemble_source(p.nodes[i].glue, v.first, v.second);
+        compile_to_cubin(src, v.first, nullptr);
+        msg += "ok " + v.first + " (" + std::to_string(src.size()) + " bytes of source)\n";
+      }
+    }
+  } catch (const Error& e) {
+    msg += e.what();
+    rc = fail(e);
+  } catch (const std::exception& e) {
+    msg += e.what();
+    rc = fail_std(e);
+  }
+  if (log && log_len) {
+    size_t n = std::min(log_len - 1, msg.size());
+    memcpy(log, msg.data() + (msg.size() - n), n);
+    log[n] = 0;
+  }
+  return rc;
+}
+
+int b200_kernel_source(const char* text, size_t len, int node, char* out, size_t out_len) {
+  B200_TRY
+  Program p;
+  p.ir = parse_program(text, len);
+  build_nodes(p);
+  if (node < 0 || (size_t)node >= p.nodes.size() || !p.nodes[node].has_glue) throw Error(B200_ERR_ARG, "no such kernel node");
+  auto vs = default_variants(p.ir->nodes[node], p.nodes[node].glue);
+  std::string src = assemble_source(p.nodes[node].glue, vs[0].first, vs[0].second);
+  if (out && out_len) {
+    size_t n = std::min(out_len - 1, src.size());
+    memcpy(out, src.data(), n);
+    out[n] = 0;
+  }
+  B200_END
+}
+
+}  // extern "C"

@@ -1,0 +1,743 @@
+// Device arrays, kernel lookup, host-side extent evaluation and node launchers.
+#include "runtime.hpp"
+
+#include <algorithm>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <sstream>
+
+namespace accb200 {
+
+// ---- driver -----------------------------------------------------------------------------
+void Driver::load() {
+  auto get = [](const char* name) -> void* {
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult qr;
+    cudaError_t e = cudaGetDriverEntryPoint(name, &fn, cudaEnableDefault, &qr);
+    if (e != cudaSuccess || !fn) throw Error(B200_ERR_CUDA, std::string("CUDA driver entry point '") + name + "' is unavailable");
+    return fn;
+  };
+  ModuleLoadData = (decltype(ModuleLoadData))get("cuModuleLoadData");
+  ModuleUnload = (decltype(ModuleUnload))get("cuModuleUnload");
+  ModuleGetFunction = (decltype(ModuleGetFunction))get("cuModuleGetFunction");
+  LaunchKernel = (decltype(LaunchKernel))get("cuLaunchKernel");
+  FuncSetAttribute = (decltype(FuncSetAttribute))get("cuFuncSetAttribute");
+  OccupancyMaxActiveBlocksPerMultiprocessor =
+      (decltype(OccupancyMaxActiveBlocksPerMultiprocessor))get("cuOccupancyMaxActiveBlocksPerMultiprocessor");
+  GetErrorString = (decltype(GetErrorString))get("cuGetErrorString");
+}
+
+// ---- context ------------------------------------------------------------------------------
+void Ctx::check(cudaError_t e, const char* what) {
+  if (e != cudaSuccess) throw Error(B200_ERR_CUDA, std::string(what) + ": " + cudaGetErrorString(e));
+}
+void Ctx::check(CUresult e, const char* what) {
+  if (e != CUDA_SUCCESS) {
+    const char* s = nullptr;
+    if (drv.GetErrorString) drv.GetErrorString(e, &s);
+    throw Error(B200_ERR_CUDA, std::string(what) + ": " + (s ? s : "unknown driver error"));
+  }
+}
+
+Buffer::~Buffer() {
+  if (owned && ptr && ctx) {
+    cudaSetDevice(ctx->device);
+    cudaFreeAsync(ptr, ctx->stream);
+    ctx->allocated -= (long long)bytes;
+  }
+}
+
+std::shared_ptr<Buffer> Ctx::alloc(size_t bytes) {
+  auto b = std::make_shared<Buffer>();
+  b->ctx = this;
+  b->bytes = bytes;
+  if (bytes) {
+    check(cudaMallocAsync(&b->ptr, bytes, stream), "cudaMallocAsync");
+    allocated += (long long)bytes;
+  }
+  return b;
+}
+
+int64_t DevArray::size() const {
+  int64_t n = 1;
+  for (int64_t d : shape) {
+    if (d <= 0) return 0;
+    n *= d;
+  }
+  return n;
+}
+bool DevArray::aligned16() const {
+  for (auto& b : leaf)
+    if (((uintptr_t)b->ptr & 15) != 0) return false;
+  return true;
+}
+
+DevArrayP Ctx::new_array(const Type& elt, const std::vector<int64_t>& shape) {
+  auto a = std::make_shared<DevArray>();
+  a->elt = elt;
+  a->leaf_ty = elt.leaves();
+  a->shape = shape;
+  const int64_t n = a->size();
+  for (Ty t : a->leaf_ty) a->leaf.push_back(alloc((size_t)n * ty_bytes[t]));
+  return a;
+}
+
+CompiledKernel& Ctx::kernel(const std::string& source, const std::string& entry, int threads, size_t dyn_smem) {
+  const std::string key = content_hash(source) + ":" + entry;
+  auto it = kernels.find(key);
+  if (it != kernels.end()) {
+    mem_hits++;
+    return it->second;
+  }
+  std::string cubin = compile_to_cubin(source, entry, &cstats);
+  CompiledKernel k;
+  check(drv.ModuleLoadData(&k.module, cubin.data()), "cuModuleLoadData");
+  check(drv.ModuleGetFunction(&k.fn, k.module, entry.c_str()), "cuModuleGetFunction");
+  if (dyn_smem > 48 * 1024)
+    check(drv.FuncSetAttribute(k.fn, CU_FUNC_ATTRIBUTE_MAX_DYNAMIC_SHARED_SIZE_BYTES, (int)dyn_smem), "cuFuncSetAttribute");
+  int nb = 0;
+  check(drv.OccupancyMaxActiveBlocksPerMultiprocessor(&nb, k.fn, threads, dyn_smem), "cuOccupancyMaxActiveBlocksPerMultiprocessor");
+  k.max_blocks_per_sm = std::max(1, nb);
+  return kernels.emplace(key, k).first->second;
+}
+
+void* Ctx::scan_descriptors(size_t bytes) {
+  // status words of a fresh (zeroed) buffer never match an epoch >= 1
+  if (bytes > scan_scratch_bytes || scan_epoch >= (1u << 29)) {
+    if (scan_scratch) check(cudaFreeAsync(scan_scratch, stream), "cudaFreeAsync");
+    size_t want = std::max(bytes, (size_t)1 << 20);
+    check(cudaMallocAsync(&scan_scratch, want, stream), "cudaMallocAsync");
+    check(cudaMemsetAsync(scan_scratch, 0, want, stream), "cudaMemsetAsync");
+    scan_scratch_bytes = want;
+    scan_epoch = 0;
+  }
+  ++scan_epoch;
+  return scan_scratch;
+}
+
+// ---- source assembly -------------------------------------------------------------------------
+std::string assemble_source(const Glue& g, const std::string& skeleton, const std::map<std::string, std::string>& variant) {
+  std::ostringstream o;
+  o << prelude_source() << "\n";
+  for (auto& d : g.defines) o << "#define " << d.first << " " << d.second << "\n";
+  for (auto& d : variant) o << "#define " << d.first << " " << d.second << "\n";
+  if (skeleton == "stencil") o << skeleton_source("stencil_pre") << "\n";
+  o << g.code << "\n" << skeleton_source(skeleton) << "\n";
+  return o.str();
+}
+
+namespace {
+
+struct StencilTile { int t0, t1, t2, threads; };
+StencilTile stencil_tile(int rank) {
+  if (rank == 1) return {1, 1, 2048, 256};
+  if (rank == 2) return {1, 32, 128, 256};
+  return {4, 8, 64, 256};
+}
+std::map<std::string, std::string> stencil_variant(int rank) {
+  StencilTile t = stencil_tile(rank);
+  return {{"ST_T0", std::to_string(t.t0)}, {"ST_T1", std::to_string(t.t1)}, {"ST_T2", std::to_string(t.t2)},
+          {"ST_THREADS", std::to_string(t.threads)}};
+}
+
+}  // namespace
+
+std::vector<std::pair<std::string, std::map<std::string, std::string>>> default_variants(const Node& n, const Glue& g) {
+  std::vector<std::pair<std::string, std::map<std::string, std::string>>> v;
+  switch (n.kind) {
+    case N_GENERATE: v.push_back({"elementwise", {}}); break;
+    case N_FOLD:
+      v.push_back({"fold", {{"FOLD_G", "32"}}});
+      v.push_back({"fold", {{"FOLD_G", "4"}}});
+      break;
+    case N_FOLDSEG: v.push_back({"foldseg", {{"FOLDSEG_G", "32"}}}); break;
+    case N_SCAN: case N_SCAN2: v.push_back({"scan", {}}); break;
+    case N_PERMUTE: {
+      v.push_back({"permute", {}});
+      const std::string& m = g.defines.at("PERMUTE_MODE");
+      if (m.find("ATOMIC") != std::string::npos) v.push_back({"permute", {{"PERMUTE_SMEM", "1"}, {"PERMUTE_THREADS", "1024"}}});
+      break;
+    }
+    case N_STENCIL: case N_STENCIL2: v.push_back({"stencil", stencil_variant(n.d[0].rank)}); break;
+    case N_RESHAPE: break;
+  }
+  return v;
+}
+
+// ---- host-side evaluation of closed scalar expressions (extents, sizes) ----------------------
+namespace {
+
+struct HVal {
+  Type ty;
+  std::vector<int64_t> i;   // integer leaves (also Bool)
+  std::vector<double> f;    // floating leaves (parallel vector; the unused one is 0)
+};
+
+struct HostEval {
+  Ctx* ctx;
+  const std::map<std::string, DevArrayP>* env;
+  std::vector<std::pair<std::string, HVal>> vars;
+
+  const DevArray& array(const std::string& n) {
+    auto it = env->find(n);
+    if (it == env->end() || !it->second) throw Error(B200_ERR_ARG, "array '" + n + "' is not bound");
+    return *it->second;
+  }
+  static int64_t wrap(Ty t, uint64_t v) {
+    switch (t) {
+      case I8: return (int8_t)v; case I16: return (int16_t)v; case I32: return (int32_t)v;
+      case U8: return (uint8_t)v; case U16: return (uint16_t)v; case U32: return (uint32_t)v;
+      default: return (int64_t)v;
+    }
+  }
+  HVal scalar_i(Ty t, int64_t v) { HVal r; r.ty = Type::scalar(t); r.i = {v}; r.f = {0}; return r; }
+  HVal scalar_f(Ty t, double v) { HVal r; r.ty = Type::scalar(t); r.i = {0}; r.f = {v}; return r; }
+  HVal read(const DevArray& a, int64_t lin) {
+    if (lin < 0 || lin >= a.size()) throw Error(B200_ERR_BOUNDS, "index out of bounds");
+    HVal r;
+    r.ty = a.elt;
+    for (size_t l = 0; l < a.leaf_ty.size(); ++l) {
+      Ty t = a.leaf_ty[l];
+      unsigned char buf[8] = {0};
+      ctx->check(cudaMemcpyAsync(buf, (char*)a.leaf[l]->ptr + lin * ty_bytes[t], ty_bytes[t], cudaMemcpyDeviceToHost, ctx->stream), "cudaMemcpyAsync");
+      ctx->check(cudaStreamSynchronize(ctx->stream), "cudaStreamSynchronize");
+      ctx->d2h += ty_bytes[t];
+      if (t == F32) { float v; memcpy(&v, buf, 4); r.i.push_back(0); r.f.push_back(v); }
+      else if (t == F64) { double v; memcpy(&v, buf, 8); r.i.push_back(0); r.f.push_back(v); }
+      else { uint64_t v = 0; memcpy(&v, buf, ty_bytes[t]); r.i.push_back(wrap(t, v)); r.f.push_back(0); }
+    }
+    return r;
+  }
+  HVal eval(const Expr& e) {
+    switch (e.kind) {
+      case X_CONST: {
+        Ty t = e.ty.s;
+        if (ty_is_float(t)) return scalar_f(t, e.lit == "inf" ? 1e308 * 10 : (e.lit == "-inf" ? -1e308 * 10 : strtod(e.lit.c_str(), nullptr)));
+        if (ty_is_signed(t)) return scalar_i(t, wrap(t, (uint64_t)strtoll(e.lit.c_str(), nullptr, 10)));
+        return scalar_i(t, wrap(t, strtoull(e.lit.c_str(), nullptr, 10)));
+      }
+      case X_VAR:
+        for (size_t k = vars.size(); k-- > 0;)
+          if (vars[k].first == e.name) return vars[k].second;
+        throw Error(B200_ERR_TYPE, "unbound variable in host expression");
+      case X_LET: {
+        vars.emplace_back(e.name, eval(*e.a[0]));
+        HVal r = eval(*e.a[1]);
+        vars.pop_back();
+        return r;
+      }
+      case X_TUP: {
+        HVal r;
+        r.ty = e.ty;
+        for (auto& c : e.a) {
+          HVal v = eval(*c);
+          r.i.insert(r.i.end(), v.i.begin(), v.i.end());
+          r.f.insert(r.f.end(), v.f.begin(), v.f.end());
+        }
+        return r;
+      }
+      case X_PRJ: {
+        HVal v = eval(*e.a[0]);
+        size_t off = 0;
+        for (int k = 0; k < e.n; ++k) off += v.ty.e[k].nleaves();
+        size_t cnt = v.ty.e[e.n].nleaves();
+        HVal r;
+        r.ty = e.ty;
+        r.i.assign(v.i.begin() + off, v.i.begin() + off + cnt);
+        r.f.assign(v.f.begin() + off, v.f.begin() + off + cnt);
+        return r;
+      }
+      case X_COND: return eval(*e.a[0]).i[0] != 0 ? eval(*e.a[1]) : eval(*e.a[2]);
+      case X_SHAPE: {
+        const DevArray& a = array(e.name);
+        HVal r;
+        r.ty = e.ty;
+        r.i = a.shape;
+        r.f.assign(a.shape.size(), 0);
+        return r;
+      }
+      case X_SHAPESIZE: {
+        HVal s = eval(*e.a[0]);
+        int64_t n = 1;
+        for (int64_t d : s.i) n = d <= 0 ? 0 : n * d;
+        for (int64_t d : s.i) if (d <= 0) n = 0;
+        return scalar_i(I64, n);
+      }
+      case X_TOINDEX: {
+        HVal sh = eval(*e.a[0]), ix = eval(*e.a[1]);
+        int64_t r = 0;
+        for (size_t d = 0; d < sh.i.size(); ++d) r = r * sh.i[d] + ix.i[d];
+        return scalar_i(I64, r);
+      }
+      case X_FROMINDEX: {
+        HVal sh = eval(*e.a[0]);
+        int64_t i = eval(*e.a[1]).i[0];
+        HVal r;
+        r.ty = e.ty;
+        r.i.assign(sh.i.size(), 0);
+        r.f.assign(sh.i.size(), 0);
+        for (size_t d = sh.i.size(); d-- > 0;) {
+          if (d == 0) { r.i[0] = i; break; }
+          if (sh.i[d] == 0) throw Error(B200_ERR_BOUNDS, "divide by zero");
+          r.i[d] = i % sh.i[d];
+          i /= sh.i[d];
+        }
+        return r;
+      }
+      case X_INDEX: {
+        const DevArray& a = array(e.name);
+        HVal ix = eval(*e.a[0]);
+        int64_t lin = 0;
+        for (size_t d = 0; d < a.shape.size(); ++d) {
+          if (ix.i[d] < 0 || ix.i[d] >= a.shape[d]) throw Error(B200_ERR_BOUNDS, "index out of bounds");
+          lin = lin * a.shape[d] + ix.i[d];
+        }
+        return read(a, lin);
+      }
+      case X_LINDEX: return read(array(e.name), eval(*e.a[0]).i[0]);
+      case X_APP: {
+        std::vector<HVal> args;
+        for (auto& c : e.a) args.push_back(eval(*c));
+        size_t mark = vars.size();
+        for (size_t k = 0; k < args.size(); ++k) vars.emplace_back(e.f[0]->params[k], args[k]);
+        HVal r = eval(*e.f[0]->body);
+        vars.resize(mark);
+        return r;
+      }
+      case X_PRIM: {
+        std::vector<HVal> x;
+        for (auto& c : e.a) x.push_back(eval(*c));
+        if (x.size() == 1 && x[0].ty.tuple) {
+          HVal a = x[0];
+          x.clear();
+          x.push_back(scalar_i(e.t1, a.i[0]));
+          x.back().f[0] = a.f[0];
+          x.push_back(scalar_i(e.t1, a.i[1]));
+          x.back().f[0] = a.f[1];
+        }
+        const Ty t = e.t1;
+        if (ty_is_float(t)) {
+          double a = x[0].f[0], b = x.size() > 1 ? x[1].f[0] : 0;
+          switch (e.op) {
+            case P_ADD: return scalar_f(t, a + b);
+            case P_SUB: return scalar_f(t, a - b);
+            case P_MUL: return scalar_f(t, a * b);
+            case P_FDIV: return scalar_f(t, a / b);
+            case P_LT: return scalar_i(U8, a < b);
+            case P_GT: return scalar_i(U8, a > b);
+            case P_LE: return scalar_i(U8, a <= b);
+            case P_GE: return scalar_i(U8, a >= b);
+            case P_EQ: return scalar_i(U8, a == b);
+            case P_NE: return scalar_i(U8, a != b);
+            case P_TRUNCATE: return scalar_i(e.t2, wrap(e.t2, (uint64_t)(int64_t)a));
+            default: break;
+          }
+          throw Error(B200_ERR_UNSUPPORTED, std::string("host evaluation of floating primitive '") + prim_name[e.op] + "'");
+        }
+        int64_t a = x[0].i[0], b = x.size() > 1 ? x[1].i[0] : 0;
+        const bool sg = ty_is_signed(t);
+        auto W = [&](uint64_t v) { return scalar_i(t, wrap(t, v)); };
+        switch (e.op) {
+          case P_ADD: return W((uint64_t)a + (uint64_t)b);
+          case P_SUB: return W((uint64_t)a - (uint64_t)b);
+          case P_MUL: return W((uint64_t)a * (uint64_t)b);
+          case P_NEG: return W((uint64_t)0 - (uint64_t)a);
+          case P_ABS: return W(sg && a < 0 ? (uint64_t)0 - (uint64_t)a : (uint64_t)a);
+          case P_MIN: return W((sg ? a <= b : (uint64_t)a <= (uint64_t)b) ? a : b);
+          case P_MAX: return W((sg ? a <= b : (uint64_t)a <= (uint64_t)b) ? b : a);
+          case P_QUOT: case P_REM: case P_IDIV: case P_MOD: {
+            if (b == 0) throw Error(B200_ERR_BOUNDS, "divide by zero");
+            int64_t q, r;
+            if (sg) {
+              if (b == -1) { q = (int64_t)((uint64_t)0 - (uint64_t)a); r = 0; }
+              else { q = a / b; r = a % b; }
+              if ((e.op == P_IDIV || e.op == P_MOD) && r != 0 && ((r < 0) != (b < 0))) { q -= 1; r += b; }
+            } else {
+              q = (int64_t)((uint64_t)a / (uint64_t)b);
+              r = (int64_t)((uint64_t)a % (uint64_t)b);
+            }
+            return W((uint64_t)((e.op == P_QUOT || e.op == P_IDIV) ? q : r));
+          }
+          case P_LT: return scalar_i(U8, sg ? a < b : (uint64_t)a < (uint64_t)b);
+          case P_GT: return scalar_i(U8, sg ? a > b : (uint64_t)a > (uint64_t)b);
+          case P_LE: return scalar_i(U8, sg ? a <= b : (uint64_t)a <= (uint64_t)b);
+          case P_GE: return scalar_i(U8, sg ? a >= b : (uint64_t)a >= (uint64_t)b);
+          case P_EQ: return scalar_i(U8, a == b);
+          case P_NE: return scalar_i(U8, a != b);
+          case P_LAND: return scalar_i(U8, a != 0 && b != 0);
+          case P_LOR: return scalar_i(U8, a != 0 || b != 0);
+          case P_LNOT: return scalar_i(U8, a == 0);
+          case P_FROMINTEGRAL:
+            if (ty_is_float(e.t2)) return scalar_f(e.t2, sg ? (double)a : (double)(uint64_t)a);
+            return scalar_i(e.t2, wrap(e.t2, (uint64_t)a));
+          default: break;
+        }
+        throw Error(B200_ERR_UNSUPPORTED, std::string("host evaluation of primitive '") + prim_name[e.op] + "'");
+      }
+      default: break;
+    }
+    throw Error(B200_ERR_UNSUPPORTED, "expression form not supported in an extent");
+  }
+};
+
+// ---- launching ----------------------------------------------------------------------------------
+struct Launcher {
+  Ctx* ctx;
+  const std::map<std::string, DevArrayP>* env;
+  const Glue* glue;
+  std::map<std::string, int64_t> named;
+  std::vector<DevArrayP> outs;
+
+  DevArrayP arr(const std::string& n) const {
+    auto it = env->find(n);
+    if (it == env->end() || !it->second) throw Error(B200_ERR_ARG, "array '" + n + "' is not bound");
+    return it->second;
+  }
+  std::vector<uint64_t> block() const {
+    std::vector<uint64_t> pb;
+    for (auto& s : glue->slots) {
+      switch (s.kind) {
+        case Slot::ARR_LEAF: pb.push_back((uint64_t)(uintptr_t)arr(s.name)->leaf[s.idx]->ptr); break;
+        case Slot::ARR_DIM: pb.push_back((uint64_t)arr(s.name)->shape[s.idx]); break;
+        case Slot::OUT_LEAF: pb.push_back((uint64_t)(uintptr_t)outs.at(s.idx / 64)->leaf[s.idx % 64]->ptr); break;
+        case Slot::NAMED: {
+          auto it = named.find(s.name);
+          pb.push_back(it == named.end() ? 0 : (uint64_t)it->second);
+          break;
+        }
+      }
+    }
+    if (pb.empty()) pb.push_back(0);
+    if (pb.size() * 8 > 4000) throw Error(B200_ERR_UNSUPPORTED, "kernel parameter block exceeds 4 KB");
+    return pb;
+  }
+  void launch(CompiledKernel& k, int64_t grid, int threads, size_t smem) {
+    if (grid <= 0) return;
+    if (grid > 2147483647LL) throw Error(B200_ERR_UNSUPPORTED, "grid too large");
+    std::vector<uint64_t> pb = block();
+    void* args[1] = {pb.data()};
+    ctx->check(ctx->drv.LaunchKernel(k.fn, (unsigned)grid, 1, 1, (unsigned)threads, 1, 1, (unsigned)smem, (CUstream)ctx->stream, args, nullptr),
+               "cuLaunchKernel");
+    ctx->launches++;
+  }
+  // extent of a delayed operand + whether its streams all have exactly that shape
+  void bind_delayed(const std::string& D, const std::vector<int64_t>& ext, size_t k) {
+    bool fast = true;
+    for (auto& a : glue->streams.at(k)) {
+      DevArrayP x = arr(a);
+      if (x->shape != ext || !x->aligned16()) fast = false;
+    }
+    for (size_t d = 0; d < ext.size(); ++d) named[D + "_e" + std::to_string(d)] = ext[d];
+    named[D + "_fast"] = fast ? 1 : 0;
+  }
+  bool fast(const std::string& D) const { return named.at(D + "_fast") != 0; }
+};
+
+int64_t prod_outer(const std::vector<int64_t>& sh) {
+  int64_t r = 1;
+  for (size_t d = 0; d + 1 < sh.size(); ++d) r = sh[d] <= 0 ? 0 : r * sh[d];
+  for (size_t d = 0; d + 1 < sh.size(); ++d) if (sh[d] <= 0) r = 0;
+  return r;
+}
+int64_t size_of(const std::vector<int64_t>& sh) {
+  int64_t r = 1;
+  for (int64_t d : sh) if (d <= 0) return 0; else r *= d;
+  return r;
+}
+int pow2_at_least(int64_t v) {
+  int g = 1;
+  while (g < v && g < 32) g <<= 1;
+  return g;
+}
+size_t struct_bytes(const Type& elt) {
+  // size of the generated element struct (natural alignment, C layout)
+  size_t off = 0, maxa = 1;
+  for (Ty t : elt.leaves()) {
+    size_t a = ty_bytes[t];
+    off = (off + a - 1) / a * a + a;
+    maxa = std::max(maxa, a);
+  }
+  off = (off + maxa - 1) / maxa * maxa;
+  return std::max(off, (size_t)1);
+}
+
+}  // namespace
+
+// Arrays are released right after their last use, so a chain of nodes (e.g. one
+// hundred stencil iterations) holds two or three arrays at a time, not all of them.
+void Program::analyse_liveness() {
+  std::map<std::string, size_t> last;
+  for (size_t i = 0; i < ir->nodes.size(); ++i) {
+    const Node& n = ir->nodes[i];
+    std::vector<std::string> used;
+    if (n.f) free_arrays(*n.f, used);
+    if (n.g) free_arrays(*n.g, used);
+    if (n.seed) free_arrays(*n.seed, used);
+    if (n.extent) free_arrays(*n.extent, used);
+    for (auto& d : n.d) {
+      if (d.extent) free_arrays(*d.extent, used);
+      if (d.index) free_arrays(*d.index, used);
+    }
+    for (auto& b : n.bnd) {
+      if (b.value) free_arrays(*b.value, used);
+      if (b.fun) free_arrays(*b.fun, used);
+    }
+    if (!n.arr.empty()) used.push_back(n.arr);
+    for (auto& u : used) last[u] = i;
+    for (auto& o : n.outs)
+      if (!last.count(o)) last[o] = i;  // never read: dies where it is born
+  }
+  dead_after.assign(ir->nodes.size(), {});
+  for (auto& kv : last) {
+    bool is_out = false;
+    for (auto& o : ir->outputs) is_out = is_out || o == kv.first;
+    if (!is_out) dead_after[kv.second].push_back(kv.first);
+  }
+}
+
+void Program::run(const std::vector<DevArrayP>& inputs, std::vector<DevArrayP>& outputs) {
+  Ctx& c = *ctx;
+  if (dead_after.size() != ir->nodes.size()) analyse_liveness();
+  if (inputs.size() != ir->inputs.size()) throw Error(B200_ERR_ARG, "wrong number of input arrays");
+  std::map<std::string, DevArrayP> env;
+  for (size_t k = 0; k < inputs.size(); ++k) {
+    const ArrayInfo& ai = ir->arrays.at(ir->inputs[k]);
+    if (!inputs[k] || inputs[k]->elt != ai.elt || (int)inputs[k]->shape.size() != ai.rank)
+      throw Error(B200_ERR_ARG, "input '" + ir->inputs[k] + "' has the wrong element type or rank");
+    env[ir->inputs[k]] = inputs[k];
+  }
+  c.runs++;
+  for (size_t ni = 0; ni < ir->nodes.size(); ++ni) {
+    const Node& n = ir->nodes[ni];
+    struct Reaper {
+      std::map<std::string, DevArrayP>& env;
+      const std::vector<std::string>& dead;
+      ~Reaper() { for (auto& d : dead) env.erase(d); }
+    } reaper{env, dead_after[ni]};
+    HostEval he{&c, &env, {}};
+    if (n.kind == N_RESHAPE) {
+      // reshapeOp (Interpreter.hs:293-303): same data, new shape; sizes must agree
+      std::vector<int64_t> sh = he.eval(*n.extent).i;
+      DevArrayP src = env.at(n.arr);
+      if (size_of(sh) != src->size()) throw Error(B200_ERR_BOUNDS, "shape mismatch");
+      auto a = std::make_shared<DevArray>(*src);
+      a->shape = sh;
+      env[n.outs[0]] = a;
+      continue;
+    }
+    NodeState& st = nodes[ni];
+    Launcher L{&c, &env, &st.glue, {}, {}};
+    L.named["err"] = (int64_t)(uintptr_t)(c.d_words + 0);
+    L.named["spin_limit"] = c.spin_limit;
+    switch (n.kind) {
+      case N_GENERATE: {
+        std::vector<int64_t> sh = he.eval(*n.extent).i;
+        const int64_t total = size_of(sh);
+        DevArrayP out = c.new_array(n.elt, sh);
+        L.outs = {out};
+        env[n.outs[0]] = out;
+        if (total == 0) break;
+        L.bind_delayed("D0", sh, 0);
+        const int64_t inner = sh.empty() ? 1 : sh.back();
+        L.named["n"] = total;
+        L.named["vec"] = (L.fast("D0") && (sh.size() <= 1 || inner % 4 == 0)) ? 1 : 0;
+        CompiledKernel& k = c.kernel(assemble_source(st.glue, "elementwise", {}), "acc_generate", 256, 0);
+        int64_t work = L.named["vec"] ? (total + 3) / 4 : total;
+        int64_t grid = std::min<int64_t>((work + 255) / 256, (int64_t)c.sm_count * k.max_blocks_per_sm * 4);
+        L.launch(k, std::max<int64_t>(grid, 1), 256, 0);
+        break;
+      }
+      case N_FOLD: {
+        std::vector<int64_t> ext = he.eval(*n.d[0].extent).i;
+        const int64_t m = std::max<int64_t>(ext.back(), 0);
+        const int64_t rows = prod_outer(ext);
+        std::vector<int64_t> osh(ext.begin(), ext.end() - 1);
+        if (!n.seed && m == 0) throw Error(B200_ERR_BOUNDS, "empty array");  // Interpreter.hs:386
+        DevArrayP out = c.new_array(n.elt, osh);
+        L.outs = {out};
+        env[n.outs[0]] = out;
+        if (rows == 0) break;
+        L.bind_delayed("D0", ext, 0);
+        L.named["n"] = m;
+        L.named["rows"] = rows;
+        L.named["vec"] = (L.fast("D0") && (rows == 1 || m % 4 == 0)) ? 1 : 0;
+        if (rows <= 8 && (rows == 1 || m >= (1 << 16))) {
+          std::map<std::string, std::string> var = {{"FOLD_G", "32"}};
+          CompiledKernel& k = c.kernel(assemble_source(st.glue, "fold", var), "acc_fold_all", 256, 0);
+          const int64_t ntiles = (m + 1023) / 1024;
+          int64_t grid = std::max<int64_t>(1, std::min<int64_t>(ntiles, (int64_t)c.sm_count * k.max_blocks_per_sm));
+          const size_t sb = struct_bytes(n.elt);
+          auto scratch = c.alloc((size_t)grid * sb + 16);
+          auto flags = c.alloc((size_t)grid * 4);
+          L.named["scratch"] = (int64_t)(uintptr_t)scratch->ptr;
+          L.named["flags"] = (int64_t)(uintptr_t)flags->ptr;
+          L.named["counter"] = (int64_t)(uintptr_t)(c.d_words + 1);
+          for (int64_t r = 0; r < rows; ++r) {
+            L.named["row"] = r;
+            L.launch(k, grid, 256, 0);
+          }
+        } else {
+          const int g = pow2_at_least((m + 7) / 8);
+          std::map<std::string, std::string> var = {{"FOLD_G", std::to_string(g)}};
+          CompiledKernel& k = c.kernel(assemble_source(st.glue, "fold", var), "acc_fold_rows", 256, 0);
+          const int64_t warps = (rows + (32 / g) - 1) / (32 / g);
+          int64_t grid = std::min<int64_t>((warps + 7) / 8, (int64_t)c.sm_count * k.max_blocks_per_sm);
+          L.launch(k, std::max<int64_t>(grid, 1), 256, 0);
+        }
+        break;
+      }
+      case N_FOLDSEG: {
+        std::vector<int64_t> ext = he.eval(*n.d[0].extent).i;
+        std::vector<int64_t> sext = he.eval(*n.d[1].extent).i;
+        if (sext[0] <= 0) throw Error(B200_ERR_BOUNDS, "empty segment descriptor");  // Interpreter.hs:398
+        const int64_t segs = sext[0] - 1;
+        const int64_t m = std::max<int64_t>(ext.back(), 0);
+        const int64_t rows = prod_outer(ext);
+        std::vector<int64_t> osh(ext.begin(), ext.end() - 1);
+        osh.push_back(segs);
+        DevArrayP out = c.new_array(n.elt, osh);
+        L.outs = {out};
+        env[n.outs[0]] = out;
+        if (rows * segs == 0) break;
+        L.bind_delayed("D0", ext, 0);
+        L.bind_delayed("D1", sext, 1);
+        L.named["segs"] = segs;
+        L.named["rows"] = rows;
+        L.named["vec"] = (L.fast("D0") && (rows == 1 || m % 4 == 0)) ? 1 : 0;
+        const int g = pow2_at_least((m / std::max<int64_t>(segs, 1) + 7) / 8);
+        std::map<std::string, std::string> var = {{"FOLDSEG_G", std::to_string(g)}};
+        CompiledKernel& k = c.kernel(assemble_source(st.glue, "foldseg", var), "acc_foldseg", 256, 0);
+        const int64_t warps = (rows * segs + (32 / g) - 1) / (32 / g);
+        int64_t grid = std::min<int64_t>((warps + 7) / 8, (int64_t)c.sm_count * k.max_blocks_per_sm);
+        L.launch(k, std::max<int64_t>(grid, 1), 256, 0);
+        break;
+      }
+      case N_SCAN: case N_SCAN2: {
+        std::vector<int64_t> ext = he.eval(*n.d[0].extent).i;
+        const int64_t m = std::max<int64_t>(ext.back(), 0);
+        const int64_t rows = prod_outer(ext);
+        const int mode = n.kind == N_SCAN2 ? 2 : (n.seed ? 1 : 0);
+        std::vector<int64_t> osh(ext.begin(), ext.end());
+        osh.back() = mode == 1 ? m + 1 : m;
+        DevArrayP out = c.new_array(n.elt, osh);
+        L.outs = {out};
+        env[n.outs[0]] = out;
+        if (mode == 2) {
+          DevArrayP sums = c.new_array(n.elt, std::vector<int64_t>(ext.begin(), ext.end() - 1));
+          L.outs.push_back(sums);
+          env[n.outs[1]] = sums;
+        }
+        if (rows == 0 || (mode == 0 && m == 0)) break;
+        L.bind_delayed("D0", ext, 0);
+        const int64_t tile = 8 * 4 * 128;
+        const int64_t tiles_per_row = std::max<int64_t>(1, (m + tile - 1) / tile);
+        const int64_t total_tiles = rows * tiles_per_row;
+        const bool right = n.right;
+        bool in_vec = L.fast("D0") && (right ? (m % 4 == 0) : (rows == 1 || m % 4 == 0));
+        bool out_vec;
+        if (mode == 1) out_vec = right ? ((m + 1) % 4 == 0) : (rows == 1 || (m + 1) % 4 == 0);
+        else out_vec = right ? (m % 4 == 0) : (rows == 1 || m % 4 == 0);
+        const size_t sb = struct_bytes(n.elt);
+        const size_t status_bytes = ((size_t)total_tiles * 4 + 255) / 256 * 256;
+        const size_t val_bytes = ((size_t)total_tiles * sb + 255) / 256 * 256;
+        char* base = (char*)c.scan_descriptors(status_bytes + 2 * val_bytes);
+        L.named["n"] = m;
+        L.named["rows"] = rows;
+        L.named["tiles_per_row"] = tiles_per_row;
+        L.named["in_vec"] = in_vec;
+        L.named["out_vec"] = out_vec;
+        L.named["status"] = (int64_t)(uintptr_t)base;
+        L.named["agg"] = (int64_t)(uintptr_t)(base + status_bytes);
+        L.named["incl"] = (int64_t)(uintptr_t)(base + status_bytes + val_bytes);
+        L.named["counter"] = (int64_t)(uintptr_t)(c.d_words + 2);
+        L.named["epoch"] = c.scan_epoch;
+        CompiledKernel& k = c.kernel(assemble_source(st.glue, "scan", {}), "acc_scan", 256, 0);
+        L.launch(k, total_tiles, 256, 0);
+        break;
+      }
+      case N_PERMUTE: {
+        DevArrayP def = env.at(n.arr);
+        std::vector<int64_t> ext = he.eval(*n.d[0].extent).i;
+        const int64_t total = size_of(ext);
+        DevArrayP out = c.new_array(n.elt, def->shape);
+        for (size_t l = 0; l < out->leaf.size(); ++l)
+          if (out->leaf[l]->bytes)
+            c.check(cudaMemcpyAsync(out->leaf[l]->ptr, def->leaf[l]->ptr, out->leaf[l]->bytes, cudaMemcpyDeviceToDevice, c.stream), "cudaMemcpyAsync");
+        L.outs = {out};
+        env[n.outs[0]] = out;
+        if (total == 0) break;
+        L.bind_delayed("D0", ext, 0);
+        const int64_t inner = ext.empty() ? 1 : ext.back();
+        const int64_t out_n = out->size();
+        L.named["n"] = total;
+        L.named["vec"] = (L.fast("D0") && (ext.size() <= 1 || inner % 4 == 0)) ? 1 : 0;
+        L.named["out_n"] = out_n;
+        for (size_t d = 0; d < def->shape.size(); ++d) L.named["out_d" + std::to_string(d)] = def->shape[d];
+        const std::string& mode = st.glue.defines.at("PERMUTE_MODE");
+        std::shared_ptr<Buffer> locks;
+        if (mode == "PERMUTE_LOCK") {
+          locks = c.alloc((size_t)std::max<int64_t>(out_n, 1) * 4);
+          c.check(cudaMemsetAsync(locks->ptr, 0, locks->bytes, c.stream), "cudaMemsetAsync");
+          L.named["locks"] = (int64_t)(uintptr_t)locks->ptr;
+        }
+        const bool atomic = mode.find("ATOMIC") != std::string::npos;
+        const int bytes = atomic ? atoi(st.glue.defines.at("PERMUTE_BYTES").c_str()) : 0;
+        const int64_t cap = 200 * 1024;
+        const char* no_priv = getenv("ACCELERATE_B200_NO_PRIVATISE");
+        if (atomic && !no_priv && out_n > 0 && total >= 8 * out_n && total >= (1 << 16)) {
+          // CTA-private copy of the first `priv` target elements in shared memory
+          const int64_t priv = std::min<int64_t>(out_n, cap / bytes);
+          const size_t smem = (size_t)priv * bytes;
+          std::map<std::string, std::string> var = {{"PERMUTE_SMEM", "1"}, {"PERMUTE_THREADS", "1024"}};
+          CompiledKernel& k = c.kernel(assemble_source(st.glue, "permute", var), "acc_permute", 1024, smem);
+          if (smem > 48 * 1024) c.check(c.drv.FuncSetAttribute(k.fn, CU_FUNC_ATTRIBUTE_MAX_DYNAMIC_SHARED_SIZE_BYTES, (int)smem), "cuFuncSetAttribute");
+          int nb = 1;
+          c.check(c.drv.OccupancyMaxActiveBlocksPerMultiprocessor(&nb, k.fn, 1024, smem), "occupancy");
+          L.named["priv"] = priv;
+          const int64_t work = (total + 3) / 4;
+          int64_t grid = std::min<int64_t>((work + 1023) / 1024, (int64_t)c.sm_count * std::max(nb, 1));
+          L.launch(k, std::max<int64_t>(grid, 1), 1024, smem);
+        } else {
+          L.named["priv"] = 0;
+          CompiledKernel& k = c.kernel(assemble_source(st.glue, "permute", {}), "acc_permute", 512, 0);
+          const int64_t work = L.named["vec"] ? (total + 3) / 4 : total;
+          int64_t grid = std::min<int64_t>((work + 511) / 512, (int64_t)c.sm_count * k.max_blocks_per_sm * 2);
+          L.launch(k, std::max<int64_t>(grid, 1), 512, 0);
+        }
+        break;
+      }
+      case N_STENCIL: case N_STENCIL2: {
+        const int rank = n.d[0].rank;
+        std::vector<std::vector<int64_t>> ext;
+        for (auto& d : n.d) ext.push_back(he.eval(*d.extent).i);
+        std::vector<int64_t> osh = ext[0];
+        for (size_t a = 1; a < ext.size(); ++a)
+          for (int d = 0; d < rank; ++d) osh[d] = std::min(osh[d], ext[a][d]);  // Shape.hs:81-91
+        DevArrayP out = c.new_array(n.elt, osh);
+        L.outs = {out};
+        env[n.outs[0]] = out;
+        if (size_of(osh) == 0) break;
+        for (size_t a = 0; a < ext.size(); ++a) L.bind_delayed("D" + std::to_string(a), ext[a], a);
+        int64_t o[3] = {1, 1, 1};
+        for (int d = 0; d < rank; ++d) o[d + 3 - rank] = osh[d];
+        StencilTile t = stencil_tile(rank);
+        const int64_t tiles0 = (o[0] + t.t0 - 1) / t.t0, tiles1 = (o[1] + t.t1 - 1) / t.t1, tiles2 = (o[2] + t.t2 - 1) / t.t2;
+        L.named["o0"] = o[0];
+        L.named["o1"] = o[1];
+        L.named["o2"] = o[2];
+        L.named["tiles1"] = tiles1;
+        L.named["tiles2"] = tiles2;
+        L.named["vec"] = (o[2] % 4 == 0 && out->aligned16()) ? 1 : 0;
+        CompiledKernel& k = c.kernel(assemble_source(st.glue, "stencil", stencil_variant(rank)), "acc_stencil", t.threads, 0);
+        L.launch(k, tiles0 * tiles1 * tiles2, t.threads, 0);
+        break;
+      }
+      case N_RESHAPE: break;
+    }
+  }
+  outputs.clear();
+  for (auto& o : ir->outputs) outputs.push_back(env.at(o));
+}
+
+}  // namespace accb200

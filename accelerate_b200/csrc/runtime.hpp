@@ -1,0 +1,112 @@
+// Runtime of the B200 backend: device arrays, kernel compilation (NVRTC) with a
+// content-hashed cache, host-side evaluation of extents, and one launcher per
+// array node.
+#pragma once
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include <atomic>
+#include <map>
+#include <memory>
+#include <mutex>
+#include <string>
+#include <vector>
+
+#include "codegen.hpp"
+#include "ir.hpp"
+
+namespace accb200 {
+
+// ---- driver entry points, resolved through the runtime (no link-time libcuda) ----
+struct Driver {
+  CUresult (*ModuleLoadData)(CUmodule*, const void*) = nullptr;
+  CUresult (*ModuleUnload)(CUmodule) = nullptr;
+  CUresult (*ModuleGetFunction)(CUfunction*, CUmodule, const char*) = nullptr;
+  CUresult (*LaunchKernel)(CUfunction, unsigned, unsigned, unsigned, unsigned, unsigned, unsigned, unsigned, CUstream, void**,
+                           void**) = nullptr;
+  CUresult (*FuncSetAttribute)(CUfunction, CUfunction_attribute, int) = nullptr;
+  CUresult (*OccupancyMaxActiveBlocksPerMultiprocessor)(int*, CUfunction, int, size_t) = nullptr;
+  CUresult (*GetErrorString)(CUresult, const char**) = nullptr;
+  void load();
+};
+
+// ---- compiled kernels --------------------------------------------------------------
+struct CompiledKernel {
+  CUmodule module = nullptr;
+  CUfunction fn = nullptr;
+  int max_blocks_per_sm = 0;  // for the launch configuration it was queried with
+};
+
+// Compile `source` for sm_100a; returns the cubin.  Throws Error(B200_ERR_COMPILE)
+// with the NVRTC log.  Results are cached on disk by content hash.
+struct CompileStats { std::atomic<long long> compiled{0}, disk_hits{0}; };
+std::string compile_to_cubin(const std::string& source, const std::string& name, CompileStats* stats);
+std::string content_hash(const std::string& s);
+
+// ---- device arrays -------------------------------------------------------------------
+struct Ctx;
+struct Buffer {
+  Ctx* ctx = nullptr;
+  void* ptr = nullptr;
+  size_t bytes = 0;
+  bool owned = true;
+  ~Buffer();
+};
+struct DevArray {
+  Type elt;
+  std::vector<Ty> leaf_ty;
+  std::vector<int64_t> shape;
+  std::vector<std::shared_ptr<Buffer>> leaf;
+  int64_t size() const;
+  bool aligned16() const;
+};
+typedef std::shared_ptr<DevArray> DevArrayP;
+
+struct Ctx {
+  int device = 0;
+  int sm_count = 148;
+  cudaStream_t stream = nullptr;
+  Driver drv;
+  std::mutex mu;
+  std::map<uint64_t, DevArrayP> arrays;
+  uint64_t next_id = 1;
+  // device words: [0] error status, [1] fold ticket counter, [2] scan ticket counter
+  int* d_words = nullptr;
+  // scan descriptors (persistent, epoch-tagged)
+  void* scan_scratch = nullptr;
+  size_t scan_scratch_bytes = 0;
+  uint32_t scan_epoch = 0;
+  std::map<std::string, CompiledKernel> kernels;  // by content hash of the source
+  CompileStats cstats;
+  std::atomic<long long> launches{0}, h2d{0}, d2h{0}, mem_hits{0}, allocated{0}, runs{0};
+  long long spin_limit = 1 << 22;
+
+  DevArrayP new_array(const Type& elt, const std::vector<int64_t>& shape);
+  std::shared_ptr<Buffer> alloc(size_t bytes);
+  void check(cudaError_t e, const char* what);
+  void check(CUresult e, const char* what);
+  CompiledKernel& kernel(const std::string& source, const std::string& entry, int threads, size_t dyn_smem);
+  void* scan_descriptors(size_t bytes);
+};
+
+// ---- programs ------------------------------------------------------------------------
+struct NodeState {
+  Glue glue;
+  bool has_glue = false;
+};
+struct Program {
+  Ctx* ctx = nullptr;
+  std::unique_ptr<ProgramIR> ir;
+  std::vector<NodeState> nodes;
+  std::vector<std::vector<std::string>> dead_after;  // arrays whose last use is node i
+  void analyse_liveness();
+  void run(const std::vector<DevArrayP>& inputs, std::vector<DevArrayP>& outputs);
+};
+
+// Source text of one kernel variant: prelude, defines, generated code, skeleton.
+std::string assemble_source(const Glue& g, const std::string& skeleton, const std::map<std::string, std::string>& variant);
+// Default variants of a node (used by the build-time compile check).
+std::vector<std::pair<std::string, std::map<std::string, std::string>>> default_variants(const Node& n, const Glue& g);
+
+}  // namespace accb200

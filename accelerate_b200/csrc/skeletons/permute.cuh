@@ -1,0 +1,181 @@
+// permute (Interpreter.hs:585-624): the output starts as a copy of the defaults
+// (made by the host before this kernel); every source element whose index
+// function yields `Just ix` is combined into out[ix] as `f new old`.
+//
+// How the update is applied (PERMUTE_MODE, chosen by the code generator):
+//   PERMUTE_ATOMIC_*  f is (+)/min/max/and/or/xor on a 32/64-bit scalar: one
+//                     fire-and-forget reduction (red.global), optionally staged
+//                     through a CTA-private copy of the first `priv` target
+//                     elements in shared memory when the target is small;
+//   PERMUTE_CAS       any other f on a 32/64-bit scalar: compare-and-swap loop;
+//   PERMUTE_STORE     `permute const`: plain store (targets assumed unique);
+//   PERMUTE_LOCK      everything else (tuples, narrow types): one spin lock per
+//                     target element, bounded by `spin_limit`.
+// f must be associative and commutative (Language.hs:707), so update order is free.
+//
+// Named parameters: n, vec, out_n, priv, locks, err, spin_limit.
+// HBM traffic: source stream bytes per element (+ the target, amortised).
+
+#ifndef PERMUTE_THREADS
+#define PERMUTE_THREADS 512
+#endif
+#define PERMUTE_ATOMIC_ADD 1
+#define PERMUTE_ATOMIC_MIN 2
+#define PERMUTE_ATOMIC_MAX 3
+#define PERMUTE_ATOMIC_AND 4
+#define PERMUTE_ATOMIC_OR 5
+#define PERMUTE_ATOMIC_XOR 6
+#define PERMUTE_CAS 7
+#define PERMUTE_STORE 8
+#define PERMUTE_LOCK 9
+#ifndef PERMUTE_SMEM
+#define PERMUTE_SMEM 0
+#endif
+#define PERMUTE_IS_ATOMIC (PERMUTE_MODE >= PERMUTE_ATOMIC_ADD && PERMUTE_MODE <= PERMUTE_ATOMIC_XOR)
+
+#if PERMUTE_IS_ATOMIC || PERMUTE_MODE == PERMUTE_CAS
+#if PERMUTE_BYTES == 4
+typedef u32 permute_word;
+#else
+typedef u64 permute_word;
+#endif
+__device__ __forceinline__ permute_word permute_bits(PERMUTE_T v) { return *reinterpret_cast<permute_word*>(&v); }
+__device__ __forceinline__ PERMUTE_T permute_val(permute_word w) { return *reinterpret_cast<PERMUTE_T*>(&w); }
+#endif
+
+#if PERMUTE_IS_ATOMIC
+// works on global and shared addresses alike
+__device__ __forceinline__ void permute_atomic(PERMUTE_T* addr, PERMUTE_T v) {
+#if PERMUTE_MODE == PERMUTE_ATOMIC_ADD
+#if PERMUTE_FLOAT
+  atomicAdd(addr, v);
+#else
+  atomicAdd(reinterpret_cast<permute_word*>(addr), permute_bits(v));
+#endif
+#elif PERMUTE_MODE == PERMUTE_ATOMIC_MIN
+#if PERMUTE_SIGNED && PERMUTE_BYTES == 4
+  atomicMin(reinterpret_cast<int*>(addr), (int)v);
+#elif PERMUTE_SIGNED
+  atomicMin(reinterpret_cast<long long*>(addr), (long long)v);
+#else
+  atomicMin(reinterpret_cast<permute_word*>(addr), permute_bits(v));
+#endif
+#elif PERMUTE_MODE == PERMUTE_ATOMIC_MAX
+#if PERMUTE_SIGNED && PERMUTE_BYTES == 4
+  atomicMax(reinterpret_cast<int*>(addr), (int)v);
+#elif PERMUTE_SIGNED
+  atomicMax(reinterpret_cast<long long*>(addr), (long long)v);
+#else
+  atomicMax(reinterpret_cast<permute_word*>(addr), permute_bits(v));
+#endif
+#elif PERMUTE_MODE == PERMUTE_ATOMIC_AND
+  atomicAnd(reinterpret_cast<permute_word*>(addr), permute_bits(v));
+#elif PERMUTE_MODE == PERMUTE_ATOMIC_OR
+  atomicOr(reinterpret_cast<permute_word*>(addr), permute_bits(v));
+#else
+  atomicXor(reinterpret_cast<permute_word*>(addr), permute_bits(v));
+#endif
+}
+// the value that leaves a target element unchanged
+__device__ __forceinline__ PERMUTE_T permute_identity() {
+#if PERMUTE_MODE == PERMUTE_ATOMIC_MIN
+#if PERMUTE_SIGNED
+  return (PERMUTE_T)(((permute_word)1 << (PERMUTE_BYTES * 8 - 1)) - 1);
+#else
+  return (PERMUTE_T)~(permute_word)0;
+#endif
+#elif PERMUTE_MODE == PERMUTE_ATOMIC_MAX
+#if PERMUTE_SIGNED
+  return permute_val((permute_word)1 << (PERMUTE_BYTES * 8 - 1));
+#else
+  return (PERMUTE_T)0;
+#endif
+#elif PERMUTE_MODE == PERMUTE_ATOMIC_AND
+  return permute_val(~(permute_word)0);
+#else
+  return (PERMUTE_T)0;
+#endif
+}
+#endif
+
+#if PERMUTE_SMEM
+extern __shared__ __align__(16) unsigned char permute_smem_raw[];
+#endif
+
+__device__ __forceinline__ void permute_update(const Params& p, i64 dst, const elt_t& v) {
+#if PERMUTE_IS_ATOMIC
+#if PERMUTE_SMEM
+  if (dst < p.priv) { permute_atomic(reinterpret_cast<PERMUTE_T*>(permute_smem_raw) + dst, v.l0); return; }
+#endif
+  permute_atomic(p.out0_l0 + dst, v.l0);
+#elif PERMUTE_MODE == PERMUTE_CAS
+  permute_word* a = reinterpret_cast<permute_word*>(p.out0_l0 + dst);
+  permute_word old = *reinterpret_cast<volatile permute_word*>(a), assumed;
+  do {
+    assumed = old;
+    elt_t cur;
+    cur.l0 = permute_val(assumed);
+    const elt_t nv = F_combine(p, v, cur);
+    old = atomicCAS(a, assumed, permute_bits(nv.l0));
+  } while (assumed != old);
+#elif PERMUTE_MODE == PERMUTE_STORE
+  OUT0_store(p, dst, v);
+#else
+  unsigned* lock = reinterpret_cast<unsigned*>(p.locks) + dst;
+  i64 spins = 0;
+  for (;;) {
+    if (atomicCAS(lock, 0u, 1u) == 0u) {
+      __threadfence();
+      const elt_t cur = OUT0_load(p, dst);
+      OUT0_store(p, dst, F_combine(p, v, cur));
+      __threadfence();
+      atomicExch(lock, 0u);
+      break;
+    }
+    if (++spins > p.spin_limit) { acc_fail(p.err, 110 /* ETIMEDOUT */); break; }
+    __nanosleep(40);
+  }
+#endif
+}
+
+extern "C" __global__ void __launch_bounds__(PERMUTE_THREADS) acc_permute(const Params p) {
+  const i64 n = p.n;
+  const i64 inner = D0_INNER;
+  const i64 tid = (i64)blockIdx.x * PERMUTE_THREADS + threadIdx.x;
+  const i64 nthreads = (i64)gridDim.x * PERMUTE_THREADS;
+#if PERMUTE_SMEM
+  PERMUTE_T* sm = reinterpret_cast<PERMUTE_T*>(permute_smem_raw);
+  for (i64 b = threadIdx.x; b < p.priv; b += PERMUTE_THREADS) sm[b] = permute_identity();
+  __syncthreads();
+#endif
+  i64 done = 0;
+  if (p.vec) {
+    const i64 nv = n >> 2;
+    for (i64 v = tid; v < nv; v += nthreads) {
+      const i64 i = v << 2;
+      i64 row = 0, j = i;
+      if (inner != n) { row = i / inner; j = i - row * inner; }
+      elt_t x[4];
+      D0_get4(p, row, j, x);
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        i64 dst;
+        if (P_index(p, row, j + k, dst)) permute_update(p, dst, x[k]);
+      }
+    }
+    done = nv << 2;
+  }
+  for (i64 i = done + tid; i < n; i += nthreads) {
+    i64 row = 0, j = i;
+    if (inner != n) { row = i / inner; j = i - row * inner; }
+    i64 dst;
+    if (P_index(p, row, j, dst)) permute_update(p, dst, D0_get(p, row, j));
+  }
+#if PERMUTE_SMEM
+  __syncthreads();
+  for (i64 b = threadIdx.x; b < p.priv; b += PERMUTE_THREADS) {
+    const PERMUTE_T v = sm[b];
+    if (permute_bits(v) != permute_bits(permute_identity())) permute_atomic(p.out0_l0 + b, v);
+  }
+#endif
+}

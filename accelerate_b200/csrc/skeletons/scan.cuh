@@ -1,0 +1,340 @@
+// scanl / scanl1 / scanl' / scanr / scanr1 / scanr' along the innermost dimension
+// (Interpreter.hs:427-582) as ONE pass over the data: every tile publishes its
+// aggregate, then looks back over its predecessors' descriptors (aggregate or
+// inclusive prefix) to find its exclusive prefix, so each element is read once
+// and written once (8 B/element for 4-byte types).
+//
+// Positions are handled in *logical* order q = 0..n-1: q = i for left scans and
+// q = n-1-i for right scans, with the combination function flipped for right
+// scans (out[i] = f x[i] out[i+1]).  The function need only be associative;
+// operand order is preserved everywhere.
+//
+// Tiles are handed out by a ticket counter, so a tile's predecessors have
+// always started before it: the look-back wait cannot deadlock.  It is bounded
+// anyway: after `spin_limit` polls the kernel records ETIMEDOUT in the status
+// word and leaves.
+//
+// Descriptors live in scratch memory and are tagged with a launch epoch, so
+// they need no clearing between launches: status = epoch << 2 | state.
+//
+// Named parameters: n, rows, tiles_per_row, in_vec, out_vec, status, agg, incl,
+// counter, epoch, err, spin_limit.
+// ACC_SCAN_MODE: 0 inclusive (scanl1/scanr1); 1 seeded, n+1 results per row
+// (scanl/scanr); 2 seeded, n results + row totals in a second array (scanl'/scanr').
+
+#define SCAN_THREADS 256
+#define SCAN_WARPS (SCAN_THREADS / 32)
+#ifndef SCAN_ROUNDS
+#define SCAN_ROUNDS 4
+#endif
+#define SCAN_WARP_ELEMS (SCAN_ROUNDS * 128)
+#define SCAN_TILE (SCAN_WARPS * SCAN_WARP_ELEMS)
+#define SCAN_ST_AGG 1u
+#define SCAN_ST_PREFIX 2u
+
+#if ACC_SCAN2
+#define ACC_SCAN_MODE 2
+#elif ACC_SEEDED
+#define ACC_SCAN_MODE 1
+#else
+#define ACC_SCAN_MODE 0
+#endif
+
+// a . b with a earlier than b in logical order
+__device__ __forceinline__ elt_t scan_op(const Params& p, const elt_t& a, const elt_t& b) {
+#if ACC_RIGHT
+  return F_combine(p, b, a);
+#else
+  return F_combine(p, a, b);
+#endif
+}
+// a := a . b where either side may be absent
+__device__ __forceinline__ void scan_join(const Params& p, elt_t& a, bool& ha, const elt_t& b, bool hb) {
+  if (hb) {
+    if (ha) a = scan_op(p, a, b);
+    else { a = b; ha = true; }
+  }
+}
+// a := b . a (b earlier)
+__device__ __forceinline__ void scan_join_front(const Params& p, const elt_t& b, bool hb, elt_t& a, bool& ha) {
+  if (hb) {
+    if (ha) a = scan_op(p, b, a);
+    else { a = b; ha = true; }
+  }
+}
+template <class T> __device__ __forceinline__ T scan_ld_volatile(const T* src) {
+  T r;
+  if (sizeof(T) % 4 == 0) {
+    const volatile u32* s = reinterpret_cast<const volatile u32*>(src);
+    u32* d = reinterpret_cast<u32*>(&r);
+    for (unsigned i = 0; i < sizeof(T) / 4; ++i) d[i] = s[i];
+  } else {
+    const volatile u8* s = reinterpret_cast<const volatile u8*>(src);
+    u8* d = reinterpret_cast<u8*>(&r);
+    for (unsigned i = 0; i < sizeof(T); ++i) d[i] = s[i];
+  }
+  return r;
+}
+
+// physical position of logical position q in the input row
+__device__ __forceinline__ i64 scan_phys(i64 n, i64 q) {
+#if ACC_RIGHT
+  return n - 1 - q;
+#else
+  return q;
+#endif
+}
+
+template <bool FULL>
+__device__ __forceinline__ void scan_tile(const Params& p, const i64 T, const i64 row, const i64 tt, elt_t* sm_v, int* sm_h,
+                                          elt_t* sm_excl, int* sm_flag) {
+  const i64 n = p.n;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const i64 tile_q0 = tt * SCAN_TILE;
+  const i64 warp_q0 = tile_q0 + (i64)warp * SCAN_WARP_ELEMS;
+  const bool in_vec = p.in_vec != 0, out_vec = p.out_vec != 0;
+
+  // ---- load; thread-local inclusive scan of each group of four ----------------
+  elt_t item[SCAN_ROUNDS][4];
+  bool valid[SCAN_ROUNDS][4];
+#pragma unroll
+  for (int r = 0; r < SCAN_ROUNDS; ++r) {
+    const i64 q = warp_q0 + r * 128 + lane * 4;
+    if (FULL && in_vec) {
+#if ACC_RIGHT
+      elt_t t4[4];
+      D0_get4(p, row, n - 4 - q, t4);
+#pragma unroll
+      for (int k = 0; k < 4; ++k) item[r][k] = t4[3 - k];
+#else
+      D0_get4(p, row, q, item[r]);
+#endif
+#pragma unroll
+      for (int k = 0; k < 4; ++k) valid[r][k] = true;
+    } else {
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        valid[r][k] = FULL || (q + k < n);
+        if (valid[r][k]) item[r][k] = D0_get(p, row, scan_phys(n, q + k));
+      }
+    }
+  }
+  elt_t tot[SCAN_ROUNDS];
+  bool htot[SCAN_ROUNDS];
+#pragma unroll
+  for (int r = 0; r < SCAN_ROUNDS; ++r) {
+    tot[r] = item[r][0];
+    htot[r] = valid[r][0];
+#pragma unroll
+    for (int k = 1; k < 4; ++k) {
+      if (valid[r][k]) {
+        item[r][k] = scan_op(p, item[r][k - 1], item[r][k]);
+        tot[r] = item[r][k];
+      }
+    }
+  }
+  // ---- warp-level inclusive scans of the per-thread totals, one per round ------
+  elt_t lane_excl[SCAN_ROUNDS];
+  bool hlane_excl[SCAN_ROUNDS];
+  elt_t carry;           // rounds 0..r-1 of this warp
+  bool hcarry = false;
+  elt_t round_carry[SCAN_ROUNDS];
+  bool hround_carry[SCAN_ROUNDS];
+#pragma unroll
+  for (int r = 0; r < SCAN_ROUNDS; ++r) {
+    elt_t v = tot[r];
+    bool h = htot[r];
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+      const elt_t o = acc_shfl_up(v, d);
+      const int oh = __shfl_up_sync(ACC_FULL_MASK, (int)h, d);
+      if (lane >= d) scan_join_front(p, o, FULL || oh != 0, v, h);
+    }
+    const elt_t e = acc_shfl_up(v, 1);
+    const int eh = __shfl_up_sync(ACC_FULL_MASK, (int)h, 1);
+    lane_excl[r] = e;
+    hlane_excl[r] = lane > 0 && (FULL || eh != 0);
+    const elt_t rt = acc_shfl_idx(v, 31);
+    const int rh = __shfl_sync(ACC_FULL_MASK, (int)h, 31);
+    round_carry[r] = carry;
+    hround_carry[r] = hcarry;
+    scan_join(p, carry, hcarry, rt, FULL || rh != 0);
+  }
+  // carry now holds the warp's total
+  if (lane == 0) { sm_v[warp] = carry; sm_h[warp] = hcarry; }
+  __syncthreads();
+
+  // ---- tile aggregate, look-back (warp 0), tile exclusive prefix ---------------
+  if (warp == 0) {
+    elt_t agg;
+    bool hagg = false;
+#pragma unroll
+    for (int w = 0; w < SCAN_WARPS; ++w) scan_join(p, agg, hagg, sm_v[w], sm_h[w] != 0);
+    elt_t excl;
+    bool hexcl = false;
+    volatile u32* status = reinterpret_cast<volatile u32*>(p.status);
+    elt_t* d_agg = reinterpret_cast<elt_t*>(p.agg);
+    elt_t* d_incl = reinterpret_cast<elt_t*>(p.incl);
+    const u32 epoch = (u32)p.epoch;
+    int failed = 0;
+    if (tt == 0) {
+#if ACC_SEEDED
+      excl = F_seed(p);
+      hexcl = true;
+#endif
+    } else {
+      if (lane == 0) {
+        // an empty aggregate cannot occur: only the last tile of a row can be partial, and it has no successor
+        d_agg[T] = agg;
+        __threadfence();
+        status[T] = (epoch << 2) | SCAN_ST_AGG;
+      }
+      const i64 row_first = T - tt;
+      i64 look = T - 1;
+      for (;;) {
+        const i64 idx = look - lane;
+        const bool inrow = idx >= row_first;
+        u32 st = 0;
+        if (inrow) {
+          i64 spins = 0;
+          for (;;) {
+            st = status[idx];
+            if ((st >> 2) == epoch) break;
+            if (++spins > p.spin_limit) { failed = 1; break; }
+            __nanosleep(20);
+          }
+        }
+        failed = __any_sync(ACC_FULL_MASK, failed);
+        if (failed) break;
+        const bool is_prefix = inrow && (st & 3u) == SCAN_ST_PREFIX;
+        const unsigned pm = __ballot_sync(ACC_FULL_MASK, is_prefix);
+        const int nearest = pm ? (__ffs((int)pm) - 1) : 31;
+        elt_t v;
+        bool hv = inrow && lane <= nearest;
+        if (hv) {
+          __threadfence();
+          v = scan_ld_volatile(is_prefix ? d_incl + idx : d_agg + idx);
+        }
+        // lane l holds tile look-l: higher lanes are earlier
+#pragma unroll
+        for (int d = 1; d < 32; d <<= 1) {
+          const elt_t o = acc_shfl_down(v, d);
+          const int oh = __shfl_down_sync(ACC_FULL_MASK, (int)hv, d);
+          if (lane + d < 32) scan_join_front(p, o, oh != 0, v, hv);
+        }
+        scan_join_front(p, v, hv, excl, hexcl);  // meaningful in lane 0
+        if (pm != 0 || look - 32 < row_first) break;
+        look -= 32;
+      }
+    }
+    if (lane == 0) {
+      if (failed) {
+        acc_fail(p.err, 110 /* ETIMEDOUT */);
+      } else {
+        elt_t inc = excl;
+        bool hinc = hexcl;
+        scan_join(p, inc, hinc, agg, hagg);
+        if (hinc) d_incl[T] = inc;
+        __threadfence();
+        status[T] = (epoch << 2) | SCAN_ST_PREFIX;
+#if ACC_SCAN_MODE != 0
+        if (tt == p.tiles_per_row - 1) {
+          // the row's total (seed included)
+#if ACC_SCAN_MODE == 1
+#if ACC_RIGHT
+          OUT0_store(p, row * (n + 1), inc);
+#else
+          OUT0_store(p, row * (n + 1) + n, inc);
+#endif
+#else
+          OUT1_store(p, row, inc);
+#endif
+        }
+#endif
+      }
+      *sm_excl = excl;
+      sm_flag[0] = hexcl ? 1 : 0;
+      sm_flag[1] = failed;
+    }
+  }
+  __syncthreads();
+  if (sm_flag[1]) return;
+
+  // ---- per-thread prefixes and stores ----------------------------------------------
+  elt_t base = *sm_excl;
+  bool hbase = sm_flag[0] != 0;
+  for (int w = 0; w < warp; ++w) scan_join(p, base, hbase, sm_v[w], sm_h[w] != 0);
+#if ACC_SCAN_MODE == 1
+  const i64 out_row = row * (n + 1);
+#else
+  const i64 out_row = row * n;
+#endif
+#pragma unroll
+  for (int r = 0; r < SCAN_ROUNDS; ++r) {
+    const i64 q = warp_q0 + r * 128 + lane * 4;
+    elt_t pre = base;
+    bool hpre = hbase;
+    scan_join(p, pre, hpre, round_carry[r], hround_carry[r]);
+    scan_join(p, pre, hpre, lane_excl[r], hlane_excl[r]);
+    elt_t o[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+#if ACC_SCAN_MODE == 0
+      o[k] = item[r][k];
+      if (valid[r][k] && hpre) o[k] = scan_op(p, pre, item[r][k]);
+#else
+      // exclusive value: everything before position q+k (the seed guarantees it exists)
+      if (k == 0) o[k] = pre;
+      else if (valid[r][k - 1]) o[k] = scan_op(p, pre, item[r][k - 1]);
+#endif
+    }
+    // where the four values go
+#if ACC_SCAN_MODE == 1 && ACC_RIGHT
+    const i64 pos0 = out_row + n - q;          // descending
+#elif ACC_RIGHT
+    const i64 pos0 = out_row + n - 1 - q;      // descending
+#else
+    const i64 pos0 = out_row + q;              // ascending
+#endif
+    if (FULL && out_vec) {
+#if ACC_RIGHT
+      elt_t w[4] = {o[3], o[2], o[1], o[0]};
+      OUT0_store4(p, pos0 - 3, w);
+#else
+      OUT0_store4(p, pos0, o);
+#endif
+    } else {
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        if (valid[r][k]) {
+#if ACC_RIGHT
+          OUT0_store(p, pos0 - k, o[k]);
+#else
+          OUT0_store(p, pos0 + k, o[k]);
+#endif
+        }
+      }
+    }
+  }
+}
+
+extern "C" __global__ void __launch_bounds__(SCAN_THREADS) acc_scan(const Params p) {
+  __shared__ elt_t sm_v[SCAN_WARPS];
+  __shared__ int sm_h[SCAN_WARPS];
+  __shared__ elt_t sm_excl;
+  __shared__ int sm_flag[2];
+  __shared__ unsigned sm_ticket;
+  const i64 total_tiles = p.rows * p.tiles_per_row;
+  if (threadIdx.x == 0) {
+    unsigned* counter = reinterpret_cast<unsigned*>(p.counter);
+    sm_ticket = atomicAdd(counter, 1u);
+    if ((i64)sm_ticket == total_tiles - 1) *counter = 0u;  // every ticket has been handed out
+  }
+  __syncthreads();
+  const i64 T = sm_ticket;
+  const i64 row = T / p.tiles_per_row;
+  const i64 tt = T - row * p.tiles_per_row;
+  const bool full = (tt + 1) * SCAN_TILE <= p.n;
+  if (full) scan_tile<true>(p, T, row, tt, sm_v, sm_h, &sm_excl, sm_flag);
+  else scan_tile<false>(p, T, row, tt, sm_v, sm_h, &sm_excl, sm_flag);
+}

@@ -252,7 +252,9 @@ def rem(a, b): return a._bin("rem", b)
 def div(a, b): return a._bin("idiv", b)
 def mod(a, b): return a._bin("mod", b)
 def atan2(a, b): return a._bin("atan2", b)
-def log_base(b, x): return b._bin("logbase", x)
+def log_base(b, x):
+    b = b if isinstance(b, Exp) else lift(b, x.ty)
+    return b._bin("logbase", x)
 def rotate_l(a, n): return _shift("rotl", a, n)
 def rotate_r(a, n): return _shift("rotr", a, n)
 

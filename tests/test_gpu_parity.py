@@ -1,0 +1,382 @@
+"""GPU parity: every skeleton against the CPU oracle on the same seeded inputs.
+
+Sizes, element types and the monoids follow the reference's nofib suite
+(Test/NoFib/Prelude/{Fold,Scan,Permute,Stencil}.hs); edge sizes cover tile and
+warp boundaries of the kernels.  Integers must match bit for bit; floating-point
+reductions use the reference's own tolerance (Test/Similar.hs:90-91,
+absRelTol 0.00005 0.005 for Float) or the tighter one stated in the test."""
+import numpy as np
+import pytest
+
+import accelerate_b200 as A
+from tests.util import check
+
+pytestmark = pytest.mark.gpu
+add = lambda a, b: a + b  # noqa: E731
+SIZES_1D = [0, 1, 2, 31, 32, 33, 127, 128, 129, 255, 256, 257, 1023, 1024, 1025, 4095, 4096, 4097, 8193, 50001]
+rng = np.random.default_rng(42)
+F32_TOL = dict(rtol=5e-3, atol=5e-5)   # Test/Similar.hs:90-91
+
+
+def ints(n, dtype=np.int32, lo=-1000, hi=1000):
+    return rng.integers(lo, hi, size=n).astype(dtype)
+
+
+def floats(n, dtype=np.float32):
+    return rng.uniform(-1, 1, size=n).astype(dtype)
+
+
+# ---- elementwise ----------------------------------------------------------------
+@pytest.mark.parametrize("n", [0, 1, 3, 4, 5, 1000, 4099])
+def test_map_zipwith(n):
+    x, y = floats(n), floats(n)
+    check(A.zipWith(lambda a, b: a * b + 1.5, x, y))
+    check(A.map(lambda a: A.cond(a > 0.0, A.sqrt(a), -a), x), rtol=1e-6)
+    check(A.zipWith(lambda a, b: A.tup(a + b, a.ne(b)), ints(n), ints(n)))
+
+
+def test_zipwith_intersect_2d():
+    a, b = ints((7, 12)), ints((5, 16))
+    check(A.zipWith(add, a, b))
+    check(A.zipWith(add, ints((8, 16)), ints((8, 16))))
+
+
+def test_backpermute_transpose():
+    m = ints((13, 21))
+    mu = A.use(m)
+    check(A.backpermute(A.index(21, 13), lambda ix: A.index(ix[1], ix[0]), mu))
+
+
+def test_generate_index_math():
+    check(A.generate(A.index(5, 7), lambda ix: ix[0] * 100 + ix[1]))
+    check(A.generate(A.index(3, 4, 6), lambda ix: A.to_index(A.index(3, 4, 6), ix) % 5))
+
+
+@pytest.mark.parametrize("ty", ["i8", "i16", "i32", "i64", "u8", "u16", "u32", "u64"])
+def test_integer_primitives(ty):
+    dt = A.NP_OF[ty]
+    info = np.iinfo(dt)
+    x = rng.integers(info.min, info.max, size=257, dtype=dt, endpoint=True)
+    y = rng.integers(info.min, info.max, size=257, dtype=dt, endpoint=True)
+    y[y == 0] = 3
+    sh = rng.integers(0, 70, size=257).astype(np.int64)
+    xs, ys, ss = A.use(x), A.use(y), A.use(sh)
+
+    def f(ix):
+        a, b, s = xs[ix], ys[ix], ss[ix]
+        return A.tup(a + b, a - b, a * b, -a, abs(a), A.signum(a), A.quot(a, b), A.rem(a, b), a // b, a % b,
+                     a & b, a | b, a ^ b, ~a, a << s, a >> s, A.rotate_l(a, s), A.rotate_r(a, s),
+                     A.pop_count(a), A.count_leading_zeros(a), A.count_trailing_zeros(a),
+                     A.max_(a, b), A.min_(a, b), a < b, a >= b, a.eq(b),
+                     A.from_integral(a, "i64"), A.from_integral(a, "u8"), A.from_integral(a, "f32"), A.from_integral(a, "f64"))
+    check(A.generate(A.index(257), f))
+
+
+@pytest.mark.parametrize("ty", ["f32", "f64"])
+def test_float_primitives_exact(ty):
+    dt = A.NP_OF[ty]
+    x = (rng.normal(size=300) * 50).astype(dt)
+    y = (rng.normal(size=300) * 3).astype(dt)
+    x[:6] = [0.5, 1.5, 2.5, -0.5, -1.5, -2.5]
+    xs, ys = A.use(x), A.use(y)
+
+    def f(ix):
+        a, b = xs[ix], ys[ix]
+        return A.tup(a + b, a - b, a * b, a / b, -a, abs(a), A.signum(a), A.recip(b), A.sqrt(abs(a)),
+                     A.truncate(a), A.round_(a), A.floor(a), A.ceiling(a), A.round_(a, "i32"),
+                     A.max_(a, b), A.min_(a, b), a < b, a.eq(b), A.is_nan(a / a),
+                     A.to_floating(a, "f64"), A.to_floating(a, "f32"), A.bitcast(a, "u32" if ty == "f32" else "u64"))
+    check(A.generate(A.index(300), f))
+
+
+def test_float_transcendentals():
+    x = rng.uniform(0.1, 3.0, size=500).astype(np.float32)
+    xs = A.use(x)
+    check(A.generate(A.index(500), lambda ix: A.tup(A.sin(xs[ix]), A.cos(xs[ix]), A.exp(xs[ix]), A.log(xs[ix]), A.tanh(xs[ix]),
+                                                     xs[ix] ** 1.5, A.atan2(xs[ix], 2.0), A.log_base(2.0, xs[ix]))), rtol=4e-7 * 8)
+
+
+def test_while_loop():
+    # collatz step count
+    x = rng.integers(1, 1000, size=200).astype(np.int64)
+    xs = A.use(x)
+
+    def f(ix):
+        st = A.while_(lambda s: s[0] > 1, lambda s: A.tup(A.cond((s[0] % 2).eq(0), s[0] // 2, 3 * s[0] + 1), s[1] + 1),
+                      A.tup(xs[ix], A.constant(0)))
+        return st[1]
+    check(A.generate(A.index(200), f))
+
+
+# ---- fold -------------------------------------------------------------------------
+@pytest.mark.parametrize("n", SIZES_1D)
+def test_fold_sum_int(n):
+    check(A.fold(add, 0, ints(n)))
+    check(A.fold(add, 42, ints(n, np.int64)))          # non-neutral seed (Fold.hs:55-60)
+
+
+@pytest.mark.parametrize("n", SIZES_1D[1:])
+def test_fold1_minmax(n):
+    check(A.fold1(A.max_, ints(n)))
+    check(A.fold1(A.min_, floats(n)))
+
+
+@pytest.mark.parametrize("n", [1, 100, 4096, 100003, 1 << 20])
+def test_dotp(n):
+    # Test/NoFib/Imaginary/DotP.hs:75-82
+    x, y = floats(n), floats(n)
+    check(A.fold(add, 0.0, A.zipWith(lambda a, b: a * b, x, y)), rtol=1e-4, atol=1e-4)
+
+
+def test_dotp_config0():
+    g = np.random.default_rng(42)
+    x = g.uniform(-1, 1, 1 << 20).astype(np.float32)
+    y = g.uniform(-1, 1, 1 << 20).astype(np.float32)
+    got = check(A.fold(add, 0.0, A.zipWith(lambda a, b: a * b, x, y)), rtol=1e-4, atol=1e-4)
+    assert abs(float(got) - float(np.dot(x.astype(np.float64), y.astype(np.float64)))) < 1e-4 * 600
+
+
+@pytest.mark.parametrize("shape", [(1, 1), (3, 5), (16, 64), (7, 129), (50, 1000), (5, 4096), (2, 3, 33), (4, 0), (0, 7), (300, 4), (3, 70000)])
+def test_fold_rows(shape):
+    m = ints(shape)
+    check(A.fold(add, 7, m))
+    if shape[-1] > 0:
+        check(A.fold1(A.max_, floats(shape)))
+
+
+def _mss(a, b):
+    # maximum segment sum monoid: non-commutative (Test/NoFib/Prelude/Fold.hs:287-309)
+    return A.tup(A.max_(a[0], A.max_(b[0], a[2] + b[1])), A.max_(a[1], a[3] + b[1]), A.max_(b[2], a[2] + b[3]), a[3] + b[3])
+
+
+@pytest.mark.parametrize("n", [1, 2, 33, 129, 1025, 4097, 20000])
+def test_fold_non_commutative(n):
+    x = ints(n, np.int64, -50, 50)
+    xs = A.map(lambda v: A.tup(A.max_(v, 0), A.max_(v, 0), A.max_(v, 0), v), x)
+    check(A.fold1(_mss, xs))
+    check(A.fold(_mss, A.tup(0, 0, 0, 0), xs))
+    m = ints((9, n // 3 + 1), np.int64, -50, 50)
+    check(A.fold1(_mss, A.map(lambda v: A.tup(A.max_(v, 0), A.max_(v, 0), A.max_(v, 0), v), m)))
+
+
+def test_fold_empty_error():
+    from accelerate_b200.backend import B200Error
+    with pytest.raises(B200Error):
+        A.backend.run(A.fold1(add, ints(0)))
+
+
+# ---- foldSeg -----------------------------------------------------------------------
+@pytest.mark.parametrize("nseg,maxlen", [(1, 5), (7, 0), (64, 128), (300, 40), (50, 3000)])
+def test_foldseg(nseg, maxlen):
+    lens = rng.integers(0, maxlen + 1, size=nseg).astype(np.int32)
+    n = int(lens.sum())
+    x = ints(n)
+    check(A.foldSeg(add, 0, x, lens))
+    lens1 = np.maximum(lens, 1)
+    x1 = ints(int(lens1.sum()))
+    check(A.fold1Seg(add, x1, lens1))
+    check(A.fold1Seg(A.max_, floats(int(lens1.sum())), lens1.astype(np.int64)))
+
+
+def test_foldseg_2d_and_noncommutative():
+    lens = np.array([3, 0, 5, 1, 7], np.int64)
+    m = ints((6, 16), np.int64, -50, 50)
+    check(A.foldSeg(add, 0, m, lens))
+    xs = A.map(lambda v: A.tup(A.max_(v, 0), A.max_(v, 0), A.max_(v, 0), v), m)
+    check(A.foldSeg(_mss, A.tup(0, 0, 0, 0), xs, lens))
+
+
+def test_fold1seg_empty_segment_error():
+    from accelerate_b200.backend import B200Error
+    with pytest.raises(B200Error):
+        A.backend.run(A.fold1Seg(add, ints(8), np.array([3, 0, 5], np.int32)))
+
+
+# ---- scans -------------------------------------------------------------------------
+SCAN_SIZES = [0, 1, 2, 3, 4, 5, 64, 65, 127, 128, 129, 511, 512, 513, 4095, 4096, 4097, 8192, 12289, 50001]
+
+
+@pytest.mark.parametrize("n", SCAN_SIZES)
+def test_scans_int(n):
+    x = ints(n, np.int32, 0, 100)
+    if n > 0:
+        check(A.scanl1(add, x))
+        check(A.scanr1(add, x))
+    check(A.scanl(add, 10, x))
+    check(A.scanr(add, 10, x))
+    check(list(A.scanl_prime(add, 10, x)))
+    check(list(A.scanr_prime(add, 10, x)))
+
+
+@pytest.mark.parametrize("n", [1, 1000, 4096, 70000])
+def test_scans_float_and_i64(n):
+    f = rng.uniform(0, 1, n).astype(np.float32)
+    tol = dict(rtol=1e-5 * np.sqrt(n), atol=1e-5 * np.sqrt(n))
+    check(list(A.scanl_prime(add, 0.0, f)), **tol)
+    check(A.scanl1(add, f), **tol)
+    big = rng.integers(np.iinfo(np.int64).min, np.iinfo(np.int64).max, size=n, dtype=np.int64)
+    check(A.scanr1(A.max_, big))
+    check(A.scanl1(A.min_, big))
+
+
+def _interval(a, b):
+    # non-commutative "interval" monoid (Test/NoFib/Prelude/Scan.hs:745-771)
+    return A.tup(a[0], b[1])
+
+
+@pytest.mark.parametrize("n", [1, 5, 129, 4097, 9000])
+def test_scans_non_commutative(n):
+    x = ints(n, np.int64)
+    pairs = A.map(lambda v: A.tup(v, v + 1), x)
+    check(A.scanl1(_interval, pairs))
+    check(A.scanr1(_interval, pairs))
+    check(A.scanl(_interval, A.tup(-1, -2), pairs))
+    check(A.scanr(_interval, A.tup(-1, -2), pairs))
+    check(list(A.scanl_prime(_interval, A.tup(-1, -2), pairs)))
+    check(list(A.scanr_prime(_interval, A.tup(-1, -2), pairs)))
+    m = A.map(lambda v: A.tup(A.max_(v, 0), A.max_(v, 0), A.max_(v, 0), v), x)
+    check(A.scanl1(_mss, m))
+    check(A.scanr1(_mss, m))
+
+
+@pytest.mark.parametrize("shape", [(1, 1), (3, 5), (31, 257), (4, 4096), (3, 4100), (2, 3, 9), (5, 0), (0, 5), (257, 31)])
+def test_scans_rows(shape):
+    m = ints(shape, np.int32, 0, 100)
+    if shape[-1] > 0:
+        check(A.scanl1(add, m))
+        check(A.scanr1(add, m))
+    check(A.scanl(add, 1, m))
+    check(A.scanr(add, 1, m))
+    check(list(A.scanl_prime(add, 1, m)))
+    check(list(A.scanr_prime(add, 1, m)))
+
+
+def test_scan_wraps_int32():
+    x = np.full(5000, 2_000_000_000, np.int32)
+    check(A.scanl1(add, x))
+
+
+# ---- permute -----------------------------------------------------------------------
+@pytest.mark.parametrize("n,bins", [(0, 4), (1, 1), (20, 10), (5000, 37), (100000, 1000), (200000, 70000)])
+def test_histogram(n, bins):
+    keys = rng.integers(0, bins, size=n).astype(np.int32)
+    k = A.use(keys)
+    check(A.permute(add, A.fill(bins, A.constant(np.int32(0))), lambda ix: A.Just_(A.index(A.from_integral(k[ix], "i64"))),
+                    A.fill(k.shape, A.constant(np.int32(1)))))
+
+
+def test_permute_float_dropped():
+    n, bins = 100000, 1 << 10
+    keys = rng.integers(0, 1 << 30, size=n).astype(np.int32)
+    drop = (rng.uniform(size=n) < 0.1).astype(np.uint8)
+    vals = rng.uniform(0, 1, n).astype(np.float32)
+    k, d = A.use(keys), A.use(drop)
+    acc = A.permute(add, A.fill(bins, A.constant(np.float32(0))),
+                    lambda ix: A.cond(d[ix].ne(0), A.Nothing_(1), A.Just_(A.index(A.from_integral(k[ix], "i64") % bins))), vals)
+    check(acc, rtol=1e-5 * np.sqrt(n / bins), atol=1e-5 * np.sqrt(n / bins))
+
+
+def test_permute_minmax_cas_and_scatter():
+    n, bins = 20000, 97
+    keys = rng.integers(0, bins, size=n).astype(np.int64)
+    k = A.use(keys)
+    p = lambda ix: A.Just_(A.index(k[ix]))  # noqa: E731
+    check(A.permute(A.max_, A.fill(bins, A.constant(np.int32(-5))), p, ints(n)))
+    check(A.permute(A.min_, A.fill(bins, A.constant(np.int64(5))), p, ints(n, np.int64)))
+    check(A.permute(A.min_, A.fill(bins, A.constant(np.float32(5))), p, floats(n)))          # CAS loop
+    check(A.permute(lambda a, b: a * b, A.fill(bins, A.constant(np.int64(1))), p, ints(n, np.int64, 1, 4)))  # CAS loop
+    check(A.permute(lambda a, b: a | b, A.fill(bins, A.constant(np.uint32(0))), p, ints(n, np.uint32, 0, 1 << 20)))
+    perm = rng.permutation(n).astype(np.int64)
+    pu = A.use(perm)
+    check(A.permute(lambda a, b: a, A.fill(n, A.constant(np.float32(0))), lambda ix: A.Just_(A.index(pu[ix])), floats(n)))
+
+
+def test_permute_tuple_lock_and_small_types():
+    n, bins = 5000, 13
+    keys = rng.integers(0, bins, size=n).astype(np.int64)
+    k = A.use(keys)
+    p = lambda ix: A.Just_(A.index(k[ix]))  # noqa: E731
+    src = A.zip(ints(n, np.int64), ints(n, np.int32, 0, 9))
+    f = lambda a, b: A.tup(a[0] + b[0], A.max_(a[1], b[1]))  # noqa: E731
+    check(A.permute(f, A.zip(A.fill(bins, A.constant(0)), A.fill(bins, A.constant(np.int32(0)))), p, src))
+    check(A.permute(add, A.fill(bins, A.constant(np.int16(0))), p, ints(n, np.int16, -3, 3)))
+
+
+def test_permute_2d_to_2d():
+    m = ints((17, 23), np.int32, 0, 5)
+    mu = A.use(m)
+    acc = A.permute(add, A.fill(A.index(5, 5), A.constant(np.int32(0))),
+                    lambda ix: A.cond((ix[0] + ix[1]) % 3 == 0 if False else ((ix[0] + ix[1]) % 3).eq(0), A.Nothing_(2),
+                                      A.Just_(A.index(A.from_integral(mu[ix], "i64"), ix[1] % 5))), mu)
+    check(acc)
+
+
+# ---- stencils ------------------------------------------------------------------------
+BOUNDARIES = [A.clamp, A.mirror, A.wrap, A.function(lambda ix: A.constant(np.float32(0.25))), A.constant_boundary(np.float32(-2.0))]
+
+
+@pytest.mark.parametrize("bnd", range(5))
+@pytest.mark.parametrize("shape", [(5, 6), (32, 128), (33, 129), (70, 300), (9, 9)])
+def test_stencil_2d_3x3(shape, bnd):
+    m = rng.uniform(0, 1, shape).astype(np.float32)
+    check(A.stencil(lambda s: 0.25 * (s[0][1] + s[2][1] + s[1][0] + s[1][2]), BOUNDARIES[bnd], m))
+    check(A.stencil(lambda s: sum((s[i][j] * float(i * 3 + j + 1) for i in range(3) for j in range(3)), A.constant(np.float32(0))), BOUNDARIES[bnd], m))
+
+
+@pytest.mark.parametrize("ext", [3, 5, 7, 9])
+def test_stencil_1d(ext):
+    x = rng.uniform(0, 1, 5000).astype(np.float32)
+    for b in BOUNDARIES[:3]:
+        check(A.stencil(lambda s: sum((s[i] * float(i + 1) for i in range(ext)), A.constant(np.float32(0))), b, x, extent=(ext,)))
+
+
+@pytest.mark.parametrize("ext", [5, 7, 9])
+def test_stencil_2d_large_patterns(ext):
+    m = ints((40, 140), np.int32, 0, 10)
+    for b in BOUNDARIES[:3]:
+        check(A.stencil(lambda s: sum((s[i][j] * (i * ext + j) for i in range(ext) for j in range(ext)), A.constant(np.int32(0))), b, m,
+                        extent=(ext, ext)))
+
+
+def test_stencil_3d():
+    v = rng.uniform(0, 1, (9, 11, 70)).astype(np.float32)
+    for b in BOUNDARIES[:3]:
+        check(A.stencil(lambda s: s[0][1][1] + s[2][1][1] + s[1][0][1] + s[1][2][1] + s[1][1][0] + s[1][1][2] - 6.0 * s[1][1][1], b, v))
+
+
+def test_stencil2_gaussian_mirror():
+    a = rng.uniform(0, 1, (37, 133)).astype(np.float32)
+    b = rng.uniform(0, 1, (35, 140)).astype(np.float32)
+    w = [[1, 2, 1], [2, 4, 2], [1, 2, 1]]
+    f = lambda s, t: sum((np.float32(w[i][j] / 16.0) * (s[i][j] + t[i][j]) for i in range(3) for j in range(3)), A.constant(np.float32(0)))  # noqa: E731
+    check(A.stencil2(f, A.mirror, a, A.mirror, b))
+
+
+def test_stencil_delayed_input_and_jacobi_iterated():
+    m = rng.uniform(0, 1, (50, 200)).astype(np.float32)
+    jac = lambda s: 0.25 * (s[0][1] + s[2][1] + s[1][0] + s[1][2])  # noqa: E731
+    acc = A.map(lambda v: v * 2.0, m)
+    for _ in range(5):
+        acc = A.stencil(jac, A.clamp, acc)
+    check(acc)
+
+
+# ---- composition ----------------------------------------------------------------------
+def test_smvm_like_pipeline():
+    # SMVM (Test/NoFib/Spectral/SMVM.hs:77-85): foldSeg over gathered products
+    nrows, ncols = 200, 300
+    lens = rng.integers(0, 12, nrows).astype(np.int32)
+    nnz = int(lens.sum())
+    cols = rng.integers(0, ncols, nnz).astype(np.int32)
+    vals = floats(nnz)
+    vec = floats(ncols)
+    v = A.use(vec)
+    prods = A.zipWith(lambda i, x: x * v[A.index(A.from_integral(i, "i64"))], cols, vals)
+    check(A.foldSeg(add, 0.0, prods, lens), **F32_TOL)
+
+
+def test_reshape_and_unit():
+    x = ints(24)
+    check(A.fold(add, 0, A.reshape(A.index(4, 6), x)))
+    s = A.fold(add, 0, x)
+    check(A.map(lambda v: v + A.the(s), x))
