@@ -47,6 +47,11 @@ void build_nodes(Program& p) {
 }
 }  // namespace
 
+namespace accb200 {
+// lets other translation units of the library (the ahead-of-time kernels) report through b200_last_error
+void set_last_error(const std::string& msg) { g_error = msg; }
+}  // namespace accb200
+
 extern "C" {
 
 const char* b200_last_error(void) { return g_error.c_str(); }

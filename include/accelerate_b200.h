@@ -104,6 +104,28 @@ int b200_compile_check(const char* text, size_t len, char* log, size_t log_len);
 /* Generated CUDA source of node `node` (default variant), for inspection. */
 int b200_kernel_source(const char* text, size_t len, int node, char* out, size_t out_len);
 
+/* Inclusive prefix sum (scanl1 (+)) of `n` Int32 values, device to device,
+ * WITHOUT allocating anything.  It has no counterpart in the reference: it
+ * exists for callers that may not allocate device memory themselves nor let
+ * this library do it — a host runtime whose collector owns all device memory
+ * and lends out only the input and output buffers, or a caller on a path where
+ * cudaMalloc's implicit device synchronisation is unacceptable.
+ *
+ * `in` and `out` are device pointers on the current device (they may not
+ * overlap); `stream` is a cudaStream_t (NULL = default stream).  The call
+ * returns after the result is complete.  The look-back descriptors of the scan
+ * live in a fixed __device__ array of about 0.8 MB that every GPU using this
+ * library holds until the process exits, hence:
+ *   - n may not exceed B200_NOALLOC_SCAN_MAX_ELEMS; more is refused (B200_ERR_ARG);
+ *   - calls on the same GPU share that array and must not overlap in time
+ *     (concurrent calls race on it); the array keeps the last call's contents
+ *     and each call clears what it needs before use;
+ *   - the first call on each device resolves the array's device address; make
+ *     that first call before beginning any stream capture.
+ * On failure the message is available from b200_last_error(). */
+#define B200_NOALLOC_SCAN_MAX_ELEMS (1LL << 28)
+int b200_scanl1_add_i32_noalloc(const int32_t* in, int32_t* out, int64_t n, void* stream);
+
 #ifdef __cplusplus
 }
 #endif
