@@ -10,6 +10,7 @@
 #include <cmath>
 #include <cstdlib>
 #include <cstring>
+#include <functional>
 #include <sstream>
 
 namespace accb200 {
@@ -106,8 +107,9 @@ class Gen {
   std::ostringstream out;
   int& tmp;
   std::vector<std::pair<std::string, CVal>> env;
-  // stream detection: (index A (var ix_param)) becomes a function parameter
-  std::string ix_param;
+  // stream detection: (index A ix) where ix evaluates to exactly the loop index becomes a
+  // function parameter supplied by the skeleton
+  std::vector<std::string> loop_ix;
   std::vector<std::string>* streams = nullptr;
   std::string ind = "  ";
 
@@ -234,7 +236,8 @@ class Gen {
       case X_PRIM: return gen_prim(e);
       case X_INDEX: {
         const Expr& ix = *e.a[0];
-        if (streams && ix.kind == X_VAR && ix.name == ix_param) {
+        CVal iv = gen(ix);
+        if (streams && iv.leaf == loop_ix) {
           // element at exactly the loop index: supplied by the skeleton
           size_t k = 0;
           for (; k < streams->size(); ++k)
@@ -245,7 +248,6 @@ class Gen {
           for (size_t i = 0; i < nl; ++i) r.leaf.push_back("s" + std::to_string(k) + "_l" + std::to_string(i));
           return r;
         }
-        CVal iv = gen(ix);
         return load(e.name, to_index(shape_of(e.name), iv.leaf));
       }
       case X_LINDEX: {
@@ -485,13 +487,16 @@ struct GlueBuilder {
 
   // The access functions of a delayed operand (see codegen.hpp: streams).
   void delayed(const std::string& D, const Fun& index, int rank, const Type& elt) {
+    delayed_custom(D, rank, elt, [&](Gen& g, const CVal& ix) { return g.apply(index, {ix}); });
+  }
+  // `body` produces the element at loop index `ix` (leaves ix0, ix1, ...)
+  void delayed_custom(const std::string& D, int rank, const Type& elt, const std::function<CVal(Gen&, const CVal&)>& body) {
     std::string S = ps.need_struct(elt);
     std::vector<std::string> streams;
     Gen g(ps, tmp);
-    g.ix_param = index.params[0];
+    g.loop_ix = index_val(rank, "ix").leaf;
     g.streams = &streams;
-    g.env.emplace_back(index.params[0], index_val(rank, "ix"));
-    CVal r = g.gen(*index.body);
+    CVal r = body(g, index_val(rank, "ix"));
     // stream value parameters
     std::string sparams, sargs_generic, sargs_lin, decl4, sargs4;
     std::ostringstream gen_loads, lin_loads, vec_loads;
@@ -649,33 +654,44 @@ Glue build_glue(const Node& n, const std::map<std::string, ArrayInfo>& arrays) {
       if (n.kind == N_SCAN || n.kind == N_SCAN2) {
         def["ACC_RIGHT"] = n.right ? "1" : "0";
         def["ACC_SCAN2"] = n.kind == N_SCAN2 ? "1" : "0";
+        std::vector<Ty> sl = n.elt.leaves();
+        if (sl.size() == 1) {
+          def["SCAN_PACKED"] = "1";
+          def["SCAN_T"] = cty(sl[0]);
+          def["SCAN_T_BYTES"] = std::to_string(ty_bytes[sl[0]]);
+        } else {
+          def["SCAN_PACKED"] = "0";
+        }
       }
       break;
     }
     case N_PERMUTE: {
-      b.delayed("D0", *n.d[0].index, n.d[0].rank, n.elt);
       b.binary_fun("F_combine", *n.f, n.elt);
       b.output(0, n.elt);
-      // index function: source index -> (tag, target linear index)
+      // One function per source element: \ix -> (tag, toIndex (shape out) target, source ! ix).
+      // Index function and source share the loop index, so every array either of them reads at
+      // exactly that index is loaded once, vectorised.
       {
-        int rank = n.d[0].rank;
-        int orank = arrays.at(n.arr).rank;
-        Gen g(b.ps, b.tmp);
-        g.env.emplace_back(n.g->params[0], b.index_val(rank, "ix"));
-        CVal r = g.gen(*n.g->body);
-        std::vector<std::string> sh, ix(r.leaf.begin() + 1, r.leaf.end());
-        for (int d = 0; d < orank; ++d) { sh.push_back("p.out_d" + std::to_string(d)); b.ps.use_named("out_d" + std::to_string(d)); }
-        std::ostringstream decomp;
-        if (rank >= 1) decomp << "  const i64 ix" << (rank - 1) << " = j;\n";
-        if (rank == 2) decomp << "  const i64 ix0 = row;\n";
-        if (rank >= 3) {
-          decomp << "  i64 r_ = row;\n";
-          for (int d = rank - 2; d >= 1; --d) decomp << "  const i64 ix" << d << " = r_ % p.D0_e" << d << "; r_ /= p.D0_e" << d << ";\n";
-          decomp << "  const i64 ix0 = r_;\n";
-        }
-        b.fns << "__device__ __forceinline__ bool P_index(const Params& p, i64 row, i64 j, i64& dst) {\n" << decomp.str() << g.out.str()
-              << "  if (" << r.leaf[0] << " == 0) return false;\n"
-              << "  dst = " << g.to_index(sh, ix) << ";\n  return true;\n}\n";
+        const int rank = n.d[0].rank;
+        const int orank = arrays.at(n.arr).rank;
+        const Type pelemT = Type::tup({Type::scalar(U8), Type::scalar(I64), n.elt});
+        std::vector<std::string> outsh;
+        for (int d = 0; d < orank; ++d) { outsh.push_back("p.out_d" + std::to_string(d)); b.ps.use_named("out_d" + std::to_string(d)); }
+        b.delayed_custom("P", rank, pelemT, [&](Gen& g, const CVal& ix) {
+          CVal m = g.apply(*n.g, {ix});            // (tag, target index)
+          CVal v = g.apply(*n.d[0].index, {ix});   // source value
+          CVal r;
+          r.ty = pelemT;
+          r.leaf.push_back(m.leaf[0]);
+          r.leaf.push_back(g.def(I64, g.to_index(outsh, std::vector<std::string>(m.leaf.begin() + 1, m.leaf.end()))));
+          r.leaf.insert(r.leaf.end(), v.leaf.begin(), v.leaf.end());
+          return r;
+        });
+        std::string S = b.ps.need_struct(pelemT);
+        size_t nl = n.elt.nleaves();
+        b.fns << "typedef " << S << " pelem_t;\n__device__ __forceinline__ " << E << " P_value(const pelem_t& e) { " << E << " r_;";
+        for (size_t i = 0; i < nl; ++i) b.fns << " r_.l" << i << " = e.l" << (i + 2) << ";";
+        b.fns << " return r_; }\n";
       }
       // how the update is applied
       std::vector<Ty> l = n.elt.leaves();

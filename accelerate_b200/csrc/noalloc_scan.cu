@@ -42,6 +42,10 @@ namespace {
 #define ACC_RIGHT 0
 #define ACC_SCAN2 0
 #define ACC_COMMUTATIVE 1
+#define SCAN_PACKED 1
+#define SCAN_T i32
+#define SCAN_T_BYTES 4
+#define SCAN_MIN_BLOCKS 4
 struct E_i32 { i32 l0; };
 typedef E_i32 elt_t;
 __device__ __forceinline__ E_i32 acc_shfl_down(const E_i32& v, int d) { E_i32 r; r.l0 = acc_shfl1_down(v.l0, d); return r; }
@@ -83,7 +87,7 @@ __device__ __forceinline__ void OUT0_store4(const Params& p, i64 lin, const E_i3
 constexpr long long kMaxElems = 1LL << 28;                      // B200_NOALLOC_SCAN_MAX_ELEMS
 constexpr long long kMaxTiles = kMaxElems / SCAN_TILE;
 constexpr size_t kHeadBytes = 256;                              // [0] ticket counter, [1] error word
-constexpr size_t kStatusBytes = (size_t)kMaxTiles * 4;
+constexpr size_t kStatusBytes = (size_t)kMaxTiles * 8;     // one packed {status, value} word per tile
 constexpr size_t kValueBytes = (size_t)kMaxTiles * sizeof(E_i32);
 constexpr size_t kScratchBytes = kHeadBytes + kStatusBytes + 2 * kValueBytes;
 static __device__ __align__(256) unsigned char g_scan_scratch[kScratchBytes];
@@ -133,7 +137,7 @@ extern "C" int b200_scanl1_add_i32_noalloc(const int32_t* in, int32_t* out, int6
   const long long tiles = (n + SCAN_TILE - 1) / SCAN_TILE;
   // the array keeps the previous call's contents: clear the counter, the error word and
   // the status words this call will read
-  e = cudaMemsetAsync(base, 0, kHeadBytes + (size_t)tiles * 4, stream);
+  e = cudaMemsetAsync(base, 0, kHeadBytes + (size_t)tiles * 8, stream);
   if (e != cudaSuccess) return fail(B200_ERR_CUDA, std::string("cudaMemsetAsync: ") + cudaGetErrorString(e));
   Params p;
   p.in_l0 = in;

@@ -135,6 +135,12 @@ StencilTile stencil_tile(int rank) {
   if (rank == 2) return {1, 32, 128, 256};
   return {4, 8, 64, 256};
 }
+// resident CTAs per SM the scan kernel is compiled for (register budget)
+std::map<std::string, std::string> scan_variant(const Type& elt) {
+  size_t bytes = 0;
+  for (Ty t : elt.leaves()) bytes += ty_bytes[t];
+  return {{"SCAN_MIN_BLOCKS", bytes <= 4 ? "4" : (bytes <= 8 ? "3" : "1")}};
+}
 std::map<std::string, std::string> stencil_variant(int rank) {
   StencilTile t = stencil_tile(rank);
   return {{"ST_T0", std::to_string(t.t0)}, {"ST_T1", std::to_string(t.t1)}, {"ST_T2", std::to_string(t.t2)},
@@ -152,7 +158,7 @@ std::vector<std::pair<std::string, std::map<std::string, std::string>>> default_
       v.push_back({"fold", {{"FOLD_G", "4"}}});
       break;
     case N_FOLDSEG: v.push_back({"foldseg", {{"FOLDSEG_G", "32"}}}); break;
-    case N_SCAN: case N_SCAN2: v.push_back({"scan", {}}); break;
+    case N_SCAN: case N_SCAN2: v.push_back({"scan", scan_variant(n.elt)}); break;
     case N_PERMUTE: {
       v.push_back({"permute", {}});
       const std::string& m = g.defines.at("PERMUTE_MODE");
@@ -639,7 +645,7 @@ void Program::run(const std::vector<DevArrayP>& inputs, std::vector<DevArrayP>& 
         if (mode == 1) out_vec = right ? ((m + 1) % 4 == 0) : (rows == 1 || (m + 1) % 4 == 0);
         else out_vec = right ? (m % 4 == 0) : (rows == 1 || m % 4 == 0);
         const size_t sb = struct_bytes(n.elt);
-        const size_t status_bytes = ((size_t)total_tiles * 4 + 255) / 256 * 256;
+        const size_t status_bytes = ((size_t)total_tiles * 16 + 255) / 256 * 256;  // packed descriptors take up to 16 bytes
         const size_t val_bytes = ((size_t)total_tiles * sb + 255) / 256 * 256;
         char* base = (char*)c.scan_descriptors(status_bytes + 2 * val_bytes);
         L.named["n"] = m;
@@ -652,7 +658,7 @@ void Program::run(const std::vector<DevArrayP>& inputs, std::vector<DevArrayP>& 
         L.named["incl"] = (int64_t)(uintptr_t)(base + status_bytes + val_bytes);
         L.named["counter"] = (int64_t)(uintptr_t)(c.d_words + 2);
         L.named["epoch"] = c.scan_epoch;
-        CompiledKernel& k = c.kernel(assemble_source(st.glue, "scan", {}), "acc_scan", 256, 0);
+        CompiledKernel& k = c.kernel(assemble_source(st.glue, "scan", scan_variant(n.elt)), "acc_scan", 256, 0);
         L.launch(k, total_tiles, 256, 0);
         break;
       }
@@ -667,11 +673,11 @@ void Program::run(const std::vector<DevArrayP>& inputs, std::vector<DevArrayP>& 
         L.outs = {out};
         env[n.outs[0]] = out;
         if (total == 0) break;
-        L.bind_delayed("D0", ext, 0);
+        L.bind_delayed("P", ext, 0);
         const int64_t inner = ext.empty() ? 1 : ext.back();
         const int64_t out_n = out->size();
         L.named["n"] = total;
-        L.named["vec"] = (L.fast("D0") && (ext.size() <= 1 || inner % 4 == 0)) ? 1 : 0;
+        L.named["vec"] = (L.fast("P") && (ext.size() <= 1 || inner % 4 == 0)) ? 1 : 0;
         L.named["out_n"] = out_n;
         for (size_t d = 0; d < def->shape.size(); ++d) L.named["out_d" + std::to_string(d)] = def->shape[d];
         const std::string& mode = st.glue.defines.at("PERMUTE_MODE");

@@ -52,6 +52,16 @@ extern "C" __global__ void __launch_bounds__(FSEG_THREADS) acc_foldseg(const Par
       if (j0 > end) j0 = end;
       for (i64 j = start + gl; j < j0; j += FOLDSEG_G) fseg_push(p, acc, have, D0_get(p, row, j));
       i64 jj = j0 + (i64)gl * 4;
+      for (; jj + 3 * FOLDSEG_G * 4 + 4 <= end; jj += 4 * FOLDSEG_G * 4) {
+        elt_t x[4][4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) D0_get4(p, row, jj + u * FOLDSEG_G * 4, x[u]);
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+#pragma unroll
+          for (int k = 0; k < 4; ++k) fseg_push(p, acc, have, x[u][k]);
+        }
+      }
       for (; jj + 4 <= end; jj += FOLDSEG_G * 4) {
         elt_t x[4];
         D0_get4(p, row, jj, x);

@@ -138,9 +138,14 @@ __device__ __forceinline__ void permute_update(const Params& p, i64 dst, const e
 #endif
 }
 
+__device__ __forceinline__ void permute_elem(const Params& p, const pelem_t& e) {
+  // the reference checks the target index (Shape.hs:102-106); here an out-of-range target is dropped
+  if (e.l0 != 0 && (u64)e.l1 < (u64)p.out_n) permute_update(p, e.l1, P_value(e));
+}
+
 extern "C" __global__ void __launch_bounds__(PERMUTE_THREADS) acc_permute(const Params p) {
   const i64 n = p.n;
-  const i64 inner = D0_INNER;
+  const i64 inner = P_INNER;
   const i64 tid = (i64)blockIdx.x * PERMUTE_THREADS + threadIdx.x;
   const i64 nthreads = (i64)gridDim.x * PERMUTE_THREADS;
 #if PERMUTE_SMEM
@@ -151,25 +156,38 @@ extern "C" __global__ void __launch_bounds__(PERMUTE_THREADS) acc_permute(const 
   i64 done = 0;
   if (p.vec) {
     const i64 nv = n >> 2;
-    for (i64 v = tid; v < nv; v += nthreads) {
+    i64 v = tid;
+    // two 128-bit groups in flight per thread
+    for (; v + nthreads < nv; v += 2 * nthreads) {
+      pelem_t x[2][4];
+#pragma unroll
+      for (int u = 0; u < 2; ++u) {
+        const i64 i = (v + u * nthreads) << 2;
+        i64 row = 0, j = i;
+        if (inner != n) { row = i / inner; j = i - row * inner; }
+        P_get4(p, row, j, x[u]);
+      }
+#pragma unroll
+      for (int u = 0; u < 2; ++u) {
+#pragma unroll
+        for (int k = 0; k < 4; ++k) permute_elem(p, x[u][k]);
+      }
+    }
+    for (; v < nv; v += nthreads) {
       const i64 i = v << 2;
       i64 row = 0, j = i;
       if (inner != n) { row = i / inner; j = i - row * inner; }
-      elt_t x[4];
-      D0_get4(p, row, j, x);
+      pelem_t x[4];
+      P_get4(p, row, j, x);
 #pragma unroll
-      for (int k = 0; k < 4; ++k) {
-        i64 dst;
-        if (P_index(p, row, j + k, dst)) permute_update(p, dst, x[k]);
-      }
+      for (int k = 0; k < 4; ++k) permute_elem(p, x[k]);
     }
     done = nv << 2;
   }
   for (i64 i = done + tid; i < n; i += nthreads) {
     i64 row = 0, j = i;
     if (inner != n) { row = i / inner; j = i - row * inner; }
-    i64 dst;
-    if (P_index(p, row, j, dst)) permute_update(p, dst, D0_get(p, row, j));
+    permute_elem(p, P_get(p, row, j));
   }
 #if PERMUTE_SMEM
   __syncthreads();

@@ -16,6 +16,10 @@
 //
 // Descriptors live in scratch memory and are tagged with a launch epoch, so
 // they need no clearing between launches: status = epoch << 2 | state.
+// SCAN_PACKED (one scalar leaf of at most 8 bytes): status and value share one
+// 8- or 16-byte word that is written and read with a single access, so the
+// look-back needs one L2 round trip per window and no fences.  Otherwise
+// (tuples) the value is written first, then a fence, then the status word.
 //
 // Named parameters: n, rows, tiles_per_row, in_vec, out_vec, status, agg, incl,
 // counter, epoch, err, spin_limit.
@@ -38,6 +42,45 @@
 #define ACC_SCAN_MODE 1
 #else
 #define ACC_SCAN_MODE 0
+#endif
+
+#ifndef SCAN_PACKED
+#define SCAN_PACKED 0
+#endif
+#ifndef SCAN_MIN_BLOCKS
+#define SCAN_MIN_BLOCKS 1
+#endif
+#if SCAN_PACKED
+#if SCAN_T_BYTES <= 4
+// [63:32] status, [31:0] value bits
+__device__ __forceinline__ void scan_desc_store(i64 base, i64 idx, u32 status, SCAN_T v) {
+  u32 bits = 0;
+  memcpy(&bits, &v, sizeof(SCAN_T));
+  const u64 w = ((u64)status << 32) | bits;
+  asm volatile("st.relaxed.gpu.global.u64 [%0], %1;" ::"l"(reinterpret_cast<u64*>(base) + idx), "l"(w) : "memory");
+}
+__device__ __forceinline__ u32 scan_desc_load(i64 base, i64 idx, SCAN_T& v) {
+  u64 w;
+  asm volatile("ld.relaxed.gpu.global.u64 %0, [%1];" : "=l"(w) : "l"(reinterpret_cast<const u64*>(base) + idx) : "memory");
+  const u32 bits = (u32)w;
+  memcpy(&v, &bits, sizeof(SCAN_T));
+  return (u32)(w >> 32);
+}
+#else
+// 16-byte descriptor {value bits, status}: one aligned 128-bit access
+__device__ __forceinline__ void scan_desc_store(i64 base, i64 idx, u32 status, SCAN_T v) {
+  u64 bits = 0;
+  memcpy(&bits, &v, sizeof(SCAN_T));
+  asm volatile("st.relaxed.gpu.global.v2.u64 [%0], {%1, %2};" ::"l"(reinterpret_cast<ulonglong2*>(base) + idx), "l"(bits), "l"((u64)status)
+               : "memory");
+}
+__device__ __forceinline__ u32 scan_desc_load(i64 base, i64 idx, SCAN_T& v) {
+  u64 bits, st;
+  asm volatile("ld.relaxed.gpu.global.v2.u64 {%0, %1}, [%2];" : "=l"(bits), "=l"(st) : "l"(reinterpret_cast<const ulonglong2*>(base) + idx) : "memory");
+  memcpy(&v, &bits, sizeof(SCAN_T));
+  return (u32)st;
+}
+#endif
 #endif
 
 // a . b with a earlier than b in logical order
@@ -185,9 +228,13 @@ __device__ __forceinline__ void scan_tile(const Params& p, const i64 T, const i6
     } else {
       if (lane == 0) {
         // an empty aggregate cannot occur: only the last tile of a row can be partial, and it has no successor
+#if SCAN_PACKED
+        scan_desc_store(p.status, T, (epoch << 2) | SCAN_ST_AGG, agg.l0);
+#else
         d_agg[T] = agg;
         __threadfence();
         status[T] = (epoch << 2) | SCAN_ST_AGG;
+#endif
       }
       const i64 row_first = T - tt;
       i64 look = T - 1;
@@ -195,13 +242,20 @@ __device__ __forceinline__ void scan_tile(const Params& p, const i64 T, const i6
         const i64 idx = look - lane;
         const bool inrow = idx >= row_first;
         u32 st = 0;
+        elt_t v;
         if (inrow) {
           i64 spins = 0;
           for (;;) {
+#if SCAN_PACKED
+            st = scan_desc_load(p.status, idx, v.l0);
+#else
             st = status[idx];
+#endif
             if ((st >> 2) == epoch) break;
             if (++spins > p.spin_limit) { failed = 1; break; }
+#if !SCAN_PACKED
             __nanosleep(20);
+#endif
           }
         }
         failed = __any_sync(ACC_FULL_MASK, failed);
@@ -209,12 +263,13 @@ __device__ __forceinline__ void scan_tile(const Params& p, const i64 T, const i6
         const bool is_prefix = inrow && (st & 3u) == SCAN_ST_PREFIX;
         const unsigned pm = __ballot_sync(ACC_FULL_MASK, is_prefix);
         const int nearest = pm ? (__ffs((int)pm) - 1) : 31;
-        elt_t v;
         bool hv = inrow && lane <= nearest;
+#if !SCAN_PACKED
         if (hv) {
           __threadfence();
           v = scan_ld_volatile(is_prefix ? d_incl + idx : d_agg + idx);
         }
+#endif
         // lane l holds tile look-l: higher lanes are earlier
 #pragma unroll
         for (int d = 1; d < 32; d <<= 1) {
@@ -234,9 +289,13 @@ __device__ __forceinline__ void scan_tile(const Params& p, const i64 T, const i6
         elt_t inc = excl;
         bool hinc = hexcl;
         scan_join(p, inc, hinc, agg, hagg);
+#if SCAN_PACKED
+        scan_desc_store(p.status, T, (epoch << 2) | SCAN_ST_PREFIX, inc.l0);
+#else
         if (hinc) d_incl[T] = inc;
         __threadfence();
         status[T] = (epoch << 2) | SCAN_ST_PREFIX;
+#endif
 #if ACC_SCAN_MODE != 0
         if (tt == p.tiles_per_row - 1) {
           // the row's total (seed included)
@@ -318,7 +377,7 @@ __device__ __forceinline__ void scan_tile(const Params& p, const i64 T, const i6
   }
 }
 
-extern "C" __global__ void __launch_bounds__(SCAN_THREADS) acc_scan(const Params p) {
+extern "C" __global__ void __launch_bounds__(SCAN_THREADS, SCAN_MIN_BLOCKS) acc_scan(const Params p) {
   __shared__ elt_t sm_v[SCAN_WARPS];
   __shared__ int sm_h[SCAN_WARPS];
   __shared__ elt_t sm_excl;
