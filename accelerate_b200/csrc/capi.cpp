@@ -343,7 +343,10 @@ int b200_kernel_source(const char* text, size_t len, int node, char* out, size_t
   build_nodes(p);
   if (node < 0 || (size_t)node >= p.nodes.size() || !p.nodes[node].has_glue) throw Error(B200_ERR_ARG, "no such kernel node");
   auto vs = default_variants(p.ir->nodes[node], p.nodes[node].glue);
-  std::string src = assemble_source(p.nodes[node].glue, vs[0].first, vs[0].second);
+  size_t which = 0;
+  if (const char* e = getenv("ACCELERATE_B200_SOURCE_VARIANT")) which = (size_t)atoi(e);
+  if (which >= vs.size()) throw Error(B200_ERR_ARG, "no such kernel variant");
+  std::string src = assemble_source(p.nodes[node].glue, vs[which].first, vs[which].second);
   if (out && out_len) {
     size_t n = std::min(out_len - 1, src.size());
     memcpy(out, src.data(), n);

@@ -7,6 +7,7 @@
 // compiled with --fmad=false).
 #include "codegen.hpp"
 
+#include <algorithm>
 #include <cmath>
 #include <cstdlib>
 #include <cstring>
@@ -547,6 +548,10 @@ struct GlueBuilder {
     fns << "__device__ __forceinline__ void " << D << "_get4(const Params& p, i64 row, i64 j, " << S << " (&o)[4]) {\n" << decomp.str()
         << "  const i64 lin = row * " << inner << " + j; (void)lin;\n" << vec_loads.str()
         << "  _Pragma(\"unroll\") for (int k = 0; k < 4; ++k) o[k] = " << D << "_body(p" << ixa4 << sargs4 << ");\n}\n";
+    // same with the linear address of the first element supplied by the caller
+    fns << "__device__ __forceinline__ void " << D << "_get4_lin(const Params& p, i64 lin, i64 row, i64 j, " << S << " (&o)[4]) {\n" << decomp.str()
+        << "  (void)lin;\n" << vec_loads.str()
+        << "  _Pragma(\"unroll\") for (int k = 0; k < 4; ++k) o[k] = " << D << "_body(p" << ixa4 << sargs4 << ");\n}\n";
     glue.defines[D + "_NSTREAMS"] = std::to_string(streams.size());
     glue.defines[D + "_INNER"] = rank >= 1 ? "(p." + D + "_e" + std::to_string(rank - 1) + ")" : "((i64)1)";
   }
@@ -792,7 +797,8 @@ Glue build_glue(const Node& n, const std::map<std::string, ArrayInfo>& arrays) {
         for (size_t i = 0; i < l.size(); ++i) fill << "  sm" << A << "_l" << i << "[pos] = v.l" << i << ";\n";
         fill << "}\n";
       }
-      // the stencil function applied to taps read from shared memory
+      // The stencil function over taps named ST_TAP(input, leaf, d0, d1, d2); the skeleton decides
+      // where taps live (a shared-memory tile, or per-thread register windows for rank 2).
       {
         Gen g(b.ps, b.tmp);
         for (size_t a = 0; a < nin; ++a) {
@@ -801,14 +807,13 @@ Glue build_glue(const Node& n, const std::map<std::string, ArrayInfo>& arrays) {
           size_t nl = n.d[a].elt.nleaves();
           const auto& ext = n.st_extent[a];
           // enumerate offsets in tuple order: outermost dimension outermost, -r..+r
-          std::vector<int> o(rank, 0);
           std::vector<int> idx(rank, 0);
           for (;;) {
             int off3[3] = {0, 0, 0};
             for (int d = 0; d < rank; ++d) off3[d + 3 - rank] = idx[d] - ext[d] / 2;
             for (size_t i = 0; i < nl; ++i) {
               std::ostringstream t;
-              t << "sm" << a << "_l" << i << "[ST_IDX" << a << "(l0 + (" << off3[0] << "), l1 + (" << off3[1] << "), l2 + (" << off3[2] << "))]";
+              t << "ST_TAP(" << a << ", " << i << ", " << off3[0] << ", " << off3[1] << ", " << off3[2] << ")";
               taps.leaf.push_back(t.str());
             }
             int d = rank - 1;
@@ -818,9 +823,75 @@ Glue build_glue(const Node& n, const std::map<std::string, ArrayInfo>& arrays) {
           g.env.emplace_back(n.f->params[a], taps);
         }
         CVal r = g.gen(*n.f->body);
-        b.fns << smem.str() << fill.str();
+        b.fns << "#if ST_REG\n";
+        if (rank == 2) {
+          // register-window variant: each thread owns four neighbouring columns and keeps ST_H rows
+          int rymax = 0;
+          for (size_t a = 0; a < nin; ++a) rymax = std::max(rymax, n.st_extent[a][0] / 2);
+          def["ST_RYMAX"] = std::to_string(rymax);
+          def["ST_H"] = std::to_string(2 * rymax + 1);
+          std::string win_decl, win_params, win_args, issue_all, commit_all, lane_fast;
+          for (size_t a = 0; a < nin; ++a) {
+            const std::string A = std::to_string(a);
+            const int rx = n.st_extent[a][1] / 2;
+            def["ST_W" + A] = std::to_string(4 + 2 * rx);
+            const std::string S = b.ps.need_struct(n.d[a].elt);
+            std::vector<Ty> l = n.d[a].elt.leaves();
+            std::string wp, wa;
+            for (size_t i = 0; i < l.size(); ++i) {
+              const std::string w = "w" + A + "_l" + std::to_string(i);
+              win_decl += cty(l[i]) + " " + w + "[ST_HW][ST_W" + A + "]; ";
+              win_params += std::string(win_params.empty() ? "" : ", ") + "const " + cty(l[i]) + " (&" + w + ")[ST_HW][ST_W" + A + "]";
+              win_args += std::string(win_args.empty() ? "" : ", ") + w;
+              wp += ", " + cty(l[i]) + " (&" + w + ")[ST_HW][ST_W" + A + "]";
+              wa += ", " + w;
+            }
+            issue_all += "ST2_issue" + A + "<SLOT>(p, GY, gx0, lf" + A + wa + "); ";
+            lane_fast += "const bool lf" + A + " = p.D" + A + "_fast != 0 && (p.D" + A + "_e1 & 3) == 0 && gx0 >= 0 && gx0 + 4 <= (int)p.D" + A + "_e1; ";
+            commit_all += "ST2_commit" + A + "<SLOT>(lane" + wa + "); ";
+            // which input row supplies global row gy (or -1: evaluate element by element)
+            const std::string e0 = "p.D" + A + "_e0", e1 = "p.D" + A + "_e1";
+            std::string rowmap;   // in terms of the 32-bit locals gy, e0
+            switch (n.bnd[a].kind) {
+              case BND_CLAMP: rowmap = "gy < 0 ? 0 : (gy >= e0 ? e0 - 1 : gy)"; break;
+              case BND_MIRROR: rowmap = "gy < 0 ? -gy : (gy >= e0 ? e0 - (gy - e0 + 2) : gy)"; break;
+              case BND_WRAP: rowmap = "gy < 0 ? e0 + gy : (gy >= e0 ? gy - e0 : gy)"; break;
+              default: rowmap = "(gy >= 0 && gy < e0) ? gy : -1"; break;
+            }
+            // Request a row straight into window slot SLOT (the thread's own four columns).  The
+            // commit step, run just before the row is first used, takes the rx columns to either
+            // side from the neighbouring lanes.
+            b.fns << "template <int SLOT> __device__ __forceinline__ void ST2_issue" << A << "(const Params& p, int gy, int gx0, bool lane_fast" << wp << ") {\n"
+                  << "  " << S << " own[4];\n"
+                  << "  const int e0 = (int)" << e0 << ", e1 = (int)" << e1 << ";\n"
+                  << "  int my = " << rowmap << ";\n  if (my >= e0) my = -1;\n"
+                  << "  if (lane_fast && my >= 0) D" << A << "_get4_lin(p, (i64)my * (i64)e1 + (i64)gx0, my, gx0, own);\n"
+                  << "  else { _Pragma(\"unroll\") for (int k = 0; k < 4; ++k) own[k] = ST_bounded" << A << "(p, 0, gy, gx0 + k); }\n";
+            for (size_t i = 0; i < l.size(); ++i)
+              b.fns << "  _Pragma(\"unroll\") for (int k = 0; k < 4; ++k) w" << A << "_l" << i << "[SLOT][" << rx << " + k] = own[k].l" << i << ";\n";
+            b.fns << "}\n";
+            b.fns << "template <int SLOT> __device__ __forceinline__ void ST2_commit" << A << "(int lane" << wp << ") {\n  (void)lane;\n";
+            for (int j = 1; j <= rx; ++j) {
+              for (size_t i = 0; i < l.size(); ++i) {
+                const std::string w = "w" + A + "_l" + std::to_string(i);
+                b.fns << "  " << w << "[SLOT][" << (rx - j) << "] = acc_shfl1_up(" << w << "[SLOT][" << (rx + 4 - j) << "], 1);\n"
+                      << "  " << w << "[SLOT][" << (rx + 3 + j) << "] = acc_shfl1_down(" << w << "[SLOT][" << (rx + j - 1) << "], 1);\n";
+              }
+            }
+            b.fns << "}\n";
+          }
+          def["ST2_WIN_DECL"] = win_decl;
+          def["ST2_WIN_PARAMS"] = win_params;
+          def["ST2_WIN_ARGS"] = win_args;
+          def["ST2_ISSUE_ALL(SLOT, GY)"] = issue_all;
+          def["ST2_COMMIT_ALL(SLOT)"] = commit_all;
+          def["ST2_LANE_FAST_DECL"] = lane_fast;
+          b.fns << "template <int K, int PH> __device__ __forceinline__ " << E << " ST2_apply(const Params& p, ST2_WIN_PARAMS) {\n" << g.out.str()
+                << b.ret_struct(E, r) << "}\n";
+        }
+        b.fns << "#else\n" << smem.str() << fill.str();
         b.fns << "__device__ __forceinline__ " << E << " ST_apply(const Params& p, int l0, int l1, int l2) {\n" << g.out.str()
-              << b.ret_struct(E, r) << "}\n";
+              << b.ret_struct(E, r) << "}\n#endif\n";
       }
       b.output(0, n.elt);
       break;

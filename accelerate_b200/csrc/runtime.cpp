@@ -123,6 +123,7 @@ std::string assemble_source(const Glue& g, const std::string& skeleton, const st
   for (auto& d : g.defines) o << "#define " << d.first << " " << d.second << "\n";
   for (auto& d : variant) o << "#define " << d.first << " " << d.second << "\n";
   if (skeleton == "stencil") o << skeleton_source("stencil_pre") << "\n";
+  if (skeleton == "stencil2d") o << skeleton_source("stencil2d_pre") << "\n";
   o << g.code << "\n" << skeleton_source(skeleton) << "\n";
   return o.str();
 }
@@ -139,7 +140,7 @@ StencilTile stencil_tile(int rank) {
 std::map<std::string, std::string> scan_variant(const Type& elt) {
   size_t bytes = 0;
   for (Ty t : elt.leaves()) bytes += ty_bytes[t];
-  return {{"SCAN_MIN_BLOCKS", bytes <= 4 ? "4" : (bytes <= 8 ? "3" : "1")}};
+  return {{"SCAN_MIN_BLOCKS", bytes <= 4 ? "4" : (bytes <= 8 ? "2" : "1")}};
 }
 std::map<std::string, std::string> stencil_variant(int rank) {
   StencilTile t = stencil_tile(rank);
@@ -165,7 +166,10 @@ std::vector<std::pair<std::string, std::map<std::string, std::string>>> default_
       if (m.find("ATOMIC") != std::string::npos) v.push_back({"permute", {{"PERMUTE_SMEM", "1"}, {"PERMUTE_THREADS", "1024"}}});
       break;
     }
-    case N_STENCIL: case N_STENCIL2: v.push_back({"stencil", stencil_variant(n.d[0].rank)}); break;
+    case N_STENCIL: case N_STENCIL2:
+      v.push_back({"stencil", stencil_variant(n.d[0].rank)});
+      if (n.d[0].rank == 2) v.push_back({"stencil2d", {}});
+      break;
     case N_RESHAPE: break;
   }
   return v;
@@ -735,6 +739,21 @@ void Program::run(const std::vector<DevArrayP>& inputs, std::vector<DevArrayP>& 
         L.named["tiles1"] = tiles1;
         L.named["tiles2"] = tiles2;
         L.named["vec"] = (o[2] % 4 == 0 && out->aligned16()) ? 1 : 0;
+        if (rank == 2 && o[1] < 2000000000 && o[2] < 2000000000 && !getenv("ACCELERATE_B200_STENCIL_SMEM")) {
+          // register-window kernel: warp tasks of 128 columns x 64 rows
+          auto tune = [](const char* name, int dflt) { const char* e = getenv(name); return e && *e ? atoi(e) : dflt; };
+          const int warps = tune("ACCELERATE_B200_ST2_WARPS", 4), rows = tune("ACCELERATE_B200_ST2_ROWS", 64);
+          const int minb = tune("ACCELERATE_B200_ST2_MIN_BLOCKS", 1), depth = tune("ACCELERATE_B200_ST2_DEPTH", 4);
+          const int64_t strips = (o[2] + 119) / 120, rowblocks = (o[1] + rows - 1) / rows;  // 120 output columns per warp
+          L.named["tiles1"] = rowblocks;
+          L.named["tiles2"] = strips;
+          std::map<std::string, std::string> var = {{"ST2_WARPS", std::to_string(warps)}, {"ST2_ROWS", std::to_string(rows)},
+                                                    {"ST2_MIN_BLOCKS", std::to_string(minb)}, {"ST2_DEPTH", std::to_string(depth)}};
+          CompiledKernel& k2 = c.kernel(assemble_source(st.glue, "stencil2d", var), "acc_stencil2d", warps * 32, 0);
+          const int64_t ctas = (strips * rowblocks + warps - 1) / warps;
+          L.launch(k2, ctas, warps * 32, 0);  // one warp per task; the hardware scheduler balances the tail
+          break;
+        }
         CompiledKernel& k = c.kernel(assemble_source(st.glue, "stencil", stencil_variant(rank)), "acc_stencil", t.threads, 0);
         L.launch(k, tiles0 * tiles1 * tiles2, t.threads, 0);
         break;

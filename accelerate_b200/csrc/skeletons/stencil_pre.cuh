@@ -2,6 +2,8 @@
 // which declares the shared-memory tiles and reads taps through ST_IDX<a>.
 // Arrays of rank < 3 are padded with leading dimensions of extent 1.
 // ST_T0..ST_T2: output tile extents (outermost first); ST_R<a>_<d>: halo radii.
+#define ST_REG 0
+#define ST_TAP(a, i, d0, d1, d2) sm##a##_l##i[ST_IDX##a(l0 + (d0), l1 + (d1), l2 + (d2))]
 #define ST_P0_0 (ST_T0 + 2 * ST_R0_0)
 #define ST_P0_1 (ST_T1 + 2 * ST_R0_1)
 #define ST_P0_2 (ST_T2 + 2 * ST_R0_2)
