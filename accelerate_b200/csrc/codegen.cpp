@@ -548,6 +548,30 @@ struct GlueBuilder {
     fns << "__device__ __forceinline__ void " << D << "_get4(const Params& p, i64 row, i64 j, " << S << " (&o)[4]) {\n" << decomp.str()
         << "  const i64 lin = row * " << inner << " + j; (void)lin;\n" << vec_loads.str()
         << "  _Pragma(\"unroll\") for (int k = 0; k < 4; ++k) o[k] = " << D << "_body(p" << ixa4 << sargs4 << ");\n}\n";
+    // the same from shared-memory copies of the streams' tiles (one pointer per stream leaf)
+    if (!streams.empty()) {
+      std::string sm_params, sm_loads, call_ptrs, bulk;
+      size_t off = 0;   // in units of tile elements times bytes: offsets are (off * SCAN_TILE)
+      for (size_t k = 0; k < streams.size(); ++k) {
+        const ArrayInfo& ai = ps.array(streams[k]);
+        std::vector<Ty> l = ai.elt.leaves();
+        for (size_t i = 0; i < l.size(); ++i) {
+          const std::string sv = "s" + std::to_string(k) + "_l" + std::to_string(i);
+          sm_params += ", const " + cty(l[i]) + "* sm_" + sv;
+          sm_loads += "  " + cty(l[i]) + " " + sv + "[4]; acc_lds4(sm_" + sv + ", " + sv + ");\n";
+          call_ptrs += ", reinterpret_cast<const " + cty(l[i]) + "*>((BASE) + " + std::to_string(off) + " * SCAN_TILE) + (E)";
+          bulk += "acc_bulk_g2s((BASE) + " + std::to_string(off) + " * SCAN_TILE, p." + streams[k] + "_l" + std::to_string(i) + " + (SRC), SCAN_TILE * " +
+                  std::to_string(ty_bytes[l[i]]) + ", BAR); ";
+          off += ty_bytes[l[i]];
+        }
+      }
+      fns << "__device__ __forceinline__ void " << D << "_get4_sm_impl(const Params& p, i64 row, i64 j" << sm_params << ", " << S << " (&o)[4]) {\n"
+          << decomp.str() << sm_loads << "  _Pragma(\"unroll\") for (int k = 0; k < 4; ++k) o[k] = " << D << "_body(p" << ixa4 << sargs4 << ");\n}\n";
+      glue.defines[D + "_get4_sm(P, ROW, J, BASE, E, O)"] = D + "_get4_sm_impl(P, ROW, J" + call_ptrs + ", O)";
+      glue.defines[D + "_BULK_ISSUE(BASE, BAR, SRC)"] = bulk;
+      glue.defines[D + "_STAGE_BYTES"] = "(" + std::to_string(off) + " * SCAN_TILE)";
+      glue.defines[D + "_STREAM_BYTES"] = std::to_string(off);
+    }
     // same with the linear address of the first element supplied by the caller
     fns << "__device__ __forceinline__ void " << D << "_get4_lin(const Params& p, i64 lin, i64 row, i64 j, " << S << " (&o)[4]) {\n" << decomp.str()
         << "  (void)lin;\n" << vec_loads.str()
@@ -905,7 +929,7 @@ Glue build_glue(const Node& n, const std::map<std::string, ArrayInfo>& arrays) {
     case N_FOLD: named = {"n", "rows", "row", "vec", "scratch", "flags", "counter"}; break;
     case N_FOLDSEG: named = {"segs", "rows", "vec", "err"}; break;
     case N_SCAN: case N_SCAN2:
-      named = {"n", "rows", "tiles_per_row", "in_vec", "out_vec", "status", "agg", "incl", "counter", "epoch", "err", "spin_limit"};
+      named = {"n", "rows", "tiles_per_row", "total_tiles", "in_vec", "out_vec", "status", "agg", "incl", "counter", "epoch", "err", "spin_limit", "trace"};
       break;
     case N_PERMUTE: named = {"n", "vec", "out_n", "priv", "locks", "err", "spin_limit"}; break;
     case N_STENCIL: case N_STENCIL2: named = {"o0", "o1", "o2", "tiles1", "tiles2", "vec"}; break;

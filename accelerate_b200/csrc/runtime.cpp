@@ -137,10 +137,23 @@ StencilTile stencil_tile(int rank) {
   return {4, 8, 64, 256};
 }
 // resident CTAs per SM the scan kernel is compiled for (register budget)
+// elements per thread (4 per round): large tiles keep the look-back chain off the critical path
+int scan_rounds(const Type& elt) {
+  size_t bytes = 0;
+  for (Ty t : elt.leaves()) bytes += ty_bytes[t];
+  int r = bytes <= 8 ? 8 : 4;
+  if (const char* e = getenv("ACCELERATE_B200_SCAN_ROUNDS")) r = std::max(1, atoi(e));
+  return r;
+}
 std::map<std::string, std::string> scan_variant(const Type& elt) {
   size_t bytes = 0;
   for (Ty t : elt.leaves()) bytes += ty_bytes[t];
-  return {{"SCAN_MIN_BLOCKS", bytes <= 4 ? "4" : (bytes <= 8 ? "2" : "1")}};
+  const int rounds = scan_rounds(elt);
+  std::string minb = bytes * rounds <= 16 ? "4" : (bytes * rounds <= 64 ? "2" : "1");
+  if (const char* e = getenv("ACCELERATE_B200_SCAN_MIN_BLOCKS")) minb = e;
+  std::map<std::string, std::string> v = {{"SCAN_MIN_BLOCKS", minb}, {"SCAN_ROUNDS", std::to_string(rounds)}};
+  if (const char* e = getenv("ACCELERATE_B200_SCAN_LOOK")) v["SCAN_LOOK"] = e;
+  return v;
 }
 std::map<std::string, std::string> stencil_variant(int rank) {
   StencilTile t = stencil_tile(rank);
@@ -159,7 +172,17 @@ std::vector<std::pair<std::string, std::map<std::string, std::string>>> default_
       v.push_back({"fold", {{"FOLD_G", "4"}}});
       break;
     case N_FOLDSEG: v.push_back({"foldseg", {{"FOLDSEG_G", "32"}}}); break;
-    case N_SCAN: case N_SCAN2: v.push_back({"scan", scan_variant(n.elt)}); break;
+    case N_SCAN: case N_SCAN2: {
+      v.push_back({"scan", scan_variant(n.elt)});
+      if (!g.streams.empty() && !g.streams[0].empty()) {
+        auto var = scan_variant(n.elt);
+        var["SCAN_PIPE"] = "1";
+        var["SCAN_STAGES"] = "4";
+        if (var["SCAN_MIN_BLOCKS"] == "4") var["SCAN_MIN_BLOCKS"] = "3";
+        v.push_back({"scan", var});
+      }
+      break;
+    }
     case N_PERMUTE: {
       v.push_back({"permute", {}});
       const std::string& m = g.defines.at("PERMUTE_MODE");
@@ -640,7 +663,7 @@ void Program::run(const std::vector<DevArrayP>& inputs, std::vector<DevArrayP>& 
         }
         if (rows == 0 || (mode == 0 && m == 0)) break;
         L.bind_delayed("D0", ext, 0);
-        const int64_t tile = 8 * 4 * 128;
+        const int64_t tile = 8 * (int64_t)scan_rounds(n.elt) * 128;
         const int64_t tiles_per_row = std::max<int64_t>(1, (m + tile - 1) / tile);
         const int64_t total_tiles = rows * tiles_per_row;
         const bool right = n.right;
@@ -662,6 +685,42 @@ void Program::run(const std::vector<DevArrayP>& inputs, std::vector<DevArrayP>& 
         L.named["incl"] = (int64_t)(uintptr_t)(base + status_bytes + val_bytes);
         L.named["counter"] = (int64_t)(uintptr_t)(c.d_words + 2);
         L.named["epoch"] = c.scan_epoch;
+        const bool pipe_ok = !st.glue.streams.at(0).empty() && L.fast("D0") && in_vec && getenv("ACCELERATE_B200_SCAN_PIPE");
+        if (pipe_ok) {
+          // persistent CTAs, input staged through shared memory by the bulk-copy engine
+          const size_t stream_bytes = (size_t)atoi(st.glue.defines.at("D0_STREAM_BYTES").c_str());
+          const size_t stage_bytes = stream_bytes * (size_t)tile;
+          int stages = (int)std::min<size_t>(4, std::max<size_t>(2, (72 * 1024) / stage_bytes));
+          if (const char* e = getenv("ACCELERATE_B200_SCAN_STAGES")) stages = std::max(2, atoi(e));
+          const size_t smem = stage_bytes * stages;
+          if (smem <= 200 * 1024) {
+            std::map<std::string, std::string> var = scan_variant(n.elt);
+            var["SCAN_PIPE"] = "1";
+            var["SCAN_STAGES"] = std::to_string(stages);
+            // shared memory, not registers, limits residency here: leave the compiler more registers
+            if (var["SCAN_MIN_BLOCKS"] == "4") var["SCAN_MIN_BLOCKS"] = "3";
+            CompiledKernel& k = c.kernel(assemble_source(st.glue, "scan", var), "acc_scan_pipe", 256, smem);
+            L.named["total_tiles"] = total_tiles;
+            const int64_t grid = std::min<int64_t>(total_tiles, (int64_t)c.sm_count * k.max_blocks_per_sm);
+            L.launch(k, grid, 256, smem);
+            break;
+          }
+        }
+        if (const char* tpath = getenv("ACCELERATE_B200_SCAN_TRACE")) {
+          // diagnostic: per-tile phase timestamps written to a file (8 x u64 per tile)
+          auto var = scan_variant(n.elt);
+          var["SCAN_TRACE"] = "1";
+          auto tbuf = c.alloc((size_t)total_tiles * 64);
+          c.check(cudaMemsetAsync(tbuf->ptr, 0, tbuf->bytes, c.stream), "cudaMemsetAsync");
+          L.named["trace"] = (int64_t)(uintptr_t)tbuf->ptr;
+          CompiledKernel& kt = c.kernel(assemble_source(st.glue, "scan", var), "acc_scan", 256, 0);
+          L.launch(kt, total_tiles, 256, 0);
+          std::vector<uint64_t> host((size_t)total_tiles * 8);
+          c.check(cudaMemcpyAsync(host.data(), tbuf->ptr, tbuf->bytes, cudaMemcpyDeviceToHost, c.stream), "cudaMemcpyAsync");
+          c.check(cudaStreamSynchronize(c.stream), "cudaStreamSynchronize");
+          if (FILE* f = fopen(tpath, "wb")) { fwrite(host.data(), 8, host.size(), f); fclose(f); }
+          break;
+        }
         CompiledKernel& k = c.kernel(assemble_source(st.glue, "scan", scan_variant(n.elt)), "acc_scan", 256, 0);
         L.launch(k, total_tiles, 256, 0);
         break;

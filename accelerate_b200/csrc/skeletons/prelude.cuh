@@ -168,6 +168,13 @@ template <class T> struct acc_vec4<T, 1> {
 template <class T> __device__ __forceinline__ void acc_ld4(const T* p, T (&o)[4]) { acc_vec4<T, (int)sizeof(T)>::ld(p, o); }
 template <class T> __device__ __forceinline__ void acc_st4(T* p, const T (&o)[4]) { acc_vec4<T, (int)sizeof(T)>::st(p, o); }
 
+// four consecutive elements from shared memory (address aligned to 4 * sizeof(T))
+template <class T> __device__ __forceinline__ void acc_lds4(const T* p, T (&o)[4]) {
+  struct __align__(sizeof(T) * 4) quad { T v[4]; };
+  const quad q = *reinterpret_cast<const quad*>(p);
+  _Pragma("unroll") for (int k = 0; k < 4; ++k) o[k] = q.v[k];
+}
+
 // Record the first device-side failure (a bounded wait that gave up, ...).
 __device__ __forceinline__ void acc_fail(i64 err_ptr, int code) {
   atomicCAS(reinterpret_cast<int*>(err_ptr), 0, code);

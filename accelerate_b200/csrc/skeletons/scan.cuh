@@ -33,6 +33,22 @@
 #endif
 #define SCAN_WARP_ELEMS (SCAN_ROUNDS * 128)
 #define SCAN_TILE (SCAN_WARPS * SCAN_WARP_ELEMS)
+#ifndef SCAN_LOOK
+#define SCAN_LOOK 2
+#endif
+// SCAN_TRACE: diagnostic build that records, per tile, nanosecond timestamps of its phases
+// (8 words per tile at the address in the named parameter `trace`).
+#ifndef SCAN_TRACE
+#define SCAN_TRACE 0
+#endif
+#if SCAN_TRACE
+__device__ __forceinline__ u64 scan_now() { u64 t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); return t; }
+#define SCAN_MARK(T, K) do { if (threadIdx.x == 0) reinterpret_cast<u64*>(p.trace)[(T) * 8 + (K)] = scan_now(); } while (0)
+#define SCAN_MARK_VAL(T, K, V) do { if (threadIdx.x == 0) reinterpret_cast<u64*>(p.trace)[(T) * 8 + (K)] = (u64)(V); } while (0)
+#else
+#define SCAN_MARK(T, K) do { } while (0)
+#define SCAN_MARK_VAL(T, K, V) do { } while (0)
+#endif
 #define SCAN_ST_AGG 1u
 #define SCAN_ST_PREFIX 2u
 
@@ -128,40 +144,17 @@ __device__ __forceinline__ i64 scan_phys(i64 n, i64 q) {
 #endif
 }
 
+// Everything after the tile's elements are in registers: local scans, aggregate,
+// look-back, per-thread prefixes, stores.
 template <bool FULL>
-__device__ __forceinline__ void scan_tile(const Params& p, const i64 T, const i64 row, const i64 tt, elt_t* sm_v, int* sm_h,
-                                          elt_t* sm_excl, int* sm_flag) {
+__device__ __forceinline__ void scan_tile_body(const Params& p, const i64 T, const i64 row, const i64 tt, elt_t (&item)[SCAN_ROUNDS][4],
+                                               bool (&valid)[SCAN_ROUNDS][4], elt_t* sm_v, int* sm_h, elt_t* sm_excl, int* sm_flag) {
   const i64 n = p.n;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const i64 tile_q0 = tt * SCAN_TILE;
   const i64 warp_q0 = tile_q0 + (i64)warp * SCAN_WARP_ELEMS;
-  const bool in_vec = p.in_vec != 0, out_vec = p.out_vec != 0;
-
-  // ---- load; thread-local inclusive scan of each group of four ----------------
-  elt_t item[SCAN_ROUNDS][4];
-  bool valid[SCAN_ROUNDS][4];
-#pragma unroll
-  for (int r = 0; r < SCAN_ROUNDS; ++r) {
-    const i64 q = warp_q0 + r * 128 + lane * 4;
-    if (FULL && in_vec) {
-#if ACC_RIGHT
-      elt_t t4[4];
-      D0_get4(p, row, n - 4 - q, t4);
-#pragma unroll
-      for (int k = 0; k < 4; ++k) item[r][k] = t4[3 - k];
-#else
-      D0_get4(p, row, q, item[r]);
-#endif
-#pragma unroll
-      for (int k = 0; k < 4; ++k) valid[r][k] = true;
-    } else {
-#pragma unroll
-      for (int k = 0; k < 4; ++k) {
-        valid[r][k] = FULL || (q + k < n);
-        if (valid[r][k]) item[r][k] = D0_get(p, row, scan_phys(n, q + k));
-      }
-    }
-  }
+  const bool out_vec = p.out_vec != 0;
+  SCAN_MARK(T, 1);   // the tile's elements have been requested
   elt_t tot[SCAN_ROUNDS];
   bool htot[SCAN_ROUNDS];
 #pragma unroll
@@ -206,6 +199,7 @@ __device__ __forceinline__ void scan_tile(const Params& p, const i64 T, const i6
   // carry now holds the warp's total
   if (lane == 0) { sm_v[warp] = carry; sm_h[warp] = hcarry; }
   __syncthreads();
+  SCAN_MARK(T, 2);   // local scans done
 
   // ---- tile aggregate, look-back (warp 0), tile exclusive prefix ---------------
   if (warp == 0) {
@@ -238,48 +232,75 @@ __device__ __forceinline__ void scan_tile(const Params& p, const i64 T, const i6
       }
       const i64 row_first = T - tt;
       i64 look = T - 1;
+      int windows = 0;
+      // Each lane inspects SCAN_LOOK consecutive predecessors per step (distance
+      // SCAN_LOOK*lane + j from `look`), so one L2 round trip covers 32*SCAN_LOOK tiles: the
+      // rate at which prefixes propagate, not bandwidth, is what limits a single-pass scan.
       for (;;) {
-        const i64 idx = look - lane;
-        const bool inrow = idx >= row_first;
-        u32 st = 0;
-        elt_t v;
-        if (inrow) {
-          i64 spins = 0;
-          for (;;) {
+        u32 st[SCAN_LOOK];
+        elt_t v[SCAN_LOOK];
+        bool in[SCAN_LOOK], ready[SCAN_LOOK];
+#pragma unroll
+        for (int j = 0; j < SCAN_LOOK; ++j) {
+          in[j] = look - (i64)(SCAN_LOOK * lane + j) >= row_first;
+          ready[j] = !in[j];
+          st[j] = 0;
+        }
+        for (i64 spins = 0;; ++spins) {
+          bool all = true;
+#pragma unroll
+          for (int j = 0; j < SCAN_LOOK; ++j) {
+            if (!ready[j]) {
+              const i64 idx = look - (i64)(SCAN_LOOK * lane + j);
 #if SCAN_PACKED
-            st = scan_desc_load(p.status, idx, v.l0);
+              st[j] = scan_desc_load(p.status, idx, v[j].l0);
 #else
-            st = status[idx];
+              st[j] = status[idx];
 #endif
-            if ((st >> 2) == epoch) break;
-            if (++spins > p.spin_limit) { failed = 1; break; }
-#if !SCAN_PACKED
-            __nanosleep(20);
-#endif
+              ready[j] = (st[j] >> 2) == epoch;
+              all = all && ready[j];
+            }
           }
+          if (all) break;
+          if (spins > p.spin_limit) { failed = 1; break; }
         }
         failed = __any_sync(ACC_FULL_MASK, failed);
         if (failed) break;
-        const bool is_prefix = inrow && (st & 3u) == SCAN_ST_PREFIX;
-        const unsigned pm = __ballot_sync(ACC_FULL_MASK, is_prefix);
-        const int nearest = pm ? (__ffs((int)pm) - 1) : 31;
-        bool hv = inrow && lane <= nearest;
+        // nearest inclusive prefix held by this lane (smallest j), if any
+        int jp = SCAN_LOOK;
+#pragma unroll
+        for (int j = SCAN_LOOK - 1; j >= 0; --j)
+          if (in[j] && (st[j] & 3u) == SCAN_ST_PREFIX) jp = j;
+        const unsigned pm = __ballot_sync(ACC_FULL_MASK, jp < SCAN_LOOK);
+        const int lstar = pm ? (__ffs((int)pm) - 1) : 32;
+        // this lane's contribution: entries up to (and including) the nearest prefix, oldest first
+        const int last = lane < lstar ? SCAN_LOOK - 1 : (lane == lstar ? jp : -1);
 #if !SCAN_PACKED
-        if (hv) {
-          __threadfence();
-          v = scan_ld_volatile(is_prefix ? d_incl + idx : d_agg + idx);
-        }
+        __threadfence();
+#pragma unroll
+        for (int j = 0; j < SCAN_LOOK; ++j)
+          if (in[j] && j <= last) {
+            const i64 idx = look - (i64)(SCAN_LOOK * lane + j);
+            v[j] = scan_ld_volatile((st[j] & 3u) == SCAN_ST_PREFIX ? d_incl + idx : d_agg + idx);
+          }
 #endif
-        // lane l holds tile look-l: higher lanes are earlier
+        elt_t c;
+        bool hc = false;
+#pragma unroll
+        for (int j = SCAN_LOOK - 1; j >= 0; --j)
+          if (in[j] && j <= last) scan_join(p, c, hc, v[j], true);
+        // lane l holds older tiles than lane l-1
 #pragma unroll
         for (int d = 1; d < 32; d <<= 1) {
-          const elt_t o = acc_shfl_down(v, d);
-          const int oh = __shfl_down_sync(ACC_FULL_MASK, (int)hv, d);
-          if (lane + d < 32) scan_join_front(p, o, oh != 0, v, hv);
+          const elt_t o = acc_shfl_down(c, d);
+          const int oh = __shfl_down_sync(ACC_FULL_MASK, (int)hc, d);
+          if (lane + d < 32) scan_join_front(p, o, oh != 0, c, hc);
         }
-        scan_join_front(p, v, hv, excl, hexcl);  // meaningful in lane 0
-        if (pm != 0 || look - 32 < row_first) break;
-        look -= 32;
+        scan_join_front(p, c, hc, excl, hexcl);  // meaningful in lane 0
+        ++windows;
+        SCAN_MARK_VAL(T, 6, windows);
+        if (pm != 0 || look - 32 * SCAN_LOOK < row_first) break;
+        look -= 32 * SCAN_LOOK;
       }
     }
     if (lane == 0) {
@@ -317,6 +338,7 @@ __device__ __forceinline__ void scan_tile(const Params& p, const i64 T, const i6
     }
   }
   __syncthreads();
+  SCAN_MARK(T, 3);   // exclusive prefix known
   if (sm_flag[1]) return;
 
   // ---- per-thread prefixes and stores ----------------------------------------------
@@ -375,6 +397,45 @@ __device__ __forceinline__ void scan_tile(const Params& p, const i64 T, const i6
       }
     }
   }
+  SCAN_MARK(T, 4);   // stores issued
+}
+
+template <bool FULL>
+__device__ __forceinline__ void scan_tile(const Params& p, const i64 T, const i64 row, const i64 tt, elt_t* sm_v, int* sm_h,
+                                          elt_t* sm_excl, int* sm_flag) {
+  const i64 n = p.n;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const i64 tile_q0 = tt * SCAN_TILE;
+  const i64 warp_q0 = tile_q0 + (i64)warp * SCAN_WARP_ELEMS;
+  const bool in_vec = p.in_vec != 0;
+  SCAN_MARK(T, 0);   // tile started
+
+  // ---- load; thread-local inclusive scan of each group of four ----------------
+  elt_t item[SCAN_ROUNDS][4];
+  bool valid[SCAN_ROUNDS][4];
+#pragma unroll
+  for (int r = 0; r < SCAN_ROUNDS; ++r) {
+    const i64 q = warp_q0 + r * 128 + lane * 4;
+    if (FULL && in_vec) {
+#if ACC_RIGHT
+      elt_t t4[4];
+      D0_get4(p, row, n - 4 - q, t4);
+#pragma unroll
+      for (int k = 0; k < 4; ++k) item[r][k] = t4[3 - k];
+#else
+      D0_get4(p, row, q, item[r]);
+#endif
+#pragma unroll
+      for (int k = 0; k < 4; ++k) valid[r][k] = true;
+    } else {
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        valid[r][k] = FULL || (q + k < n);
+        if (valid[r][k]) item[r][k] = D0_get(p, row, scan_phys(n, q + k));
+      }
+    }
+  }
+  scan_tile_body<FULL>(p, T, row, tt, item, valid, sm_v, sm_h, sm_excl, sm_flag);
 }
 
 extern "C" __global__ void __launch_bounds__(SCAN_THREADS, SCAN_MIN_BLOCKS) acc_scan(const Params p) {
@@ -397,3 +458,164 @@ extern "C" __global__ void __launch_bounds__(SCAN_THREADS, SCAN_MIN_BLOCKS) acc_
   if (full) scan_tile<true>(p, T, row, tt, sm_v, sm_h, &sm_excl, sm_flag);
   else scan_tile<false>(p, T, row, tt, sm_v, sm_h, &sm_excl, sm_flag);
 }
+
+// ---------------------------------------------------------------------------------
+// acc_scan_pipe: the same scan with the input staged through shared memory by the
+// bulk-copy engine.  Persistent CTAs keep SCAN_STAGES tiles in flight each
+// (cp.async.bulk global -> shared, completion on an mbarrier), so HBM stays busy
+// while a CTA waits in the look-back; tickets are taken one stage ahead.  Used when
+// every array the scanned expression reads at the loop index has the fast layout
+// and rows are 16-byte aligned (in_vec); a partial last tile of a row is loaded
+// with ordinary loads instead.
+// Extra named parameter: total_tiles.
+// ---------------------------------------------------------------------------------
+#if defined(SCAN_PIPE) && SCAN_PIPE
+#ifndef SCAN_STAGES
+#define SCAN_STAGES 4
+#endif
+
+__device__ __forceinline__ u32 scan_smem_addr(const void* ptr) { return (u32)__cvta_generic_to_shared(ptr); }
+__device__ __forceinline__ void scan_mbar_init(u64* bar, int count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(scan_smem_addr(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void scan_mbar_expect(u64* bar, u32 bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(scan_smem_addr(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool scan_mbar_try_wait(u64* bar, u32 parity) {
+  u32 ok;
+  asm volatile(
+      "{\n\t.reg .pred q;\n\tmbarrier.try_wait.parity.shared::cta.b64 q, [%1], %2;\n\tselp.u32 %0, 1, 0, q;\n\t}"
+      : "=r"(ok)
+      : "r"(scan_smem_addr(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// global -> shared bulk copy; src and dst 16-byte aligned, bytes a multiple of 16
+__device__ __forceinline__ void acc_bulk_g2s(void* dst, const void* src, u32 bytes, u64* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(scan_smem_addr(dst)), "l"(src),
+               "r"(bytes), "r"(scan_smem_addr(bar))
+               : "memory");
+}
+
+extern __shared__ __align__(128) unsigned char scan_pipe_smem[];
+
+extern "C" __global__ void __launch_bounds__(SCAN_THREADS, SCAN_MIN_BLOCKS) acc_scan_pipe(const Params p) {
+  __shared__ elt_t sm_v[SCAN_WARPS];
+  __shared__ int sm_h[SCAN_WARPS];
+  __shared__ elt_t sm_excl;
+  __shared__ int sm_flag[2];
+  __shared__ __align__(8) u64 full_bar[SCAN_STAGES];
+  __shared__ i64 stage_tile[SCAN_STAGES];
+  __shared__ int stage_direct[SCAN_STAGES];
+  __shared__ u32 stage_parity[SCAN_STAGES];
+  u32 uses[SCAN_STAGES];                 // thread 0: completed copy phases per stage barrier
+#pragma unroll
+  for (int s = 0; s < SCAN_STAGES; ++s) uses[s] = 0;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const i64 n = p.n;
+  const i64 total_tiles = p.total_tiles;
+  unsigned* counter = reinterpret_cast<unsigned*>(p.counter);
+  unsigned* exits = counter + 1;
+
+  // thread 0: take the next ticket for stage s and request its data
+  auto fetch = [&](int s) {
+    const i64 T = (i64)atomicAdd(counter, 1u);
+    stage_tile[s] = T;
+    stage_direct[s] = 1;
+    if (T >= total_tiles) return;
+    const i64 row = T / p.tiles_per_row;
+    const i64 tt = T - row * p.tiles_per_row;
+    const i64 q0 = tt * SCAN_TILE;
+    if (q0 + SCAN_TILE > n) return;        // partial tile: ordinary loads
+    stage_direct[s] = 0;
+    stage_parity[s] = uses[s] & 1u;       // the barrier phase this request completes
+    uses[s] += 1;
+#if ACC_RIGHT
+    const i64 src = row * n + (n - q0 - SCAN_TILE);
+#else
+    const i64 src = row * n + q0;
+#endif
+    unsigned char* base = scan_pipe_smem + (size_t)s * D0_STAGE_BYTES;
+    scan_mbar_expect(&full_bar[s], (u32)D0_STAGE_BYTES);
+    D0_BULK_ISSUE(base, &full_bar[s], src)
+  };
+
+  if (tid == 0) {
+    for (int s = 0; s < SCAN_STAGES; ++s) scan_mbar_init(&full_bar[s], 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+  if (tid == 0)
+    for (int s = 0; s < SCAN_STAGES; ++s) fetch(s);
+  __syncthreads();
+
+  for (i64 it = 0;; ++it) {
+    const int s = (int)(it % SCAN_STAGES);
+    const u32 parity = stage_parity[s];
+    const i64 T = stage_tile[s];
+    if (T >= total_tiles) break;
+    const int direct = stage_direct[s];
+    const i64 row = T / p.tiles_per_row;
+    const i64 tt = T - row * p.tiles_per_row;
+    const i64 warp_q0 = tt * SCAN_TILE + (i64)warp * SCAN_WARP_ELEMS;
+    elt_t item[SCAN_ROUNDS][4];
+    bool valid[SCAN_ROUNDS][4];
+    int failed = 0;
+    if (!direct) {
+      i64 spins = 0;
+      while (!scan_mbar_try_wait(&full_bar[s], parity)) {
+        if (++spins > p.spin_limit) { failed = 1; break; }
+      }
+      if (!failed) {
+        const unsigned char* base = scan_pipe_smem + (size_t)s * D0_STAGE_BYTES;
+#pragma unroll
+        for (int r = 0; r < SCAN_ROUNDS; ++r) {
+          const int e = warp * SCAN_WARP_ELEMS + r * 128 + lane * 4;   // logical offset within the tile
+          const i64 q = warp_q0 + r * 128 + lane * 4;
+#if ACC_RIGHT
+          elt_t t4[4];
+          D0_get4_sm(p, row, n - 4 - q, base, SCAN_TILE - 4 - e, t4);
+#pragma unroll
+          for (int k = 0; k < 4; ++k) item[r][k] = t4[3 - k];
+#else
+          D0_get4_sm(p, row, q, base, e, item[r]);
+#endif
+#pragma unroll
+          for (int k = 0; k < 4; ++k) valid[r][k] = true;
+        }
+      }
+    }
+    if (__syncthreads_or(failed)) {     // also: every thread is done reading stage s
+      if (tid == 0) acc_fail(p.err, 110 /* ETIMEDOUT */);
+      break;
+    }
+    if (tid == 0) fetch(s);            // refill the stage while this tile is processed
+    if (!direct) {
+      scan_tile_body<true>(p, T, row, tt, item, valid, sm_v, sm_h, &sm_excl, sm_flag);
+    } else {
+      scan_tile<false>(p, T, row, tt, sm_v, sm_h, &sm_excl, sm_flag);   // only partial tiles come this way
+    }
+    __syncthreads();                   // shared scratch of the tile body is reused by the next tile
+    if (sm_flag[1]) break;
+  }
+  // Leaving early (a wait gave up) must not abandon bulk copies that are still in flight into
+  // this CTA's shared memory: wait for every requested stage, again with a limit.  After a
+  // normal end nothing is pending (the remaining tickets were past the last tile).
+  __syncthreads();
+  if (tid == 0) {
+    for (int s = 0; s < SCAN_STAGES; ++s) {
+      if (stage_tile[s] < total_tiles && !stage_direct[s]) {
+        i64 spins = 0;
+        while (!scan_mbar_try_wait(&full_bar[s], stage_parity[s]))
+          if (++spins > p.spin_limit) break;
+      }
+    }
+  }
+  // the last CTA to leave re-arms the ticket counter for the next launch
+  __syncthreads();
+  if (tid == 0) {
+    __threadfence();
+    if (atomicAdd(exits, 1u) == gridDim.x - 1) { *counter = 0u; *exits = 0u; }
+  }
+}
+#endif
