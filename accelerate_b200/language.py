@@ -601,9 +601,25 @@ def permute(f, defaults, p, a):
 
 
 def scatter(to, defaults, xs):
-    """``scatter`` (Prelude.hs): ``permute const``, unique targets assumed."""
+    """``scatter`` (Prelude.hs:1755-1766): ``permute const``; the source is cut to
+    ``shape to `intersect` shape xs``; targets are assumed unique."""
     to, xs = use(to), use(xs)
-    return permute(lambda new, old: new, defaults, lambda ix: Just_(index(to[ix])), xs)
+    src = backpermute(intersect(to.shape, xs.shape), lambda ix: ix, xs)
+    return permute(lambda new, old: new, defaults, lambda ix: Just_(index(to[ix])), src)
+
+
+def scatterIf(to, mask, pred, defaults, xs):
+    """``scatterIf`` (Prelude.hs:1780-1793)."""
+    to, mask, xs = use(to), use(mask), use(xs)
+    src = backpermute(intersect(to.shape, xs.shape), lambda ix: ix, xs)
+    return permute(lambda new, old: new, defaults,
+                   lambda ix: cond(pred(mask[ix]), Just_(index(to[ix])), Nothing_(1)), src)
+
+
+def gather(frm, xs):
+    """``gather`` (Prelude.hs:1701-1706): ``backpermute (shape from) (\\ix -> I1 (from ! ix))``."""
+    frm, xs = use(frm), use(xs)
+    return backpermute(frm.shape, lambda ix: index(frm[ix]), xs)
 
 
 class Boundary:

@@ -1,0 +1,128 @@
+"""Extract known-answer vectors for the hot path from the reference's own files.
+
+Run once in a checkout where the reference tree is available:
+
+    python tests/golden/make_golden.py /path/to/reference
+
+It reads (never executes) the haddock examples in
+``src/Data/Array/Accelerate/{Language,Prelude}.hs`` and the regression tests
+under ``src/Data/Array/Accelerate/Test/NoFib/{Issues,Misc}`` and writes
+``tests/golden/reference_vectors.json``: for each case the expected result
+(shape + flat values, or a list of tuples) together with the file and line it
+was taken from.  The inputs and programs of the cases are restated in
+``tests/test_oracle_golden.py`` next to the citation.
+"""
+import json
+import os
+import re
+import sys
+
+NUM = re.compile(r"-?\d+(?:\.\d+)?")
+
+
+def parse_shape(text):
+    m = re.search(r"\(Z((?:\s*:\.\s*\d+)+)\)", text)
+    if m:
+        return [int(x) for x in re.findall(r"\d+", m.group(1))]
+    if re.search(r"Scalar Z", text) or re.search(r"fromList Z ", text):
+        return []
+    raise ValueError("no shape in: " + text[:80])
+
+
+def doctest_output(lines, command, occurrence=1):
+    """Output block that follows the `occurrence`-th haddock line `-- >>> command`."""
+    seen = 0
+    for i, l in enumerate(lines):
+        if l.strip().startswith("-- >>>") and l.strip()[6:].strip() == command:
+            seen += 1
+            if seen == occurrence:
+                out = []
+                for m in lines[i + 1:]:
+                    s = m.strip()
+                    if s == "--" or s.startswith("-- >>>") or not s.startswith("--"):
+                        break
+                    out.append(s[2:])
+                text = " ".join(out)
+                shape = parse_shape(text)
+                body = text[text.index("["):]
+                return i + 1, shape, [float(v) if "." in v else int(v) for v in NUM.findall(body)]
+    raise KeyError(command)
+
+
+def issue_list(lines, name):
+    """Values of `name = fromList (...) [ ... ]` in a regression test."""
+    for i, l in enumerate(lines):
+        if re.match(rf"{name}\s*=\s*fromList", l):
+            text = l
+            j = i
+            while text.count("[") > text.count("]"):
+                j += 1
+                text += lines[j]
+            shape = parse_shape(text)
+            body = text[text.index("["):]
+            tuples = re.findall(r"\(([^()]*)\)", body)
+            if tuples:
+                vals = [[float(v) if "." in v else int(v) for v in NUM.findall(t)] for t in tuples]
+            else:
+                vals = [float(v) if "." in v else int(v) for v in NUM.findall(body)]
+            return i + 1, shape, vals
+    raise KeyError(name)
+
+
+def main(ref):
+    base = os.path.join(ref, "src", "Data", "Array", "Accelerate")
+    out = {}
+
+    def add(key, path, line, shape, values):
+        out[key] = {"source": f"{os.path.relpath(path, ref)}:{line}", "shape": shape, "values": values}
+
+    doc_cases = {
+        "Language.hs": [
+            ("generate_plus1", "run $ generate (I1 10) (\\(I1 i) -> i + 1) :: Vector Int", 1),
+            ("map_plus1", "run $ map (+1) (use xs)", 1),
+            ("zipWith_plus", "run $ zipWith (+) (use xs) (use ys)", 1),
+            ("fold_plus_42", "run $ fold (+) 42 (use mat)", 1),
+            ("maximum_segment_sum", "run $ maximumSegmentSum (use vec)", 1),
+            ("scanl_vec", "run $ scanl (+) 10 (use vec)", 1),
+            ("scanl_mat", "run $ scanl (+) 0 (use mat)", 1),
+            ("scanl_prime_vec_res", "res", 1),
+            ("scanl_prime_vec_sum", "sum", 1),
+            ("scanl_prime_mat_res", "res", 2),
+            ("scanl_prime_mat_sums", "sums", 1),
+            ("scanl1_mat", "run $ scanl1 (+) (use mat)", 1),
+            ("permute_histogram", "run $ histogram (use xs)", 1),
+            ("permute_identity", "run $ identity 5 :: Matrix Int", 1),
+            ("backpermute_transpose", "run $ backpermute (swap (shape mat')) swap mat'", 1),
+        ],
+        "Prelude.hs": [
+            ("foldSeg_mat", "run $ foldSeg (+) 0 (use mat) (use seg)", 1),
+            ("sum_mat", "run $ sum (use mat)", 1),
+            ("minimum_mat", "run $ minimum (use mat)", 1),
+            ("maximum_mat", "run $ maximum (use mat)", 1),
+            ("gather", "run $ gather (use from) (use input)", 1),
+            ("scatter", "run $ scatter (use to) (fill (constant (Z:.10)) 0) (use input)", 1),
+        ],
+    }
+    for fname, cases in doc_cases.items():
+        path = os.path.join(base, fname)
+        lines = open(path, encoding="utf-8").read().splitlines()
+        for key, cmd, occ in cases:
+            line, shape, vals = doctest_output(lines, cmd, occ)
+            add(key, path, line, shape, vals)
+
+    issues = os.path.join(base, "Test", "NoFib", "Issues")
+    for fname, names in [("Issue137.hs", ["ref1"]), ("Issue185.hs", ["ref1", "ref2", "ref3", "ref4", "ref5", "ref6"]),
+                         ("Issue228.hs", ["ref1"]), ("Issue362.hs", ["e1", "e2"]), ("Issue114.hs", ["ref1"])]:
+        path = os.path.join(issues, fname)
+        lines = open(path, encoding="utf-8").read().splitlines()
+        for nm in names:
+            line, shape, vals = issue_list(lines, nm)
+            add(f"{fname[:-3].lower()}_{nm}", path, line, shape, vals)
+
+    dst = os.path.join(os.path.dirname(os.path.abspath(__file__)), "reference_vectors.json")
+    json.dump(out, open(dst, "w"), indent=1, sort_keys=True)
+    print(f"wrote {len(out)} cases to {dst}")
+
+
+if __name__ == "__main__":
+    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")

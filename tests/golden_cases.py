@@ -1,0 +1,160 @@
+"""The reference's own known-answer cases for the hot path, restated with the
+Python front end.  Expected values live in tests/golden/reference_vectors.json
+(extracted from the reference's files by tests/golden/make_golden.py); each
+case cites where its program and inputs are written in the reference
+(paths relative to src/Data/Array/Accelerate/)."""
+import json
+import os
+
+import numpy as np
+
+import accelerate_b200 as A
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+VECTORS = json.load(open(os.path.join(HERE, "golden", "reference_vectors.json")))
+add = lambda a, b: a + b  # noqa: E731
+I = np.int64  # Haskell Int
+
+
+def _mss(x, y):
+    # Language.hs:501-508
+    return A.tup(A.max_(x[0], A.max_(y[0], x[2] + y[1])), A.max_(x[1], x[3] + y[1]), A.max_(y[2], x[2] + y[3]), x[3] + y[3])
+
+
+def _issue137():
+    # Test/NoFib/Issues/Issue137.hs:37-56
+    sz = 3000
+    interm = np.array([8 - (a % 17) for a in range(1, sz + 1)], I)
+    ms = np.array([a // 8 for a in range(1, sz + 1)], I)
+    inf = 10000
+    infs = A.generate(A.index(384), lambda ix: A.tup(A.constant(inf), A.constant(inf)))
+    inp = A.map(lambda v: A.tup(abs(v), A.constant(inf)), interm)
+    msa = A.use(ms)
+
+    def f(a, b):
+        return A.cond(a[0] <= b[0], A.tup(a[0], A.min_(a[1], b[0])), A.tup(b[0], A.min_(b[1], a[0])))
+    return A.permute(f, infs, lambda ix: A.Just_(A.index(msa[ix])), inp)
+
+
+def _gather_if(frm, mask, pred, over, xs):
+    # Test/NoFib/Issues/Issue185.hs:112-124
+    g = A.zip(A.gather(frm, xs), over)
+    pf = A.map(pred, mask)
+    return A.zipWith(lambda ok, gv: A.cond(ok, gv[0], gv[1]), pf, g)
+
+
+def _merge(e1, e2):
+    # Test/NoFib/Issues/Issue228.hs:58-68
+    return A.tup(e1[0] * e2[0], e1[0] * e2[1] + e1[1])
+
+
+def _efloat_add(a, b):
+    # Test/NoFib/Issues/Issue114.hs:52-59
+    val = a[0] + b[0]
+    det = val - a[0]
+    err = a[0] - (val - det) + (b[0] - det) + a[1] + b[1]
+    return A.tup(val, err)
+
+
+def cases():
+    vec10 = np.arange(10, dtype=I)
+    mat5x10 = np.arange(50, dtype=I).reshape(5, 10)
+    mat4x10 = np.arange(40, dtype=I).reshape(4, 10)
+    xs3x5 = np.arange(15, dtype=I).reshape(3, 5)
+    ys5x10 = np.arange(1, 51, dtype=I).reshape(5, 10)
+    hist = np.array([0, 0, 1, 2, 1, 1, 2, 4, 8, 3, 4, 9, 8, 3, 2, 5, 5, 3, 1, 2], I)
+    hu = A.use(hist)
+    mss_in = np.array([-2, 1, -3, 4, -1, 2, 1, -5, 4, 0], I)
+    m34 = np.array([1, 4, 3, 8, 0, 2, 8, 4, 7, 9, 8, 8], I).reshape(3, 4)
+    to = np.array([1, 3, 7, 2, 5, 8], I)
+    frm = np.array([1, 3, 7, 2, 5, 3], I)
+    mask = np.array([3, 4, 9, 2, 7, 5], np.int32)
+    zeros9 = np.zeros(9, I)
+    in7 = np.array([1, 9, 6, 4, 4, 2, 5], I)
+    in3 = np.array([1, 9, 6], I)
+    in9 = np.array([1, 9, 6, 4, 4, 2, 0, 1, 2], I)
+    gt4 = lambda v: v > 4  # noqa: E731
+    matu = A.use(mat5x10)
+    sp, ss = A.scanl_prime(add, 0, vec10)
+    mp, ms = A.scanl_prime(add, 0, mat4x10)
+    t4 = np.arange(10, dtype=I)
+    efl = (np.full(100, 1.01, np.float32), np.zeros(100, np.float32))
+    c = {
+        "generate_plus1": A.generate(A.index(10), lambda ix: ix[0] + 1),                              # Language.hs:288
+        "map_plus1": A.map(lambda x: x + 1, vec10),                                                   # Language.hs:412-416
+        "zipWith_plus": A.zipWith(add, xs3x5, ys5x10),                                                # Language.hs:430-446
+        "fold_plus_42": A.fold(add, 42, mat5x10),                                                     # Language.hs:473-482
+        "maximum_segment_sum": A.map(lambda t: t[0], A.fold1(_mss, A.map(lambda x: A.let_(A.max_(x, 0), lambda y: A.tup(y, y, y, x)), mss_in))),
+        "scanl_vec": A.scanl(add, 10, vec10),                                                         # Language.hs:595-596
+        "scanl_mat": A.scanl(add, 0, mat4x10),                                                        # Language.hs:599-600
+        "scanl_prime_vec_res": sp, "scanl_prime_vec_sum": ss,                                         # Language.hs:623-627
+        "scanl_prime_mat_res": mp, "scanl_prime_mat_sums": ms,                                        # Language.hs:630-638
+        "scanl1_mat": A.scanl1(add, mat4x10),                                                         # Language.hs:653-654
+        "permute_histogram": A.permute(add, A.fill(10, A.constant(0)), lambda ix: A.Just_(A.index(hu[ix])), A.fill(hu.shape, A.constant(1))),
+        "permute_identity": A.permute(lambda a, b: a, A.fill(A.index(5, 5), A.constant(0)), lambda ix: A.Just_(A.index(ix[0], ix[0])),
+                                      A.fill(A.index(5), A.constant(1))),                             # Language.hs:734-743
+        "backpermute_transpose": A.backpermute(A.index(matu.shape[1], matu.shape[0]), lambda ix: A.index(ix[1], ix[0]), matu),
+        "foldSeg_mat": A.foldSeg(add, 0, mat5x10, np.array([1, 4, 0, 3], I)),                         # Prelude.hs:689-702
+        "sum_mat": A.sum(np.arange(10, dtype=I).reshape(2, 5)),                                       # Prelude.hs:822-823
+        "minimum_mat": A.minimum(m34), "maximum_mat": A.maximum(m34),                                 # Prelude.hs:849-877
+        "gather": A.gather(frm, in9),                                                                 # Prelude.hs:1696-1698
+        "scatter": A.scatter(to, A.fill(10, A.constant(0)), in7),                                     # Prelude.hs:1750-1752
+        "issue137_ref1": _issue137(),
+        "issue185_ref1": A.scatter(to, zeros9, in7),                                                  # Issue185.hs:49-54
+        "issue185_ref2": A.scatter(to, zeros9, in3),                                                  # Issue185.hs:60-65
+        "issue185_ref3": A.scatterIf(to, mask, gt4, zeros9, in7),                                     # Issue185.hs:71-80
+        "issue185_ref4": A.scatterIf(to, mask, gt4, zeros9, in3),                                     # Issue185.hs:86-95
+        "issue185_ref5": A.gather(frm, in9),                                                          # Issue185.hs:101-105
+        "issue185_ref6": _gather_if(frm, mask, gt4, np.full(6, 6, I), in9),                           # Issue185.hs:111-124
+        "issue228_ref1": A.fold(_merge, A.tup(1, 0), (np.array([1, 0, 1], I), np.array([1, 0, 1], I))),   # Issue228.hs:36-50
+        "issue362_e1": A.scanl1(lambda x, y: A.tup(*[x[i] + y[i] for i in range(4)]), tuple([t4] * 4)),   # Issue362.hs:39-47
+        "issue362_e2": A.scanl1(lambda x, y: A.tup(*[x[i] + y[i] for i in range(5)]), tuple([t4] * 5)),   # Issue362.hs:54-62
+        "issue114_ref1": A.fold1(_efloat_add, efl),                                                    # Issue114.hs:61-77
+    }
+    return c
+
+
+def expected(key, got):
+    """The reference's expected value in the layout `got` has (ndarray or tuple of leaves)."""
+    v = VECTORS[key]
+    shape = tuple(v["shape"])
+    if isinstance(got, tuple):
+        cols = list(zip(*v["values"]))
+        return tuple(np.array(c, dtype=g.dtype).reshape(shape) for c, g in zip(cols, got))
+    return np.array(v["values"], dtype=got.dtype).reshape(shape)
+
+
+def extra_cases():
+    """Known answers given in closed form by the reference's tests."""
+    out = {}
+    # Test/NoFib/Misc/Scanl1.hs:32-39: scanl1 (+) over [1..] of shape 257 x 31
+    sh = (257, 31)
+    arr = np.arange(1, sh[0] * sh[1] + 1, dtype=I).reshape(sh)
+    i, j = np.indices(sh)
+    intsum = lambda n, m: m * (m + 1) // 2 - (n - 1) * n // 2  # noqa: E731
+    out["misc_scanl1"] = (A.scanl1(add, arr), intsum(1 + i * 31, 1 + i * 31 + j).astype(I))
+    # Test/NoFib/Issues/Issue364.hs:52-54, 66-99: scanl of the interval monoid at sizes 64 and 65
+    for n in (64, 65):
+        for dt in (np.int8, np.int16, np.int32, np.int64, np.float32, np.float64):
+            t = A.TY_OF_NP[np.dtype(dt)]
+            one = A.tup(A.constant(dt(-1), t), A.constant(dt(-1), t))
+            top = A.tup(A.constant(dt(-2), t), A.constant(dt(-2), t))
+
+            def teq(x, y):
+                return A.land(x[0].eq(y[0]), x[1].eq(y[1]))
+
+            def iappend(x, y, one=one, top=top):
+                return A.cond(teq(x, one), y, A.cond(teq(y, one), x, A.cond(A.lor(teq(x, top), teq(y, top)), top,
+                              A.cond((x[1] + 1).eq(y[0]), A.tup(x[0], y[1]), top))))
+            iv = np.arange(n).astype(dt)
+            term = A.scanl(iappend, one, (iv, iv))
+            exp = (np.concatenate([[-1], np.zeros(n)]).astype(dt), np.concatenate([[-1], np.arange(n)]).astype(dt))
+            out[f"issue364_{t}_{n}"] = (term, exp)
+    # Test/NoFib/Issues/Issue114.hs:79-84: compensated prefix sums (compared with the suite's Float tolerance)
+    efl = (np.full(100, 1.01, np.float32), np.zeros(100, np.float32))
+    exp = (np.array([1.01 * k for k in range(1, 101)], np.float32), np.zeros(100, np.float32))
+    out["issue114_ref2"] = (A.scanl1(_efloat_add, efl), exp)
+    # Test/NoFib/Issues/Issue93.hs:30-37
+    xs = np.array([[5]], I)
+    out["issue93"] = (A.permute(lambda c, _: c, A.fill(A.use(xs).shape, A.constant(0)), lambda ix: A.Just_(ix), xs), xs)
+    return out
