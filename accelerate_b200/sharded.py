@@ -1,0 +1,320 @@
+"""Data-parallel execution over several GPUs: one process per GPU, arrays split
+along the outermost dimension, at most one exchange step per skeleton.
+
+  fold to a scalar   local fold1, all-gather of the partials, combine in rank
+                     order (keeps non-commutative functions correct)
+  per-row folds,     row blocks; no communication
+  maps, foldSeg      (foldSeg: the split falls on a segment boundary)
+  1-D scans          local fold1 -> all-gather of the totals -> exclusive scan of
+                     the totals gives each rank its carry-in -> local seeded scan
+  permute            private full-size target per rank (rank 0 starts from the
+                     defaults, the others from the combination's identity),
+                     then all-reduce
+  stencil            row slabs with `radius` halo rows exchanged with the two
+                     neighbours (send/recv) before every application
+
+Collectives go through ``torch.distributed`` (NCCL over NVLink on GPUs; gloo on
+CPU in the tests).  The local work is delegated to an *executor*: the GPU
+executor below runs programs through the C-ABI library and exposes device
+arrays to torch without copying.  Nothing here computes array results on the
+CPU.
+"""
+from __future__ import annotations
+
+import numpy as np
+import torch
+import torch.distributed as dist
+
+from . import language as L
+
+
+class GpuExecutor:
+    """Runs terms on this rank's GPU; arrays are ``backend.DeviceArray``."""
+
+    def __init__(self, ctx):
+        from . import backend
+        self.backend, self.ctx = backend, ctx
+        self.stream = torch.cuda.ExternalStream(ctx.stream(), device=torch.device("cuda", ctx.device))
+        self._progs = {}
+
+    def run(self, key, build, inputs):
+        """``build(*params)`` -> term(s); cached under ``key`` + input signature."""
+        sig = (key, tuple((a.elt if L.is_scalar(a.elt) else tuple(a.elt), len(a.shape)) for a in inputs))
+        ent = self._progs.get(sig)
+        if ent is None:
+            L.reset_names()
+            params = [L.param(len(a.shape), a.elt) for a in inputs]
+            res = build(*params)
+            single = not isinstance(res, (list, tuple))
+            prog = L.build_program(res)
+            order = [next(i for i, q in enumerate(params) if q.node is n) for n in prog.inputs]
+            ent = self._progs[sig] = (prog, order, single)
+        prog, order, single = ent
+        outs = self.ctx.execute(prog.text, [inputs[k] for k in order], len(prog.outputs))
+        for o, (_, elt) in zip(outs, prog.outputs):
+            o.elt = elt
+        return outs[0] if single else outs
+
+    def from_host(self, a):
+        return self.ctx.from_host(a)
+
+    def to_host(self, a):
+        return a.download()
+
+    def tensor(self, a, leaf=0):
+        """Zero-copy torch view of one leaf of a device array."""
+        dt = np.dtype(L.NP_OF[a.leaf_types[leaf]])
+        n = int(np.prod(a.shape)) if len(a.shape) else 1
+        if n == 0:
+            return torch.empty(a.shape, dtype=torch.from_numpy(np.empty(0, dt)).dtype, device=self.stream.device)
+
+        class View:
+            pass
+        v = View()
+        v.__cuda_array_interface__ = {"shape": tuple(a.shape) if len(a.shape) else (1,), "typestr": dt.str, "data": (a.devptr(leaf), False),
+                                      "version": 3}
+        t = torch.as_tensor(v, device=self.stream.device)
+        t._keepalive = a
+        return t
+
+    def wrap(self, t, elt):
+        """Device array over a torch tensor's memory (the tensor must stay alive)."""
+        a = self.ctx.wrap(elt, tuple(t.shape), [t.data_ptr()])
+        a._keepalive = t
+        return a
+
+    def empty(self, elt, shape):
+        return self.ctx.array(elt, tuple(shape))
+
+    def slice1d(self, a, lo, hi):
+        """Elements [lo, hi) of a vector of scalars as a view (no copy)."""
+        item = np.dtype(L.NP_OF[a.leaf_types[0]]).itemsize
+        v = self.ctx.wrap(a.elt, (hi - lo,), [a.devptr(0) + lo * item])
+        v._keepalive = a
+        return v
+
+    def collective(self):
+        """Context in which torch collectives are ordered after this executor's kernels."""
+        return torch.cuda.stream(self.stream)
+
+    def sync(self):
+        self.ctx.sync()
+
+
+class Sharded:
+    """Sharded skeletons over an executor and a process group."""
+
+    def __init__(self, executor, group=None):
+        self.ex = executor
+        self.group = group
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+
+    # -- helpers ------------------------------------------------------------------
+    def _all_gather_scalars(self, arr):
+        """Replicated vector of every rank's rank-0 (or 1-element) array."""
+        outs = []
+        for leaf in range(len(arr.leaf_types) if hasattr(arr, "leaf_types") else 1):
+            t = self.ex.tensor(arr, leaf).reshape(1)
+            g = torch.empty(self.world, dtype=t.dtype, device=t.device)
+            with self.ex.collective():
+                if self.world > 1:
+                    dist.all_gather_into_tensor(g, t, group=self.group)
+                else:
+                    g.copy_(t)
+            outs.append(g)
+        return outs
+
+    def _gathered_array(self, arr):
+        """All ranks' scalars as one local array of shape (world,) (element type kept)."""
+        leaves = self._all_gather_scalars(arr)
+        if len(leaves) == 1:
+            return self.ex.wrap(leaves[0], arr.elt)
+        # tuples: one wrapped leaf each, zipped by a program
+        parts = [self.ex.wrap(t, ty) for t, ty in zip(leaves, L.flatten_ty(arr.elt))]
+        return self.ex.run(("zipleaves", len(parts)), lambda *ps: L.generate(ps[0].shape, lambda ix: _retuple(arr.elt, [p[ix] for p in ps])), parts)
+
+    # -- folds ------------------------------------------------------------------------
+    def fold_all(self, f, z, shard, key="fold_all"):
+        """``fold f z`` of a vector split across ranks; the result is replicated.
+        Shards must be non-empty (fold1 of the local part)."""
+        part = self.ex.run((key, "local"), lambda x: L.fold1(f, x), [shard])
+        allp = self._gathered_array(part)
+        if z is None:
+            return self.ex.run((key, "final1"), lambda p: L.fold1(f, p), [allp])
+        return self.ex.run((key, "final", repr(z)), lambda p: L.fold(f, z, p), [allp])
+
+    def fold_rows(self, f, z, rows_block, key="fold_rows"):
+        """Per-row fold of this rank's block of rows: no communication."""
+        return self.ex.run((key, repr(z)), lambda x: L.fold(f, z, x), [rows_block])
+
+    # -- scans ------------------------------------------------------------------------
+    def scan1d(self, kind, f, z, shard, key="scan"):
+        """1-D ``scanl``/``scanl1``/``scanl'``/``scanr``/``scanr1``/``scanr'`` of a vector
+        split into contiguous chunks in rank order.  Returns this rank's part of the
+        result (and, for the primed forms, the replicated total).
+
+        scanl / scanr: rank r holds out[r*n .. (r+1)*n); the last rank additionally holds
+        out[N] (its part has n+1 elements).
+        """
+        right = kind in ("scanr", "scanr1", "scanr'")
+        seeded = kind in ("scanl", "scanr", "scanl'", "scanr'")
+        primed = kind.endswith("'")
+        r, G = self.rank, self.world
+        total = self.ex.run((key, "total"), lambda x: L.fold1(f, x), [shard])
+        totals = self._gathered_array(total)
+        # carry-in: everything that comes logically before this chunk
+        if not right:
+            if seeded:
+                carries = self.ex.run((key, "carryL", repr(z)), lambda t: L.scanl(f, z, t), [totals])       # G+1 entries
+            else:
+                carries = self.ex.run((key, "carryL1"), lambda t: L.scanl1(f, t), [totals])                 # carry of rank r = entry r-1
+        else:
+            if seeded:
+                carries = self.ex.run((key, "carryR", repr(z)), lambda t: L.scanr(f, z, t), [totals])       # entry r+1 = carry of rank r
+            else:
+                carries = self.ex.run((key, "carryR1"), lambda t: L.scanr1(f, t), [totals])
+        n = shard.shape[0]
+        if not right:
+            idx = r if seeded else r - 1
+        else:
+            idx = r + 1
+        has_carry = seeded or (not right and r > 0) or (right and r < G - 1)
+        if not has_carry:
+            # first chunk of an unseeded scan
+            return self.ex.run((key, "plain", kind), lambda x: (L.scanl1 if not right else L.scanr1)(f, x), [shard])
+        pick = lambda c: c[L.index(idx)]  # noqa: E731
+        op = L.scanr if right else L.scanl
+        full = self.ex.run((key, "seeded", kind, idx), lambda x, c: op(f, pick(c), x), [shard, carries])    # n+1 values
+        if primed:
+            tot_idx = 0 if right else G
+            tot = self.ex.run((key, "tot", tot_idx), lambda c: L.unit(c[L.index(tot_idx)]), [carries])
+            part = self._slice(full, 1, n + 1) if right else self._slice(full, 0, n)
+            return part, tot
+        if seeded:
+            # the chunk's n values; the rank holding the end of the vector also keeps the extra element
+            # (scanl: out[N] = total; scanr: out[N] = seed)
+            return full if r == G - 1 else self._slice(full, 0, n)
+        # inclusive: drop the carry itself
+        return self._slice(full, 0, n) if right else self._slice(full, 1, n + 1)
+
+    def _slice(self, arr, lo, hi):
+        if hasattr(self.ex, "slice1d"):
+            return self.ex.slice1d(arr, lo, hi)          # a view, no copy
+        return self.ex.run(("slice", lo, hi), lambda x: L.backpermute(L.index(hi - lo), lambda ix: L.index(ix[0] + lo), x), [arr])
+
+    # -- permute ----------------------------------------------------------------------
+    def permute(self, op, defaults, index_fn, inputs, build_source, key="permute"):
+        """``permute (op)`` with ``op`` in {"add", "min", "max"}: every rank combines its
+        source shard into a private full-size target (rank 0 from the defaults, the others
+        from the identity), then the targets are all-reduced.  ``index_fn(ix, *inputs)`` and
+        ``build_source(*inputs)`` are given the rank's input shards."""
+        f = {"add": lambda a, b: a + b, "min": L.min_, "max": L.max_}[op]
+        elt = defaults.elt
+        if self.rank == 0:
+            start = defaults
+        else:
+            ident = {"add": lambda t: L.lift(0, t), "min": lambda t: L.max_bound(t) if not L.is_float(t) else L.lift(float("inf"), t),
+                     "max": lambda t: L.min_bound(t) if not L.is_float(t) else L.lift(float("-inf"), t)}[op](elt)
+            start = self.ex.run((key, "ident", op), lambda d: L.fill(d.shape, ident), [defaults])
+        out = self.ex.run((key, op), lambda d, *xs: L.permute(f, d, lambda ix: index_fn(ix, *xs), build_source(*xs)), [start] + list(inputs))
+        if self.world > 1:
+            t = self.ex.tensor(out)
+            with self.ex.collective():
+                dist.all_reduce(t, op={"add": dist.ReduceOp.SUM, "min": dist.ReduceOp.MIN, "max": dist.ReduceOp.MAX}[op], group=self.group)
+        return out
+
+    # -- stencils -----------------------------------------------------------------------
+    def stencil_iterate(self, f, boundary, slab, iterations, radius=1, key="stencil"):
+        """Apply a rank-2 stencil ``iterations`` times to an array split into row slabs.
+        Interior ranks keep ``radius`` halo rows on either side of their slab; the halos are
+        refreshed from the neighbours before each application (wrap boundaries also connect
+        the first and last rank).  Returns this rank's slab of the result."""
+        r, G = self.rank, self.world
+        wrap = boundary.kind == "wrap" and G > 1
+        up = (r - 1) % G if (r > 0 or wrap) else None
+        down = (r + 1) % G if (r < G - 1 or wrap) else None
+        rows, cols = slab.shape
+        top, bot = (radius if up is not None else 0), (radius if down is not None else 0)
+        if G == 1:
+            cur = slab
+            for _ in range(iterations):
+                cur = self.ex.run((key, "it"), lambda x: L.stencil(f, boundary, x), [cur])
+            return cur
+        ext = self.ex.run((key, "extend", top, bot), lambda x: L.generate(L.index(rows + top + bot, cols),
+                          lambda ix: L.cond(L.land(ix[0] >= top, ix[0] < top + rows), x[L.index(L.min_(L.max_(ix[0] - top, 0), rows - 1), ix[1])],
+                                            L.lift(0, slab.elt)), slab.elt), [slab])
+        for _ in range(iterations):
+            self._exchange_halos(ext, rows, cols, top, bot, up, down, radius)
+            ext = self.ex.run((key, "it"), lambda x: L.stencil(f, boundary, x), [ext])
+        return self._rows(ext, top, top + rows)
+
+    def stencil2(self, f, b1, slab1, b2, slab2, radius=1, key="stencil2"):
+        """One application of a rank-2 ``stencil2`` to two arrays split into the same row slabs."""
+        r, G = self.rank, self.world
+        if G == 1:
+            return self.ex.run((key, "single"), lambda x, y: L.stencil2(f, b1, x, b2, y), [slab1, slab2])
+        exts = []
+        geo = None
+        for slab, b in ((slab1, b1), (slab2, b2)):
+            wrap = b.kind == "wrap"
+            up = (r - 1) % G if (r > 0 or wrap) else None
+            down = (r + 1) % G if (r < G - 1 or wrap) else None
+            rows, cols = slab.shape
+            top, bot = (radius if up is not None else 0), (radius if down is not None else 0)
+            ext = self.ex.run((key, "extend", top, bot), lambda x: L.generate(L.index(rows + top + bot, cols),
+                              lambda ix: L.cond(L.land(ix[0] >= top, ix[0] < top + rows), x[L.index(L.min_(L.max_(ix[0] - top, 0), rows - 1), ix[1])],
+                                                L.lift(0, slab.elt)), slab.elt), [slab])
+            self._exchange_halos(ext, rows, cols, top, bot, up, down, radius)
+            exts.append(ext)
+            if geo is None:
+                geo = (top, rows)
+            elif geo != (top, rows):
+                raise ValueError("stencil2 over slabs needs the same halo layout for both arrays")
+        out = self.ex.run((key, "apply"), lambda x, y: L.stencil2(f, b1, x, b2, y), exts)
+        return self._rows(out, geo[0], geo[0] + geo[1])
+
+    def _rows(self, arr, lo, hi):
+        cols = arr.shape[1]
+        return self.ex.run(("rows", lo, hi), lambda x: L.backpermute(L.index(hi - lo, cols), lambda ix: L.index(ix[0] + lo, ix[1]), x), [arr])
+
+    def _exchange_halos(self, ext, rows, cols, top, bot, up, down, radius):
+        t = self.ex.tensor(ext)
+        ops = []
+        # sends first (up, down), then receives (from down, from up): with two ranks and a wrap
+        # boundary both neighbours are the same peer, and point-to-point messages between one
+        # pair are matched in posting order
+        if up is not None:
+            ops.append(dist.P2POp(dist.isend, t[top:top + radius], up, self.group))
+        if down is not None:
+            ops.append(dist.P2POp(dist.isend, t[top + rows - radius:top + rows], down, self.group))
+        if down is not None:
+            ops.append(dist.P2POp(dist.irecv, t[top + rows:top + rows + bot], down, self.group))
+        if up is not None:
+            ops.append(dist.P2POp(dist.irecv, t[0:top], up, self.group))
+        if ops:
+            with self.ex.collective():
+                for w in dist.batch_isend_irecv(ops):
+                    w.wait()
+
+
+def _retuple(elt, leaves):
+    it = iter(leaves)
+
+    def go(t):
+        if L.is_scalar(t):
+            return next(it)
+        return L.tup(*[go(c) for c in t])
+    return go(elt)
+
+
+def split_segments(offsets, parts):
+    """Boundaries (segment indices) that split a segmented vector into ``parts`` chunks
+    of nearly equal element counts; each boundary falls on a segment boundary."""
+    offsets = np.asarray(offsets)
+    n = int(offsets[-1])
+    cuts = [0]
+    for k in range(1, parts):
+        cuts.append(int(np.searchsorted(offsets, k * n // parts, side="left")))
+    cuts.append(len(offsets) - 1)
+    return cuts

@@ -143,6 +143,8 @@ def suite(scale=0, seed=42, rank=0):
     W.append(Workload("jacobi5_clamp_x100_f32", "configs[4]", [grid(seed)], jac, side * side_c * iters, 8 * side * side_c * iters, "acc_stencil", iters))
     W.append(Workload("stencil2_gauss_mirror_f32", "configs[4]", [grid(seed), grid(seed + 1)],
                       lambda a, b: A.stencil2(gauss2, A.mirror, a, A.mirror, b), side * side_c, 12 * side * side_c, "acc_stencil", 1))
+    for w in W:
+        w.bins = bins16 if w.name == "permute_hist_i32" else bins20
     return W
 
 
@@ -172,6 +174,52 @@ class Bound:
         for o, buf in zip(outs, out_bufs):
             res.append(o.download(out=[buf] if buf is not None else None))
         return res
+
+
+class ShardedBound:
+    """A workload on one rank of a multi-GPU run: this rank's shard is resident; each run does
+    the local kernels plus the skeleton's one exchange step (accelerate_b200.sharded)."""
+
+    def __init__(self, sh, w, host):
+        self.sh, self.w, self.host = sh, w, host
+        self.dev = None
+        self.aux = {}
+
+    def upload(self):
+        ex = self.sh.ex
+        self.dev = [ex.from_host(h) for h in self.host]
+        name = self.w.name
+        if name == "permute_hist_i32":
+            self.aux["defaults"] = ex.from_host(np.zeros(self.w.bins, np.int32))
+        if name == "permute_add_f32":
+            self.aux["defaults"] = ex.from_host(np.zeros(self.w.bins, np.float32))
+
+    def run(self):
+        sh, d, name = self.sh, self.dev, self.w.name
+        ex = sh.ex
+        if name == "fold1seg_add_i32":
+            return ex.run("c1a", lambda v, l: A.fold1Seg(add, v, l), d)            # segments never straddle ranks
+        if name == "fold_max_rows_f32":
+            return ex.run("c1b", lambda m: A.fold1(A.max_, m), d)                  # row blocks
+        if name == "scanl1_add_i32":
+            return sh.scan1d("scanl1", add, None, d[0], key="c2a")
+        if name == "scanl_prime_add_f32":
+            return sh.scan1d("scanl'", add, 0.0, d[0], key="c2b")
+        if name == "scanr1_max_i64":
+            return sh.scan1d("scanr1", A.max_, None, d[0], key="c2c")
+        if name == "permute_hist_i32":
+            return sh.permute("add", self.aux["defaults"], lambda ix, k: A.Just_(A.index(A.from_integral(k[ix], "i64"))), d,
+                              lambda k: A.fill(k.shape, A.constant(np.int32(1))), key="c3a")
+        if name == "permute_add_f32":
+            bins = self.w.bins
+            return sh.permute("add", self.aux["defaults"],
+                              lambda ix, k, v: A.cond(k[ix] < 0, A.Nothing_(1), A.Just_(A.index(A.from_integral(k[ix], "i64") % bins))), d,
+                              lambda k, v: v, key="c3b")
+        if name == "jacobi5_clamp_x100_f32":
+            return sh.stencil_iterate(jacobi, A.clamp, d[0], 100, key="c4a")
+        if name == "stencil2_gauss_mirror_f32":
+            return sh.stencil2(gauss2, A.mirror, d[0], A.mirror, d[1], key="c4b")
+        raise KeyError(name)
 
 
 class ClockSampler:
@@ -292,8 +340,12 @@ def main():
         ws = [w for w in ws if any(s in w.name for s in args.only.split(","))]
     t_gen = time.perf_counter()
     bound = []
+    sharded = None
+    if world > 1:
+        from accelerate_b200.sharded import GpuExecutor, Sharded
+        sharded = Sharded(GpuExecutor(ctx))
     for w in ws:
-        b = Bound(ctx, w, [f() for f in w.inputs])
+        b = ShardedBound(sharded, w, [f() for f in w.inputs]) if sharded else Bound(ctx, w, [f() for f in w.inputs])
         b.upload()
         bound.append(b)
     ctx.sync()
@@ -352,7 +404,7 @@ def main():
 
     # end to end: pinned host buffers in, results back to pinned host buffers
     e2e = None
-    if not args.no_e2e:
+    if not args.no_e2e and world == 1:
         h2d = d2h = 0
         pinned_in, outs_buf = [], []
         for b in bound:
