@@ -196,6 +196,17 @@ class Gen {
           r.leaf.insert(r.leaf.end(), v.leaf.begin(), v.leaf.end());
         }
         return r;
+      case X_SNOC:
+        for (auto& c : e.a) {
+          CVal v = gen(*c);
+          r.leaf.insert(r.leaf.end(), v.leaf.begin(), v.leaf.end());
+        }
+        return r;
+      case X_INIT: {
+        CVal v = gen(*e.a[0]);
+        r.leaf.assign(v.leaf.begin(), v.leaf.end() - v.ty.e.back().nleaves());
+        return r;
+      }
       case X_PRJ: {
         CVal v = gen(*e.a[0]);
         size_t off = 0;

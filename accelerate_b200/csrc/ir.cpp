@@ -208,6 +208,29 @@ std::unique_ptr<Expr> parse_expr(const Sx& x, TEnv& env) {
     std::vector<Type> ts;
     for (size_t i = 1; i < x.size(); ++i) ts.push_back(sub(i).ty);
     e->ty = Type::tup(std::move(ts));
+  } else if (h == "snoc") {
+    // Pair as the reference builds tuples (snoc lists, AST.hs:536-540): (snoc l r) appends r as one
+    // more component to the tuple l; (tup) is Nil.  (((), a), b) thus becomes the flat tuple (a, b).
+    e->kind = X_SNOC;
+    Expr& l = sub(1);
+    Expr& r = sub(2);
+    if (!l.ty.tuple) throw Error(B200_ERR_TYPE, "snoc: left operand is not a tuple");
+    std::vector<Type> ts = l.ty.e;
+    ts.push_back(r.ty);
+    e->ty = Type::tup(std::move(ts));
+  } else if (h == "last") {
+    // the final component of a tuple (the right part of a pair pattern)
+    e->kind = X_PRJ;
+    Expr& v = sub(1);
+    if (!v.ty.tuple || v.ty.e.empty()) throw Error(B200_ERR_TYPE, "last of a non-tuple or empty tuple");
+    e->n = (int)v.ty.e.size() - 1;
+    e->ty = v.ty.e.back();
+  } else if (h == "init") {
+    // all components but the last (the left part of a pair pattern)
+    e->kind = X_INIT;
+    Expr& v = sub(1);
+    if (!v.ty.tuple || v.ty.e.empty()) throw Error(B200_ERR_TYPE, "init of a non-tuple or empty tuple");
+    e->ty = Type::tup(std::vector<Type>(v.ty.e.begin(), v.ty.e.end() - 1));
   } else if (h == "prj") {
     e->kind = X_PRJ;
     e->n = atoi(x.at(1).s.c_str());

@@ -77,7 +77,7 @@ extern const char* const prim_name[P_NPRIMS];
 
 enum ExprKind {
   X_CONST, X_VAR, X_LET, X_TUP, X_PRJ, X_COND, X_WHILE, X_PRIM, X_INDEX, X_LINDEX, X_SHAPE,
-  X_SHAPESIZE, X_TOINDEX, X_FROMINDEX, X_COERCE, X_UNDEF, X_APP, X_CASE
+  X_SHAPESIZE, X_TOINDEX, X_FROMINDEX, X_COERCE, X_UNDEF, X_APP, X_CASE, X_SNOC, X_INIT
 };
 
 struct Fun;

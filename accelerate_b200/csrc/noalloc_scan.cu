@@ -14,7 +14,7 @@
 // Limits and sharing rules (also stated in include/accelerate_b200.h):
 //  * at most B200_NOALLOC_SCAN_MAX_ELEMS (2^28) elements per call; larger
 //    inputs are refused with B200_ERR_ARG;
-//  * every GPU that loads this library carries the array (about 0.8 MB) until
+//  * every GPU that loads this library carries the array (about 1 MB) until
 //    the process exits;
 //  * all calls on one GPU share the array.  It keeps whatever the previous
 //    call left, so each call first clears the words that must start at zero

@@ -270,6 +270,25 @@ struct HostEval {
         }
         return r;
       }
+      case X_SNOC: {
+        HVal r;
+        r.ty = e.ty;
+        for (auto& c : e.a) {
+          HVal v = eval(*c);
+          r.i.insert(r.i.end(), v.i.begin(), v.i.end());
+          r.f.insert(r.f.end(), v.f.begin(), v.f.end());
+        }
+        return r;
+      }
+      case X_INIT: {
+        HVal v = eval(*e.a[0]);
+        size_t drop = v.ty.e.back().nleaves();
+        HVal r;
+        r.ty = e.ty;
+        r.i.assign(v.i.begin(), v.i.end() - drop);
+        r.f.assign(v.f.begin(), v.f.end() - drop);
+        return r;
+      }
       case X_PRJ: {
         HVal v = eval(*e.a[0]);
         size_t off = 0;

@@ -114,7 +114,7 @@ int b200_kernel_source(const char* text, size_t len, int node, char* out, size_t
  * `in` and `out` are device pointers on the current device (they may not
  * overlap); `stream` is a cudaStream_t (NULL = default stream).  The call
  * returns after the result is complete.  The look-back descriptors of the scan
- * live in a fixed __device__ array of about 0.8 MB that every GPU using this
+ * live in a fixed __device__ array of about 1 MB that every GPU using this
  * library holds until the process exits, hence:
  *   - n may not exceed B200_NOALLOC_SCAN_MAX_ELEMS; more is refused (B200_ERR_ARG);
  *   - calls on the same GPU share that array and must not overlap in time

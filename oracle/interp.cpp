@@ -306,7 +306,7 @@ const char* op_name[] = {
 
 enum EKind {
   E_CONST, E_VAR, E_LET, E_TUP, E_PRJ, E_COND, E_WHILE, E_PRIM, E_INDEX, E_LINDEX, E_SHAPE,
-  E_SHAPESIZE, E_TOINDEX, E_FROMINDEX, E_COERCE, E_UNDEF, E_APP, E_CASE
+  E_SHAPESIZE, E_TOINDEX, E_FROMINDEX, E_COERCE, E_UNDEF, E_APP, E_CASE, E_SNOC, E_INIT
 };
 
 struct Fun;
@@ -415,6 +415,16 @@ std::unique_ptr<Exp> parse_exp(const Sx& x, Scope& sc) {
   } else if (h == "tup") {
     e->kind = E_TUP;
     for (size_t i = 1; i < x.size(); ++i) sub(i);
+  } else if (h == "snoc") {   // Pair on snoc-list tuples (AST.hs:536-540): append one component
+    e->kind = E_SNOC;
+    sub(1); sub(2);
+  } else if (h == "last") {   // the final component
+    e->kind = E_PRJ;
+    e->slot = -1;
+    sub(1);
+  } else if (h == "init") {   // all components but the last
+    e->kind = E_INIT;
+    sub(1);
   } else if (h == "prj") {
     e->kind = E_PRJ;
     e->slot = atoi(x[1].s.c_str());
@@ -723,8 +733,21 @@ Value eval(const Exp& e, Env& env) {
       for (auto& c : e.a) xs.push_back(eval(*c, env));
       return Value::tup(std::move(xs));
     }
+    case E_SNOC: {
+      Value l = eval(*e.a[0], env);
+      if (!l.tuple) throw std::runtime_error("snoc: left operand is not a tuple");
+      l.e.push_back(eval(*e.a[1], env));
+      return l;
+    }
+    case E_INIT: {
+      Value v = eval(*e.a[0], env);
+      if (!v.tuple || v.e.empty()) throw std::runtime_error("init of a non-tuple or empty tuple");
+      v.e.pop_back();
+      return v;
+    }
     case E_PRJ: {
       Value v = eval(*e.a[0], env);
+      if (v.tuple && e.slot == -1 && !v.e.empty()) return v.e.back();
       if (!v.tuple || (size_t)e.slot >= v.e.size()) throw std::runtime_error("prj: not a tuple / index out of range");
       return v.e[e.slot];
     }

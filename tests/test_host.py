@@ -105,3 +105,24 @@ def test_oracle_raises_the_references_errors():
         oracle.run(A.fold1Seg(add, np.zeros(4, np.int32), np.array([2, 0, 2], np.int32)))   # Interpreter.hs:423
     with pytest.raises(oracle.OracleError, match="out of bounds"):
         oracle.run(A.backpermute(A.index(3), lambda ix: A.index(ix[0] + 5), np.zeros(4, np.int32)))
+
+
+HASKELL_DIALECT = '''(program
+  (in a0 (array 1 f32))
+  (in a1 (array 1 f32))
+  (let a2 (fold f32 (lam ((p0 f32) (p2 f32)) (let x0 (var p0) (let x1 (var p2) (prim add f32 (snoc (snoc (tup) (var x0)) (var x1)))))) (const f32 0x0p+0)
+     (delayed (snoc (tup) (prim min i64 (snoc (snoc (tup) (last (shape a0))) (last (shape a1)))))
+              (lam ((p0 (tup i64))) (let x0 (last (var p0)) (prim mul f32 (snoc (snoc (tup) (index a0 (snoc (tup) (var x0)))) (index a1 (snoc (tup) (var x0))))))))))
+  (out a2))'''
+
+
+def test_program_text_as_the_haskell_module_writes_it(lib_built):
+    """haskell/src/Data/Array/Accelerate/B200.hs writes tuples as snoc lists ((tup), snoc, init,
+    last) and passes binary primitives one pair: dotp in that dialect runs on the oracle,
+    compiles, and still takes the vectorised path."""
+    from oracle import oracle
+    x = np.arange(8, dtype=np.float32)
+    (_, (res,)), = oracle.run_text(HASKELL_DIALECT, [((8,), [x]), ((8,), [x])])
+    assert float(res) == 140.0
+    assert "ok fold" in backend.compile_check(HASKELL_DIALECT)
+    assert "acc_ld4(p.a0_l0" in backend.kernel_source(HASKELL_DIALECT, 0)
