@@ -582,6 +582,9 @@ struct GlueBuilder {
       glue.defines[D + "_BULK_ISSUE(BASE, BAR, SRC)"] = bulk;
       glue.defines[D + "_STAGE_BYTES"] = "(" + std::to_string(off) + " * SCAN_TILE)";
       glue.defines[D + "_STREAM_BYTES"] = std::to_string(off);
+      size_t nleaves = 0;
+      for (auto& sn : streams) nleaves += ps.array(sn).elt.nleaves();
+      glue.defines[D + "_STREAM_NLEAVES"] = std::to_string(nleaves);
     }
     // same with the linear address of the first element supplied by the caller
     fns << "__device__ __forceinline__ void " << D << "_get4_lin(const Params& p, i64 lin, i64 row, i64 j, " << S << " (&o)[4]) {\n" << decomp.str()

@@ -29,8 +29,8 @@ void fnv2(const std::string& s, uint64_t& a, uint64_t& b) {
   }
 }
 
-const char* const kOptions[] = {"--gpu-architecture=sm_100a", "--std=c++17", "--fmad=false", "-lineinfo", "--diag-suppress=177,550"};
-const int kNumOptions = 5;
+const char* const kOptions[] = {"--gpu-architecture=sm_100a", "--std=c++17", "--fmad=false", "--diag-suppress=177,550"};
+const int kNumOptions = 4;
 
 std::string cache_dir() {
   const char* e = getenv("ACCELERATE_B200_CACHE_DIR");

@@ -94,7 +94,7 @@ CompiledKernel& Ctx::kernel(const std::string& source, const std::string& entry,
   CompiledKernel k;
   check(drv.ModuleLoadData(&k.module, cubin.data()), "cuModuleLoadData");
   check(drv.ModuleGetFunction(&k.fn, k.module, entry.c_str()), "cuModuleGetFunction");
-  if (dyn_smem > 48 * 1024)
+  if (dyn_smem > 32 * 1024)   // static + dynamic shared memory beyond 48 KB needs the opt-in
     check(drv.FuncSetAttribute(k.fn, CU_FUNC_ATTRIBUTE_MAX_DYNAMIC_SHARED_SIZE_BYTES, (int)dyn_smem), "cuFuncSetAttribute");
   int nb = 0;
   check(drv.OccupancyMaxActiveBlocksPerMultiprocessor(&nb, k.fn, threads, dyn_smem), "cuOccupancyMaxActiveBlocksPerMultiprocessor");
@@ -174,6 +174,9 @@ std::vector<std::pair<std::string, std::map<std::string, std::string>>> default_
     case N_FOLDSEG: v.push_back({"foldseg", {{"FOLDSEG_G", "32"}}}); break;
     case N_SCAN: case N_SCAN2: {
       v.push_back({"scan", scan_variant(n.elt)});
+      if (g.defines.count("D0_STREAM_NLEAVES") && g.defines.at("D0_STREAM_NLEAVES") == "1" && g.defines.at("SCAN_PACKED") == "1" &&
+          g.defines.at("D0_STREAM_BYTES") == g.defines.at("SCAN_T_BYTES"))
+        v.push_back({"scan", {{"SCAN_RING", "1"}, {"SCAN_ROUNDS", g.defines.at("SCAN_T_BYTES") == "8" ? "4" : "8"}, {"SCAN_SLOTS", "3"}, {"SCAN_MIN_BLOCKS", "2"}}});
       if (!g.streams.empty() && !g.streams[0].empty()) {
         auto var = scan_variant(n.elt);
         var["SCAN_PIPE"] = "1";
@@ -704,6 +707,39 @@ void Program::run(const std::vector<DevArrayP>& inputs, std::vector<DevArrayP>& 
         L.named["incl"] = (int64_t)(uintptr_t)(base + status_bytes + val_bytes);
         L.named["counter"] = (int64_t)(uintptr_t)(c.d_words + 2);
         L.named["epoch"] = c.scan_epoch;
+        // shared-memory ring kernel: one scalar leaf in, one scalar leaf of the same size out
+        {
+          const auto& df = st.glue.defines;
+          const bool packed = df.count("SCAN_PACKED") && df.at("SCAN_PACKED") == "1";
+          const bool one_stream = df.count("D0_STREAM_NLEAVES") && df.at("D0_STREAM_NLEAVES") == "1" && packed &&
+                                  df.at("D0_STREAM_BYTES") == df.at("SCAN_T_BYTES");
+          const int bytes = packed ? atoi(df.at("SCAN_T_BYTES").c_str()) : 0;
+          // 8-byte elements halve the elements a ring holds; the register-resident kernel is faster for them
+          const bool want = getenv("ACCELERATE_B200_SCAN_RING") ? true : (bytes <= 4 && !getenv("ACCELERATE_B200_SCAN_NO_RING"));
+          if (one_stream && want && L.fast("D0") && in_vec && out_vec) {
+            auto tune = [](const char* name, int dflt) { const char* e = getenv(name); return e && *e ? atoi(e) : dflt; };
+            const int rounds = tune("ACCELERATE_B200_RING_ROUNDS", bytes <= 4 ? 8 : 4);
+            const int slots = tune("ACCELERATE_B200_RING_SLOTS", 3);
+            const int minb = tune("ACCELERATE_B200_RING_MIN_BLOCKS", 2);
+            const int64_t rtile = 8 * (int64_t)rounds * 128;
+            const int64_t r_tiles_per_row = std::max<int64_t>(1, (m + rtile - 1) / rtile);
+            const int64_t r_total = rows * r_tiles_per_row;
+            const size_t smem = (size_t)slots * rtile * bytes;
+            std::map<std::string, std::string> var = {{"SCAN_RING", "1"}, {"SCAN_ROUNDS", std::to_string(rounds)}, {"SCAN_SLOTS", std::to_string(slots)},
+                                                      {"SCAN_MIN_BLOCKS", std::to_string(minb)}};
+            if (const char* e = getenv("ACCELERATE_B200_SCAN_LOOK")) var["SCAN_LOOK"] = e;
+            const size_t r_status = ((size_t)r_total * 16 + 255) / 256 * 256;
+            char* rbase = (char*)c.scan_descriptors(r_status);
+            L.named["tiles_per_row"] = r_tiles_per_row;
+            L.named["total_tiles"] = r_total;
+            L.named["status"] = (int64_t)(uintptr_t)rbase;
+            L.named["epoch"] = c.scan_epoch;
+            CompiledKernel& k = c.kernel(assemble_source(st.glue, "scan", var), "acc_scan_ring", 256, smem);
+            const int64_t grid = std::min<int64_t>(r_total, (int64_t)c.sm_count * k.max_blocks_per_sm);
+            L.launch(k, grid, 256, smem);
+            break;
+          }
+        }
         const bool pipe_ok = !st.glue.streams.at(0).empty() && L.fast("D0") && in_vec && getenv("ACCELERATE_B200_SCAN_PIPE");
         if (pipe_ok) {
           // persistent CTAs, input staged through shared memory by the bulk-copy engine
@@ -778,6 +814,7 @@ void Program::run(const std::vector<DevArrayP>& inputs, std::vector<DevArrayP>& 
           const int64_t priv = std::min<int64_t>(out_n, cap / bytes);
           const size_t smem = (size_t)priv * bytes;
           std::map<std::string, std::string> var = {{"PERMUTE_SMEM", "1"}, {"PERMUTE_THREADS", "1024"}};
+          if (const char* e = getenv("ACCELERATE_B200_PERMUTE_UNROLL")) var["PERMUTE_UNROLL"] = e;
           CompiledKernel& k = c.kernel(assemble_source(st.glue, "permute", var), "acc_permute", 1024, smem);
           if (smem > 48 * 1024) c.check(c.drv.FuncSetAttribute(k.fn, CU_FUNC_ATTRIBUTE_MAX_DYNAMIC_SHARED_SIZE_BYTES, (int)smem), "cuFuncSetAttribute");
           int nb = 1;
@@ -788,7 +825,9 @@ void Program::run(const std::vector<DevArrayP>& inputs, std::vector<DevArrayP>& 
           L.launch(k, std::max<int64_t>(grid, 1), 1024, smem);
         } else {
           L.named["priv"] = 0;
-          CompiledKernel& k = c.kernel(assemble_source(st.glue, "permute", {}), "acc_permute", 512, 0);
+          std::map<std::string, std::string> pvar;
+          if (const char* e = getenv("ACCELERATE_B200_PERMUTE_UNROLL")) pvar["PERMUTE_UNROLL"] = e;
+          CompiledKernel& k = c.kernel(assemble_source(st.glue, "permute", pvar), "acc_permute", 512, 0);
           const int64_t work = L.named["vec"] ? (total + 3) / 4 : total;
           int64_t grid = std::min<int64_t>((work + 511) / 512, (int64_t)c.sm_count * k.max_blocks_per_sm * 2);
           L.launch(k, std::max<int64_t>(grid, 1), 512, 0);

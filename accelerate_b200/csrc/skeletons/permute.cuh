@@ -31,6 +31,9 @@
 #ifndef PERMUTE_SMEM
 #define PERMUTE_SMEM 0
 #endif
+#ifndef PERMUTE_UNROLL
+#define PERMUTE_UNROLL 4
+#endif
 #define PERMUTE_IS_ATOMIC (PERMUTE_MODE >= PERMUTE_ATOMIC_ADD && PERMUTE_MODE <= PERMUTE_ATOMIC_XOR)
 
 #if PERMUTE_IS_ATOMIC || PERMUTE_MODE == PERMUTE_CAS
@@ -157,18 +160,18 @@ extern "C" __global__ void __launch_bounds__(PERMUTE_THREADS) acc_permute(const 
   if (p.vec) {
     const i64 nv = n >> 2;
     i64 v = tid;
-    // two 128-bit groups in flight per thread
-    for (; v + nthreads < nv; v += 2 * nthreads) {
-      pelem_t x[2][4];
+    // PERMUTE_UNROLL 128-bit groups in flight per thread
+    for (; v + (PERMUTE_UNROLL - 1) * nthreads < nv; v += PERMUTE_UNROLL * nthreads) {
+      pelem_t x[PERMUTE_UNROLL][4];
 #pragma unroll
-      for (int u = 0; u < 2; ++u) {
+      for (int u = 0; u < PERMUTE_UNROLL; ++u) {
         const i64 i = (v + u * nthreads) << 2;
         i64 row = 0, j = i;
         if (inner != n) { row = i / inner; j = i - row * inner; }
         P_get4(p, row, j, x[u]);
       }
 #pragma unroll
-      for (int u = 0; u < 2; ++u) {
+      for (int u = 0; u < PERMUTE_UNROLL; ++u) {
 #pragma unroll
         for (int k = 0; k < 4; ++k) permute_elem(p, x[u][k]);
       }

@@ -619,3 +619,417 @@ extern "C" __global__ void __launch_bounds__(SCAN_THREADS, SCAN_MIN_BLOCKS) acc_
   }
 }
 #endif
+
+// ---------------------------------------------------------------------------------
+// acc_scan_ring: persistent CTAs that keep SCAN_SLOTS tiles each in a shared-memory
+// ring.  A tile is bulk-copied in (cp.async.bulk + mbarrier), scanned locally IN PLACE
+// as soon as it arrives (its aggregate is published at once), and then simply waits
+// in shared memory until its exclusive prefix is known; warp 0 advances the look-back
+// of the oldest unresolved tile without blocking, and resolved tiles are combined with
+// their prefix and streamed out.  Unlike acc_scan, tile data does not occupy registers
+// while the look-back is pending, so a SM keeps several times more elements in flight
+// and the look-back latency no longer idles the memory system.
+// Requirements (checked by the host): one scalar leaf (SCAN_PACKED), exactly one stream
+// leaf of the same size, fast layout, in_vec and out_vec.  Partial tiles (the last of a
+// row) are handled by scan_tile<false> inside the same kernel.
+// Extra named parameter: total_tiles.
+// ---------------------------------------------------------------------------------
+#if defined(SCAN_RING) && SCAN_RING
+#ifndef SCAN_SLOTS
+#define SCAN_SLOTS 6
+#endif
+#define RING_SLOT_BYTES (SCAN_TILE * SCAN_T_BYTES)
+#define RING_LOADING 0
+#define RING_SCANNED 1
+#define RING_RESOLVED 2
+#define RING_DONE 3
+
+__device__ __forceinline__ u32 ring_smem_addr(const void* ptr) { return (u32)__cvta_generic_to_shared(ptr); }
+__device__ __forceinline__ void ring_mbar_init(u64* bar, int count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(ring_smem_addr(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void ring_mbar_expect(u64* bar, u32 bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(ring_smem_addr(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool ring_mbar_try_wait(u64* bar, u32 parity) {
+  u32 ok;
+  asm volatile(
+      "{\n\t.reg .pred q;\n\tmbarrier.try_wait.parity.shared::cta.b64 q, [%1], %2;\n\tselp.u32 %0, 1, 0, q;\n\t}"
+      : "=r"(ok)
+      : "r"(ring_smem_addr(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ void ring_bulk_g2s(void* dst, const void* src, u32 bytes, u64* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(ring_smem_addr(dst)), "l"(src),
+               "r"(bytes), "r"(ring_smem_addr(bar))
+               : "memory");
+}
+#define acc_bulk_g2s ring_bulk_g2s
+struct __align__(SCAN_T_BYTES * 4) ring_quad { SCAN_T v[4]; };
+// four values at logical offsets e..e+3 of a slot (right-to-left scans keep physical order in the slot)
+__device__ __forceinline__ void ring_st4(unsigned char* base, int e, const elt_t (&v)[4]) {
+  ring_quad q;
+#if ACC_RIGHT
+  q.v[0] = v[3].l0; q.v[1] = v[2].l0; q.v[2] = v[1].l0; q.v[3] = v[0].l0;
+  *reinterpret_cast<ring_quad*>(reinterpret_cast<SCAN_T*>(base) + (SCAN_TILE - 4 - e)) = q;
+#else
+  q.v[0] = v[0].l0; q.v[1] = v[1].l0; q.v[2] = v[2].l0; q.v[3] = v[3].l0;
+  *reinterpret_cast<ring_quad*>(reinterpret_cast<SCAN_T*>(base) + e) = q;
+#endif
+}
+__device__ __forceinline__ void ring_ld4(const unsigned char* base, int e, elt_t (&v)[4]) {
+#if ACC_RIGHT
+  const ring_quad q = *reinterpret_cast<const ring_quad*>(reinterpret_cast<const SCAN_T*>(base) + (SCAN_TILE - 4 - e));
+  v[0].l0 = q.v[3]; v[1].l0 = q.v[2]; v[2].l0 = q.v[1]; v[3].l0 = q.v[0];
+#else
+  const ring_quad q = *reinterpret_cast<const ring_quad*>(reinterpret_cast<const SCAN_T*>(base) + e);
+  v[0].l0 = q.v[0]; v[1].l0 = q.v[1]; v[2].l0 = q.v[2]; v[3].l0 = q.v[3];
+#endif
+}
+
+extern __shared__ __align__(128) unsigned char scan_ring_smem[];
+
+extern "C" __global__ void __launch_bounds__(SCAN_THREADS, SCAN_MIN_BLOCKS) acc_scan_ring(const Params p) {
+  __shared__ elt_t sm_v[SCAN_WARPS];
+  __shared__ int sm_h[SCAN_WARPS];
+  __shared__ elt_t sm_excl1;
+  __shared__ int sm_flag1[2];
+  __shared__ __align__(8) u64 full_bar[SCAN_SLOTS];
+  __shared__ i64 slot_tile[SCAN_SLOTS];
+  __shared__ u32 slot_parity[SCAN_SLOTS], slot_uses[SCAN_SLOTS];
+  __shared__ int slot_direct[SCAN_SLOTS], slot_state[SCAN_SLOTS], slot_hexcl[SCAN_SLOTS];
+  __shared__ elt_t slot_agg[SCAN_SLOTS], slot_excl[SCAN_SLOTS];
+  __shared__ i64 sh_resolved;
+  __shared__ int ctl[4];      // [0] scan a slot, [1] finish a slot, [2] leave, [3] a wait gave up
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const i64 n = p.n;
+  const i64 total_tiles = p.total_tiles;
+  const u32 epoch = (u32)p.epoch;
+  unsigned* counter = reinterpret_cast<unsigned*>(p.counter);
+  unsigned* exits = counter + 1;
+
+  // thread 0: next ticket into slot s; full tiles are requested from the copy engine
+  auto fetch = [&](int s) {
+    const i64 T = (i64)atomicAdd(counter, 1u);
+    slot_tile[s] = T;
+    slot_direct[s] = 1;
+    slot_state[s] = RING_LOADING;
+    if (T >= total_tiles) return;
+    const i64 row = T / p.tiles_per_row;
+    const i64 tt = T - row * p.tiles_per_row;
+    const i64 q0 = tt * SCAN_TILE;
+    if (q0 + SCAN_TILE > n) return;
+    slot_direct[s] = 0;
+    slot_parity[s] = slot_uses[s] & 1u;
+    slot_uses[s] += 1;
+#if ACC_RIGHT
+    const i64 src = row * n + (n - q0 - SCAN_TILE);
+#else
+    const i64 src = row * n + q0;
+#endif
+    unsigned char* base = scan_ring_smem + (size_t)s * RING_SLOT_BYTES;
+    ring_mbar_expect(&full_bar[s], (u32)RING_SLOT_BYTES);
+    D0_BULK_ISSUE(base, &full_bar[s], src)
+  };
+
+  if (tid == 0) {
+    for (int s = 0; s < SCAN_SLOTS; ++s) { ring_mbar_init(&full_bar[s], 1); slot_uses[s] = 0; }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    sh_resolved = 0;
+  }
+  __syncthreads();
+  if (tid == 0)
+    for (int s = 0; s < SCAN_SLOTS; ++s) fetch(s);
+  __syncthreads();
+
+  i64 pos_scan = 0, pos_fin = 0;        // ring positions, identical in every thread
+  // look-back state of warp 0 for ring position `resolved`
+  i64 resolved = 0;
+  bool lb_started = false;
+  i64 lb_look = 0, lb_polls = 0;
+  elt_t lb_excl;
+  bool lb_hexcl = false;
+  // a requested, not yet inspected window of descriptors (SCAN_LOOK per lane)
+  bool pend = false;
+  i64 pend_row_first = 0;
+  u32 pst[SCAN_LOOK];
+  elt_t pv[SCAN_LOOK];
+  bool pin[SCAN_LOOK];
+
+  for (;;) {
+    if (warp == 0) {
+      int do_scan = 0, do_exit = 0, fail = 0;
+      const int ss = (int)(pos_scan % SCAN_SLOTS);
+      const bool has_slot = pos_scan < pos_fin + SCAN_SLOTS;
+      const bool scan_work = has_slot && slot_tile[ss] < total_tiles;
+      if (scan_work) {
+        int arrived = slot_direct[ss];
+        if (!arrived && lane == 0) arrived = ring_mbar_try_wait(&full_bar[ss], slot_parity[ss]) ? 1 : 0;
+        do_scan = __shfl_sync(ACC_FULL_MASK, arrived, 0);
+      }
+      // (1) consume the descriptor window requested at the end of the previous iteration: its
+      //     round trip to L2 overlapped with that iteration's scan / finish work
+      if (pend) {
+        pend = false;
+        const int rs = (int)(resolved % SCAN_SLOTS);
+        const i64 T = slot_tile[rs];
+        bool all = true;
+#pragma unroll
+        for (int j = 0; j < SCAN_LOOK; ++j)
+          if (pin[j]) all = all && ((pst[j] >> 2) == epoch);
+        if (__all_sync(ACC_FULL_MASK, all)) {
+          int jp = SCAN_LOOK;
+#pragma unroll
+          for (int j = SCAN_LOOK - 1; j >= 0; --j)
+            if (pin[j] && (pst[j] & 3u) == SCAN_ST_PREFIX) jp = j;
+          const unsigned pm = __ballot_sync(ACC_FULL_MASK, jp < SCAN_LOOK);
+          const int lstar = pm ? (__ffs((int)pm) - 1) : 32;
+          const int last = lane < lstar ? SCAN_LOOK - 1 : (lane == lstar ? jp : -1);
+          elt_t c;
+          bool hc = false;
+#pragma unroll
+          for (int j = SCAN_LOOK - 1; j >= 0; --j)
+            if (pin[j] && j <= last) scan_join(p, c, hc, pv[j], true);
+#pragma unroll
+          for (int d = 1; d < 32; d <<= 1) {
+            const elt_t o = acc_shfl_down(c, d);
+            const int oh = __shfl_down_sync(ACC_FULL_MASK, (int)hc, d);
+            if (lane + d < 32) scan_join_front(p, o, oh != 0, c, hc);
+          }
+          scan_join_front(p, c, hc, lb_excl, lb_hexcl);     // meaningful in lane 0
+          if (pm != 0 || lb_look - 32 * SCAN_LOOK < pend_row_first) {
+            if (lane == 0) {
+              elt_t inc = lb_excl;
+              bool hinc = lb_hexcl;
+              scan_join(p, inc, hinc, slot_agg[rs], true);
+              scan_desc_store(p.status, T, (epoch << 2) | SCAN_ST_PREFIX, inc.l0);
+              slot_excl[rs] = lb_excl;
+              slot_hexcl[rs] = lb_hexcl ? 1 : 0;
+              slot_state[rs] = RING_RESOLVED;
+            }
+            resolved += 1;
+            lb_started = false;
+          } else {
+            lb_look -= 32 * SCAN_LOOK;
+          }
+        } else if (++lb_polls > p.spin_limit) {
+          fail = 1;
+        }
+      }
+      // (2) positions whose prefix was known when they were scanned (first tile of a row, partial tiles)
+      for (int guard = 0; guard < SCAN_SLOTS && resolved < pos_scan; ++guard) {
+        if (slot_state[(int)(resolved % SCAN_SLOTS)] < RING_RESOLVED) break;
+        resolved += 1;
+        lb_started = false;
+      }
+      // (3) request the next window for the oldest unresolved, already scanned position
+      if (resolved < pos_scan && !fail) {
+        const int rs = (int)(resolved % SCAN_SLOTS);
+        const i64 T = slot_tile[rs];
+        const i64 row = T / p.tiles_per_row;
+        const i64 tt = T - row * p.tiles_per_row;
+        pend_row_first = T - tt;
+        if (!lb_started) { lb_started = true; lb_look = T - 1; lb_hexcl = false; lb_polls = 0; }
+#pragma unroll
+        for (int j = 0; j < SCAN_LOOK; ++j) {
+          const i64 idx = lb_look - (i64)(SCAN_LOOK * lane + j);
+          pin[j] = idx >= pend_row_first;
+          pst[j] = 0;
+          if (pin[j]) pst[j] = scan_desc_load(p.status, idx, pv[j].l0);
+        }
+        pend = true;
+      }
+      const int fs = (int)(pos_fin % SCAN_SLOTS);
+      do_exit = (pos_fin == pos_scan && !scan_work) ? 1 : 0;
+      (void)fs;
+      if (lane == 0) {
+        ctl[0] = do_scan;
+        ctl[2] = do_exit;
+        ctl[3] = fail;
+        sh_resolved = resolved;
+      }
+    }
+    __syncthreads();
+    const i64 res_now = sh_resolved;
+    if (ctl[3]) { if (tid == 0) acc_fail(p.err, 110 /* ETIMEDOUT */); break; }
+    if (ctl[2]) break;
+
+    if (ctl[0]) {
+      // ---- local scan of the slot at pos_scan, in place ---------------------------------------
+      const int ss = (int)(pos_scan % SCAN_SLOTS);
+      const i64 T = slot_tile[ss];
+      const i64 row = T / p.tiles_per_row;
+      const i64 tt = T - row * p.tiles_per_row;
+      if (slot_direct[ss]) {
+        scan_tile<false>(p, T, row, tt, sm_v, sm_h, &sm_excl1, sm_flag1);    // partial tile: start to finish
+        __syncthreads();
+        if (tid == 0) slot_state[ss] = RING_DONE;
+      } else {
+        unsigned char* base = scan_ring_smem + (size_t)ss * RING_SLOT_BYTES;
+        const i64 warp_q0 = tt * SCAN_TILE + (i64)warp * SCAN_WARP_ELEMS;
+        elt_t item[SCAN_ROUNDS][4];
+#pragma unroll
+        for (int r = 0; r < SCAN_ROUNDS; ++r) {
+          const int e = warp * SCAN_WARP_ELEMS + r * 128 + lane * 4;
+          const i64 q = warp_q0 + r * 128 + lane * 4;
+#if ACC_RIGHT
+          elt_t t4[4];
+          D0_get4_sm(p, row, n - 4 - q, base, SCAN_TILE - 4 - e, t4);
+#pragma unroll
+          for (int k = 0; k < 4; ++k) item[r][k] = t4[3 - k];
+#else
+          D0_get4_sm(p, row, q, base, e, item[r]);
+#endif
+#pragma unroll
+          for (int k = 1; k < 4; ++k) item[r][k] = scan_op(p, item[r][k - 1], item[r][k]);
+        }
+        elt_t lane_excl[SCAN_ROUNDS], round_carry[SCAN_ROUNDS];
+        elt_t carry;
+        bool hcarry = false;
+#pragma unroll
+        for (int r = 0; r < SCAN_ROUNDS; ++r) {
+          elt_t v = item[r][3];
+#pragma unroll
+          for (int d = 1; d < 32; d <<= 1) {
+            const elt_t o = acc_shfl_up(v, d);
+            if (lane >= d) v = scan_op(p, o, v);
+          }
+          lane_excl[r] = acc_shfl_up(v, 1);
+          const elt_t rt = acc_shfl_idx(v, 31);
+          round_carry[r] = carry;
+          if (r == 0) { carry = rt; hcarry = true; }
+          else carry = scan_op(p, carry, rt);
+        }
+        (void)hcarry;
+        if (lane == 0) sm_v[warp] = carry;
+        __syncthreads();
+        elt_t wbase;
+        bool hwb = false;
+        for (int w = 0; w < warp; ++w) scan_join(p, wbase, hwb, sm_v[w], true);
+#pragma unroll
+        for (int r = 0; r < SCAN_ROUNDS; ++r) {
+          const int e = warp * SCAN_WARP_ELEMS + r * 128 + lane * 4;
+          elt_t pre = wbase;
+          bool hpre = hwb;
+          scan_join(p, pre, hpre, round_carry[r], r > 0);
+          scan_join(p, pre, hpre, lane_excl[r], lane > 0);
+          elt_t o[4];
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+#if ACC_SCAN_MODE == 0
+            o[k] = hpre ? scan_op(p, pre, item[r][k]) : item[r][k];          // tile-local inclusive value
+#else
+            if (k == 0) o[k] = pre;                                            // tile-local exclusive value (none at offset 0)
+            else o[k] = hpre ? scan_op(p, pre, item[r][k - 1]) : item[r][k - 1];
+#endif
+          }
+          ring_st4(base, e, o);
+        }
+        if (tid == 0) {
+          elt_t agg = sm_v[0];
+          for (int w = 1; w < SCAN_WARPS; ++w) agg = scan_op(p, agg, sm_v[w]);
+          slot_agg[ss] = agg;
+          if (tt == 0) {
+            // first tile of a row: its exclusive prefix is the seed (or nothing)
+            elt_t inc = agg;
+#if ACC_SEEDED
+            const elt_t z = F_seed(p);
+            inc = scan_op(p, z, agg);
+            slot_excl[ss] = z;
+            slot_hexcl[ss] = 1;
+#else
+            slot_hexcl[ss] = 0;
+#endif
+            scan_desc_store(p.status, T, (epoch << 2) | SCAN_ST_PREFIX, inc.l0);
+            slot_state[ss] = RING_RESOLVED;
+          } else {
+            scan_desc_store(p.status, T, (epoch << 2) | SCAN_ST_AGG, agg.l0);
+            slot_state[ss] = RING_SCANNED;
+          }
+        }
+      }
+      pos_scan += 1;
+      __syncthreads();
+    }
+
+    if (pos_fin < res_now) {
+      // ---- the oldest slot knows its prefix: combine and stream out ------------------------------
+      const int fs = (int)(pos_fin % SCAN_SLOTS);
+      if (slot_state[fs] != RING_DONE) {
+        const i64 T = slot_tile[fs];
+        const i64 row = T / p.tiles_per_row;
+        const i64 tt = T - row * p.tiles_per_row;
+        const unsigned char* base = scan_ring_smem + (size_t)fs * RING_SLOT_BYTES;
+        const elt_t excl = slot_excl[fs];
+        const bool hexcl = slot_hexcl[fs] != 0;
+        (void)hexcl;
+#if ACC_SCAN_MODE == 1
+        const i64 out_row = row * (n + 1);
+#else
+        const i64 out_row = row * n;
+#endif
+#pragma unroll
+        for (int r = 0; r < SCAN_ROUNDS; ++r) {
+          const int e = warp * SCAN_WARP_ELEMS + r * 128 + lane * 4;
+          const i64 q = tt * SCAN_TILE + e;
+          elt_t v[4], o[4];
+          ring_ld4(base, e, v);
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+#if ACC_SCAN_MODE == 0
+            o[k] = hexcl ? scan_op(p, excl, v[k]) : v[k];
+#else
+            o[k] = (e + k == 0) ? excl : scan_op(p, excl, v[k]);
+#endif
+          }
+#if ACC_SCAN_MODE == 1 && ACC_RIGHT
+          const i64 pos0 = out_row + n - q;
+#elif ACC_RIGHT
+          const i64 pos0 = out_row + n - 1 - q;
+#else
+          const i64 pos0 = out_row + q;
+#endif
+#if ACC_RIGHT
+          elt_t w[4] = {o[3], o[2], o[1], o[0]};
+          OUT0_store4(p, pos0 - 3, w);
+#else
+          OUT0_store4(p, pos0, o);
+#endif
+        }
+#if ACC_SCAN_MODE != 0
+        if (tid == 0 && tt == p.tiles_per_row - 1) {
+          const elt_t tot = scan_op(p, excl, slot_agg[fs]);
+#if ACC_SCAN_MODE == 1
+#if ACC_RIGHT
+          OUT0_store(p, row * (n + 1), tot);
+#else
+          OUT0_store(p, row * (n + 1) + n, tot);
+#endif
+#else
+          OUT1_store(p, row, tot);
+#endif
+        }
+#endif
+      }
+      __syncthreads();                 // everyone is done reading the slot
+      if (tid == 0) fetch(fs);
+      pos_fin += 1;
+    }
+    __syncthreads();
+  }
+  // wait (bounded) for bulk copies still in flight into this CTA's shared memory
+  __syncthreads();
+  if (tid == 0) {
+    for (int s = 0; s < SCAN_SLOTS; ++s) {
+      if (slot_tile[s] < total_tiles && !slot_direct[s] && slot_state[s] == RING_LOADING) {
+        i64 spins = 0;
+        while (!ring_mbar_try_wait(&full_bar[s], slot_parity[s]))
+          if (++spins > p.spin_limit) break;
+      }
+    }
+    __threadfence();
+    if (atomicAdd(exits, 1u) == gridDim.x - 1) { *counter = 0u; *exits = 0u; }
+  }
+}
+#endif
