@@ -868,7 +868,7 @@ Glue build_glue(const Node& n, const std::map<std::string, ArrayInfo>& arrays) {
           for (size_t a = 0; a < nin; ++a) rymax = std::max(rymax, n.st_extent[a][0] / 2);
           def["ST_RYMAX"] = std::to_string(rymax);
           def["ST_H"] = std::to_string(2 * rymax + 1);
-          std::string win_decl, win_params, win_args, issue_all, commit_all, lane_fast;
+          std::string win_decl, win_params, win_args, issue_all, commit_all, lane_fast, issue_fast, all_fast, min_e0;
           for (size_t a = 0; a < nin; ++a) {
             const std::string A = std::to_string(a);
             const int rx = n.st_extent[a][1] / 2;
@@ -885,6 +885,9 @@ Glue build_glue(const Node& n, const std::map<std::string, ArrayInfo>& arrays) {
               wa += ", " + w;
             }
             issue_all += "ST2_issue" + A + "<SLOT>(p, GY, gx0, lf" + A + wa + "); ";
+            issue_fast += "ST2_issue_fast" + A + "<SLOT>(p, GY, gx0" + wa + "); ";
+            all_fast += std::string(all_fast.empty() ? "" : " && ") + "lf" + A;
+            min_e0 = min_e0.empty() ? "(int)p.D" + A + "_e0" : "min(" + min_e0 + ", (int)p.D" + A + "_e0)";
             lane_fast += "const bool lf" + A + " = p.D" + A + "_fast != 0 && (p.D" + A + "_e1 & 3) == 0 && gx0 >= 0 && gx0 + 4 <= (int)p.D" + A + "_e1; ";
             commit_all += "ST2_commit" + A + "<SLOT>(lane" + wa + "); ";
             // which input row supplies global row gy (or -1: evaluate element by element)
@@ -908,6 +911,13 @@ Glue build_glue(const Node& n, const std::map<std::string, ArrayInfo>& arrays) {
             for (size_t i = 0; i < l.size(); ++i)
               b.fns << "  _Pragma(\"unroll\") for (int k = 0; k < 4; ++k) w" << A << "_l" << i << "[SLOT][" << rx << " + k] = own[k].l" << i << ";\n";
             b.fns << "}\n";
+            // the same for a row known to be inside the array, read by a lane on the vector path
+            b.fns << "template <int SLOT> __device__ __forceinline__ void ST2_issue_fast" << A << "(const Params& p, int gy, int gx0" << wp << ") {\n"
+                  << "  " << S << " own[4];\n"
+                  << "  D" << A << "_get4_lin(p, (i64)gy * (i64)(int)" << e1 << " + (i64)gx0, gy, gx0, own);\n";
+            for (size_t i = 0; i < l.size(); ++i)
+              b.fns << "  _Pragma(\"unroll\") for (int k = 0; k < 4; ++k) w" << A << "_l" << i << "[SLOT][" << rx << " + k] = own[k].l" << i << ";\n";
+            b.fns << "}\n";
             b.fns << "template <int SLOT> __device__ __forceinline__ void ST2_commit" << A << "(int lane" << wp << ") {\n  (void)lane;\n";
             for (int j = 1; j <= rx; ++j) {
               for (size_t i = 0; i < l.size(); ++i) {
@@ -924,6 +934,9 @@ Glue build_glue(const Node& n, const std::map<std::string, ArrayInfo>& arrays) {
           def["ST2_ISSUE_ALL(SLOT, GY)"] = issue_all;
           def["ST2_COMMIT_ALL(SLOT)"] = commit_all;
           def["ST2_LANE_FAST_DECL"] = lane_fast;
+          def["ST2_ISSUE_ALL_FAST(SLOT, GY)"] = issue_fast;
+          def["ST2_ALL_LANE_FAST"] = "(" + all_fast + ")";
+          def["ST2_MIN_E0"] = "(" + min_e0 + ")";
           b.fns << "template <int K, int PH> __device__ __forceinline__ " << E << " ST2_apply(const Params& p, ST2_WIN_PARAMS) {\n" << g.out.str()
                 << b.ret_struct(E, r) << "}\n";
         }

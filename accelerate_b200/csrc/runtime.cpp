@@ -155,6 +155,18 @@ std::map<std::string, std::string> scan_variant(const Type& elt) {
   if (const char* e = getenv("ACCELERATE_B200_SCAN_LOOK")) v["SCAN_LOOK"] = e;
   return v;
 }
+// launch shape of the register-window rank-2 stencil kernel (overridable for tuning)
+struct Stencil2dShape { int warps, rows, minb, depth; };
+Stencil2dShape stencil2d_shape() {
+  auto tune = [](const char* name, int dflt) { const char* e = getenv(name); return e && *e ? atoi(e) : dflt; };
+  return {tune("ACCELERATE_B200_ST2_WARPS", 4), tune("ACCELERATE_B200_ST2_ROWS", 64), tune("ACCELERATE_B200_ST2_MIN_BLOCKS", 1),
+          tune("ACCELERATE_B200_ST2_DEPTH", 4)};
+}
+std::map<std::string, std::string> stencil2d_variant() {
+  Stencil2dShape s = stencil2d_shape();
+  return {{"ST2_WARPS", std::to_string(s.warps)}, {"ST2_ROWS", std::to_string(s.rows)}, {"ST2_MIN_BLOCKS", std::to_string(s.minb)},
+          {"ST2_DEPTH", std::to_string(s.depth)}};
+}
 std::map<std::string, std::string> stencil_variant(int rank) {
   StencilTile t = stencil_tile(rank);
   return {{"ST_T0", std::to_string(t.t0)}, {"ST_T1", std::to_string(t.t1)}, {"ST_T2", std::to_string(t.t2)},
@@ -194,7 +206,7 @@ std::vector<std::pair<std::string, std::map<std::string, std::string>>> default_
     }
     case N_STENCIL: case N_STENCIL2:
       v.push_back({"stencil", stencil_variant(n.d[0].rank)});
-      if (n.d[0].rank == 2) v.push_back({"stencil2d", {}});
+      if (n.d[0].rank == 2) v.push_back({"stencil2d", stencil2d_variant()});
       break;
     case N_RESHAPE: break;
   }
@@ -858,14 +870,12 @@ void Program::run(const std::vector<DevArrayP>& inputs, std::vector<DevArrayP>& 
         L.named["vec"] = (o[2] % 4 == 0 && out->aligned16()) ? 1 : 0;
         if (rank == 2 && o[1] < 2000000000 && o[2] < 2000000000 && !getenv("ACCELERATE_B200_STENCIL_SMEM")) {
           // register-window kernel: warp tasks of 128 columns x 64 rows
-          auto tune = [](const char* name, int dflt) { const char* e = getenv(name); return e && *e ? atoi(e) : dflt; };
-          const int warps = tune("ACCELERATE_B200_ST2_WARPS", 4), rows = tune("ACCELERATE_B200_ST2_ROWS", 64);
-          const int minb = tune("ACCELERATE_B200_ST2_MIN_BLOCKS", 1), depth = tune("ACCELERATE_B200_ST2_DEPTH", 4);
+          const Stencil2dShape shp = stencil2d_shape();
+          const int warps = shp.warps, rows = shp.rows;
           const int64_t strips = (o[2] + 119) / 120, rowblocks = (o[1] + rows - 1) / rows;  // 120 output columns per warp
           L.named["tiles1"] = rowblocks;
           L.named["tiles2"] = strips;
-          std::map<std::string, std::string> var = {{"ST2_WARPS", std::to_string(warps)}, {"ST2_ROWS", std::to_string(rows)},
-                                                    {"ST2_MIN_BLOCKS", std::to_string(minb)}, {"ST2_DEPTH", std::to_string(depth)}};
+          const std::map<std::string, std::string> var = stencil2d_variant();
           CompiledKernel& k2 = c.kernel(assemble_source(st.glue, "stencil2d", var), "acc_stencil2d", warps * 32, 0);
           const int64_t ctas = (strips * rowblocks + warps - 1) / warps;
           L.launch(k2, ctas, warps * 32, 0);  // one warp per task; the hardware scheduler balances the tail

@@ -60,6 +60,21 @@
     }                                                                                  \
   }
 
+// The same step for a warp whose rows all lie inside the arrays and whose lanes are all on the
+// vector path: no row redirection, no range checks, one predicated vector store.
+#define ST2_FSTEP(PH)                                                                  \
+  if ((PH) < ST_HW) {                                                                  \
+    const int yy = y + (PH);                                                           \
+    ST2_ISSUE_ALL_FAST(((PH) + ST_HW - 1) % ST_HW, yy + ST_RYMAX + ST2_DEPTH)          \
+    ST2_COMMIT_ALL(((PH) + 2 * ST_RYMAX) % ST_HW)                                      \
+    elt_t o[4];                                                                        \
+    o[0] = ST2_apply<0, (PH) % ST_HW>(p, ST2_WIN_ARGS);                                \
+    o[1] = ST2_apply<1, (PH) % ST_HW>(p, ST2_WIN_ARGS);                                \
+    o[2] = ST2_apply<2, (PH) % ST_HW>(p, ST2_WIN_ARGS);                                \
+    o[3] = ST2_apply<3, (PH) % ST_HW>(p, ST2_WIN_ARGS);                                \
+    if (writer) OUT0_store4(p, (i64)yy * (i64)o2 + (i64)gx0, o);                       \
+  }
+
 extern "C" __global__ void __launch_bounds__(ST2_THREADS, ST2_MIN_BLOCKS) acc_stencil2d(const Params p) {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const i64 ntasks = p.tiles1 * p.tiles2;
@@ -81,7 +96,17 @@ extern "C" __global__ void __launch_bounds__(ST2_THREADS, ST2_MIN_BLOCKS) acc_st
   ST2_PROLOGUE(8) ST2_PROLOGUE(9) ST2_PROLOGUE(10) ST2_PROLOGUE(11) ST2_PROLOGUE(12) ST2_PROLOGUE(13) ST2_PROLOGUE(14) ST2_PROLOGUE(15)
   ST2_PROLOGUE_COMMIT(0) ST2_PROLOGUE_COMMIT(1) ST2_PROLOGUE_COMMIT(2) ST2_PROLOGUE_COMMIT(3)
   ST2_PROLOGUE_COMMIT(4) ST2_PROLOGUE_COMMIT(5) ST2_PROLOGUE_COMMIT(6) ST2_PROLOGUE_COMMIT(7)
-  for (int y = y0; y < y1; y += ST_HW) {
+  int y = y0;
+  // rows y0-ry .. y1+ry+depth-1 inside every input, every lane on the vector path (interior strips)
+  const bool interior = __all_sync(ACC_FULL_MASK, ST2_ALL_LANE_FAST && (st_vec || !writer)) && y0 - ST_RYMAX >= 0 &&
+                        y1 + ST_RYMAX + ST2_DEPTH <= ST2_MIN_E0;
+  if (interior) {
+    for (; y + ST_HW <= y1; y += ST_HW) {
+      ST2_FSTEP(0) ST2_FSTEP(1) ST2_FSTEP(2) ST2_FSTEP(3) ST2_FSTEP(4) ST2_FSTEP(5) ST2_FSTEP(6) ST2_FSTEP(7)
+      ST2_FSTEP(8) ST2_FSTEP(9) ST2_FSTEP(10) ST2_FSTEP(11) ST2_FSTEP(12) ST2_FSTEP(13) ST2_FSTEP(14) ST2_FSTEP(15) ST2_FSTEP(16)
+    }
+  }
+  for (; y < y1; y += ST_HW) {
     ST2_STEP(0) ST2_STEP(1) ST2_STEP(2) ST2_STEP(3) ST2_STEP(4) ST2_STEP(5) ST2_STEP(6) ST2_STEP(7)
     ST2_STEP(8) ST2_STEP(9) ST2_STEP(10) ST2_STEP(11) ST2_STEP(12) ST2_STEP(13) ST2_STEP(14) ST2_STEP(15) ST2_STEP(16)
   }
