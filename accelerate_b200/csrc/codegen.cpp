@@ -956,7 +956,7 @@ Glue build_glue(const Node& n, const std::map<std::string, ArrayInfo>& arrays) {
     case N_FOLD: named = {"n", "rows", "row", "vec", "scratch", "flags", "counter"}; break;
     case N_FOLDSEG: named = {"segs", "rows", "vec", "err"}; break;
     case N_SCAN: case N_SCAN2:
-      named = {"n", "rows", "tiles_per_row", "total_tiles", "in_vec", "out_vec", "status", "agg", "incl", "counter", "epoch", "err", "spin_limit", "trace"};
+      named = {"n", "rows", "tiles_per_row", "total_tiles", "in_vec", "out_vec", "status", "agg", "incl", "gstatus", "groups_per_row", "counter", "epoch", "err", "spin_limit", "trace"};
       break;
     case N_PERMUTE: named = {"n", "vec", "out_n", "priv", "locks", "err", "spin_limit"}; break;
     case N_STENCIL: case N_STENCIL2: named = {"o0", "o1", "o2", "tiles1", "tiles2", "vec"}; break;

@@ -137,6 +137,8 @@ StencilTile stencil_tile(int rank) {
   return {4, 8, 64, 256};
 }
 // resident CTAs per SM the scan kernel is compiled for (register budget)
+constexpr int SCAN_DESC_STRIDE_DEFAULT = 16;
+constexpr int SCAN_BACKOFF_DEFAULT = 0;
 // elements per thread (4 per round): large tiles keep the look-back chain off the critical path
 int scan_rounds(const Type& elt) {
   size_t bytes = 0;
@@ -154,6 +156,17 @@ std::map<std::string, std::string> scan_variant(const Type& elt) {
   std::map<std::string, std::string> v = {{"SCAN_MIN_BLOCKS", minb}, {"SCAN_ROUNDS", std::to_string(rounds)}};
   if (const char* e = getenv("ACCELERATE_B200_SCAN_LOOK")) v["SCAN_LOOK"] = e;
   return v;
+}
+// Spacing of look-back descriptors (in descriptors) and pause after an unsuccessful poll.
+// Spread descriptors cost total_tiles * 16 * stride bytes of scratch, so long lists of tiles stay dense.
+int scan_desc_stride(int64_t total_tiles) {
+  if (const char* e = getenv("ACCELERATE_B200_SCAN_DESC_STRIDE")) return std::max(1, atoi(e));
+  return total_tiles <= 65536 ? SCAN_DESC_STRIDE_DEFAULT : 1;
+}
+void scan_poll_variant(std::map<std::string, std::string>& v, int64_t total_tiles) {
+  v["SCAN_DESC_STRIDE"] = std::to_string(scan_desc_stride(total_tiles));
+  const char* e = getenv("ACCELERATE_B200_SCAN_BACKOFF");
+  v["SCAN_BACKOFF_NS"] = e && *e ? std::string(e) : std::to_string(SCAN_BACKOFF_DEFAULT);
 }
 // launch shape of the register-window rank-2 stencil kernel (overridable for tuning)
 struct Stencil2dShape { int warps, rows, minb, depth; };
@@ -706,7 +719,7 @@ void Program::run(const std::vector<DevArrayP>& inputs, std::vector<DevArrayP>& 
         if (mode == 1) out_vec = right ? ((m + 1) % 4 == 0) : (rows == 1 || (m + 1) % 4 == 0);
         else out_vec = right ? (m % 4 == 0) : (rows == 1 || m % 4 == 0);
         const size_t sb = struct_bytes(n.elt);
-        const size_t status_bytes = ((size_t)total_tiles * 16 + 255) / 256 * 256;  // packed descriptors take up to 16 bytes
+        const size_t status_bytes = ((size_t)total_tiles * 16 * scan_desc_stride(total_tiles) + 255) / 256 * 256;  // packed descriptors take up to 16 bytes
         const size_t val_bytes = ((size_t)total_tiles * sb + 255) / 256 * 256;
         char* base = (char*)c.scan_descriptors(status_bytes + 2 * val_bytes);
         L.named["n"] = m;
@@ -740,15 +753,39 @@ void Program::run(const std::vector<DevArrayP>& inputs, std::vector<DevArrayP>& 
             std::map<std::string, std::string> var = {{"SCAN_RING", "1"}, {"SCAN_ROUNDS", std::to_string(rounds)}, {"SCAN_SLOTS", std::to_string(slots)},
                                                       {"SCAN_MIN_BLOCKS", std::to_string(minb)}};
             if (const char* e = getenv("ACCELERATE_B200_SCAN_LOOK")) var["SCAN_LOOK"] = e;
-            const size_t r_status = ((size_t)r_total * 16 + 255) / 256 * 256;
-            char* rbase = (char*)c.scan_descriptors(r_status);
+            scan_poll_variant(var, r_total);
+            const int dstride = scan_desc_stride(r_total);
+            const size_t r_status = ((size_t)r_total * 16 * dstride + 255) / 256 * 256;
+            const int look = getenv("ACCELERATE_B200_SCAN_LOOK") ? atoi(getenv("ACCELERATE_B200_SCAN_LOOK")) : 2;
+            const int64_t groups_per_row = (r_tiles_per_row + 32 * look - 1) / (32 * look);
+            const size_t g_status = ((size_t)(rows * groups_per_row) * 16 * dstride + 255) / 256 * 256;
+            char* rbase = (char*)c.scan_descriptors(r_status + g_status);
+            L.named["gstatus"] = (int64_t)(uintptr_t)(rbase + r_status);
+            L.named["groups_per_row"] = groups_per_row;
             L.named["tiles_per_row"] = r_tiles_per_row;
             L.named["total_tiles"] = r_total;
             L.named["status"] = (int64_t)(uintptr_t)rbase;
             L.named["epoch"] = c.scan_epoch;
-            CompiledKernel& k = c.kernel(assemble_source(st.glue, "scan", var), "acc_scan_ring", 256, smem);
+            std::shared_ptr<Buffer> tbuf;
+            const char* tpath = getenv("ACCELERATE_B200_SCAN_TRACE");
+            if (tpath) {
+              var["SCAN_TRACE"] = "1";
+              tbuf = c.alloc((size_t)r_total * 64);
+              c.check(cudaMemsetAsync(tbuf->ptr, 0, tbuf->bytes, c.stream), "cudaMemsetAsync");
+              L.named["trace"] = (int64_t)(uintptr_t)tbuf->ptr;
+            }
+            const int lbw = std::max(1, tune("ACCELERATE_B200_RING_LB_WARPS", 1));
+            var["SCAN_LB_WARPS"] = std::to_string(lbw);
+            const int threads = 256 + 32 * lbw;     // 8 worker warps + the look-back warps
+            CompiledKernel& k = c.kernel(assemble_source(st.glue, "scan", var), "acc_scan_ring", threads, smem);
             const int64_t grid = std::min<int64_t>(r_total, (int64_t)c.sm_count * k.max_blocks_per_sm);
-            L.launch(k, grid, 256, smem);
+            L.launch(k, grid, threads, smem);
+            if (tpath) {
+              std::vector<uint64_t> host((size_t)r_total * 8);
+              c.check(cudaMemcpyAsync(host.data(), tbuf->ptr, tbuf->bytes, cudaMemcpyDeviceToHost, c.stream), "cudaMemcpyAsync");
+              c.check(cudaStreamSynchronize(c.stream), "cudaStreamSynchronize");
+              if (FILE* f = fopen(tpath, "wb")) { fwrite(host.data(), 8, host.size(), f); fclose(f); }
+            }
             break;
           }
         }
@@ -776,6 +813,7 @@ void Program::run(const std::vector<DevArrayP>& inputs, std::vector<DevArrayP>& 
         if (const char* tpath = getenv("ACCELERATE_B200_SCAN_TRACE")) {
           // diagnostic: per-tile phase timestamps written to a file (8 x u64 per tile)
           auto var = scan_variant(n.elt);
+          scan_poll_variant(var, total_tiles);
           var["SCAN_TRACE"] = "1";
           auto tbuf = c.alloc((size_t)total_tiles * 64);
           c.check(cudaMemsetAsync(tbuf->ptr, 0, tbuf->bytes, c.stream), "cudaMemsetAsync");
@@ -788,7 +826,9 @@ void Program::run(const std::vector<DevArrayP>& inputs, std::vector<DevArrayP>& 
           if (FILE* f = fopen(tpath, "wb")) { fwrite(host.data(), 8, host.size(), f); fclose(f); }
           break;
         }
-        CompiledKernel& k = c.kernel(assemble_source(st.glue, "scan", scan_variant(n.elt)), "acc_scan", 256, 0);
+        auto svar = scan_variant(n.elt);
+        scan_poll_variant(svar, total_tiles);
+        CompiledKernel& k = c.kernel(assemble_source(st.glue, "scan", svar), "acc_scan", 256, 0);
         L.launch(k, total_tiles, 256, 0);
         break;
       }

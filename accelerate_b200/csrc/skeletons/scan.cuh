@@ -63,9 +63,32 @@ __device__ __forceinline__ u64 scan_now() { u64 t; asm volatile("mov.u64 %0, %%g
 #ifndef SCAN_PACKED
 #define SCAN_PACKED 0
 #endif
+// Barrier over the SCAN_THREADS threads that process tiles.  The ring kernel runs one extra
+// warp (the look-back warp) that must not take part, so it uses a named barrier instead.
+#if defined(SCAN_RING) && SCAN_RING
+#define SCAN_SYNC() asm volatile("bar.sync 1, %0;" ::"n"(SCAN_THREADS) : "memory")
+#else
+#define SCAN_SYNC() __syncthreads()
+#endif
 #ifndef SCAN_MIN_BLOCKS
 #define SCAN_MIN_BLOCKS 1
 #endif
+// Descriptors of neighbouring tiles are polled by every CTA working near the front of the scan.
+// Packed densely they share a few cache lines, i.e. one L2 slice serves all those polls; spread
+// SCAN_DESC_STRIDE descriptors apart, they fall into different lines and slices.
+#ifndef SCAN_DESC_STRIDE
+#define SCAN_DESC_STRIDE 1
+#endif
+// pause after a look-back poll that found a predecessor not ready (polling harder only slows
+// the stores being waited for)
+#ifndef SCAN_BACKOFF_NS
+#define SCAN_BACKOFF_NS 0
+#endif
+__device__ __forceinline__ void scan_backoff() {
+#if SCAN_BACKOFF_NS > 0
+  __nanosleep(SCAN_BACKOFF_NS);
+#endif
+}
 #if SCAN_PACKED
 #if SCAN_T_BYTES <= 4
 // [63:32] status, [31:0] value bits
@@ -73,11 +96,11 @@ __device__ __forceinline__ void scan_desc_store(i64 base, i64 idx, u32 status, S
   u32 bits = 0;
   memcpy(&bits, &v, sizeof(SCAN_T));
   const u64 w = ((u64)status << 32) | bits;
-  asm volatile("st.relaxed.gpu.global.u64 [%0], %1;" ::"l"(reinterpret_cast<u64*>(base) + idx), "l"(w) : "memory");
+  asm volatile("st.relaxed.gpu.global.u64 [%0], %1;" ::"l"(reinterpret_cast<u64*>(base) + idx * SCAN_DESC_STRIDE), "l"(w) : "memory");
 }
 __device__ __forceinline__ u32 scan_desc_load(i64 base, i64 idx, SCAN_T& v) {
   u64 w;
-  asm volatile("ld.relaxed.gpu.global.u64 %0, [%1];" : "=l"(w) : "l"(reinterpret_cast<const u64*>(base) + idx) : "memory");
+  asm volatile("ld.relaxed.gpu.global.u64 %0, [%1];" : "=l"(w) : "l"(reinterpret_cast<const u64*>(base) + idx * SCAN_DESC_STRIDE) : "memory");
   const u32 bits = (u32)w;
   memcpy(&v, &bits, sizeof(SCAN_T));
   return (u32)(w >> 32);
@@ -87,12 +110,12 @@ __device__ __forceinline__ u32 scan_desc_load(i64 base, i64 idx, SCAN_T& v) {
 __device__ __forceinline__ void scan_desc_store(i64 base, i64 idx, u32 status, SCAN_T v) {
   u64 bits = 0;
   memcpy(&bits, &v, sizeof(SCAN_T));
-  asm volatile("st.relaxed.gpu.global.v2.u64 [%0], {%1, %2};" ::"l"(reinterpret_cast<ulonglong2*>(base) + idx), "l"(bits), "l"((u64)status)
+  asm volatile("st.relaxed.gpu.global.v2.u64 [%0], {%1, %2};" ::"l"(reinterpret_cast<ulonglong2*>(base) + idx * SCAN_DESC_STRIDE), "l"(bits), "l"((u64)status)
                : "memory");
 }
 __device__ __forceinline__ u32 scan_desc_load(i64 base, i64 idx, SCAN_T& v) {
   u64 bits, st;
-  asm volatile("ld.relaxed.gpu.global.v2.u64 {%0, %1}, [%2];" : "=l"(bits), "=l"(st) : "l"(reinterpret_cast<const ulonglong2*>(base) + idx) : "memory");
+  asm volatile("ld.relaxed.gpu.global.v2.u64 {%0, %1}, [%2];" : "=l"(bits), "=l"(st) : "l"(reinterpret_cast<const ulonglong2*>(base) + idx * SCAN_DESC_STRIDE) : "memory");
   memcpy(&v, &bits, sizeof(SCAN_T));
   return (u32)st;
 }
@@ -198,7 +221,7 @@ __device__ __forceinline__ void scan_tile_body(const Params& p, const i64 T, con
   }
   // carry now holds the warp's total
   if (lane == 0) { sm_v[warp] = carry; sm_h[warp] = hcarry; }
-  __syncthreads();
+  SCAN_SYNC();
   SCAN_MARK(T, 2);   // local scans done
 
   // ---- tile aggregate, look-back (warp 0), tile exclusive prefix ---------------
@@ -263,6 +286,7 @@ __device__ __forceinline__ void scan_tile_body(const Params& p, const i64 T, con
           }
           if (all) break;
           if (spins > p.spin_limit) { failed = 1; break; }
+          scan_backoff();
         }
         failed = __any_sync(ACC_FULL_MASK, failed);
         if (failed) break;
@@ -337,7 +361,7 @@ __device__ __forceinline__ void scan_tile_body(const Params& p, const i64 T, con
       sm_flag[1] = failed;
     }
   }
-  __syncthreads();
+  SCAN_SYNC();
   SCAN_MARK(T, 3);   // exclusive prefix known
   if (sm_flag[1]) return;
 
@@ -639,6 +663,10 @@ extern "C" __global__ void __launch_bounds__(SCAN_THREADS, SCAN_MIN_BLOCKS) acc_
 #define SCAN_SLOTS 6
 #endif
 #define RING_SLOT_BYTES (SCAN_TILE * SCAN_T_BYTES)
+#define RING_GROUP (32 * SCAN_LOOK)
+#define RING_PH_OWN 0
+#define RING_PH_GROUPS 1
+#define RING_PH_COMPUTE 2
 #define RING_LOADING 0
 #define RING_SCANNED 1
 #define RING_RESOLVED 2
@@ -690,18 +718,31 @@ __device__ __forceinline__ void ring_ld4(const unsigned char* base, int e, elt_t
 
 extern __shared__ __align__(128) unsigned char scan_ring_smem[];
 
-extern "C" __global__ void __launch_bounds__(SCAN_THREADS, SCAN_MIN_BLOCKS) acc_scan_ring(const Params p) {
+template <class T> __device__ __forceinline__ T ring_ldv(const T* p) { return *reinterpret_cast<const volatile T*>(p); }
+template <class T> __device__ __forceinline__ void ring_stv(T* p, T v) { *reinterpret_cast<volatile T*>(p) = v; }
+
+// Threads 0 .. SCAN_THREADS-1 (the workers) reduce arriving tiles and scan resolved tiles out of
+// shared memory; SCAN_LB_WARPS further warps only run look-backs (ring position r is handled by
+// warp r mod SCAN_LB_WARPS), so the look-back latency never stalls the workers.
+#ifndef SCAN_LB_WARPS
+#define SCAN_LB_WARPS 1
+#endif
+#define RING_THREADS (SCAN_THREADS + 32 * SCAN_LB_WARPS)
+#define RING_ACT_SCAN 1
+#define RING_ACT_FIN 2
+#define RING_ACT_EXIT 4
+
+extern "C" __global__ void __launch_bounds__(RING_THREADS, SCAN_MIN_BLOCKS) acc_scan_ring(const Params p) {
   __shared__ elt_t sm_v[SCAN_WARPS];
   __shared__ int sm_h[SCAN_WARPS];
   __shared__ elt_t sm_excl1;
   __shared__ int sm_flag1[2];
   __shared__ __align__(8) u64 full_bar[SCAN_SLOTS];
-  __shared__ i64 slot_tile[SCAN_SLOTS];
+  __shared__ i64 slot_tile[SCAN_SLOTS], slot_pos[SCAN_SLOTS];
   __shared__ u32 slot_parity[SCAN_SLOTS], slot_uses[SCAN_SLOTS];
   __shared__ int slot_direct[SCAN_SLOTS], slot_state[SCAN_SLOTS], slot_hexcl[SCAN_SLOTS];
   __shared__ elt_t slot_agg[SCAN_SLOTS], slot_excl[SCAN_SLOTS];
-  __shared__ i64 sh_resolved;
-  __shared__ int ctl[4];      // [0] scan a slot, [1] finish a slot, [2] leave, [3] a wait gave up
+  __shared__ int ctl_act, sh_fail;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const i64 n = p.n;
   const i64 total_tiles = p.total_tiles;
@@ -709,80 +750,142 @@ extern "C" __global__ void __launch_bounds__(SCAN_THREADS, SCAN_MIN_BLOCKS) acc_
   unsigned* counter = reinterpret_cast<unsigned*>(p.counter);
   unsigned* exits = counter + 1;
 
-  // thread 0: next ticket into slot s; full tiles are requested from the copy engine
-  auto fetch = [&](int s) {
+  // worker thread 0: next ticket into slot s for ring position `pos`
+  auto fetch = [&](int s, i64 pos) {
     const i64 T = (i64)atomicAdd(counter, 1u);
     slot_tile[s] = T;
     slot_direct[s] = 1;
     slot_state[s] = RING_LOADING;
-    if (T >= total_tiles) return;
-    const i64 row = T / p.tiles_per_row;
-    const i64 tt = T - row * p.tiles_per_row;
-    const i64 q0 = tt * SCAN_TILE;
-    if (q0 + SCAN_TILE > n) return;
-    slot_direct[s] = 0;
-    slot_parity[s] = slot_uses[s] & 1u;
-    slot_uses[s] += 1;
+    if (T < total_tiles) {
+      const i64 row = T / p.tiles_per_row;
+      const i64 tt = T - row * p.tiles_per_row;
+      const i64 q0 = tt * SCAN_TILE;
+      if (q0 + SCAN_TILE <= n) {
+        slot_direct[s] = 0;
+        slot_parity[s] = slot_uses[s] & 1u;
+        slot_uses[s] += 1;
 #if ACC_RIGHT
-    const i64 src = row * n + (n - q0 - SCAN_TILE);
+        const i64 src = row * n + (n - q0 - SCAN_TILE);
 #else
-    const i64 src = row * n + q0;
+        const i64 src = row * n + q0;
 #endif
-    unsigned char* base = scan_ring_smem + (size_t)s * RING_SLOT_BYTES;
-    ring_mbar_expect(&full_bar[s], (u32)RING_SLOT_BYTES);
-    D0_BULK_ISSUE(base, &full_bar[s], src)
+        unsigned char* base = scan_ring_smem + (size_t)s * RING_SLOT_BYTES;
+        SCAN_MARK(T, 0);   // requested
+        ring_mbar_expect(&full_bar[s], (u32)RING_SLOT_BYTES);
+        D0_BULK_ISSUE(base, &full_bar[s], src)
+      }
+    }
+    __threadfence_block();
+    ring_stv(&slot_pos[s], pos);          // the look-back warp may now look at the slot
   };
 
   if (tid == 0) {
-    for (int s = 0; s < SCAN_SLOTS; ++s) { ring_mbar_init(&full_bar[s], 1); slot_uses[s] = 0; }
+    for (int s = 0; s < SCAN_SLOTS; ++s) { ring_mbar_init(&full_bar[s], 1); slot_uses[s] = 0; slot_pos[s] = -1; }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    sh_resolved = 0;
+    ctl_act = 0;
+    sh_fail = 0;
   }
   __syncthreads();
   if (tid == 0)
-    for (int s = 0; s < SCAN_SLOTS; ++s) fetch(s);
+    for (int s = 0; s < SCAN_SLOTS; ++s) fetch(s, s);
   __syncthreads();
 
-  i64 pos_scan = 0, pos_fin = 0;        // ring positions, identical in every thread
-  // look-back state of warp 0 for ring position `resolved`
-  i64 resolved = 0;
-  bool lb_started = false;
-  i64 lb_look = 0, lb_polls = 0;
-  elt_t lb_excl;
-  bool lb_hexcl = false;
-  // a requested, not yet inspected window of descriptors (SCAN_LOOK per lane)
-  bool pend = false;
-  i64 pend_row_first = 0;
-  u32 pst[SCAN_LOOK];
-  elt_t pv[SCAN_LOOK];
-  bool pin[SCAN_LOOK];
-
-  for (;;) {
-    if (warp == 0) {
-      int do_scan = 0, do_exit = 0, fail = 0;
-      const int ss = (int)(pos_scan % SCAN_SLOTS);
-      const bool has_slot = pos_scan < pos_fin + SCAN_SLOTS;
-      const bool scan_work = has_slot && slot_tile[ss] < total_tiles;
-      if (scan_work) {
-        int arrived = slot_direct[ss];
-        if (!arrived && lane == 0) arrived = ring_mbar_try_wait(&full_bar[ss], slot_parity[ss]) ? 1 : 0;
-        do_scan = __shfl_sync(ACC_FULL_MASK, arrived, 0);
+  if (warp >= SCAN_WARPS) {
+    // ================= look-back warps =================================================
+    // Hierarchical walk: tiles of a row are grouped by RING_GROUP.  Phase OWN reads the earlier
+    // tiles of the own group; phase GROUPS reads 32 group descriptors per step (aggregate or
+    // inclusive prefix of a whole group); phase COMPUTE summarises a group nobody has summarised
+    // yet from its tile descriptors and publishes the summary for every later walker.
+    int lb_failed = 0;
+    for (i64 r = warp - SCAN_WARPS;; r += SCAN_LB_WARPS) {
+      const int s = (int)(r % SCAN_SLOTS);
+      i64 spins = 0;
+      int failed = 0;
+      while (ring_ldv(&slot_pos[s]) != r) {
+        if (++spins > p.spin_limit || ring_ldv(&sh_fail)) { failed = 1; break; }
+        __nanosleep(40);                             // leave the issue slots to the workers
       }
-      // (1) consume the descriptor window requested at the end of the previous iteration: its
-      //     round trip to L2 overlapped with that iteration's scan / finish work
-      if (pend) {
-        pend = false;
-        const int rs = (int)(resolved % SCAN_SLOTS);
-        const i64 T = slot_tile[rs];
-        bool all = true;
+      if (failed) { lb_failed = 1; break; }
+      __threadfence_block();
+      const i64 T = slot_tile[s];
+      if (T >= total_tiles) break;
+      int st0;
+      spins = 0;
+      while ((st0 = ring_ldv(&slot_state[s])) < RING_SCANNED) {
+        if (++spins > p.spin_limit || ring_ldv(&sh_fail)) { failed = 1; break; }
+        __nanosleep(40);
+      }
+      if (failed) { lb_failed = 1; break; }
+      __threadfence_block();
+      if (st0 >= RING_RESOLVED) continue;           // first tile of a row / partial tile: nothing to do
+      const i64 row = T / p.tiles_per_row;
+      const i64 tt = T - row * p.tiles_per_row;
+      const i64 row_first = T - tt;
+      const i64 gid = tt / RING_GROUP;
+      const i64 group_base = row * p.groups_per_row;
+      elt_t excl;
+      bool hexcl = false;
+      int phase = (tt % RING_GROUP == 0) ? RING_PH_GROUPS : RING_PH_OWN;
+      i64 g = gid - 1;
+      i64 polls = 0;
+      int steps = 0;
+      bool done = false;
+      while (!done) {
+        ++steps;
+        if (phase == RING_PH_GROUPS) {
+          const i64 gi = g - lane;
+          const bool in = gi >= 0;
+          u32 st = 0;
+          elt_t v;
+          if (in) st = scan_desc_load(p.gstatus, group_base + gi, v.l0);
+          const bool ready = in && (st >> 2) == epoch;
+          const unsigned pm = __ballot_sync(ACC_FULL_MASK, ready && (st & 3u) == SCAN_ST_PREFIX);
+          const unsigned em = __ballot_sync(ACC_FULL_MASK, in && !ready);
+          const int lp = pm ? (__ffs((int)pm) - 1) : 32;
+          const int lm = em ? (__ffs((int)em) - 1) : 32;
+          elt_t c = v;
+          bool hc = in && (lp < lm ? lane <= lp : lane < lm);
 #pragma unroll
-        for (int j = 0; j < SCAN_LOOK; ++j)
-          if (pin[j]) all = all && ((pst[j] >> 2) == epoch);
-        if (__all_sync(ACC_FULL_MASK, all)) {
+          for (int d = 1; d < 32; d <<= 1) {
+            const elt_t o = acc_shfl_down(c, d);
+            const int oh = __shfl_down_sync(ACC_FULL_MASK, (int)hc, d);
+            if (lane + d < 32) scan_join_front(p, o, oh != 0, c, hc);
+          }
+          scan_join_front(p, c, hc, excl, hexcl);           // meaningful in lane 0
+          if (lp < lm) done = true;
+          else if (lm < 32) { g -= lm; phase = RING_PH_COMPUTE; }
+          else { g -= 32; if (g < 0) done = true; }         // (group 0 is never a plain aggregate: not reached)
+        } else {
+          // tiles hi, hi-1, ..., lo of the row (at most RING_GROUP = 32 * SCAN_LOOK of them)
+          const i64 hi = phase == RING_PH_OWN ? tt - 1 : g * RING_GROUP + RING_GROUP - 1;
+          const i64 lo = phase == RING_PH_OWN ? gid * RING_GROUP : g * RING_GROUP;
+          u32 st[SCAN_LOOK];
+          elt_t v[SCAN_LOOK];
+          bool in[SCAN_LOOK], ready[SCAN_LOOK];
+#pragma unroll
+          for (int j = 0; j < SCAN_LOOK; ++j) {
+            in[j] = hi - (i64)(SCAN_LOOK * lane + j) >= lo;
+            ready[j] = !in[j];
+            st[j] = 0;
+          }
+          for (;;) {                                  // entries found ready are not read again
+            bool all = true;
+#pragma unroll
+            for (int j = 0; j < SCAN_LOOK; ++j)
+              if (!ready[j]) {
+                st[j] = scan_desc_load(p.status, row_first + hi - (i64)(SCAN_LOOK * lane + j), v[j].l0);
+                ready[j] = (st[j] >> 2) == epoch;
+                all = all && ready[j];
+              }
+            if (__all_sync(ACC_FULL_MASK, all)) break;
+            if (++polls > p.spin_limit || ring_ldv(&sh_fail)) { failed = 1; break; }
+            scan_backoff();
+          }
+          if (failed) break;
           int jp = SCAN_LOOK;
 #pragma unroll
           for (int j = SCAN_LOOK - 1; j >= 0; --j)
-            if (pin[j] && (pst[j] & 3u) == SCAN_ST_PREFIX) jp = j;
+            if (in[j] && (st[j] & 3u) == SCAN_ST_PREFIX) jp = j;
           const unsigned pm = __ballot_sync(ACC_FULL_MASK, jp < SCAN_LOOK);
           const int lstar = pm ? (__ffs((int)pm) - 1) : 32;
           const int last = lane < lstar ? SCAN_LOOK - 1 : (lane == lstar ? jp : -1);
@@ -790,237 +893,256 @@ extern "C" __global__ void __launch_bounds__(SCAN_THREADS, SCAN_MIN_BLOCKS) acc_
           bool hc = false;
 #pragma unroll
           for (int j = SCAN_LOOK - 1; j >= 0; --j)
-            if (pin[j] && j <= last) scan_join(p, c, hc, pv[j], true);
+            if (in[j] && j <= last) scan_join(p, c, hc, v[j], true);
 #pragma unroll
           for (int d = 1; d < 32; d <<= 1) {
             const elt_t o = acc_shfl_down(c, d);
             const int oh = __shfl_down_sync(ACC_FULL_MASK, (int)hc, d);
             if (lane + d < 32) scan_join_front(p, o, oh != 0, c, hc);
           }
-          scan_join_front(p, c, hc, lb_excl, lb_hexcl);     // meaningful in lane 0
-          if (pm != 0 || lb_look - 32 * SCAN_LOOK < pend_row_first) {
-            if (lane == 0) {
-              elt_t inc = lb_excl;
-              bool hinc = lb_hexcl;
-              scan_join(p, inc, hinc, slot_agg[rs], true);
-              scan_desc_store(p.status, T, (epoch << 2) | SCAN_ST_PREFIX, inc.l0);
-              slot_excl[rs] = lb_excl;
-              slot_hexcl[rs] = lb_hexcl ? 1 : 0;
-              slot_state[rs] = RING_RESOLVED;
-            }
-            resolved += 1;
-            lb_started = false;
-          } else {
-            lb_look -= 32 * SCAN_LOOK;
+          if (phase == RING_PH_COMPUTE && lane == 0 && hc)     // summary of group g, for every later walker
+            scan_desc_store(p.gstatus, group_base + g, (epoch << 2) | (pm ? SCAN_ST_PREFIX : SCAN_ST_AGG), c.l0);
+          scan_join_front(p, c, hc, excl, hexcl);             // meaningful in lane 0
+          if (pm != 0) done = true;
+          else {
+            g = (phase == RING_PH_OWN) ? gid - 1 : g - 1;
+            phase = RING_PH_GROUPS;
+            if (g < 0) done = true;                           // start of the row reached
           }
-        } else if (++lb_polls > p.spin_limit) {
-          fail = 1;
         }
       }
-      // (2) positions whose prefix was known when they were scanned (first tile of a row, partial tiles)
-      for (int guard = 0; guard < SCAN_SLOTS && resolved < pos_scan; ++guard) {
-        if (slot_state[(int)(resolved % SCAN_SLOTS)] < RING_RESOLVED) break;
-        resolved += 1;
-        lb_started = false;
-      }
-      // (3) request the next window for the oldest unresolved, already scanned position
-      if (resolved < pos_scan && !fail) {
-        const int rs = (int)(resolved % SCAN_SLOTS);
-        const i64 T = slot_tile[rs];
-        const i64 row = T / p.tiles_per_row;
-        const i64 tt = T - row * p.tiles_per_row;
-        pend_row_first = T - tt;
-        if (!lb_started) { lb_started = true; lb_look = T - 1; lb_hexcl = false; lb_polls = 0; }
-#pragma unroll
-        for (int j = 0; j < SCAN_LOOK; ++j) {
-          const i64 idx = lb_look - (i64)(SCAN_LOOK * lane + j);
-          pin[j] = idx >= pend_row_first;
-          pst[j] = 0;
-          if (pin[j]) pst[j] = scan_desc_load(p.status, idx, pv[j].l0);
-        }
-        pend = true;
-      }
-      const int fs = (int)(pos_fin % SCAN_SLOTS);
-      do_exit = (pos_fin == pos_scan && !scan_work) ? 1 : 0;
-      (void)fs;
+      if (failed) { lb_failed = 1; break; }
       if (lane == 0) {
-        ctl[0] = do_scan;
-        ctl[2] = do_exit;
-        ctl[3] = fail;
-        sh_resolved = resolved;
+        elt_t inc = excl;
+        bool hinc = hexcl;
+        scan_join(p, inc, hinc, slot_agg[s], true);
+        scan_desc_store(p.status, T, (epoch << 2) | SCAN_ST_PREFIX, inc.l0);
+        if ((tt % RING_GROUP) == RING_GROUP - 1)              // also the inclusive prefix of its whole group
+          scan_desc_store(p.gstatus, group_base + gid, (epoch << 2) | SCAN_ST_PREFIX, inc.l0);
+        slot_excl[s] = excl;
+        slot_hexcl[s] = hexcl ? 1 : 0;
+#if SCAN_TRACE
+        reinterpret_cast<u64*>(p.trace)[T * 8 + 3] = scan_now();   // prefix known
+        reinterpret_cast<u64*>(p.trace)[T * 8 + 6] = (u64)steps;
+#endif
+        __threadfence_block();
+        ring_stv(&slot_state[s], RING_RESOLVED);
       }
+      __syncwarp();
     }
-    __syncthreads();
-    const i64 res_now = sh_resolved;
-    if (ctl[3]) { if (tid == 0) acc_fail(p.err, 110 /* ETIMEDOUT */); break; }
-    if (ctl[2]) break;
-
-    if (ctl[0]) {
-      // ---- local scan of the slot at pos_scan, in place ---------------------------------------
-      const int ss = (int)(pos_scan % SCAN_SLOTS);
-      const i64 T = slot_tile[ss];
-      const i64 row = T / p.tiles_per_row;
-      const i64 tt = T - row * p.tiles_per_row;
-      if (slot_direct[ss]) {
-        scan_tile<false>(p, T, row, tt, sm_v, sm_h, &sm_excl1, sm_flag1);    // partial tile: start to finish
-        __syncthreads();
-        if (tid == 0) slot_state[ss] = RING_DONE;
-      } else {
-        unsigned char* base = scan_ring_smem + (size_t)ss * RING_SLOT_BYTES;
-        const i64 warp_q0 = tt * SCAN_TILE + (i64)warp * SCAN_WARP_ELEMS;
-        elt_t item[SCAN_ROUNDS][4];
-#pragma unroll
-        for (int r = 0; r < SCAN_ROUNDS; ++r) {
-          const int e = warp * SCAN_WARP_ELEMS + r * 128 + lane * 4;
-          const i64 q = warp_q0 + r * 128 + lane * 4;
-#if ACC_RIGHT
-          elt_t t4[4];
-          D0_get4_sm(p, row, n - 4 - q, base, SCAN_TILE - 4 - e, t4);
-#pragma unroll
-          for (int k = 0; k < 4; ++k) item[r][k] = t4[3 - k];
-#else
-          D0_get4_sm(p, row, q, base, e, item[r]);
-#endif
-#pragma unroll
-          for (int k = 1; k < 4; ++k) item[r][k] = scan_op(p, item[r][k - 1], item[r][k]);
-        }
-        elt_t lane_excl[SCAN_ROUNDS], round_carry[SCAN_ROUNDS];
-        elt_t carry;
-        bool hcarry = false;
-#pragma unroll
-        for (int r = 0; r < SCAN_ROUNDS; ++r) {
-          elt_t v = item[r][3];
-#pragma unroll
-          for (int d = 1; d < 32; d <<= 1) {
-            const elt_t o = acc_shfl_up(v, d);
-            if (lane >= d) v = scan_op(p, o, v);
-          }
-          lane_excl[r] = acc_shfl_up(v, 1);
-          const elt_t rt = acc_shfl_idx(v, 31);
-          round_carry[r] = carry;
-          if (r == 0) { carry = rt; hcarry = true; }
-          else carry = scan_op(p, carry, rt);
-        }
-        (void)hcarry;
-        if (lane == 0) sm_v[warp] = carry;
-        __syncthreads();
-        elt_t wbase;
-        bool hwb = false;
-        for (int w = 0; w < warp; ++w) scan_join(p, wbase, hwb, sm_v[w], true);
-#pragma unroll
-        for (int r = 0; r < SCAN_ROUNDS; ++r) {
-          const int e = warp * SCAN_WARP_ELEMS + r * 128 + lane * 4;
-          elt_t pre = wbase;
-          bool hpre = hwb;
-          scan_join(p, pre, hpre, round_carry[r], r > 0);
-          scan_join(p, pre, hpre, lane_excl[r], lane > 0);
-          elt_t o[4];
-#pragma unroll
-          for (int k = 0; k < 4; ++k) {
-#if ACC_SCAN_MODE == 0
-            o[k] = hpre ? scan_op(p, pre, item[r][k]) : item[r][k];          // tile-local inclusive value
-#else
-            if (k == 0) o[k] = pre;                                            // tile-local exclusive value (none at offset 0)
-            else o[k] = hpre ? scan_op(p, pre, item[r][k - 1]) : item[r][k - 1];
-#endif
-          }
-          ring_st4(base, e, o);
-        }
-        if (tid == 0) {
-          elt_t agg = sm_v[0];
-          for (int w = 1; w < SCAN_WARPS; ++w) agg = scan_op(p, agg, sm_v[w]);
-          slot_agg[ss] = agg;
-          if (tt == 0) {
-            // first tile of a row: its exclusive prefix is the seed (or nothing)
-            elt_t inc = agg;
-#if ACC_SEEDED
-            const elt_t z = F_seed(p);
-            inc = scan_op(p, z, agg);
-            slot_excl[ss] = z;
-            slot_hexcl[ss] = 1;
-#else
-            slot_hexcl[ss] = 0;
-#endif
-            scan_desc_store(p.status, T, (epoch << 2) | SCAN_ST_PREFIX, inc.l0);
-            slot_state[ss] = RING_RESOLVED;
-          } else {
-            scan_desc_store(p.status, T, (epoch << 2) | SCAN_ST_AGG, agg.l0);
-            slot_state[ss] = RING_SCANNED;
-          }
-        }
+    // a wait gave up: tell the workers (the flag may also have been raised by them)
+    if (lb_failed && lane == 0) ring_stv(&sh_fail, 1);
+  } else {
+    // ================= workers ==========================================================
+    i64 pos_scan = 0, pos_fin = 0;        // ring positions, identical in every worker thread
+    i64 idle = 0;                         // thread 0: consecutive iterations without anything to do
+    for (;;) {
+      if (tid == 0) {
+        int act = 0;
+        const int fs = (int)(pos_fin % SCAN_SLOTS), ss = (int)(pos_scan % SCAN_SLOTS);
+        if (pos_fin < pos_scan && ring_ldv(&slot_state[fs]) >= RING_RESOLVED) act |= RING_ACT_FIN;
+        const bool has_slot = pos_scan < pos_fin + SCAN_SLOTS;
+        const bool scan_work = has_slot && slot_tile[ss] < total_tiles;
+        if (scan_work && (slot_direct[ss] || ring_mbar_try_wait(&full_bar[ss], slot_parity[ss]))) act |= RING_ACT_SCAN;
+        if (pos_fin == pos_scan && !scan_work) act = RING_ACT_EXIT;
+        idle = act ? 0 : idle + 1;
+        if (idle > p.spin_limit) ring_stv(&sh_fail, 1);     // neither data nor a prefix ever arrived: give up
+        if (ring_ldv(&sh_fail)) act = RING_ACT_EXIT;
+        ctl_act = act;
       }
-      pos_scan += 1;
-      __syncthreads();
-    }
+      SCAN_SYNC();
+      const int act = ctl_act;
+      if (act & RING_ACT_EXIT) break;
 
-    if (pos_fin < res_now) {
-      // ---- the oldest slot knows its prefix: combine and stream out ------------------------------
-      const int fs = (int)(pos_fin % SCAN_SLOTS);
-      if (slot_state[fs] != RING_DONE) {
-        const i64 T = slot_tile[fs];
+      if (act & RING_ACT_SCAN) {
+        // ---- local scan of the slot at pos_scan, in place ---------------------------------------
+        const int ss = (int)(pos_scan % SCAN_SLOTS);
+        const i64 T = slot_tile[ss];
         const i64 row = T / p.tiles_per_row;
         const i64 tt = T - row * p.tiles_per_row;
-        const unsigned char* base = scan_ring_smem + (size_t)fs * RING_SLOT_BYTES;
-        const elt_t excl = slot_excl[fs];
-        const bool hexcl = slot_hexcl[fs] != 0;
-        (void)hexcl;
-#if ACC_SCAN_MODE == 1
-        const i64 out_row = row * (n + 1);
+        if (slot_direct[ss]) {
+          scan_tile<false>(p, T, row, tt, sm_v, sm_h, &sm_excl1, sm_flag1);    // partial tile: start to finish
+          SCAN_SYNC();
+          if (tid == 0) {
+            if (sm_flag1[1]) ring_stv(&sh_fail, 1);
+            __threadfence_block();
+            ring_stv(&slot_state[ss], RING_DONE);
+          }
+        } else {
+          // Only the tile's aggregate is needed now; publishing it promptly matters more than
+          // anything else, because every later tile of the row waits for it.  The scan itself is
+          // done when the tile's prefix is known (finish step), straight from shared memory.
+          const unsigned char* base = scan_ring_smem + (size_t)ss * RING_SLOT_BYTES;
+          const i64 warp_q0 = tt * SCAN_TILE + (i64)warp * SCAN_WARP_ELEMS;
+          SCAN_MARK(T, 1);   // arrived
+          elt_t tot;
+#pragma unroll
+          for (int r = 0; r < SCAN_ROUNDS; ++r) {
+            const int e = warp * SCAN_WARP_ELEMS + r * 128 + lane * 4;
+            const i64 q = warp_q0 + r * 128 + lane * 4;
+            elt_t t4[4];
+#if ACC_RIGHT
+            D0_get4_sm(p, row, n - 4 - q, base, SCAN_TILE - 4 - e, t4);
+            elt_t v = scan_op(p, scan_op(p, scan_op(p, t4[3], t4[2]), t4[1]), t4[0]);
 #else
-        const i64 out_row = row * n;
+            D0_get4_sm(p, row, q, base, e, t4);
+            elt_t v = scan_op(p, scan_op(p, scan_op(p, t4[0], t4[1]), t4[2]), t4[3]);
+#endif
+            // lanes in order within the round, rounds in order within the warp
+#pragma unroll
+            for (int d = 1; d < 32; d <<= 1) {
+              const elt_t o = acc_shfl_down(v, d);
+              if (lane + d < 32) v = scan_op(p, v, o);
+            }
+            if (r == 0) tot = v;
+            else tot = scan_op(p, tot, v);
+          }
+          if (lane == 0) sm_v[warp] = tot;
+          SCAN_SYNC();
+          if (tid == 0) {
+            elt_t agg = sm_v[0];
+            for (int w = 1; w < SCAN_WARPS; ++w) agg = scan_op(p, agg, sm_v[w]);
+            slot_agg[ss] = agg;
+            SCAN_MARK(T, 2);   // aggregate published
+            if (tt == 0) {
+              // first tile of a row: its exclusive prefix is the seed (or nothing)
+              elt_t inc = agg;
+#if ACC_SEEDED
+              const elt_t z = F_seed(p);
+              inc = scan_op(p, z, agg);
+              slot_excl[ss] = z;
+              slot_hexcl[ss] = 1;
+#else
+              slot_hexcl[ss] = 0;
+#endif
+              scan_desc_store(p.status, T, (epoch << 2) | SCAN_ST_PREFIX, inc.l0);
+              __threadfence_block();
+              ring_stv(&slot_state[ss], RING_RESOLVED);
+            } else {
+              scan_desc_store(p.status, T, (epoch << 2) | SCAN_ST_AGG, agg.l0);
+              __threadfence_block();
+              ring_stv(&slot_state[ss], RING_SCANNED);
+            }
+          }
+        }
+        pos_scan += 1;
+        SCAN_SYNC();
+      }
+
+      if (act & RING_ACT_FIN) {
+        // ---- the oldest slot knows its prefix: combine and stream out ------------------------------
+        const int fs = (int)(pos_fin % SCAN_SLOTS);
+        if (slot_state[fs] != RING_DONE) {
+          const i64 T = slot_tile[fs];
+          const i64 row = T / p.tiles_per_row;
+          const i64 tt = T - row * p.tiles_per_row;
+          const unsigned char* base = scan_ring_smem + (size_t)fs * RING_SLOT_BYTES;
+          const elt_t excl = slot_excl[fs];
+          const bool hexcl = slot_hexcl[fs] != 0;
+#if ACC_SCAN_MODE == 1
+          const i64 out_row = row * (n + 1);
+#else
+          const i64 out_row = row * n;
+#endif
+          const i64 warp_q0 = tt * SCAN_TILE + (i64)warp * SCAN_WARP_ELEMS;
+          elt_t item[SCAN_ROUNDS][4];
+#pragma unroll
+          for (int r = 0; r < SCAN_ROUNDS; ++r) {
+            const int e = warp * SCAN_WARP_ELEMS + r * 128 + lane * 4;
+            const i64 q = warp_q0 + r * 128 + lane * 4;
+#if ACC_RIGHT
+            elt_t t4[4];
+            D0_get4_sm(p, row, n - 4 - q, base, SCAN_TILE - 4 - e, t4);
+#pragma unroll
+            for (int k = 0; k < 4; ++k) item[r][k] = t4[3 - k];
+#else
+            D0_get4_sm(p, row, q, base, e, item[r]);
 #endif
 #pragma unroll
-        for (int r = 0; r < SCAN_ROUNDS; ++r) {
-          const int e = warp * SCAN_WARP_ELEMS + r * 128 + lane * 4;
-          const i64 q = tt * SCAN_TILE + e;
-          elt_t v[4], o[4];
-          ring_ld4(base, e, v);
+            for (int k = 1; k < 4; ++k) item[r][k] = scan_op(p, item[r][k - 1], item[r][k]);
+          }
+          elt_t lane_excl[SCAN_ROUNDS], round_carry[SCAN_ROUNDS];
+          elt_t carry;
 #pragma unroll
-          for (int k = 0; k < 4; ++k) {
+          for (int r = 0; r < SCAN_ROUNDS; ++r) {
+            elt_t v = item[r][3];
+#pragma unroll
+            for (int d = 1; d < 32; d <<= 1) {
+              const elt_t o = acc_shfl_up(v, d);
+              if (lane >= d) v = scan_op(p, o, v);
+            }
+            lane_excl[r] = acc_shfl_up(v, 1);
+            const elt_t rt = acc_shfl_idx(v, 31);
+            round_carry[r] = carry;
+            if (r == 0) carry = rt;
+            else carry = scan_op(p, carry, rt);
+          }
+          if (lane == 0) sm_v[warp] = carry;
+          SCAN_SYNC();
+          elt_t wbase = excl;             // everything before this warp's part: tile prefix, then earlier warps
+          bool hwb = hexcl;
+          for (int w = 0; w < warp; ++w) scan_join(p, wbase, hwb, sm_v[w], true);
+#pragma unroll
+          for (int r = 0; r < SCAN_ROUNDS; ++r) {
+            const int e = warp * SCAN_WARP_ELEMS + r * 128 + lane * 4;
+            const i64 q = tt * SCAN_TILE + e;
+            elt_t pre = wbase;
+            bool hpre = hwb;
+            scan_join(p, pre, hpre, round_carry[r], r > 0);
+            scan_join(p, pre, hpre, lane_excl[r], lane > 0);
+            elt_t o[4];
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
 #if ACC_SCAN_MODE == 0
-            o[k] = hexcl ? scan_op(p, excl, v[k]) : v[k];
+              o[k] = hpre ? scan_op(p, pre, item[r][k]) : item[r][k];
 #else
-            o[k] = (e + k == 0) ? excl : scan_op(p, excl, v[k]);
+              if (k == 0) o[k] = pre;                                // the seed guarantees a prefix exists
+              else o[k] = scan_op(p, pre, item[r][k - 1]);
+#endif
+            }
+#if ACC_SCAN_MODE == 1 && ACC_RIGHT
+            const i64 pos0 = out_row + n - q;
+#elif ACC_RIGHT
+            const i64 pos0 = out_row + n - 1 - q;
+#else
+            const i64 pos0 = out_row + q;
+#endif
+#if ACC_RIGHT
+            elt_t w[4] = {o[3], o[2], o[1], o[0]};
+            OUT0_store4(p, pos0 - 3, w);
+#else
+            OUT0_store4(p, pos0, o);
 #endif
           }
-#if ACC_SCAN_MODE == 1 && ACC_RIGHT
-          const i64 pos0 = out_row + n - q;
-#elif ACC_RIGHT
-          const i64 pos0 = out_row + n - 1 - q;
-#else
-          const i64 pos0 = out_row + q;
-#endif
-#if ACC_RIGHT
-          elt_t w[4] = {o[3], o[2], o[1], o[0]};
-          OUT0_store4(p, pos0 - 3, w);
-#else
-          OUT0_store4(p, pos0, o);
-#endif
-        }
 #if ACC_SCAN_MODE != 0
-        if (tid == 0 && tt == p.tiles_per_row - 1) {
-          const elt_t tot = scan_op(p, excl, slot_agg[fs]);
+          if (tid == 0 && tt == p.tiles_per_row - 1) {
+            const elt_t tot = scan_op(p, excl, slot_agg[fs]);
 #if ACC_SCAN_MODE == 1
 #if ACC_RIGHT
-          OUT0_store(p, row * (n + 1), tot);
+            OUT0_store(p, row * (n + 1), tot);
 #else
-          OUT0_store(p, row * (n + 1) + n, tot);
+            OUT0_store(p, row * (n + 1) + n, tot);
 #endif
 #else
-          OUT1_store(p, row, tot);
+            OUT1_store(p, row, tot);
 #endif
+          }
+#endif
+          SCAN_MARK(T, 4);   // stores issued
         }
-#endif
+        SCAN_SYNC();                     // everyone is done reading the slot
+        if (tid == 0) fetch(fs, pos_fin + SCAN_SLOTS);
+        pos_fin += 1;
       }
-      __syncthreads();                 // everyone is done reading the slot
-      if (tid == 0) fetch(fs);
-      pos_fin += 1;
+      if (act == 0) __nanosleep(64);
+      SCAN_SYNC();
     }
-    __syncthreads();
   }
-  // wait (bounded) for bulk copies still in flight into this CTA's shared memory
+  // everybody meets here; the look-back warp leaves its loop when it sees a tile past the end,
+  // a failure flag, or an expired wait (in which case it raises the flag itself)
   __syncthreads();
   if (tid == 0) {
+    // wait (bounded) for bulk copies still in flight into this CTA's shared memory
     for (int s = 0; s < SCAN_SLOTS; ++s) {
       if (slot_tile[s] < total_tiles && !slot_direct[s] && slot_state[s] == RING_LOADING) {
         i64 spins = 0;
@@ -1028,6 +1150,7 @@ extern "C" __global__ void __launch_bounds__(SCAN_THREADS, SCAN_MIN_BLOCKS) acc_
           if (++spins > p.spin_limit) break;
       }
     }
+    if (sh_fail) acc_fail(p.err, 110 /* ETIMEDOUT */);
     __threadfence();
     if (atomicAdd(exits, 1u) == gridDim.x - 1) { *counter = 0u; *exits = 0u; }
   }
