@@ -161,12 +161,33 @@ std::map<std::string, std::string> scan_variant(const Type& elt) {
 // Spread descriptors cost total_tiles * 16 * stride bytes of scratch, so long lists of tiles stay dense.
 int scan_desc_stride(int64_t total_tiles) {
   if (const char* e = getenv("ACCELERATE_B200_SCAN_DESC_STRIDE")) return std::max(1, atoi(e));
-  return total_tiles <= 65536 ? SCAN_DESC_STRIDE_DEFAULT : 1;
+  // at most 64 MiB of descriptors
+  return total_tiles <= 262144 ? SCAN_DESC_STRIDE_DEFAULT : (total_tiles <= 1048576 ? 4 : 1);
 }
 void scan_poll_variant(std::map<std::string, std::string>& v, int64_t total_tiles) {
   v["SCAN_DESC_STRIDE"] = std::to_string(scan_desc_stride(total_tiles));
   const char* e = getenv("ACCELERATE_B200_SCAN_BACKOFF");
   v["SCAN_BACKOFF_NS"] = e && *e ? std::string(e) : std::to_string(SCAN_BACKOFF_DEFAULT);
+}
+// shape of the shared-memory ring scan kernel (overridable for tuning)
+struct RingShape { int rounds, slots, minb, lbw, redw, look; };
+RingShape scan_ring_shape(int bytes) {
+  auto tune = [](const char* name, int dflt) { const char* e = getenv(name); return e && *e ? atoi(e) : dflt; };
+  RingShape r;
+  r.rounds = tune("ACCELERATE_B200_RING_ROUNDS", bytes <= 4 ? 8 : 4);
+  r.slots = tune("ACCELERATE_B200_RING_SLOTS", 3);
+  r.minb = tune("ACCELERATE_B200_RING_MIN_BLOCKS", 2);
+  r.lbw = std::max(1, tune("ACCELERATE_B200_RING_LB_WARPS", 1));
+  r.redw = std::max(1, tune("ACCELERATE_B200_RING_RED_WARPS", 2));
+  r.look = std::max(1, tune("ACCELERATE_B200_SCAN_LOOK", 2));
+  return r;
+}
+std::map<std::string, std::string> scan_ring_variant(const RingShape& r, int64_t total_tiles) {
+  std::map<std::string, std::string> v = {{"SCAN_RING", "1"}, {"SCAN_ROUNDS", std::to_string(r.rounds)}, {"SCAN_SLOTS", std::to_string(r.slots)},
+                                          {"SCAN_MIN_BLOCKS", std::to_string(r.minb)}, {"SCAN_LB_WARPS", std::to_string(r.lbw)},
+                                          {"RING_RED_WARPS", std::to_string(r.redw)}, {"SCAN_LOOK", std::to_string(r.look)}};
+  scan_poll_variant(v, total_tiles);
+  return v;
 }
 // launch shape of the register-window rank-2 stencil kernel (overridable for tuning)
 struct Stencil2dShape { int warps, rows, minb, depth; };
@@ -198,10 +219,14 @@ std::vector<std::pair<std::string, std::map<std::string, std::string>>> default_
       break;
     case N_FOLDSEG: v.push_back({"foldseg", {{"FOLDSEG_G", "32"}}}); break;
     case N_SCAN: case N_SCAN2: {
-      v.push_back({"scan", scan_variant(n.elt)});
+      {
+        auto sv = scan_variant(n.elt);
+        scan_poll_variant(sv, 1);
+        v.push_back({"scan", sv});
+      }
       if (g.defines.count("D0_STREAM_NLEAVES") && g.defines.at("D0_STREAM_NLEAVES") == "1" && g.defines.at("SCAN_PACKED") == "1" &&
           g.defines.at("D0_STREAM_BYTES") == g.defines.at("SCAN_T_BYTES"))
-        v.push_back({"scan", {{"SCAN_RING", "1"}, {"SCAN_ROUNDS", g.defines.at("SCAN_T_BYTES") == "8" ? "4" : "8"}, {"SCAN_SLOTS", "3"}, {"SCAN_MIN_BLOCKS", "2"}}});
+        v.push_back({"scan", scan_ring_variant(scan_ring_shape(atoi(g.defines.at("SCAN_T_BYTES").c_str())), 1)});
       if (!g.streams.empty() && !g.streams[0].empty()) {
         auto var = scan_variant(n.elt);
         var["SCAN_PIPE"] = "1";
@@ -742,21 +767,15 @@ void Program::run(const std::vector<DevArrayP>& inputs, std::vector<DevArrayP>& 
           // 8-byte elements halve the elements a ring holds; the register-resident kernel is faster for them
           const bool want = getenv("ACCELERATE_B200_SCAN_RING") ? true : (bytes <= 4 && !getenv("ACCELERATE_B200_SCAN_NO_RING"));
           if (one_stream && want && L.fast("D0") && in_vec && out_vec) {
-            auto tune = [](const char* name, int dflt) { const char* e = getenv(name); return e && *e ? atoi(e) : dflt; };
-            const int rounds = tune("ACCELERATE_B200_RING_ROUNDS", bytes <= 4 ? 8 : 4);
-            const int slots = tune("ACCELERATE_B200_RING_SLOTS", 3);
-            const int minb = tune("ACCELERATE_B200_RING_MIN_BLOCKS", 2);
+            const RingShape rs = scan_ring_shape(bytes);
+            const int rounds = rs.rounds, slots = rs.slots, look = rs.look;
             const int64_t rtile = 8 * (int64_t)rounds * 128;
             const int64_t r_tiles_per_row = std::max<int64_t>(1, (m + rtile - 1) / rtile);
             const int64_t r_total = rows * r_tiles_per_row;
             const size_t smem = (size_t)slots * rtile * bytes;
-            std::map<std::string, std::string> var = {{"SCAN_RING", "1"}, {"SCAN_ROUNDS", std::to_string(rounds)}, {"SCAN_SLOTS", std::to_string(slots)},
-                                                      {"SCAN_MIN_BLOCKS", std::to_string(minb)}};
-            if (const char* e = getenv("ACCELERATE_B200_SCAN_LOOK")) var["SCAN_LOOK"] = e;
-            scan_poll_variant(var, r_total);
+            std::map<std::string, std::string> var = scan_ring_variant(rs, r_total);
             const int dstride = scan_desc_stride(r_total);
             const size_t r_status = ((size_t)r_total * 16 * dstride + 255) / 256 * 256;
-            const int look = getenv("ACCELERATE_B200_SCAN_LOOK") ? atoi(getenv("ACCELERATE_B200_SCAN_LOOK")) : 2;
             const int64_t groups_per_row = (r_tiles_per_row + 32 * look - 1) / (32 * look);
             const size_t g_status = ((size_t)(rows * groups_per_row) * 16 * dstride + 255) / 256 * 256;
             char* rbase = (char*)c.scan_descriptors(r_status + g_status);
@@ -774,9 +793,7 @@ void Program::run(const std::vector<DevArrayP>& inputs, std::vector<DevArrayP>& 
               c.check(cudaMemsetAsync(tbuf->ptr, 0, tbuf->bytes, c.stream), "cudaMemsetAsync");
               L.named["trace"] = (int64_t)(uintptr_t)tbuf->ptr;
             }
-            const int lbw = std::max(1, tune("ACCELERATE_B200_RING_LB_WARPS", 1));
-            var["SCAN_LB_WARPS"] = std::to_string(lbw);
-            const int threads = 256 + 32 * lbw;     // 8 worker warps + the look-back warps
+            const int threads = 256 + 32 * rs.redw + 32 * rs.lbw;     // 8 finisher warps, the reducer warps, the look-back warps
             CompiledKernel& k = c.kernel(assemble_source(st.glue, "scan", var), "acc_scan_ring", threads, smem);
             const int64_t grid = std::min<int64_t>(r_total, (int64_t)c.sm_count * k.max_blocks_per_sm);
             L.launch(k, grid, threads, smem);

@@ -727,10 +727,19 @@ template <class T> __device__ __forceinline__ void ring_stv(T* p, T v) { *reinte
 #ifndef SCAN_LB_WARPS
 #define SCAN_LB_WARPS 1
 #endif
-#define RING_THREADS (SCAN_THREADS + 32 * SCAN_LB_WARPS)
+#ifndef RING_RED_WARPS
+#define RING_RED_WARPS 2
+#endif
+#define RING_THREADS (SCAN_THREADS + 32 * RING_RED_WARPS + 32 * SCAN_LB_WARPS)
 #define RING_ACT_SCAN 1
 #define RING_ACT_FIN 2
 #define RING_ACT_EXIT 4
+
+// The partial tile at the end of a row is rare and register-hungry (it carries its own look-back):
+// kept out of line so that it does not set the register budget of the common path.
+__device__ __noinline__ void ring_partial_tile(const Params& p, i64 T, i64 row, i64 tt, elt_t* sm_v, int* sm_h, elt_t* sm_excl, int* sm_flag) {
+  scan_tile<false>(p, T, row, tt, sm_v, sm_h, sm_excl, sm_flag);
+}
 
 extern "C" __global__ void __launch_bounds__(RING_THREADS, SCAN_MIN_BLOCKS) acc_scan_ring(const Params p) {
   __shared__ elt_t sm_v[SCAN_WARPS];
@@ -743,6 +752,7 @@ extern "C" __global__ void __launch_bounds__(RING_THREADS, SCAN_MIN_BLOCKS) acc_
   __shared__ int slot_direct[SCAN_SLOTS], slot_state[SCAN_SLOTS], slot_hexcl[SCAN_SLOTS];
   __shared__ elt_t slot_agg[SCAN_SLOTS], slot_excl[SCAN_SLOTS];
   __shared__ int ctl_act, sh_fail;
+  __shared__ elt_t red_v[2][RING_RED_WARPS];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const i64 n = p.n;
   const i64 total_tiles = p.total_tiles;
@@ -790,14 +800,14 @@ extern "C" __global__ void __launch_bounds__(RING_THREADS, SCAN_MIN_BLOCKS) acc_
     for (int s = 0; s < SCAN_SLOTS; ++s) fetch(s, s);
   __syncthreads();
 
-  if (warp >= SCAN_WARPS) {
+  if (warp >= SCAN_WARPS + RING_RED_WARPS) {
     // ================= look-back warps =================================================
     // Hierarchical walk: tiles of a row are grouped by RING_GROUP.  Phase OWN reads the earlier
     // tiles of the own group; phase GROUPS reads 32 group descriptors per step (aggregate or
     // inclusive prefix of a whole group); phase COMPUTE summarises a group nobody has summarised
     // yet from its tile descriptors and publishes the summary for every later walker.
     int lb_failed = 0;
-    for (i64 r = warp - SCAN_WARPS;; r += SCAN_LB_WARPS) {
+    for (i64 r = warp - SCAN_WARPS - RING_RED_WARPS;; r += SCAN_LB_WARPS) {
       const int s = (int)(r % SCAN_SLOTS);
       i64 spins = 0;
       int failed = 0;
@@ -809,6 +819,7 @@ extern "C" __global__ void __launch_bounds__(RING_THREADS, SCAN_MIN_BLOCKS) acc_
       __threadfence_block();
       const i64 T = slot_tile[s];
       if (T >= total_tiles) break;
+      if (slot_direct[s]) continue;                 // partial tile: the finishers do it start to finish
       int st0;
       spins = 0;
       while ((st0 = ring_ldv(&slot_state[s])) < RING_SCANNED) {
@@ -817,7 +828,7 @@ extern "C" __global__ void __launch_bounds__(RING_THREADS, SCAN_MIN_BLOCKS) acc_
       }
       if (failed) { lb_failed = 1; break; }
       __threadfence_block();
-      if (st0 >= RING_RESOLVED) continue;           // first tile of a row / partial tile: nothing to do
+      if (st0 >= RING_RESOLVED) continue;           // first tile of a row: nothing to do
       const i64 row = T / p.tiles_per_row;
       const i64 tt = T - row * p.tiles_per_row;
       const i64 row_first = T - tt;
@@ -932,210 +943,239 @@ extern "C" __global__ void __launch_bounds__(RING_THREADS, SCAN_MIN_BLOCKS) acc_
     }
     // a wait gave up: tell the workers (the flag may also have been raised by them)
     if (lb_failed && lane == 0) ring_stv(&sh_fail, 1);
-  } else {
-    // ================= workers ==========================================================
-    i64 pos_scan = 0, pos_fin = 0;        // ring positions, identical in every worker thread
-    i64 idle = 0;                         // thread 0: consecutive iterations without anything to do
-    for (;;) {
-      if (tid == 0) {
-        int act = 0;
-        const int fs = (int)(pos_fin % SCAN_SLOTS), ss = (int)(pos_scan % SCAN_SLOTS);
-        if (pos_fin < pos_scan && ring_ldv(&slot_state[fs]) >= RING_RESOLVED) act |= RING_ACT_FIN;
-        const bool has_slot = pos_scan < pos_fin + SCAN_SLOTS;
-        const bool scan_work = has_slot && slot_tile[ss] < total_tiles;
-        if (scan_work && (slot_direct[ss] || ring_mbar_try_wait(&full_bar[ss], slot_parity[ss]))) act |= RING_ACT_SCAN;
-        if (pos_fin == pos_scan && !scan_work) act = RING_ACT_EXIT;
-        idle = act ? 0 : idle + 1;
-        if (idle > p.spin_limit) ring_stv(&sh_fail, 1);     // neither data nor a prefix ever arrived: give up
-        if (ring_ldv(&sh_fail)) act = RING_ACT_EXIT;
-        ctl_act = act;
+  } else if (warp >= SCAN_WARPS) {
+    // ================= reducers ========================================================
+    // Every later tile of the row waits for this tile's aggregate, so it is computed by warps that
+    // do nothing else, the moment the data has arrived; the scan itself is left to the finishers.
+    const int rt = tid - SCAN_THREADS, rw = warp - SCAN_WARPS;
+    int red_failed = 0;
+    for (i64 r = 0;; ++r) {
+      const int s = (int)(r % SCAN_SLOTS);
+      i64 spins = 0;
+      while (ring_ldv(&slot_pos[s]) != r) {
+        if (++spins > p.spin_limit || ring_ldv(&sh_fail)) { red_failed = 1; break; }
+        __nanosleep(40);
       }
-      SCAN_SYNC();
-      const int act = ctl_act;
-      if (act & RING_ACT_EXIT) break;
-
-      if (act & RING_ACT_SCAN) {
-        // ---- local scan of the slot at pos_scan, in place ---------------------------------------
-        const int ss = (int)(pos_scan % SCAN_SLOTS);
-        const i64 T = slot_tile[ss];
-        const i64 row = T / p.tiles_per_row;
-        const i64 tt = T - row * p.tiles_per_row;
-        if (slot_direct[ss]) {
-          scan_tile<false>(p, T, row, tt, sm_v, sm_h, &sm_excl1, sm_flag1);    // partial tile: start to finish
-          SCAN_SYNC();
-          if (tid == 0) {
-            if (sm_flag1[1]) ring_stv(&sh_fail, 1);
-            __threadfence_block();
-            ring_stv(&slot_state[ss], RING_DONE);
-          }
-        } else {
-          // Only the tile's aggregate is needed now; publishing it promptly matters more than
-          // anything else, because every later tile of the row waits for it.  The scan itself is
-          // done when the tile's prefix is known (finish step), straight from shared memory.
-          const unsigned char* base = scan_ring_smem + (size_t)ss * RING_SLOT_BYTES;
-          const i64 warp_q0 = tt * SCAN_TILE + (i64)warp * SCAN_WARP_ELEMS;
-          SCAN_MARK(T, 1);   // arrived
-          elt_t tot;
-#pragma unroll
-          for (int r = 0; r < SCAN_ROUNDS; ++r) {
-            const int e = warp * SCAN_WARP_ELEMS + r * 128 + lane * 4;
-            const i64 q = warp_q0 + r * 128 + lane * 4;
-            elt_t t4[4];
-#if ACC_RIGHT
-            D0_get4_sm(p, row, n - 4 - q, base, SCAN_TILE - 4 - e, t4);
-            elt_t v = scan_op(p, scan_op(p, scan_op(p, t4[3], t4[2]), t4[1]), t4[0]);
-#else
-            D0_get4_sm(p, row, q, base, e, t4);
-            elt_t v = scan_op(p, scan_op(p, scan_op(p, t4[0], t4[1]), t4[2]), t4[3]);
+      if (red_failed) break;
+      __threadfence_block();
+      const i64 T = slot_tile[s];
+      if (T >= total_tiles) break;
+      if (slot_direct[s]) continue;                 // partial tile: the finishers do it start to finish
+      spins = 0;
+      while (!ring_mbar_try_wait(&full_bar[s], slot_parity[s])) {
+        if (++spins > p.spin_limit || ring_ldv(&sh_fail)) { red_failed = 1; break; }
+      }
+      if (red_failed) break;
+      const i64 row = T / p.tiles_per_row;
+      const i64 tt = T - row * p.tiles_per_row;
+      const unsigned char* base = scan_ring_smem + (size_t)s * RING_SLOT_BYTES;
+#if SCAN_TRACE
+      if (rt == 0) reinterpret_cast<u64*>(p.trace)[T * 8 + 1] = scan_now();   // arrived
 #endif
-            // lanes in order within the round, rounds in order within the warp
+      // warp rw reduces elements [rw, rw + 1) * SCAN_TILE / RING_RED_WARPS in rounds of 128
+      constexpr int RED_ROUNDS = SCAN_TILE / (128 * RING_RED_WARPS);
+      elt_t tot;
+#if ACC_COMMUTATIVE
+      // lanes accumulate their own quads across rounds; one warp reduction at the end
+#pragma unroll 4
+      for (int k = 0; k < RED_ROUNDS; ++k) {
+        const int e = (rw * RED_ROUNDS + k) * 128 + lane * 4;
+        const i64 q = tt * SCAN_TILE + e;
+        elt_t t4[4];
+#if ACC_RIGHT
+        D0_get4_sm(p, row, n - 4 - q, base, SCAN_TILE - 4 - e, t4);
+#else
+        D0_get4_sm(p, row, q, base, e, t4);
+#endif
+        const elt_t v = scan_op(p, scan_op(p, t4[0], t4[1]), scan_op(p, t4[2], t4[3]));
+        if (k == 0) tot = v;
+        else tot = scan_op(p, tot, v);
+      }
 #pragma unroll
-            for (int d = 1; d < 32; d <<= 1) {
-              const elt_t o = acc_shfl_down(v, d);
-              if (lane + d < 32) v = scan_op(p, v, o);
-            }
-            if (r == 0) tot = v;
-            else tot = scan_op(p, tot, v);
-          }
-          if (lane == 0) sm_v[warp] = tot;
-          SCAN_SYNC();
-          if (tid == 0) {
-            elt_t agg = sm_v[0];
-            for (int w = 1; w < SCAN_WARPS; ++w) agg = scan_op(p, agg, sm_v[w]);
-            slot_agg[ss] = agg;
-            SCAN_MARK(T, 2);   // aggregate published
-            if (tt == 0) {
-              // first tile of a row: its exclusive prefix is the seed (or nothing)
-              elt_t inc = agg;
+      for (int d = 16; d >= 1; d >>= 1) tot = scan_op(p, tot, acc_shfl_down(tot, d));
+#else
+#pragma unroll 2
+      for (int k = 0; k < RED_ROUNDS; ++k) {
+        const int e = (rw * RED_ROUNDS + k) * 128 + lane * 4;
+        const i64 q = tt * SCAN_TILE + e;
+        elt_t t4[4];
+#if ACC_RIGHT
+        D0_get4_sm(p, row, n - 4 - q, base, SCAN_TILE - 4 - e, t4);
+        elt_t v = scan_op(p, scan_op(p, scan_op(p, t4[3], t4[2]), t4[1]), t4[0]);
+#else
+        D0_get4_sm(p, row, q, base, e, t4);
+        elt_t v = scan_op(p, scan_op(p, scan_op(p, t4[0], t4[1]), t4[2]), t4[3]);
+#endif
+        // lanes in order within the round, rounds in order within the warp
+#pragma unroll
+        for (int d = 1; d < 32; d <<= 1) {
+          const elt_t o = acc_shfl_down(v, d);
+          if (lane + d < 32) v = scan_op(p, v, o);
+        }
+        if (k == 0) tot = v;
+        else tot = scan_op(p, tot, v);
+      }
+#endif
+      if (lane == 0) red_v[r & 1][rw] = tot;
+      asm volatile("bar.sync 2, %0;" ::"n"(32 * RING_RED_WARPS) : "memory");
+      if (rt == 0) {
+        elt_t agg = red_v[r & 1][0];
+        for (int w = 1; w < RING_RED_WARPS; ++w) agg = scan_op(p, agg, red_v[r & 1][w]);
+        slot_agg[s] = agg;
+#if SCAN_TRACE
+        reinterpret_cast<u64*>(p.trace)[T * 8 + 2] = scan_now();   // aggregate published
+#endif
+        if (tt == 0) {
+          // first tile of a row: its exclusive prefix is the seed (or nothing)
+          elt_t inc = agg;
 #if ACC_SEEDED
-              const elt_t z = F_seed(p);
-              inc = scan_op(p, z, agg);
-              slot_excl[ss] = z;
-              slot_hexcl[ss] = 1;
+          const elt_t z = F_seed(p);
+          inc = scan_op(p, z, agg);
+          slot_excl[s] = z;
+          slot_hexcl[s] = 1;
 #else
-              slot_hexcl[ss] = 0;
+          slot_hexcl[s] = 0;
 #endif
-              scan_desc_store(p.status, T, (epoch << 2) | SCAN_ST_PREFIX, inc.l0);
-              __threadfence_block();
-              ring_stv(&slot_state[ss], RING_RESOLVED);
-            } else {
-              scan_desc_store(p.status, T, (epoch << 2) | SCAN_ST_AGG, agg.l0);
-              __threadfence_block();
-              ring_stv(&slot_state[ss], RING_SCANNED);
-            }
-          }
+          scan_desc_store(p.status, T, (epoch << 2) | SCAN_ST_PREFIX, inc.l0);
+          __threadfence_block();
+          ring_stv(&slot_state[s], RING_RESOLVED);
+        } else {
+          scan_desc_store(p.status, T, (epoch << 2) | SCAN_ST_AGG, agg.l0);
+          __threadfence_block();
+          ring_stv(&slot_state[s], RING_SCANNED);
         }
-        pos_scan += 1;
+      }
+    }
+    if (red_failed && lane == 0) ring_stv(&sh_fail, 1);
+  } else {
+    // ================= finishers ========================================================
+    // Slots are finished in ring order: once a slot knows its exclusive prefix, the tile is scanned
+    // straight out of shared memory and stored, and the slot is handed to the next ticket.
+    i64 idle = 0;                          // thread 0: consecutive polls without anything to do
+    for (i64 r = 0;; ++r) {
+      const int fs = (int)(r % SCAN_SLOTS);
+      const i64 T = slot_tile[fs];         // written by thread 0 before a SCAN_SYNC
+      if (T >= total_tiles) break;
+      const i64 row = T / p.tiles_per_row;
+      const i64 tt = T - row * p.tiles_per_row;
+      if (slot_direct[fs]) {
+        ring_partial_tile(p, T, row, tt, sm_v, sm_h, &sm_excl1, sm_flag1);    // partial tile: start to finish
         SCAN_SYNC();
-      }
-
-      if (act & RING_ACT_FIN) {
-        // ---- the oldest slot knows its prefix: combine and stream out ------------------------------
-        const int fs = (int)(pos_fin % SCAN_SLOTS);
-        if (slot_state[fs] != RING_DONE) {
-          const i64 T = slot_tile[fs];
-          const i64 row = T / p.tiles_per_row;
-          const i64 tt = T - row * p.tiles_per_row;
-          const unsigned char* base = scan_ring_smem + (size_t)fs * RING_SLOT_BYTES;
-          const elt_t excl = slot_excl[fs];
-          const bool hexcl = slot_hexcl[fs] != 0;
-#if ACC_SCAN_MODE == 1
-          const i64 out_row = row * (n + 1);
-#else
-          const i64 out_row = row * n;
-#endif
-          const i64 warp_q0 = tt * SCAN_TILE + (i64)warp * SCAN_WARP_ELEMS;
-          elt_t item[SCAN_ROUNDS][4];
-#pragma unroll
-          for (int r = 0; r < SCAN_ROUNDS; ++r) {
-            const int e = warp * SCAN_WARP_ELEMS + r * 128 + lane * 4;
-            const i64 q = warp_q0 + r * 128 + lane * 4;
-#if ACC_RIGHT
-            elt_t t4[4];
-            D0_get4_sm(p, row, n - 4 - q, base, SCAN_TILE - 4 - e, t4);
-#pragma unroll
-            for (int k = 0; k < 4; ++k) item[r][k] = t4[3 - k];
-#else
-            D0_get4_sm(p, row, q, base, e, item[r]);
-#endif
-#pragma unroll
-            for (int k = 1; k < 4; ++k) item[r][k] = scan_op(p, item[r][k - 1], item[r][k]);
+        if (tid == 0 && sm_flag1[1]) ring_stv(&sh_fail, 1);
+      } else {
+        if (tid == 0) {
+          idle = 0;
+          while (ring_ldv(&slot_state[fs]) < RING_RESOLVED) {
+            if (++idle > p.spin_limit) ring_stv(&sh_fail, 1);     // the prefix never arrived: give up
+            if (ring_ldv(&sh_fail)) break;
+            __nanosleep(40);
           }
-          elt_t lane_excl[SCAN_ROUNDS], round_carry[SCAN_ROUNDS];
-          elt_t carry;
-#pragma unroll
-          for (int r = 0; r < SCAN_ROUNDS; ++r) {
-            elt_t v = item[r][3];
-#pragma unroll
-            for (int d = 1; d < 32; d <<= 1) {
-              const elt_t o = acc_shfl_up(v, d);
-              if (lane >= d) v = scan_op(p, o, v);
-            }
-            lane_excl[r] = acc_shfl_up(v, 1);
-            const elt_t rt = acc_shfl_idx(v, 31);
-            round_carry[r] = carry;
-            if (r == 0) carry = rt;
-            else carry = scan_op(p, carry, rt);
-          }
-          if (lane == 0) sm_v[warp] = carry;
-          SCAN_SYNC();
-          elt_t wbase = excl;             // everything before this warp's part: tile prefix, then earlier warps
-          bool hwb = hexcl;
-          for (int w = 0; w < warp; ++w) scan_join(p, wbase, hwb, sm_v[w], true);
-#pragma unroll
-          for (int r = 0; r < SCAN_ROUNDS; ++r) {
-            const int e = warp * SCAN_WARP_ELEMS + r * 128 + lane * 4;
-            const i64 q = tt * SCAN_TILE + e;
-            elt_t pre = wbase;
-            bool hpre = hwb;
-            scan_join(p, pre, hpre, round_carry[r], r > 0);
-            scan_join(p, pre, hpre, lane_excl[r], lane > 0);
-            elt_t o[4];
-#pragma unroll
-            for (int k = 0; k < 4; ++k) {
-#if ACC_SCAN_MODE == 0
-              o[k] = hpre ? scan_op(p, pre, item[r][k]) : item[r][k];
-#else
-              if (k == 0) o[k] = pre;                                // the seed guarantees a prefix exists
-              else o[k] = scan_op(p, pre, item[r][k - 1]);
-#endif
-            }
-#if ACC_SCAN_MODE == 1 && ACC_RIGHT
-            const i64 pos0 = out_row + n - q;
-#elif ACC_RIGHT
-            const i64 pos0 = out_row + n - 1 - q;
-#else
-            const i64 pos0 = out_row + q;
-#endif
-#if ACC_RIGHT
-            elt_t w[4] = {o[3], o[2], o[1], o[0]};
-            OUT0_store4(p, pos0 - 3, w);
-#else
-            OUT0_store4(p, pos0, o);
-#endif
-          }
-#if ACC_SCAN_MODE != 0
-          if (tid == 0 && tt == p.tiles_per_row - 1) {
-            const elt_t tot = scan_op(p, excl, slot_agg[fs]);
-#if ACC_SCAN_MODE == 1
-#if ACC_RIGHT
-            OUT0_store(p, row * (n + 1), tot);
-#else
-            OUT0_store(p, row * (n + 1) + n, tot);
-#endif
-#else
-            OUT1_store(p, row, tot);
-#endif
-          }
-#endif
-          SCAN_MARK(T, 4);   // stores issued
+          ctl_act = ring_ldv(&sh_fail) ? RING_ACT_EXIT : RING_ACT_FIN;
         }
-        SCAN_SYNC();                     // everyone is done reading the slot
-        if (tid == 0) fetch(fs, pos_fin + SCAN_SLOTS);
-        pos_fin += 1;
+        SCAN_SYNC();
+        if (ctl_act == RING_ACT_EXIT) break;
+        // (the data was seen complete by the reducers, whose state change this thread observed
+        // through thread 0 and the barrier; testing the barrier again costs nothing and makes the
+        // bulk copy's writes visible to this thread in its own right)
+        ring_mbar_try_wait(&full_bar[fs], slot_parity[fs]);
+        SCAN_MARK(T, 5);   // finish starts
+        const unsigned char* base = scan_ring_smem + (size_t)fs * RING_SLOT_BYTES;
+        const elt_t excl = slot_excl[fs];
+        const bool hexcl = slot_hexcl[fs] != 0;
+#if ACC_SCAN_MODE == 1
+        const i64 out_row = row * (n + 1);
+#else
+        const i64 out_row = row * n;
+#endif
+        const i64 warp_q0 = tt * SCAN_TILE + (i64)warp * SCAN_WARP_ELEMS;
+        elt_t item[SCAN_ROUNDS][4];
+#pragma unroll
+        for (int r2 = 0; r2 < SCAN_ROUNDS; ++r2) {
+          const int e = warp * SCAN_WARP_ELEMS + r2 * 128 + lane * 4;
+          const i64 q = warp_q0 + r2 * 128 + lane * 4;
+#if ACC_RIGHT
+          elt_t t4[4];
+          D0_get4_sm(p, row, n - 4 - q, base, SCAN_TILE - 4 - e, t4);
+#pragma unroll
+          for (int k = 0; k < 4; ++k) item[r2][k] = t4[3 - k];
+#else
+          D0_get4_sm(p, row, q, base, e, item[r2]);
+#endif
+#pragma unroll
+          for (int k = 1; k < 4; ++k) item[r2][k] = scan_op(p, item[r2][k - 1], item[r2][k]);
+        }
+        elt_t lane_excl[SCAN_ROUNDS], round_carry[SCAN_ROUNDS];
+        elt_t carry;
+#pragma unroll
+        for (int r2 = 0; r2 < SCAN_ROUNDS; ++r2) {
+          elt_t v = item[r2][3];
+#pragma unroll
+          for (int d = 1; d < 32; d <<= 1) {
+            const elt_t o = acc_shfl_up(v, d);
+            if (lane >= d) v = scan_op(p, o, v);
+          }
+          lane_excl[r2] = acc_shfl_up(v, 1);
+          const elt_t rtot = acc_shfl_idx(v, 31);
+          round_carry[r2] = carry;
+          if (r2 == 0) carry = rtot;
+          else carry = scan_op(p, carry, rtot);
+        }
+        if (lane == 0) sm_v[warp] = carry;
+        SCAN_SYNC();
+        elt_t wbase = excl;             // everything before this warp's part: tile prefix, then earlier warps
+        bool hwb = hexcl;
+        for (int w = 0; w < warp; ++w) scan_join(p, wbase, hwb, sm_v[w], true);
+#pragma unroll
+        for (int r2 = 0; r2 < SCAN_ROUNDS; ++r2) {
+          const int e = warp * SCAN_WARP_ELEMS + r2 * 128 + lane * 4;
+          const i64 q = tt * SCAN_TILE + e;
+          elt_t pre = wbase;
+          bool hpre = hwb;
+          scan_join(p, pre, hpre, round_carry[r2], r2 > 0);
+          scan_join(p, pre, hpre, lane_excl[r2], lane > 0);
+          elt_t o[4];
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+#if ACC_SCAN_MODE == 0
+            o[k] = hpre ? scan_op(p, pre, item[r2][k]) : item[r2][k];
+#else
+            if (k == 0) o[k] = pre;                                // the seed guarantees a prefix exists
+            else o[k] = scan_op(p, pre, item[r2][k - 1]);
+#endif
+          }
+#if ACC_SCAN_MODE == 1 && ACC_RIGHT
+          const i64 pos0 = out_row + n - q;
+#elif ACC_RIGHT
+          const i64 pos0 = out_row + n - 1 - q;
+#else
+          const i64 pos0 = out_row + q;
+#endif
+#if ACC_RIGHT
+          elt_t w4[4] = {o[3], o[2], o[1], o[0]};
+          OUT0_store4(p, pos0 - 3, w4);
+#else
+          OUT0_store4(p, pos0, o);
+#endif
+        }
+#if ACC_SCAN_MODE != 0
+        if (tid == 0 && tt == p.tiles_per_row - 1) {
+          const elt_t tot = scan_op(p, excl, slot_agg[fs]);
+#if ACC_SCAN_MODE == 1
+#if ACC_RIGHT
+          OUT0_store(p, row * (n + 1), tot);
+#else
+          OUT0_store(p, row * (n + 1) + n, tot);
+#endif
+#else
+          OUT1_store(p, row, tot);
+#endif
+        }
+#endif
+        SCAN_MARK(T, 4);   // stores issued
       }
-      if (act == 0) __nanosleep(64);
-      SCAN_SYNC();
+      SCAN_SYNC();                     // everyone is done reading the slot (and sm_v)
+      if (tid == 0) fetch(fs, r + SCAN_SLOTS);
+      SCAN_SYNC();                     // the slot's next tile is known to every finisher
     }
   }
   // everybody meets here; the look-back warp leaves its loop when it sees a tile past the end,
