@@ -193,7 +193,7 @@ std::map<std::string, std::string> scan_ring_variant(const RingShape& r, int64_t
 struct Stencil2dShape { int warps, rows, minb, depth; };
 Stencil2dShape stencil2d_shape() {
   auto tune = [](const char* name, int dflt) { const char* e = getenv(name); return e && *e ? atoi(e) : dflt; };
-  return {tune("ACCELERATE_B200_ST2_WARPS", 4), tune("ACCELERATE_B200_ST2_ROWS", 64), tune("ACCELERATE_B200_ST2_MIN_BLOCKS", 1),
+  return {tune("ACCELERATE_B200_ST2_WARPS", 4), tune("ACCELERATE_B200_ST2_ROWS", 32), tune("ACCELERATE_B200_ST2_MIN_BLOCKS", 1),
           tune("ACCELERATE_B200_ST2_DEPTH", 4)};
 }
 std::map<std::string, std::string> stencil2d_variant() {
@@ -926,7 +926,7 @@ void Program::run(const std::vector<DevArrayP>& inputs, std::vector<DevArrayP>& 
         L.named["tiles2"] = tiles2;
         L.named["vec"] = (o[2] % 4 == 0 && out->aligned16()) ? 1 : 0;
         if (rank == 2 && o[1] < 2000000000 && o[2] < 2000000000 && !getenv("ACCELERATE_B200_STENCIL_SMEM")) {
-          // register-window kernel: warp tasks of 128 columns x 64 rows
+          // register-window kernel: warp tasks of 128 columns x ST2_ROWS (32) rows
           const Stencil2dShape shp = stencil2d_shape();
           const int warps = shp.warps, rows = shp.rows;
           const int64_t strips = (o[2] + 119) / 120, rowblocks = (o[1] + rows - 1) / rows;  // 120 output columns per warp

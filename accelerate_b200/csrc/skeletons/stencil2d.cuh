@@ -25,7 +25,7 @@
 #define ST2_WARPS 4
 #endif
 #ifndef ST2_ROWS
-#define ST2_ROWS 64
+#define ST2_ROWS 32
 #endif
 #ifndef ST2_MIN_BLOCKS
 #define ST2_MIN_BLOCKS 1

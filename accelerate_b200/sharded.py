@@ -93,12 +93,31 @@ class GpuExecutor:
         v._keepalive = a
         return v
 
+    def rows_view(self, a, lo, hi):
+        """Rows [lo, hi) of a rank-2 array as a view (rows are contiguous: no copy)."""
+        cols = a.shape[1]
+        ptrs = [a.devptr(k) + lo * cols * np.dtype(L.NP_OF[t]).itemsize for k, t in enumerate(a.leaf_types)]
+        v = self.ctx.wrap(a.elt, (hi - lo, cols), ptrs)
+        v._keepalive = a
+        return v
+
     def collective(self):
         """Context in which torch collectives are ordered after this executor's kernels."""
         return torch.cuda.stream(self.stream)
 
     def sync(self):
         self.ctx.sync()
+
+
+class HaloSlab:
+    """A row slab kept resident with room for its neighbours' halo rows: ``ext`` has
+    ``top + rows + bot`` rows, the slab's own rows start at ``top``.  Stencils over
+    several GPUs take and return this layout without copying."""
+
+    def __init__(self, ext, top, rows, bot):
+        self.ext, self.top, self.rows, self.bot = ext, top, rows, bot
+        self.shape = (rows, ext.shape[1])
+        self.elt = ext.elt
 
 
 class Sharded:
@@ -225,58 +244,62 @@ class Sharded:
         return out
 
     # -- stencils -----------------------------------------------------------------------
-    def stencil_iterate(self, f, boundary, slab, iterations, radius=1, key="stencil"):
-        """Apply a rank-2 stencil ``iterations`` times to an array split into row slabs.
-        Interior ranks keep ``radius`` halo rows on either side of their slab; the halos are
-        refreshed from the neighbours before each application (wrap boundaries also connect
-        the first and last rank).  Returns this rank's slab of the result."""
+    def _neighbours(self, boundary):
         r, G = self.rank, self.world
         wrap = boundary.kind == "wrap" and G > 1
         up = (r - 1) % G if (r > 0 or wrap) else None
         down = (r + 1) % G if (r < G - 1 or wrap) else None
+        return up, down
+
+    def halo_slab(self, slab, boundary, radius=1, key="halo"):
+        """Copy a plain row slab into the resident layout with halo rows (done once, when the
+        array is distributed)."""
+        if isinstance(slab, HaloSlab):
+            return slab
+        up, down = self._neighbours(boundary)
         rows, cols = slab.shape
         top, bot = (radius if up is not None else 0), (radius if down is not None else 0)
-        if G == 1:
+        if top == 0 and bot == 0:
+            return HaloSlab(slab, 0, rows, 0)
+        ext = self.ex.run((key, "extend", top, bot), lambda x: L.generate(L.index(rows + top + bot, cols),
+                          lambda ix: L.cond(L.land(ix[0] >= top, ix[0] < top + rows), x[L.index(L.min_(L.max_(ix[0] - top, 0), rows - 1), ix[1])],
+                                            L.lift(0, slab.elt)), slab.elt), [slab])
+        return HaloSlab(ext, top, rows, bot)
+
+    def stencil_iterate(self, f, boundary, slab, iterations, radius=1, key="stencil"):
+        """Apply a rank-2 stencil ``iterations`` times to an array split into row slabs.
+        Interior ranks keep ``radius`` halo rows on either side of their slab; the halos are
+        refreshed from the neighbours before each application (wrap boundaries also connect
+        the first and last rank).  ``slab`` is a plain slab (copied into the halo layout
+        first) or a ``HaloSlab``.  Returns this rank's slab of the result, a view of the last
+        application's output."""
+        if self.world == 1 and not isinstance(slab, HaloSlab):
             cur = slab
             for _ in range(iterations):
                 cur = self.ex.run((key, "it"), lambda x: L.stencil(f, boundary, x), [cur])
             return cur
-        ext = self.ex.run((key, "extend", top, bot), lambda x: L.generate(L.index(rows + top + bot, cols),
-                          lambda ix: L.cond(L.land(ix[0] >= top, ix[0] < top + rows), x[L.index(L.min_(L.max_(ix[0] - top, 0), rows - 1), ix[1])],
-                                            L.lift(0, slab.elt)), slab.elt), [slab])
+        h = self.halo_slab(slab, boundary, radius, key)
+        up, down = self._neighbours(boundary)
+        ext = h.ext
+        cols = ext.shape[1]
         for _ in range(iterations):
-            self._exchange_halos(ext, rows, cols, top, bot, up, down, radius)
+            self._exchange_halos(ext, h.rows, cols, h.top, h.bot, up, down, radius)
             ext = self.ex.run((key, "it"), lambda x: L.stencil(f, boundary, x), [ext])
-        return self._rows(ext, top, top + rows)
+        return self.ex.rows_view(ext, h.top, h.top + h.rows)
 
     def stencil2(self, f, b1, slab1, b2, slab2, radius=1, key="stencil2"):
-        """One application of a rank-2 ``stencil2`` to two arrays split into the same row slabs."""
-        r, G = self.rank, self.world
-        if G == 1:
+        """One application of a rank-2 ``stencil2`` to two arrays split into the same row slabs
+        (plain slabs or ``HaloSlab``s)."""
+        if self.world == 1 and not isinstance(slab1, HaloSlab) and not isinstance(slab2, HaloSlab):
             return self.ex.run((key, "single"), lambda x, y: L.stencil2(f, b1, x, b2, y), [slab1, slab2])
-        exts = []
-        geo = None
-        for slab, b in ((slab1, b1), (slab2, b2)):
-            wrap = b.kind == "wrap"
-            up = (r - 1) % G if (r > 0 or wrap) else None
-            down = (r + 1) % G if (r < G - 1 or wrap) else None
-            rows, cols = slab.shape
-            top, bot = (radius if up is not None else 0), (radius if down is not None else 0)
-            ext = self.ex.run((key, "extend", top, bot), lambda x: L.generate(L.index(rows + top + bot, cols),
-                              lambda ix: L.cond(L.land(ix[0] >= top, ix[0] < top + rows), x[L.index(L.min_(L.max_(ix[0] - top, 0), rows - 1), ix[1])],
-                                                L.lift(0, slab.elt)), slab.elt), [slab])
-            self._exchange_halos(ext, rows, cols, top, bot, up, down, radius)
-            exts.append(ext)
-            if geo is None:
-                geo = (top, rows)
-            elif geo != (top, rows):
-                raise ValueError("stencil2 over slabs needs the same halo layout for both arrays")
-        out = self.ex.run((key, "apply"), lambda x, y: L.stencil2(f, b1, x, b2, y), exts)
-        return self._rows(out, geo[0], geo[0] + geo[1])
-
-    def _rows(self, arr, lo, hi):
-        cols = arr.shape[1]
-        return self.ex.run(("rows", lo, hi), lambda x: L.backpermute(L.index(hi - lo, cols), lambda ix: L.index(ix[0] + lo, ix[1]), x), [arr])
+        hs = [self.halo_slab(slab1, b1, radius, key), self.halo_slab(slab2, b2, radius, key)]
+        if (hs[0].top, hs[0].rows, hs[0].bot) != (hs[1].top, hs[1].rows, hs[1].bot):
+            raise ValueError("stencil2 over slabs needs the same halo layout for both arrays")
+        for h, b in zip(hs, (b1, b2)):
+            up, down = self._neighbours(b)
+            self._exchange_halos(h.ext, h.rows, h.ext.shape[1], h.top, h.bot, up, down, radius)
+        out = self.ex.run((key, "apply"), lambda x, y: L.stencil2(f, b1, x, b2, y), [hs[0].ext, hs[1].ext])
+        return self.ex.rows_view(out, hs[0].top, hs[0].top + hs[0].rows)
 
     def _exchange_halos(self, ext, rows, cols, top, bot, up, down, radius):
         t = self.ex.tensor(ext)

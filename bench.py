@@ -171,7 +171,8 @@ class Bound:
         dev = [self.ctx.from_host(self.host[k]) for k in self.order]
         outs = self.ctx.execute(self.prog.text, dev, len(self.prog.outputs))
         res = []
-        for o, buf in zip(outs, out_bufs):
+        for k, o in enumerate(outs):
+            buf = out_bufs[k] if out_bufs is not None else None
             res.append(o.download(out=[buf] if buf is not None else None))
         return res
 
@@ -193,6 +194,26 @@ class ShardedBound:
             self.aux["defaults"] = ex.from_host(np.zeros(self.w.bins, np.int32))
         if name == "permute_add_f32":
             self.aux["defaults"] = ex.from_host(np.zeros(self.w.bins, np.float32))
+        # stencil inputs are resident as row slabs with room for the neighbours' halo rows
+        if name == "jacobi5_clamp_x100_f32":
+            self.dev = [self.sh.halo_slab(self.dev[0], A.clamp, key="c4a")]
+        if name == "stencil2_gauss_mirror_f32":
+            self.dev = [self.sh.halo_slab(x, A.mirror, key="c4b") for x in self.dev]
+
+    def run_e2e(self, out_bufs):
+        """Host shard in, this rank's part of the result back to the host."""
+        for d in (self.dev or []):
+            if hasattr(d, "free"):
+                d.free()
+        self.upload()
+        r = self.run()
+        outs = list(r) if isinstance(r, (list, tuple)) else [r]
+        res = []
+        for k, o in enumerate(outs):
+            buf = out_bufs[k] if out_bufs is not None and k < len(out_bufs) else None
+            res.append(o.download(out=[buf] if buf is not None else None))
+        self.dev = None
+        return res
 
     def run(self):
         sh, d, name = self.sh, self.dev, self.w.name
@@ -412,7 +433,7 @@ def main():
 
     # end to end: pinned host buffers in, results back to pinned host buffers
     e2e = None
-    if not args.no_e2e and world == 1:
+    if not args.no_e2e:
         h2d = d2h = 0
         pinned_in, outs_buf = [], []
         for b in bound:
@@ -425,13 +446,14 @@ def main():
         for b, hs in zip(bound, pinned_in):
             b.host_saved, b.host = b.host, [t.numpy() for t in hs]
             for d in b.dev:
-                d.free()
+                if hasattr(d, "free"):
+                    d.free()
             b.dev = None
         ctx.sync()
         # one untimed pass to size the output buffers
         shapes = []
         for b in bound:
-            r = b.run_e2e([None] * len(b.prog.outputs))
+            r = b.run_e2e(None)
             bufs = []
             for x in r:
                 t = torch.empty(x.shape, dtype=torch.from_numpy(np.empty(0, x.dtype)).dtype, pin_memory=True)
@@ -455,10 +477,40 @@ def main():
             t = torch.tensor([ms], device="cuda")
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
             ms = float(t.item())
-        h2d = (s1["h2d_bytes"] - s0["h2d_bytes"]) // n_e2e
-        d2h = (s1["d2h_bytes"] - s0["d2h_bytes"]) // n_e2e
+        h2d = (s1["h2d_bytes"] - s0["h2d_bytes"]) // n_e2e * world      # every rank copies a shard of the same size
+        d2h = (s1["d2h_bytes"] - s0["d2h_bytes"]) // n_e2e * world
         e2e = {"value": elements_step * n_e2e / (ms * 1e-3), "unit": "elements/s", "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h),
                "ms_per_step": ms / n_e2e, "wall_ms_per_step": wall * 1e3 / n_e2e, "steps": n_e2e}
+
+    # configs[0] (dotp) beside the suite: the reference's own CPU-sized case, and the same fused
+    # zipWith+fold at a size where bandwidth rather than launch latency decides (not part of `value`)
+    c0 = None
+    if world == 1 and not args.only and args.scale == 0:
+        c0 = {}
+        g = np.random.default_rng(42)
+        for n in (1 << 20, 1 << 28):
+            hx = tiled(lambda m: g.uniform(-1, 1, m), n, np.float32)
+            hy = tiled(lambda m: g.uniform(-1, 1, m), n, np.float32)
+            w0 = Workload("dotp", "configs[0]", [], lambda x, y: A.fold(add, 0.0, A.zipWith(lambda a, b: a * b, x, y)), n, 8 * n, "acc_fold_all", 1)
+            b0 = Bound(ctx, w0, [hx, hy])
+            b0.upload()
+            for _ in range(3):
+                b0.run()
+            reps = 20
+            ea, eb = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            barrier()
+            ea.record(stream)
+            for _ in range(reps):
+                b0.run()
+            eb.record(stream)
+            barrier()
+            ms = ea.elapsed_time(eb) / reps
+            gbs = 8 * n / (ms * 1e-3) / 1e9
+            c0[f"dotp_f32_2^{n.bit_length() - 1}"] = {"ms": round(ms, 4), "elements_per_s": n / (ms * 1e-3), "achieved_gbs": round(gbs, 1),
+                                                   "frac_of_hbm_peak": round(gbs / peak, 4),
+                                                   "note": "8 MiB of input: L2-resident and launch-latency bound" if n == 1 << 20 else "2 GiB of input"}
+            for d in b0.dev:
+                d.free()
 
     cb = None
     if rank == 0 and world == 1 and not args.no_cpu:
@@ -473,7 +525,8 @@ def main():
                 "config": {"workload": "configs[1-4] skeleton suite" + (f" / 2^{args.scale}" if args.scale else ""),
                            "l2": "every input is larger than L2 (126 MB); no flush", "per_gpu_elements_per_step": sum(w.elements for w in ws),
                            "parallelism": f"dp{world}", "setup_s": round(t_gen, 1)},
-                "roofline": roofline, "per_skeleton": per, "gpu_launches": int(launches), "clocks": clocks, "e2e": e2e, "cpu_baseline": cb}
+                "roofline": roofline, "per_skeleton": per, "gpu_launches": int(launches), "clocks": clocks, "e2e": e2e, "cpu_baseline": cb,
+                "config0_dotp": c0}
         print(json.dumps(line))
     if dist is not None:
         dist.destroy_process_group()

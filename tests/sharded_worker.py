@@ -53,6 +53,9 @@ class OracleExecutor:
     def slice1d(self, a, lo, hi):
         return HostArray([x[lo:hi] for x in a.leaves], a.elt)
 
+    def rows_view(self, a, lo, hi):
+        return HostArray([x[lo:hi] for x in a.leaves], a.elt)
+
     def collective(self):
         import contextlib
         return contextlib.nullcontext()
@@ -137,6 +140,16 @@ def main(rank, world, port):
     parts = [None] * world
     dist.all_gather_object(parts, out)
     check("stencil2", np.concatenate(parts), oracle.run(A.stencil2(f2, A.mirror, grid, A.mirror, grid2)))
+    # the same from the resident halo layout (slabs distributed once with room for halo rows)
+    h1, h2 = sh.halo_slab(slab, A.mirror), sh.halo_slab(slab2, A.mirror)
+    out = ex.to_host(sh.stencil2(f2, A.mirror, h1, A.mirror, h2))
+    parts = [None] * world
+    dist.all_gather_object(parts, out)
+    check("stencil2-halo-layout", np.concatenate(parts), oracle.run(A.stencil2(f2, A.mirror, grid, A.mirror, grid2)))
+    out = ex.to_host(sh.stencil_iterate(jac, A.clamp, sh.halo_slab(slab, A.clamp), 2, key="sthalo"))
+    parts = [None] * world
+    dist.all_gather_object(parts, out)
+    check("stencil-halo-layout", np.concatenate(parts), oracle.run(A.stencil(jac, A.clamp, A.stencil(jac, A.clamp, A.use(grid)))))
     # segment split falls on segment boundaries
     off = np.concatenate([[0], np.cumsum(rng.integers(0, 9, size=50))])
     cuts = split_segments(off, world)
