@@ -46,6 +46,7 @@ def lib():
         l.b200_array_wrap.argtypes = [vp, cp, ctypes.c_int, i64p, ctypes.POINTER(vp), u64p]
         l.b200_array_upload.argtypes = [vp, ctypes.c_uint64, ctypes.c_int, vp, ctypes.c_size_t]
         l.b200_array_download.argtypes = [vp, ctypes.c_uint64, ctypes.c_int, vp, ctypes.c_size_t]
+        l.b200_array_adopt_host.argtypes = [vp, ctypes.c_uint64, ctypes.c_int, vp, ctypes.c_size_t]
         l.b200_array_free.argtypes = [vp, ctypes.c_uint64]
         l.b200_array_rank.argtypes = [vp, ctypes.c_uint64, ctypes.POINTER(ctypes.c_int)]
         l.b200_array_shape.argtypes = [vp, ctypes.c_uint64, i64p]
@@ -120,6 +121,14 @@ class DeviceArray:
             _check(lib().b200_array_upload(self.ctx.h, self.id, k, a.ctypes.data, a.nbytes))
         return self
 
+    def adopt_host(self, leaves):
+        """Lazy upload: the host arrays are copied when the array is first used on the device;
+        they are kept alive by this object until then."""
+        self._adopted = [np.ascontiguousarray(a) for a in leaves]
+        for k, a in enumerate(self._adopted):
+            _check(lib().b200_array_adopt_host(self.ctx.h, self.id, k, a.ctypes.data, a.nbytes))
+        return self
+
     def download(self, out=None):
         """Host copy: an ndarray (scalar elements) or a tuple of ndarrays."""
         res = []
@@ -172,6 +181,14 @@ class Context:
         if elt is None:
             elt = tuple(L.TY_OF_NP[x.dtype] for x in leaves) if isinstance(a, (tuple, list)) else L.TY_OF_NP[leaves[0].dtype]
         return self.array(elt, leaves[0].shape).upload(leaves)
+
+    def from_host_lazy(self, a, elt=None):
+        """As ``from_host``, but the copy happens when the array is first used (``b200_array_adopt_host``)."""
+        leaves = [np.ascontiguousarray(x) for x in (a if isinstance(a, (tuple, list)) else [a])]
+        leaves = [x.view(np.uint8) if x.dtype == np.bool_ else x for x in leaves]
+        if elt is None:
+            elt = tuple(L.TY_OF_NP[x.dtype] for x in leaves) if isinstance(a, (tuple, list)) else L.TY_OF_NP[leaves[0].dtype]
+        return self.array(elt, leaves[0].shape).adopt_host(leaves)
 
     def wrap(self, elt, shape, ptrs):
         """Adopt caller-owned device memory (one pointer per leaf)."""

@@ -152,6 +152,7 @@ int b200_array_upload(b200_ctx* ctx, uint64_t id, int leaf, const void* host, si
   DevArrayP a = lookup(c, id);
   if (leaf < 0 || (size_t)leaf >= a->leaf.size()) throw Error(B200_ERR_ARG, "leaf index out of range");
   if (bytes != a->leaf[leaf]->bytes) throw Error(B200_ERR_ARG, "upload size does not match the array");
+  if ((size_t)leaf < a->pending.size()) a->pending[leaf] = nullptr;      // an explicit upload replaces an adopted payload
   if (bytes) {
     if (!host) throw Error(B200_ERR_ARG, "null host pointer");
     c.check(cudaMemcpyAsync(a->leaf[leaf]->ptr, host, bytes, cudaMemcpyHostToDevice, c.stream), "cudaMemcpyAsync(H2D)");
@@ -159,6 +160,35 @@ int b200_array_upload(b200_ctx* ctx, uint64_t id, int leaf, const void* host, si
     c.check(cudaStreamSynchronize(c.stream), "cudaStreamSynchronize");
     c.h2d += (long long)bytes;
   }
+  B200_END
+}
+
+// Copy adopted host payloads now: the array is about to be used on the device (caller holds c.mu).
+static void materialise(Ctx& c, DevArray& a) {
+  bool any = false;
+  for (size_t k = 0; k < a.pending.size(); ++k) {
+    if (!a.pending[k]) continue;
+    const size_t bytes = a.leaf[k]->bytes;
+    c.check(cudaMemcpyAsync(a.leaf[k]->ptr, a.pending[k], bytes, cudaMemcpyHostToDevice, c.stream), "cudaMemcpyAsync(H2D)");
+    c.h2d += (long long)bytes;
+    a.pending[k] = nullptr;
+    any = true;
+  }
+  // the owner of the host buffers may let go of them as soon as the call that triggered the copy returns
+  if (any) c.check(cudaStreamSynchronize(c.stream), "cudaStreamSynchronize");
+}
+
+int b200_array_adopt_host(b200_ctx* ctx, uint64_t id, int leaf, const void* host, size_t bytes) {
+  B200_TRY
+  if (!ctx) throw Error(B200_ERR_ARG, "null context");
+  Ctx& c = ctx->c;
+  std::lock_guard<std::mutex> g(c.mu);
+  DevArrayP a = lookup(c, id);
+  if (leaf < 0 || (size_t)leaf >= a->leaf.size()) throw Error(B200_ERR_ARG, "leaf index out of range");
+  if (bytes != a->leaf[leaf]->bytes) throw Error(B200_ERR_ARG, "payload size does not match the array");
+  if (bytes && !host) throw Error(B200_ERR_ARG, "null host pointer");
+  if (a->pending.size() != a->leaf.size()) a->pending.assign(a->leaf.size(), nullptr);
+  a->pending[leaf] = bytes ? host : nullptr;
   B200_END
 }
 
@@ -183,6 +213,7 @@ int b200_array_download(b200_ctx* ctx, uint64_t id, int leaf, void* host, size_t
   DevArrayP a = lookup(c, id);
   if (leaf < 0 || (size_t)leaf >= a->leaf.size()) throw Error(B200_ERR_ARG, "leaf index out of range");
   if (bytes != a->leaf[leaf]->bytes) throw Error(B200_ERR_ARG, "download size does not match the array");
+  materialise(c, *a);
   if (bytes) {
     if (!host) throw Error(B200_ERR_ARG, "null host pointer");
     c.check(cudaMemcpyAsync(host, a->leaf[leaf]->ptr, bytes, cudaMemcpyDeviceToHost, c.stream), "cudaMemcpyAsync(D2H)");
@@ -233,6 +264,8 @@ int b200_array_devptr(b200_ctx* ctx, uint64_t id, int leaf, void** ptr) {
   std::lock_guard<std::mutex> g(ctx->c.mu);
   DevArrayP a = lookup(ctx->c, id);
   if (leaf < 0 || (size_t)leaf >= a->leaf.size()) throw Error(B200_ERR_ARG, "leaf index out of range");
+  ctx->c.check(cudaSetDevice(ctx->c.device), "cudaSetDevice");
+  materialise(ctx->c, *a);
   *ptr = a->leaf[leaf]->ptr;
   B200_END
 }
@@ -267,6 +300,7 @@ int b200_program_run(b200_program* prog, const uint64_t* in_ids, int n_in, uint6
   c.check(cudaSetDevice(c.device), "cudaSetDevice");
   std::vector<DevArrayP> ins, outs;
   for (int k = 0; k < n_in; ++k) ins.push_back(lookup(c, in_ids[k]));
+  for (auto& a : ins) materialise(c, *a);
   prog->p.run(ins, outs);
   if ((int)outs.size() != n_out) throw Error(B200_ERR_ARG, "program yields " + std::to_string(outs.size()) + " arrays");
   for (int k = 0; k < n_out; ++k) {

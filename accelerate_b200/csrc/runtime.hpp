@@ -58,6 +58,8 @@ struct DevArray {
   std::vector<Ty> leaf_ty;
   std::vector<int64_t> shape;
   std::vector<std::shared_ptr<Buffer>> leaf;
+  // host payloads adopted but not copied yet (one per leaf, nullptr = nothing pending)
+  std::vector<const void*> pending;
   int64_t size() const;
   bool aligned16() const;
 };

@@ -263,14 +263,26 @@ class ClockSampler:
         for line in self.proc.stdout:
             self.rows.append([c.strip() for c in line.split(",")])
 
+    def mark(self):
+        """The timed region starts here (the sampler itself is started before the warm-up, so
+        that nvidia-smi is already delivering samples when a short timed region begins)."""
+        self.first = len(self.rows)
+
     def stop(self):
         if self.proc:
             self.proc.terminate()
-        sm = [float(r[0]) for r in self.rows if r and r[0].replace(".", "").isdigit()]
-        mx = [float(r[1]) for r in self.rows if len(r) > 1 and r[1].replace(".", "").isdigit()]
+        first = getattr(self, "first", 0)
+        rows, window = self.rows[first:], "timed region"
+        if len(rows) < 2:
+            # the region was shorter than two sampling periods: add the samples just before it,
+            # taken while the warm-up ran the same kernels
+            rows, window = self.rows[max(0, first - 5):], "timed region and the end of the warm-up"
+        sm = [float(r[0]) for r in rows if r and r[0].replace(".", "").isdigit()]
+        mx = [float(r[1]) for r in rows if len(r) > 1 and r[1].replace(".", "").isdigit()]
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        reasons = [n for k, n in enumerate(names) if any(len(r) > 3 + k and r[3 + k].lower().startswith("active") for r in self.rows)]
-        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None, "reasons": reasons, "samples": len(sm)}
+        reasons = [n for k, n in enumerate(names) if any(len(r) > 3 + k and r[3 + k].lower().startswith("active") for r in rows)]
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None, "reasons": reasons, "samples": len(sm),
+                "window": window}
 
 
 def measured_peaks():
@@ -384,16 +396,17 @@ def main():
         ctx.sync()
 
     # warm-up (compiles kernels on first use)
+    sampler = ClockSampler(local)
+    sampler.start()
     for _ in range(max(args.warmup, 1)):
         for b in bound:
             b.run()
     barrier()
     l0 = ctx.stats()["launches"]
-    sampler = ClockSampler(local)
-    sampler.start()
     ev = [[(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in bound] for _ in range(args.steps)]
     e_start, e_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
+    sampler.mark()
     e_start.record(stream)
     for s in range(args.steps):
         for k, b in enumerate(bound):

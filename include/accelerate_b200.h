@@ -61,6 +61,13 @@ int b200_array_wrap(b200_ctx* ctx, const char* elt_type, int rank, const int64_t
 /* pokeRemote / peekRemote (Array/Remote/Class.hs:58-66): copy one leaf. */
 int b200_array_upload(b200_ctx* ctx, uint64_t id, int leaf, const void* host, size_t bytes);
 int b200_array_download(b200_ctx* ctx, uint64_t id, int leaf, void* host, size_t bytes);
+/* Lazy pokeRemote: remember the host payload of one leaf; it is copied to the device the first time
+ * the array is used (as a program input, by b200_array_devptr or by b200_array_download), as the
+ * reference's memory table uploads an array on its first withRemote (Array/Remote/LRU.hs:140-199).
+ * The payload must stay valid and unchanged until the call that uses the array has returned (the
+ * Haskell side keeps it alive with touchArrayData, Array/Data.hs:250-255).  An explicit
+ * b200_array_upload of the same leaf replaces it. */
+int b200_array_adopt_host(b200_ctx* ctx, uint64_t id, int leaf, const void* host, size_t bytes);
 /* Release (callable from any thread, e.g. a GHC finalizer; Array/Remote/Table.hs:271-284). */
 int b200_array_free(b200_ctx* ctx, uint64_t id);
 int b200_array_rank(b200_ctx* ctx, uint64_t id, int* rank);

@@ -380,3 +380,25 @@ def test_reshape_and_unit():
     check(A.fold(add, 0, A.reshape(A.index(4, 6), x)))
     s = A.fold(add, 0, x)
     check(A.map(lambda v: v + A.the(s), x))
+
+
+def test_adopt_host_uploads_on_first_use(gpu_ctx):
+    # lazy transfer (b200_array_adopt_host): nothing is copied until the array is used
+    from accelerate_b200 import language as L
+    x, y = ints(1000), floats(1000)
+    L.reset_names()
+    px, py = L.param(1, "i32"), L.param(1, "f32")
+    prog = A.build_program(A.zipWith(lambda a, b: A.from_integral(a, "f32") + b, px, py))
+    before = gpu_ctx.stats()["h2d_bytes"]
+    dx, dy = gpu_ctx.from_host_lazy(x), gpu_ctx.from_host_lazy(y)
+    assert gpu_ctx.stats()["h2d_bytes"] == before
+    order = [[px, py].index(next(q for q in (px, py) if q.node is n)) for n in prog.inputs]
+    out, = gpu_ctx.execute(prog.text, [[dx, dy][k] for k in order], 1)
+    assert gpu_ctx.stats()["h2d_bytes"] == before + x.nbytes + y.nbytes
+    assert np.array_equal(out.download(), x.astype(np.float32) + y)
+    # a download alone also triggers the copy; an explicit upload replaces an adopted payload
+    dz = gpu_ctx.from_host_lazy(x)
+    assert np.array_equal(dz.download(), x)
+    dw = gpu_ctx.from_host_lazy(x)
+    dw.upload([x + 1])
+    assert np.array_equal(dw.download(), x + 1)
