@@ -147,10 +147,17 @@ int scan_rounds(const Type& elt) {
   if (const char* e = getenv("ACCELERATE_B200_SCAN_ROUNDS")) r = std::max(1, atoi(e));
   return r;
 }
-std::map<std::string, std::string> scan_variant(const Type& elt) {
+// Short rows: the kernel's time is the latency of one tile plus the look-back chain, so many small
+// tiles that all start at once beat few large ones.
+constexpr int64_t SCAN_SMALL_ELEMS = 1 << 21;
+constexpr int SCAN_SMALL_ROUNDS = 2;
+bool scan_is_small(int64_t total_elems) {
+  return total_elems <= SCAN_SMALL_ELEMS && !getenv("ACCELERATE_B200_SCAN_ROUNDS") && !getenv("ACCELERATE_B200_SCAN_NO_SMALL");
+}
+std::map<std::string, std::string> scan_variant(const Type& elt, bool small = false) {
   size_t bytes = 0;
   for (Ty t : elt.leaves()) bytes += ty_bytes[t];
-  const int rounds = scan_rounds(elt);
+  const int rounds = small ? std::min(scan_rounds(elt), SCAN_SMALL_ROUNDS) : scan_rounds(elt);
   std::string minb = bytes * rounds <= 16 ? "4" : (bytes * rounds <= 64 ? "2" : "1");
   if (const char* e = getenv("ACCELERATE_B200_SCAN_MIN_BLOCKS")) minb = e;
   std::map<std::string, std::string> v = {{"SCAN_MIN_BLOCKS", minb}, {"SCAN_ROUNDS", std::to_string(rounds)}};
@@ -219,8 +226,8 @@ std::vector<std::pair<std::string, std::map<std::string, std::string>>> default_
       break;
     case N_FOLDSEG: v.push_back({"foldseg", {{"FOLDSEG_G", "32"}}}); break;
     case N_SCAN: case N_SCAN2: {
-      {
-        auto sv = scan_variant(n.elt);
+      for (bool small : {false, true}) {
+        auto sv = scan_variant(n.elt, small);
         scan_poll_variant(sv, 1);
         v.push_back({"scan", sv});
       }
@@ -735,7 +742,8 @@ void Program::run(const std::vector<DevArrayP>& inputs, std::vector<DevArrayP>& 
         }
         if (rows == 0 || (mode == 0 && m == 0)) break;
         L.bind_delayed("D0", ext, 0);
-        const int64_t tile = 8 * (int64_t)scan_rounds(n.elt) * 128;
+        const bool small = scan_is_small(rows * m);
+        const int64_t tile = 8 * (int64_t)(small ? std::min(scan_rounds(n.elt), SCAN_SMALL_ROUNDS) : scan_rounds(n.elt)) * 128;
         const int64_t tiles_per_row = std::max<int64_t>(1, (m + tile - 1) / tile);
         const int64_t total_tiles = rows * tiles_per_row;
         const bool right = n.right;
@@ -765,7 +773,7 @@ void Program::run(const std::vector<DevArrayP>& inputs, std::vector<DevArrayP>& 
                                   df.at("D0_STREAM_BYTES") == df.at("SCAN_T_BYTES");
           const int bytes = packed ? atoi(df.at("SCAN_T_BYTES").c_str()) : 0;
           // 8-byte elements halve the elements a ring holds; the register-resident kernel is faster for them
-          const bool want = getenv("ACCELERATE_B200_SCAN_RING") ? true : (bytes <= 4 && !getenv("ACCELERATE_B200_SCAN_NO_RING"));
+          const bool want = getenv("ACCELERATE_B200_SCAN_RING") ? true : (bytes <= 4 && !small && !getenv("ACCELERATE_B200_SCAN_NO_RING"));
           if (one_stream && want && L.fast("D0") && in_vec && out_vec) {
             const RingShape rs = scan_ring_shape(bytes);
             const int rounds = rs.rounds, slots = rs.slots, look = rs.look;
@@ -829,7 +837,7 @@ void Program::run(const std::vector<DevArrayP>& inputs, std::vector<DevArrayP>& 
         }
         if (const char* tpath = getenv("ACCELERATE_B200_SCAN_TRACE")) {
           // diagnostic: per-tile phase timestamps written to a file (8 x u64 per tile)
-          auto var = scan_variant(n.elt);
+          auto var = scan_variant(n.elt, small);
           scan_poll_variant(var, total_tiles);
           var["SCAN_TRACE"] = "1";
           auto tbuf = c.alloc((size_t)total_tiles * 64);
@@ -843,7 +851,7 @@ void Program::run(const std::vector<DevArrayP>& inputs, std::vector<DevArrayP>& 
           if (FILE* f = fopen(tpath, "wb")) { fwrite(host.data(), 8, host.size(), f); fclose(f); }
           break;
         }
-        auto svar = scan_variant(n.elt);
+        auto svar = scan_variant(n.elt, small);
         scan_poll_variant(svar, total_tiles);
         CompiledKernel& k = c.kernel(assemble_source(st.glue, "scan", svar), "acc_scan", 256, 0);
         L.launch(k, total_tiles, 256, 0);

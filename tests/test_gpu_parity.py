@@ -196,8 +196,17 @@ def test_fold1seg_empty_segment_error():
 SCAN_SIZES = [0, 1, 2, 3, 4, 5, 64, 65, 127, 128, 129, 511, 512, 513, 4095, 4096, 4097, 8192, 12289, 50001]
 
 
+@pytest.fixture(params=["auto", "long-row-kernels"])
+def scan_path(request, monkeypatch):
+    """Short rows are scanned with small tiles; the second pass forces the kernels that long rows
+    use (the shared-memory ring, 8192-element tiles) onto the same cases."""
+    if request.param == "long-row-kernels":
+        monkeypatch.setenv("ACCELERATE_B200_SCAN_NO_SMALL", "1")
+    return request.param
+
+
 @pytest.mark.parametrize("n", SCAN_SIZES)
-def test_scans_int(n):
+def test_scans_int(n, scan_path):
     x = ints(n, np.int32, 0, 100)
     if n > 0:
         check(A.scanl1(add, x))
@@ -209,7 +218,7 @@ def test_scans_int(n):
 
 
 @pytest.mark.parametrize("n", [1, 1000, 4096, 70000])
-def test_scans_float_and_i64(n):
+def test_scans_float_and_i64(n, scan_path):
     f = rng.uniform(0, 1, n).astype(np.float32)
     tol = dict(rtol=1e-5 * np.sqrt(n), atol=1e-5 * np.sqrt(n))
     check(list(A.scanl_prime(add, 0.0, f)), **tol)
@@ -225,7 +234,7 @@ def _interval(a, b):
 
 
 @pytest.mark.parametrize("n", [1, 5, 129, 4097, 9000])
-def test_scans_non_commutative(n):
+def test_scans_non_commutative(n, scan_path):
     x = ints(n, np.int64)
     pairs = A.map(lambda v: A.tup(v, v + 1), x)
     check(A.scanl1(_interval, pairs))
@@ -240,7 +249,7 @@ def test_scans_non_commutative(n):
 
 
 @pytest.mark.parametrize("shape", [(1, 1), (3, 5), (31, 257), (4, 4096), (3, 4100), (2, 3, 9), (5, 0), (0, 5), (257, 31)])
-def test_scans_rows(shape):
+def test_scans_rows(shape, scan_path):
     m = ints(shape, np.int32, 0, 100)
     if shape[-1] > 0:
         check(A.scanl1(add, m))
@@ -251,7 +260,7 @@ def test_scans_rows(shape):
     check(list(A.scanr_prime(add, 1, m)))
 
 
-def test_scan_wraps_int32():
+def test_scan_wraps_int32(scan_path):
     x = np.full(5000, 2_000_000_000, np.int32)
     check(A.scanl1(add, x))
 
