@@ -47,6 +47,7 @@ def lib():
         l.b200_array_upload.argtypes = [vp, ctypes.c_uint64, ctypes.c_int, vp, ctypes.c_size_t]
         l.b200_array_download.argtypes = [vp, ctypes.c_uint64, ctypes.c_int, vp, ctypes.c_size_t]
         l.b200_array_adopt_host.argtypes = [vp, ctypes.c_uint64, ctypes.c_int, vp, ctypes.c_size_t]
+        l.b200_array_download_async.argtypes = [vp, ctypes.c_uint64, ctypes.c_int, vp, ctypes.c_size_t]
         l.b200_array_free.argtypes = [vp, ctypes.c_uint64]
         l.b200_array_rank.argtypes = [vp, ctypes.c_uint64, ctypes.POINTER(ctypes.c_int)]
         l.b200_array_shape.argtypes = [vp, ctypes.c_uint64, i64p]
@@ -137,6 +138,14 @@ class DeviceArray:
             _check(lib().b200_array_download(self.ctx.h, self.id, k, a.ctypes.data, a.nbytes))
             res.append(a)
         return res[0] if L.is_scalar(self.elt) else tuple(res)
+
+    def download_async(self, out):
+        """Start copying every leaf into the given (pinned) host arrays on the copy-out stream; the
+        data is there after ``Context.sync()``.  The array may be freed at once."""
+        for k in range(len(self.leaf_types)):
+            a = out[k]
+            _check(lib().b200_array_download_async(self.ctx.h, self.id, k, a.ctypes.data, a.nbytes))
+        return out[0] if L.is_scalar(self.elt) else tuple(out)
 
     def free(self):
         if self.id is not None and self.ctx.h:

@@ -77,6 +77,7 @@ int b200_ctx_create(int device, uint32_t flags, b200_ctx** out) {
                                                     std::to_string(prop.major) + "." + std::to_string(prop.minor));
   c.sm_count = prop.multiProcessorCount;
   c.check(cudaStreamCreateWithFlags(&c.stream, cudaStreamNonBlocking), "cudaStreamCreate");
+  c.check(cudaStreamCreateWithFlags(&c.d2h_stream, cudaStreamNonBlocking), "cudaStreamCreate");
   // keep freed blocks in the stream-ordered pool instead of returning them to the driver
   cudaMemPool_t pool;
   c.check(cudaDeviceGetDefaultMemPool(&pool, device), "cudaDeviceGetDefaultMemPool");
@@ -94,6 +95,7 @@ void b200_ctx_destroy(b200_ctx* ctx) {
   Ctx& c = ctx->c;
   cudaSetDevice(c.device);
   cudaStreamSynchronize(c.stream);
+  cudaStreamSynchronize(c.d2h_stream);
   {
     std::lock_guard<std::mutex> g(c.mu);
     c.arrays.clear();
@@ -104,6 +106,7 @@ void b200_ctx_destroy(b200_ctx* ctx) {
   }
   cudaStreamSynchronize(c.stream);
   cudaFree(c.d_words);
+  cudaStreamDestroy(c.d2h_stream);
   cudaStreamDestroy(c.stream);
   delete ctx;
 }
@@ -223,6 +226,33 @@ int b200_array_download(b200_ctx* ctx, uint64_t id, int leaf, void* host, size_t
   B200_END
 }
 
+int b200_array_download_async(b200_ctx* ctx, uint64_t id, int leaf, void* host, size_t bytes) {
+  B200_TRY
+  if (!ctx) throw Error(B200_ERR_ARG, "null context");
+  Ctx& c = ctx->c;
+  std::lock_guard<std::mutex> g(c.mu);
+  c.check(cudaSetDevice(c.device), "cudaSetDevice");
+  DevArrayP a = lookup(c, id);
+  if (leaf < 0 || (size_t)leaf >= a->leaf.size()) throw Error(B200_ERR_ARG, "leaf index out of range");
+  if (bytes != a->leaf[leaf]->bytes) throw Error(B200_ERR_ARG, "download size does not match the array");
+  materialise(c, *a);
+  if (bytes) {
+    if (!host) throw Error(B200_ERR_ARG, "null host pointer");
+    Buffer& b = *a->leaf[leaf];
+    // the copy waits for everything enqueued on the main stream so far (the array's producer among it)
+    cudaEvent_t produced;
+    c.check(cudaEventCreateWithFlags(&produced, cudaEventDisableTiming), "cudaEventCreate");
+    c.check(cudaEventRecord(produced, c.stream), "cudaEventRecord");
+    c.check(cudaStreamWaitEvent(c.d2h_stream, produced, 0), "cudaStreamWaitEvent");
+    c.check(cudaEventDestroy(produced), "cudaEventDestroy");      // released once it has completed
+    c.check(cudaMemcpyAsync(host, b.ptr, bytes, cudaMemcpyDeviceToHost, c.d2h_stream), "cudaMemcpyAsync(D2H)");
+    if (!b.busy) c.check(cudaEventCreateWithFlags(&b.busy, cudaEventDisableTiming), "cudaEventCreate");
+    c.check(cudaEventRecord(b.busy, c.d2h_stream), "cudaEventRecord");
+    c.d2h += (long long)bytes;
+  }
+  B200_END
+}
+
 int b200_array_free(b200_ctx* ctx, uint64_t id) {
   B200_TRY
   if (!ctx) throw Error(B200_ERR_ARG, "null context");
@@ -316,6 +346,7 @@ int b200_sync(b200_ctx* ctx) {
   Ctx& c = ctx->c;
   std::lock_guard<std::mutex> g(c.mu);
   c.check(cudaSetDevice(c.device), "cudaSetDevice");
+  c.check(cudaStreamSynchronize(c.d2h_stream), "cudaStreamSynchronize");
   check_device_status(c);
   B200_END
 }

@@ -41,8 +41,13 @@ void Ctx::check(CUresult e, const char* what) {
 }
 
 Buffer::~Buffer() {
+  if (ctx && (busy || (owned && ptr))) cudaSetDevice(ctx->device);
+  if (busy && ctx) {
+    // a download may still be reading the buffer on the copy-out stream: the free is ordered after it
+    cudaStreamWaitEvent(ctx->stream, busy, 0);
+    cudaEventDestroy(busy);
+  }
   if (owned && ptr && ctx) {
-    cudaSetDevice(ctx->device);
     cudaFreeAsync(ptr, ctx->stream);
     ctx->allocated -= (long long)bytes;
   }

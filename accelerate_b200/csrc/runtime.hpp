@@ -51,6 +51,7 @@ struct Buffer {
   void* ptr = nullptr;
   size_t bytes = 0;
   bool owned = true;
+  cudaEvent_t busy = nullptr;   // last asynchronous download of this buffer (on the copy-out stream)
   ~Buffer();
 };
 struct DevArray {
@@ -69,6 +70,7 @@ struct Ctx {
   int device = 0;
   int sm_count = 148;
   cudaStream_t stream = nullptr;
+  cudaStream_t d2h_stream = nullptr;   // asynchronous downloads run here, beside kernels and uploads
   Driver drv;
   std::mutex mu;
   std::map<uint64_t, DevArrayP> arrays;

@@ -173,7 +173,8 @@ class Bound:
         res = []
         for k, o in enumerate(outs):
             buf = out_bufs[k] if out_bufs is not None else None
-            res.append(o.download(out=[buf] if buf is not None else None))
+            # results go back on the copy-out stream while the next workload's inputs come in
+            res.append(o.download_async([buf]) if buf is not None else o.download())
         return res
 
 
@@ -211,7 +212,7 @@ class ShardedBound:
         res = []
         for k, o in enumerate(outs):
             buf = out_bufs[k] if out_bufs is not None and k < len(out_bufs) else None
-            res.append(o.download(out=[buf] if buf is not None else None))
+            res.append(o.download_async([buf]) if buf is not None else o.download())
         self.dev = None
         return res
 
@@ -481,6 +482,7 @@ def main():
         for _ in range(n_e2e):
             for b, bufs in zip(bound, shapes):
                 b.run_e2e([t.numpy() for t in bufs])
+        ctx.sync()            # the last results have arrived in host memory
         e1.record(stream)
         barrier()
         wall = time.perf_counter() - t0

@@ -61,6 +61,13 @@ int b200_array_wrap(b200_ctx* ctx, const char* elt_type, int rank, const int64_t
 /* pokeRemote / peekRemote (Array/Remote/Class.hs:58-66): copy one leaf. */
 int b200_array_upload(b200_ctx* ctx, uint64_t id, int leaf, const void* host, size_t bytes);
 int b200_array_download(b200_ctx* ctx, uint64_t id, int leaf, void* host, size_t bytes);
+/* peekRemote without waiting: the copy runs on a second stream, after everything submitted so far, and
+ * beside later uploads and kernels (PCIe carries both directions at once).  `host` should be pinned
+ * memory and must not be read before b200_sync has returned; the array may be freed right away (the
+ * release is ordered after the copy).  peekRemote (Array/Remote/Class.hs:61-62) of a backend that
+ * works asynchronously; the reference tracks such work as a `Task` polled for completion
+ * (Array/Remote/LRU.hs:101-110), here b200_sync is the completion point. */
+int b200_array_download_async(b200_ctx* ctx, uint64_t id, int leaf, void* host, size_t bytes);
 /* Lazy pokeRemote: remember the host payload of one leaf; it is copied to the device the first time
  * the array is used (as a program input, by b200_array_devptr or by b200_array_download), as the
  * reference's memory table uploads an array on its first withRemote (Array/Remote/LRU.hs:140-199).
@@ -92,7 +99,7 @@ int b200_program_num_outputs(b200_program* prog, int* n);
  * download. */
 int b200_program_run(b200_program* prog, const uint64_t* in_ids, int n_in, uint64_t* out_ids, int n_out);
 
-/* Wait for all work of the context and report device-side failures. */
+/* Wait for all work of the context (asynchronous downloads included) and report device-side failures. */
 int b200_sync(b200_ctx* ctx);
 
 /* Counters (monitoring.c:26-32 in the reference's cbits): [0] kernels launched,

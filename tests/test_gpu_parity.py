@@ -411,3 +411,23 @@ def test_adopt_host_uploads_on_first_use(gpu_ctx):
     dw = gpu_ctx.from_host_lazy(x)
     dw.upload([x + 1])
     assert np.array_equal(dw.download(), x + 1)
+
+
+def test_download_async_arrives_after_sync(gpu_ctx):
+    import torch
+    x = ints(1 << 20)
+    d = gpu_ctx.from_host(x)
+    from accelerate_b200 import language as L
+    L.reset_names()
+    px = L.param(1, "i32")
+    prog = A.build_program(A.map(lambda v: v * 3 + 1, px))
+    bufs = []
+    for _ in range(3):
+        out, = gpu_ctx.execute(prog.text, [d], 1)
+        t = torch.empty(x.shape, dtype=torch.int32, pin_memory=True)
+        out.download_async([t.numpy()])
+        out.free()                       # the release is ordered after the copy
+        bufs.append(t)
+    gpu_ctx.sync()
+    for t in bufs:
+        assert np.array_equal(t.numpy(), x * 3 + 1)
