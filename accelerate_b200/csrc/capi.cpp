@@ -99,6 +99,7 @@ void b200_ctx_destroy(b200_ctx* ctx) {
   {
     std::lock_guard<std::mutex> g(c.mu);
     c.arrays.clear();
+    c.reap(true);
     for (auto& k : c.kernels)
       if (k.second.module) c.drv.ModuleUnload(k.second.module);
     c.kernels.clear();
@@ -347,6 +348,7 @@ int b200_sync(b200_ctx* ctx) {
   std::lock_guard<std::mutex> g(c.mu);
   c.check(cudaSetDevice(c.device), "cudaSetDevice");
   c.check(cudaStreamSynchronize(c.d2h_stream), "cudaStreamSynchronize");
+  c.reap(true);
   check_device_status(c);
   B200_END
 }

@@ -41,16 +41,35 @@ void Ctx::check(CUresult e, const char* what) {
 }
 
 Buffer::~Buffer() {
-  if (ctx && (busy || (owned && ptr))) cudaSetDevice(ctx->device);
-  if (busy && ctx) {
-    // a download may still be reading the buffer on the copy-out stream: the free is ordered after it
-    cudaStreamWaitEvent(ctx->stream, busy, 0);
+  if (!ctx) return;
+  if (busy) {
+    cudaSetDevice(ctx->device);
+    if (owned && ptr && cudaEventQuery(busy) != cudaSuccess) {
+      ctx->deferred.push_back({ptr, bytes, busy});     // a download is still reading the buffer
+      return;
+    }
     cudaEventDestroy(busy);
   }
-  if (owned && ptr && ctx) {
+  if (owned && ptr) {
+    cudaSetDevice(ctx->device);
     cudaFreeAsync(ptr, ctx->stream);
     ctx->allocated -= (long long)bytes;
   }
+}
+
+void Ctx::reap(bool wait) {
+  size_t kept = 0;
+  for (auto& d : deferred) {
+    if (wait) cudaEventSynchronize(d.done);
+    if (cudaEventQuery(d.done) == cudaSuccess) {
+      cudaEventDestroy(d.done);
+      cudaFreeAsync(d.ptr, stream);
+      allocated -= (long long)d.bytes;
+    } else {
+      deferred[kept++] = d;
+    }
+  }
+  deferred.resize(kept);
 }
 
 std::shared_ptr<Buffer> Ctx::alloc(size_t bytes) {
@@ -58,6 +77,7 @@ std::shared_ptr<Buffer> Ctx::alloc(size_t bytes) {
   b->ctx = this;
   b->bytes = bytes;
   if (bytes) {
+    if (!deferred.empty()) reap(false);
     check(cudaMallocAsync(&b->ptr, bytes, stream), "cudaMallocAsync");
     allocated += (long long)bytes;
   }

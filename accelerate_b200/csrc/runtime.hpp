@@ -71,6 +71,11 @@ struct Ctx {
   int sm_count = 148;
   cudaStream_t stream = nullptr;
   cudaStream_t d2h_stream = nullptr;   // asynchronous downloads run here, beside kernels and uploads
+  // buffers released while a download was still reading them: freed once that copy has completed,
+  // without making the main stream wait for it
+  struct Deferred { void* ptr; size_t bytes; cudaEvent_t done; };
+  std::vector<Deferred> deferred;
+  void reap(bool wait);
   Driver drv;
   std::mutex mu;
   std::map<uint64_t, DevArrayP> arrays;

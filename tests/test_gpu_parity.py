@@ -426,7 +426,7 @@ def test_download_async_arrives_after_sync(gpu_ctx):
         out, = gpu_ctx.execute(prog.text, [d], 1)
         t = torch.empty(x.shape, dtype=torch.int32, pin_memory=True)
         out.download_async([t.numpy()])
-        out.free()                       # the release is ordered after the copy
+        out.free()                       # the memory is not reused before the copy has completed
         bufs.append(t)
     gpu_ctx.sync()
     for t in bufs:
