@@ -81,6 +81,8 @@ foreign import ccall safe "b200_ctx_create"     c_ctxCreate    :: CInt -> Word32
 foreign import ccall safe "b200_array_new"      c_arrayNew     :: Ptr Ctx -> CString -> CInt -> Ptr Int64 -> Ptr Word64 -> IO CInt
 foreign import ccall safe "b200_array_upload"   c_arrayUpload  :: Ptr Ctx -> Word64 -> CInt -> Ptr () -> CSize -> IO CInt
 foreign import ccall safe "b200_array_download" c_arrayDownload:: Ptr Ctx -> Word64 -> CInt -> Ptr () -> CSize -> IO CInt
+-- copy on a second stream; complete after c_sync
+foreign import ccall safe "b200_array_download_async" c_arrayDownloadAsync :: Ptr Ctx -> Word64 -> CInt -> Ptr () -> CSize -> IO CInt
 -- lazy variant of c_arrayUpload: the payload is copied when the array is first used; keep it alive
 -- (touchArrayData) until the call that uses the array has returned
 foreign import ccall safe "b200_array_adopt_host" c_arrayAdoptHost :: Ptr Ctx -> Word64 -> CInt -> Ptr () -> CSize -> IO CInt
