@@ -145,6 +145,10 @@ class DeviceArray:
         for k in range(len(self.leaf_types)):
             a = out[k]
             _check(lib().b200_array_download_async(self.ctx.h, self.id, k, a.ctypes.data, a.nbytes))
+        if getattr(self, "_keepalive", None) is not None:
+            # a view over memory that another object owns: the library defers the release of an array
+            # it is copying from, but cannot know that this view's memory belongs to a different one
+            self.ctx._inflight.append(self)
         return out[0] if L.is_scalar(self.elt) else tuple(out)
 
     def free(self):
@@ -167,6 +171,7 @@ class Context:
         _check(lib().b200_ctx_create(device, 0, ctypes.byref(self.h)))
         self.device = device
         self._programs = {}
+        self._inflight = []          # views with an asynchronous download under way (kept alive until sync)
 
     def close(self):
         if self.h:
@@ -226,7 +231,10 @@ class Context:
         return [DeviceArray(self, outs[k]) for k in range(n_out)]
 
     def sync(self):
-        _check(lib().b200_sync(self.h))
+        try:
+            _check(lib().b200_sync(self.h))
+        finally:
+            self._inflight = []
 
     def stats(self):
         out = (ctypes.c_int64 * 8)()

@@ -64,7 +64,8 @@ int b200_array_download(b200_ctx* ctx, uint64_t id, int leaf, void* host, size_t
 /* peekRemote without waiting: the copy runs on a second stream, after everything submitted so far, and
  * beside later uploads and kernels (PCIe carries both directions at once).  `host` should be pinned
  * memory and must not be read before b200_sync has returned; the array may be freed right away (its
- * memory is only reused once the copy has completed).  peekRemote (Array/Remote/Class.hs:61-62) of a backend that
+ * memory is only reused once the copy has completed; memory adopted with b200_array_wrap stays the
+ * caller's to keep until then).  peekRemote (Array/Remote/Class.hs:61-62) of a backend that
  * works asynchronously; the reference tracks such work as a `Task` polled for completion
  * (Array/Remote/LRU.hs:101-110), here b200_sync is the completion point. */
 int b200_array_download_async(b200_ctx* ctx, uint64_t id, int leaf, void* host, size_t bytes);
