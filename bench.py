@@ -1,6 +1,6 @@
 #!/usr/bin/env python
-"""Benchmark of the hot path: every skeleton of BASELINE.json configs[1-4] on
-synthetic inputs of the stated shapes and distributions.
+"""Benchmark of the hot path: every skeleton of the benchmark specification's
+configs[1-4] on synthetic inputs of the stated shapes and distributions.
 
 One *step* is one pass over the suite: fold1Seg(+) i32 2^28, fold max
 65536x4096 f32, scanl1(+) i32 2^30, scanl'(+) f32 2^28, scanr1 max i64 2^28,
