@@ -431,3 +431,30 @@ def test_download_async_arrives_after_sync(gpu_ctx):
     gpu_ctx.sync()
     for t in bufs:
         assert np.array_equal(t.numpy(), x * 3 + 1)
+
+
+def test_bounded_wait_expiry_is_reported_and_the_context_stays_usable(monkeypatch):
+    # Every device-side wait has an iteration limit.  With the limit at zero a look-back that does not
+    # find its predecessors ready on the first poll gives up: the kernel records a status instead of
+    # waiting, the host reports B200_ERR_TIMEOUT, and the context keeps working afterwards.
+    from accelerate_b200 import backend, language as L
+    x = ints(1 << 20, np.int32, 0, 100)            # 512 tiles on the register kernel (no bulk copies in flight)
+    L.reset_names()
+    px = L.param(1, "i32")
+    prog = A.build_program(A.scanl1(add, px))
+    monkeypatch.setenv("ACCELERATE_B200_SPIN_LIMIT", "0")
+    ctx = backend.Context(0)
+    try:
+        d = ctx.from_host(x)
+        try:
+            out, = ctx.execute(prog.text, [d], 1)
+            got = out.download()
+            assert np.array_equal(got, np.cumsum(x, dtype=np.int32))     # every predecessor happened to be ready
+        except backend.B200Error as e:
+            assert e.code == 8, e                                        # B200_ERR_TIMEOUT
+        # the same context, same program, on an input of one tile: nothing to wait for
+        y = ints(1000, np.int32, 0, 100)
+        out, = ctx.execute(prog.text, [ctx.from_host(y)], 1)
+        assert np.array_equal(out.download(), np.cumsum(y, dtype=np.int32))
+    finally:
+        ctx.close()
