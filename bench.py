@@ -439,8 +439,8 @@ def main():
     launch_ms = per_ms[dom] / wd.launches if many else per_ms[dom]
     achieved = wd.alg_bytes / (wd.launches if many else 1) / (launch_ms * 1e-3) / 1e9
     # DRAM bytes per launch of the Jacobi kernel from the ncu capture summarised in
-    # profiles/acc_stencil2d_jacobi5_clamp.md (8192^2 case: 511.0 MB; traffic grows with the points: x4 at 16384^2)
-    traffic = 511.0e6 * 4 if (wd.name.startswith("jacobi") and args.scale == 0) else None
+    # profiles/acc_stencil2d_jacobi5_clamp.md (8192^2 case: 493.4 MB; traffic grows with the points: x4 at 16384^2)
+    traffic = 493.4e6 * 4 if (wd.name.startswith("jacobi") and args.scale == 0) else None
     roofline = {"bound": "hbm", "kernel": wd.kernel, "workload": wd.name, "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s",
                 "frac": round(achieved / peak, 4), "peak_kind": f"of {peak_kind}", "traffic": traffic,
                 "launch_ms": round(launch_ms, 4)}
