@@ -259,13 +259,6 @@ std::vector<std::pair<std::string, std::map<std::string, std::string>>> default_
       if (g.defines.count("D0_STREAM_NLEAVES") && g.defines.at("D0_STREAM_NLEAVES") == "1" && g.defines.at("SCAN_PACKED") == "1" &&
           g.defines.at("D0_STREAM_BYTES") == g.defines.at("SCAN_T_BYTES"))
         v.push_back({"scan", scan_ring_variant(scan_ring_shape(atoi(g.defines.at("SCAN_T_BYTES").c_str())), 1)});
-      if (!g.streams.empty() && !g.streams[0].empty()) {
-        auto var = scan_variant(n.elt);
-        var["SCAN_PIPE"] = "1";
-        var["SCAN_STAGES"] = "4";
-        if (var["SCAN_MIN_BLOCKS"] == "4") var["SCAN_MIN_BLOCKS"] = "3";
-        v.push_back({"scan", var});
-      }
       break;
     }
     case N_PERMUTE: {
@@ -836,27 +829,6 @@ void Program::run(const std::vector<DevArrayP>& inputs, std::vector<DevArrayP>& 
               c.check(cudaStreamSynchronize(c.stream), "cudaStreamSynchronize");
               if (FILE* f = fopen(tpath, "wb")) { fwrite(host.data(), 8, host.size(), f); fclose(f); }
             }
-            break;
-          }
-        }
-        const bool pipe_ok = !st.glue.streams.at(0).empty() && L.fast("D0") && in_vec && getenv("ACCELERATE_B200_SCAN_PIPE");
-        if (pipe_ok) {
-          // persistent CTAs, input staged through shared memory by the bulk-copy engine
-          const size_t stream_bytes = (size_t)atoi(st.glue.defines.at("D0_STREAM_BYTES").c_str());
-          const size_t stage_bytes = stream_bytes * (size_t)tile;
-          int stages = (int)std::min<size_t>(4, std::max<size_t>(2, (72 * 1024) / stage_bytes));
-          if (const char* e = getenv("ACCELERATE_B200_SCAN_STAGES")) stages = std::max(2, atoi(e));
-          const size_t smem = stage_bytes * stages;
-          if (smem <= 200 * 1024) {
-            std::map<std::string, std::string> var = scan_variant(n.elt);
-            var["SCAN_PIPE"] = "1";
-            var["SCAN_STAGES"] = std::to_string(stages);
-            // shared memory, not registers, limits residency here: leave the compiler more registers
-            if (var["SCAN_MIN_BLOCKS"] == "4") var["SCAN_MIN_BLOCKS"] = "3";
-            CompiledKernel& k = c.kernel(assemble_source(st.glue, "scan", var), "acc_scan_pipe", 256, smem);
-            L.named["total_tiles"] = total_tiles;
-            const int64_t grid = std::min<int64_t>(total_tiles, (int64_t)c.sm_count * k.max_blocks_per_sm);
-            L.launch(k, grid, 256, smem);
             break;
           }
         }

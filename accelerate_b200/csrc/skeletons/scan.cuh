@@ -484,167 +484,6 @@ extern "C" __global__ void __launch_bounds__(SCAN_THREADS, SCAN_MIN_BLOCKS) acc_
 }
 
 // ---------------------------------------------------------------------------------
-// acc_scan_pipe: the same scan with the input staged through shared memory by the
-// bulk-copy engine.  Persistent CTAs keep SCAN_STAGES tiles in flight each
-// (cp.async.bulk global -> shared, completion on an mbarrier), so HBM stays busy
-// while a CTA waits in the look-back; tickets are taken one stage ahead.  Used when
-// every array the scanned expression reads at the loop index has the fast layout
-// and rows are 16-byte aligned (in_vec); a partial last tile of a row is loaded
-// with ordinary loads instead.
-// Extra named parameter: total_tiles.
-// ---------------------------------------------------------------------------------
-#if defined(SCAN_PIPE) && SCAN_PIPE
-#ifndef SCAN_STAGES
-#define SCAN_STAGES 4
-#endif
-
-__device__ __forceinline__ u32 scan_smem_addr(const void* ptr) { return (u32)__cvta_generic_to_shared(ptr); }
-__device__ __forceinline__ void scan_mbar_init(u64* bar, int count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(scan_smem_addr(bar)), "r"(count) : "memory");
-}
-__device__ __forceinline__ void scan_mbar_expect(u64* bar, u32 bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(scan_smem_addr(bar)), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ bool scan_mbar_try_wait(u64* bar, u32 parity) {
-  u32 ok;
-  asm volatile(
-      "{\n\t.reg .pred q;\n\tmbarrier.try_wait.parity.shared::cta.b64 q, [%1], %2;\n\tselp.u32 %0, 1, 0, q;\n\t}"
-      : "=r"(ok)
-      : "r"(scan_smem_addr(bar)), "r"(parity)
-      : "memory");
-  return ok != 0;
-}
-// global -> shared bulk copy; src and dst 16-byte aligned, bytes a multiple of 16
-__device__ __forceinline__ void acc_bulk_g2s(void* dst, const void* src, u32 bytes, u64* bar) {
-  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(scan_smem_addr(dst)), "l"(src),
-               "r"(bytes), "r"(scan_smem_addr(bar))
-               : "memory");
-}
-
-extern __shared__ __align__(128) unsigned char scan_pipe_smem[];
-
-extern "C" __global__ void __launch_bounds__(SCAN_THREADS, SCAN_MIN_BLOCKS) acc_scan_pipe(const Params p) {
-  __shared__ elt_t sm_v[SCAN_WARPS];
-  __shared__ int sm_h[SCAN_WARPS];
-  __shared__ elt_t sm_excl;
-  __shared__ int sm_flag[2];
-  __shared__ __align__(8) u64 full_bar[SCAN_STAGES];
-  __shared__ i64 stage_tile[SCAN_STAGES];
-  __shared__ int stage_direct[SCAN_STAGES];
-  __shared__ u32 stage_parity[SCAN_STAGES];
-  u32 uses[SCAN_STAGES];                 // thread 0: completed copy phases per stage barrier
-#pragma unroll
-  for (int s = 0; s < SCAN_STAGES; ++s) uses[s] = 0;
-  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const i64 n = p.n;
-  const i64 total_tiles = p.total_tiles;
-  unsigned* counter = reinterpret_cast<unsigned*>(p.counter);
-  unsigned* exits = counter + 1;
-
-  // thread 0: take the next ticket for stage s and request its data
-  auto fetch = [&](int s) {
-    const i64 T = (i64)atomicAdd(counter, 1u);
-    stage_tile[s] = T;
-    stage_direct[s] = 1;
-    if (T >= total_tiles) return;
-    const i64 row = T / p.tiles_per_row;
-    const i64 tt = T - row * p.tiles_per_row;
-    const i64 q0 = tt * SCAN_TILE;
-    if (q0 + SCAN_TILE > n) return;        // partial tile: ordinary loads
-    stage_direct[s] = 0;
-    stage_parity[s] = uses[s] & 1u;       // the barrier phase this request completes
-    uses[s] += 1;
-#if ACC_RIGHT
-    const i64 src = row * n + (n - q0 - SCAN_TILE);
-#else
-    const i64 src = row * n + q0;
-#endif
-    unsigned char* base = scan_pipe_smem + (size_t)s * D0_STAGE_BYTES;
-    scan_mbar_expect(&full_bar[s], (u32)D0_STAGE_BYTES);
-    D0_BULK_ISSUE(base, &full_bar[s], src)
-  };
-
-  if (tid == 0) {
-    for (int s = 0; s < SCAN_STAGES; ++s) scan_mbar_init(&full_bar[s], 1);
-    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-  }
-  __syncthreads();
-  if (tid == 0)
-    for (int s = 0; s < SCAN_STAGES; ++s) fetch(s);
-  __syncthreads();
-
-  for (i64 it = 0;; ++it) {
-    const int s = (int)(it % SCAN_STAGES);
-    const u32 parity = stage_parity[s];
-    const i64 T = stage_tile[s];
-    if (T >= total_tiles) break;
-    const int direct = stage_direct[s];
-    const i64 row = T / p.tiles_per_row;
-    const i64 tt = T - row * p.tiles_per_row;
-    const i64 warp_q0 = tt * SCAN_TILE + (i64)warp * SCAN_WARP_ELEMS;
-    elt_t item[SCAN_ROUNDS][4];
-    bool valid[SCAN_ROUNDS][4];
-    int failed = 0;
-    if (!direct) {
-      i64 spins = 0;
-      while (!scan_mbar_try_wait(&full_bar[s], parity)) {
-        if (++spins > p.spin_limit) { failed = 1; break; }
-      }
-      if (!failed) {
-        const unsigned char* base = scan_pipe_smem + (size_t)s * D0_STAGE_BYTES;
-#pragma unroll
-        for (int r = 0; r < SCAN_ROUNDS; ++r) {
-          const int e = warp * SCAN_WARP_ELEMS + r * 128 + lane * 4;   // logical offset within the tile
-          const i64 q = warp_q0 + r * 128 + lane * 4;
-#if ACC_RIGHT
-          elt_t t4[4];
-          D0_get4_sm(p, row, n - 4 - q, base, SCAN_TILE - 4 - e, t4);
-#pragma unroll
-          for (int k = 0; k < 4; ++k) item[r][k] = t4[3 - k];
-#else
-          D0_get4_sm(p, row, q, base, e, item[r]);
-#endif
-#pragma unroll
-          for (int k = 0; k < 4; ++k) valid[r][k] = true;
-        }
-      }
-    }
-    if (__syncthreads_or(failed)) {     // also: every thread is done reading stage s
-      if (tid == 0) acc_fail(p.err, 110 /* ETIMEDOUT */);
-      break;
-    }
-    if (tid == 0) fetch(s);            // refill the stage while this tile is processed
-    if (!direct) {
-      scan_tile_body<true>(p, T, row, tt, item, valid, sm_v, sm_h, &sm_excl, sm_flag);
-    } else {
-      scan_tile<false>(p, T, row, tt, sm_v, sm_h, &sm_excl, sm_flag);   // only partial tiles come this way
-    }
-    __syncthreads();                   // shared scratch of the tile body is reused by the next tile
-    if (sm_flag[1]) break;
-  }
-  // Leaving early (a wait gave up) must not abandon bulk copies that are still in flight into
-  // this CTA's shared memory: wait for every requested stage, again with a limit.  After a
-  // normal end nothing is pending (the remaining tickets were past the last tile).
-  __syncthreads();
-  if (tid == 0) {
-    for (int s = 0; s < SCAN_STAGES; ++s) {
-      if (stage_tile[s] < total_tiles && !stage_direct[s]) {
-        i64 spins = 0;
-        while (!scan_mbar_try_wait(&full_bar[s], stage_parity[s]))
-          if (++spins > p.spin_limit) break;
-      }
-    }
-  }
-  // the last CTA to leave re-arms the ticket counter for the next launch
-  __syncthreads();
-  if (tid == 0) {
-    __threadfence();
-    if (atomicAdd(exits, 1u) == gridDim.x - 1) { *counter = 0u; *exits = 0u; }
-  }
-}
-#endif
-
-// ---------------------------------------------------------------------------------
 // acc_scan_ring: persistent CTAs that keep SCAN_SLOTS tiles each in a shared-memory
 // ring.  A tile is bulk-copied in (cp.async.bulk + mbarrier), scanned locally IN PLACE
 // as soon as it arrives (its aggregate is published at once), and then simply waits
