@@ -63,8 +63,8 @@ __device__ __forceinline__ u64 scan_now() { u64 t; asm volatile("mov.u64 %0, %%g
 #ifndef SCAN_PACKED
 #define SCAN_PACKED 0
 #endif
-// Barrier over the SCAN_THREADS threads that process tiles.  The ring kernel runs one extra
-// warp (the look-back warp) that must not take part, so it uses a named barrier instead.
+// Barrier over the SCAN_THREADS threads that process tiles.  The ring kernel runs further
+// warps (reducers, look-back) that must not take part, so it uses a named barrier instead.
 #if defined(SCAN_RING) && SCAN_RING
 #define SCAN_SYNC() asm volatile("bar.sync 1, %0;" ::"n"(SCAN_THREADS) : "memory")
 #else
@@ -485,17 +485,16 @@ extern "C" __global__ void __launch_bounds__(SCAN_THREADS, SCAN_MIN_BLOCKS) acc_
 
 // ---------------------------------------------------------------------------------
 // acc_scan_ring: persistent CTAs that keep SCAN_SLOTS tiles each in a shared-memory
-// ring.  A tile is bulk-copied in (cp.async.bulk + mbarrier), scanned locally IN PLACE
-// as soon as it arrives (its aggregate is published at once), and then simply waits
-// in shared memory until its exclusive prefix is known; warp 0 advances the look-back
-// of the oldest unresolved tile without blocking, and resolved tiles are combined with
-// their prefix and streamed out.  Unlike acc_scan, tile data does not occupy registers
-// while the look-back is pending, so a SM keeps several times more elements in flight
-// and the look-back latency no longer idles the memory system.
+// ring.  A tile is bulk-copied in (cp.async.bulk + mbarrier); reducer warps publish
+// its aggregate the moment it has arrived; a look-back warp finds its exclusive
+// prefix; finisher warps then scan the tile straight out of shared memory, store it
+// and hand the slot to the next ticket.  Unlike acc_scan, tile data does not occupy
+// registers while the look-back is pending, so a SM keeps several times more
+// elements in flight and the look-back latency idles the memory system much less.
 // Requirements (checked by the host): one scalar leaf (SCAN_PACKED), exactly one stream
 // leaf of the same size, fast layout, in_vec and out_vec.  Partial tiles (the last of a
 // row) are handled by scan_tile<false> inside the same kernel.
-// Extra named parameter: total_tiles.
+// Extra named parameters: total_tiles, gstatus, groups_per_row.
 // ---------------------------------------------------------------------------------
 #if defined(SCAN_RING) && SCAN_RING
 #ifndef SCAN_SLOTS
@@ -533,28 +532,6 @@ __device__ __forceinline__ void ring_bulk_g2s(void* dst, const void* src, u32 by
                : "memory");
 }
 #define acc_bulk_g2s ring_bulk_g2s
-struct __align__(SCAN_T_BYTES * 4) ring_quad { SCAN_T v[4]; };
-// four values at logical offsets e..e+3 of a slot (right-to-left scans keep physical order in the slot)
-__device__ __forceinline__ void ring_st4(unsigned char* base, int e, const elt_t (&v)[4]) {
-  ring_quad q;
-#if ACC_RIGHT
-  q.v[0] = v[3].l0; q.v[1] = v[2].l0; q.v[2] = v[1].l0; q.v[3] = v[0].l0;
-  *reinterpret_cast<ring_quad*>(reinterpret_cast<SCAN_T*>(base) + (SCAN_TILE - 4 - e)) = q;
-#else
-  q.v[0] = v[0].l0; q.v[1] = v[1].l0; q.v[2] = v[2].l0; q.v[3] = v[3].l0;
-  *reinterpret_cast<ring_quad*>(reinterpret_cast<SCAN_T*>(base) + e) = q;
-#endif
-}
-__device__ __forceinline__ void ring_ld4(const unsigned char* base, int e, elt_t (&v)[4]) {
-#if ACC_RIGHT
-  const ring_quad q = *reinterpret_cast<const ring_quad*>(reinterpret_cast<const SCAN_T*>(base) + (SCAN_TILE - 4 - e));
-  v[0].l0 = q.v[3]; v[1].l0 = q.v[2]; v[2].l0 = q.v[1]; v[3].l0 = q.v[0];
-#else
-  const ring_quad q = *reinterpret_cast<const ring_quad*>(reinterpret_cast<const SCAN_T*>(base) + e);
-  v[0].l0 = q.v[0]; v[1].l0 = q.v[1]; v[2].l0 = q.v[2]; v[3].l0 = q.v[3];
-#endif
-}
-
 extern __shared__ __align__(128) unsigned char scan_ring_smem[];
 
 template <class T> __device__ __forceinline__ T ring_ldv(const T* p) { return *reinterpret_cast<const volatile T*>(p); }
