@@ -166,3 +166,50 @@ def test_stencil2_gauss_mirror_16384(gpu_ctx, workloads, bench):
     # stencils: at most 1 ulp per point; with the same expression order and no fused multiply-add
     # the results are in fact identical
     assert np.array_equal(got, want)
+
+
+# Long rows in several rows: the shared-memory ring and the 8192-element register tiles with partial
+# last tiles, seeds, right-to-left order and row boundaries, at sizes the small-case tests do not reach.
+def _scan_np(x, right, seed, op):
+    acc = {"add": np.add, "max": np.maximum}[op].accumulate
+    y = x[..., ::-1] if right else x
+    if seed is not None:
+        y = np.concatenate([np.full(y.shape[:-1] + (1,), seed, y.dtype), y], axis=-1)
+    r = acc(y, axis=-1, dtype=y.dtype) if op == "add" else acc(y, axis=-1)
+    return r[..., ::-1] if right else r
+
+
+@pytest.mark.parametrize("name,shape,dtype", [
+    ("scanl1", (4, (1 << 24) + 4), np.int32),        # ring, partial last tile in every row
+    ("scanr1", (2, 1 << 24), np.int32),              # ring, right to left
+    ("scanl", (1, (1 << 25) + 3), np.int32),         # ring, seeded: n+1 results
+    ("scanr", (2, (1 << 22) + 3), np.int32),         # seeded, right to left, rows of n+1 results
+    ("scanl'", (3, (1 << 23) + 8), np.int32),        # ring, totals in a second array
+    ("scanr'", (2, 1 << 23), np.int64),              # register kernel, 8-byte elements
+    ("scanl1max", (5, (1 << 22) + 12), np.int64),
+])
+def test_long_rows_scans(gpu_ctx, name, shape, dtype):
+    g = np.random.default_rng(7)
+    x = g.integers(0, 100, size=shape).astype(dtype) if dtype == np.int32 else g.integers(-(1 << 62), 1 << 62, size=shape, dtype=np.int64)
+    add = lambda a, b: a + b  # noqa: E731
+    if name == "scanl1":
+        got, = run(gpu_ctx, lambda a: A.scanl1(add, a), [x]); want = _scan_np(x, False, None, "add")
+    elif name == "scanr1":
+        got, = run(gpu_ctx, lambda a: A.scanr1(add, a), [x]); want = _scan_np(x, True, None, "add")
+    elif name == "scanl":
+        got, = run(gpu_ctx, lambda a: A.scanl(add, 7, a), [x]); want = _scan_np(x, False, 7, "add")
+    elif name == "scanr":
+        got, = run(gpu_ctx, lambda a: A.scanr(add, 7, a), [x]); want = _scan_np(x, True, 7, "add")
+    elif name == "scanl'":
+        got, tot = run(gpu_ctx, lambda a: list(A.scanl_prime(add, 7, a)), [x])
+        full = _scan_np(x, False, 7, "add")
+        want = full[..., :-1]
+        assert np.array_equal(tot, full[..., -1])
+    elif name == "scanr'":
+        got, tot = run(gpu_ctx, lambda a: list(A.scanr_prime(A.max_, -(1 << 63), a)), [x])
+        full = _scan_np(x, True, -(1 << 63), "max")
+        want = full[..., 1:]
+        assert np.array_equal(tot, full[..., 0])
+    else:
+        got, = run(gpu_ctx, lambda a: A.scanl1(A.max_, a), [x]); want = _scan_np(x, False, None, "max")
+    assert got.shape == want.shape and np.array_equal(got, want)
