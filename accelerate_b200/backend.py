@@ -18,7 +18,7 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 _LIB_PATH = os.path.join(_HERE, "libaccb200.so")
 _lib = None
 
-ERRORS = {1: "parse", 2: "type", 3: "compile", 4: "cuda", 5: "bounds", 6: "unsupported", 7: "argument", 8: "timeout"}
+ERRORS = {1: "parse", 2: "type", 3: "compile", 4: "cuda", 5: "bounds", 6: "unsupported", 7: "argument", 8: "timeout", 9: "arithmetic"}
 
 
 class B200Error(RuntimeError):
@@ -273,10 +273,12 @@ def run_program(prog, host_inputs, ctx=None):
     return res
 
 
-def run(acc, ctx=None):
-    """``run :: Arrays a => Acc a -> a`` (Interpreter.hs:93)."""
+def run(acc, ctx=None, embed=False):
+    """``run :: Arrays a => Acc a -> a`` (Interpreter.hs:93).  With ``embed`` the arrays given to
+    ``use`` travel inside the program as ``Use`` nodes, as they do in ``run (... (use xs))``;
+    otherwise they are bound as program inputs (what ``runN`` does with its arguments)."""
     single = not isinstance(acc, (list, tuple))
-    prog = L.build_program(acc)
+    prog = L.build_program(acc, embed=embed)
     res = run_program(prog, [n.data for n in prog.inputs], ctx)
     return res[0] if single else res
 

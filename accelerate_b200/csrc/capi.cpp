@@ -37,12 +37,23 @@ Type parse_type_text(const char* s) {
   Sx x = parse_sexp(s, strlen(s));
   return parse_type(x);
 }
+// every node that launches kernels, the bodies of control nodes included, in program order
+void kernel_nodes(const std::vector<Node>& ns, std::vector<const Node*>& out) {
+  for (auto& n : ns) {
+    if (n.kind == N_USE || n.kind == N_ACOND || n.kind == N_AWHILE || n.kind == N_APPLY) {
+      for (auto& b : n.body) kernel_nodes(b.nodes, out);
+    } else if (n.kind != N_RESHAPE) {
+      out.push_back(&n);
+    }
+  }
+}
 void build_nodes(Program& p) {
-  p.nodes.resize(p.ir->nodes.size());
-  for (size_t i = 0; i < p.ir->nodes.size(); ++i) {
-    if (p.ir->nodes[i].kind == N_RESHAPE) continue;
-    p.nodes[i].glue = build_glue(p.ir->nodes[i], p.ir->arrays);
-    p.nodes[i].has_glue = true;
+  p.nodes.resize(p.ir->n_nodes);
+  std::vector<const Node*> ks;
+  kernel_nodes(p.ir->nodes, ks);
+  for (const Node* n : ks) {
+    p.nodes[n->id].glue = build_glue(*n, p.ir->arrays);
+    p.nodes[n->id].has_glue = true;
   }
 }
 }  // namespace
@@ -203,6 +214,8 @@ static int check_device_status(Ctx& c) {
   if (words[0] != 0) {
     c.check(cudaMemsetAsync(c.d_words, 0, 16, c.stream), "cudaMemsetAsync");  // also re-arms the ticket counters
     if (words[0] == 1001) throw Error(B200_ERR_BOUNDS, "empty segment");
+    if (words[0] == 1002) throw Error(B200_ERR_ARITH, "divide by zero");
+    if (words[0] == 1003) throw Error(B200_ERR_BOUNDS, "index out of bounds");
     throw Error(B200_ERR_TIMEOUT, "a device-side wait exceeded its limit (status " + std::to_string(words[0]) + "); results are incomplete");
   }
   return 0;
@@ -308,6 +321,13 @@ int b200_program_load(b200_ctx* ctx, const char* text, size_t len, b200_program*
   h->p.ctx = &ctx->c;
   h->p.ir = parse_program(text, len);
   build_nodes(h->p);
+  {
+    // arrays embedded with (use ...) go to the device once, here
+    Ctx& c = ctx->c;
+    std::lock_guard<std::mutex> g(c.mu);
+    c.check(cudaSetDevice(c.device), "cudaSetDevice");
+    h->p.upload_constants();
+  }
   *out = h.release();
   B200_END
 }
@@ -380,12 +400,14 @@ int b200_compile_check(const char* text, size_t len, char* log, size_t log_len) 
     Program p;
     p.ir = parse_program(text, len);
     build_nodes(p);
-    for (size_t i = 0; i < p.ir->nodes.size(); ++i) {
-      if (!p.nodes[i].has_glue) continue;
-      for (auto& v : default_variants(p.ir->nodes[i], p.nodes[i].glue)) {
-        std::string src = assemble_source(p.nodes[i].glue, v.first, v.second);
-        compile_to_cubin(src, v.first, nullptr);
-        msg += "ok " + v.first + " (" + std::to_string(src.size()) + " bytes of source)\n";
+    std::vector<const Node*> ks;
+    kernel_nodes(p.ir->nodes, ks);
+    for (const Node* kn : ks) {
+      for (auto& v : default_variants(*kn, p.nodes[kn->id].glue)) {
+        std::string src = assemble_source(p.nodes[kn->id].glue, v.first, v.second);
+        CompileStats cs;
+        compile_to_cubin(src, v.first, &cs);
+        msg += "ok " + v.first + " (" + std::to_string(src.size()) + " bytes of source, " + (cs.compiled ? "compiled" : "from the disk cache") + ")\n";
       }
     }
   } catch (const Error& e) {
@@ -403,17 +425,23 @@ int b200_compile_check(const char* text, size_t len, char* log, size_t log_len) 
   return rc;
 }
 
+int b200_scan_ring_aligned(int elt_bytes, int64_t n, int64_t rows, int right) {
+  return scan_ring_aligned(elt_bytes, n, rows, right != 0) ? 1 : 0;
+}
+
 int b200_kernel_source(const char* text, size_t len, int node, char* out, size_t out_len) {
   B200_TRY
   Program p;
   p.ir = parse_program(text, len);
   build_nodes(p);
-  if (node < 0 || (size_t)node >= p.nodes.size() || !p.nodes[node].has_glue) throw Error(B200_ERR_ARG, "no such kernel node");
-  auto vs = default_variants(p.ir->nodes[node], p.nodes[node].glue);
+  // `node` counts top-level nodes
+  if (node < 0 || (size_t)node >= p.ir->nodes.size() || !p.nodes[p.ir->nodes[node].id].has_glue) throw Error(B200_ERR_ARG, "no such kernel node");
+  const Node& kn = p.ir->nodes[node];
+  auto vs = default_variants(kn, p.nodes[kn.id].glue);
   size_t which = 0;
   if (const char* e = getenv("ACCELERATE_B200_SOURCE_VARIANT")) which = (size_t)atoi(e);
   if (which >= vs.size()) throw Error(B200_ERR_ARG, "no such kernel variant");
-  std::string src = assemble_source(p.nodes[node].glue, vs[which].first, vs[which].second);
+  std::string src = assemble_source(p.nodes[kn.id].glue, vs[which].first, vs[which].second);
   if (out && out_len) {
     size_t n = std::min(out_len - 1, src.size());
     memcpy(out, src.data(), n);

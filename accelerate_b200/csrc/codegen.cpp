@@ -726,7 +726,11 @@ Glue build_glue(const Node& n, const std::map<std::string, ArrayInfo>& arrays) {
           CVal r;
           r.ty = pelemT;
           r.leaf.push_back(m.leaf[0]);
-          r.leaf.push_back(g.def(I64, g.to_index(outsh, std::vector<std::string>(m.leaf.begin() + 1, m.leaf.end()))));
+          // linear target, or -1 when any component lies outside its dimension
+          std::vector<std::string> tix(m.leaf.begin() + 1, m.leaf.end());
+          std::string inside = "true";
+          for (size_t d = 0; d < tix.size(); ++d) inside += " && (u64)(" + tix[d] + ") < (u64)(" + outsh[d] + ")";
+          r.leaf.push_back(g.def(I64, "(" + inside + ") ? " + g.to_index(outsh, tix) + " : (i64)-1"));
           r.leaf.insert(r.leaf.end(), v.leaf.begin(), v.leaf.end());
           return r;
         });
@@ -956,7 +960,7 @@ Glue build_glue(const Node& n, const std::map<std::string, ArrayInfo>& arrays) {
     case N_FOLD: named = {"n", "rows", "row", "vec", "scratch", "flags", "counter"}; break;
     case N_FOLDSEG: named = {"segs", "rows", "vec", "err"}; break;
     case N_SCAN: case N_SCAN2:
-      named = {"n", "rows", "tiles_per_row", "total_tiles", "in_vec", "out_vec", "status", "agg", "incl", "gstatus", "groups_per_row", "counter", "epoch", "err", "spin_limit", "trace"};
+      named = {"n", "rows", "tiles_per_row", "total_tiles", "in_vec", "out_vec", "status", "agg", "incl", "gstatus", "groups_per_row", "counter", "epoch", "err", "spin_limit"};
       break;
     case N_PERMUTE: named = {"n", "vec", "out_n", "priv", "locks", "err", "spin_limit"}; break;
     case N_STENCIL: case N_STENCIL2: named = {"o0", "o1", "o2", "tiles1", "tiles2", "vec"}; break;

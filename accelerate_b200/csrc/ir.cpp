@@ -453,12 +453,78 @@ std::string sx_text(const Sx& x) {
   return r + ")";
 }
 
-void parse_node(ProgramIR& p, const Sx& bind, TEnv& env) {
+void parse_node(ProgramIR& p, std::vector<Node>& into, const Sx& bind, TEnv& env);
+
+void define_array(ProgramIR& p, const std::string& name, const ArrayInfo& ai) {
+  if (p.arrays.count(name)) throw Error(B200_ERR_PARSE, "array variable '" + name + "' is defined twice");
+  p.arrays[name] = ai;
+}
+
+// (afun ((p (array R T)) ...) (let ..)* (out n ...))   or   (branch (let ..)* (out n ...))
+Body parse_body(ProgramIR& p, const Sx& x, TEnv& env, bool with_params) {
+  if (x.head() != (with_params ? "afun" : "branch")) throw Error(B200_ERR_PARSE, std::string("expected (") + (with_params ? "afun" : "branch") + " ...)");
+  Body b;
+  size_t i = 1;
+  if (with_params) {
+    const Sx& ps = x.at(1);
+    for (auto& q : ps.k) {
+      const Sx& at = q.at(1);
+      if (at.head() != "array") throw Error(B200_ERR_PARSE, "expected (name (array rank elt)) in an array function");
+      ArrayInfo ai;
+      ai.rank = atoi(at.at(1).s.c_str());
+      ai.elt = parse_type(at.at(2));
+      define_array(p, q.at(0).s, ai);
+      b.params.push_back(q.at(0).s);
+      b.param_info.push_back(ai);
+    }
+    i = 2;
+  }
+  bool seen_out = false;
+  for (; i < x.size(); ++i) {
+    const Sx& f = x.k[i];
+    if (f.head() == "let") {
+      parse_node(p, b.nodes, f, env);
+    } else if (f.head() == "out") {
+      for (size_t j = 1; j < f.size(); ++j) {
+        env.array(f.k[j].s);
+        b.outs.push_back(f.k[j].s);
+      }
+      seen_out = true;
+    } else {
+      throw Error(B200_ERR_PARSE, "unknown form '" + f.head() + "' in an array function");
+    }
+  }
+  if (!seen_out || b.outs.empty()) throw Error(B200_ERR_PARSE, "array function has no (out ...)");
+  return b;
+}
+
+std::vector<ArrayInfo> body_result(const ProgramIR& p, const Body& b) {
+  std::vector<ArrayInfo> r;
+  for (auto& o : b.outs) r.push_back(p.arrays.at(o));
+  return r;
+}
+bool same_arrays(const std::vector<ArrayInfo>& a, const std::vector<ArrayInfo>& b) {
+  if (a.size() != b.size()) return false;
+  for (size_t i = 0; i < a.size(); ++i)
+    if (a[i].rank != b[i].rank || a[i].elt != b[i].elt) return false;
+  return true;
+}
+
+int hex_digit(char c) {
+  if (c >= '0' && c <= '9') return c - '0';
+  if (c >= 'a' && c <= 'f') return c - 'a' + 10;
+  if (c >= 'A' && c <= 'F') return c - 'A' + 10;
+  throw Error(B200_ERR_PARSE, "bad hexadecimal digit in (use ...)");
+}
+
+void parse_node(ProgramIR& p, std::vector<Node>& into, const Sx& bind, TEnv& env) {
   const Sx& lhs = bind.at(1);
   const Sx& x = bind.at(2);
   Node n;
-  n.text = sx_text(x);
+  n.id = p.n_nodes++;
   const std::string k = x.head();
+  // (control nodes are not hashed into any kernel: their text, which may embed whole arrays, is not kept)
+  if (k != "use" && k != "acond" && k != "awhile" && k != "apply") n.text = sx_text(x);
   auto is_operand = [](const Sx& s) { return s.head() == "manifest" || s.head() == "delayed"; };
   std::vector<ArrayInfo> outs;
   if (k == "generate") {
@@ -543,6 +609,70 @@ void parse_node(ProgramIR& p, const Sx& bind, TEnv& env) {
         n.f->param_ty[1] != stencil_arg_type(n.st_extent[1], n.d[1].elt) || n.f->result() != n.elt)
       throw Error(B200_ERR_TYPE, "stencil2: function type does not match the patterns");
     outs.push_back({n.d[0].rank, n.elt});
+  } else if (k == "use") {
+    // (use (array R ELT) (shape d0 ..) (hex LEAF0) (hex LEAF1) ...): Use, Interpreter.hs:231
+    n.kind = N_USE;
+    const Sx& at = x.at(1);
+    if (at.head() != "array" || x.at(2).head() != "shape") throw Error(B200_ERR_PARSE, "expected (use (array rank elt) (shape ...) (hex ...)...)");
+    const int rank = atoi(at.at(1).s.c_str());
+    n.elt = parse_type(at.at(2));
+    if ((int)x.at(2).size() - 1 != rank) throw Error(B200_ERR_TYPE, "use: shape does not have the declared rank");
+    int64_t count = 1;
+    for (int d = 0; d < rank; ++d) {
+      n.use_shape.push_back(atoll(x.at(2).at(1 + d).s.c_str()));
+      count = n.use_shape.back() <= 0 ? 0 : count * n.use_shape.back();
+    }
+    for (int64_t d : n.use_shape) if (d <= 0) count = 0;
+    std::vector<Ty> leaves = n.elt.leaves();
+    if (x.size() != 3 + leaves.size()) throw Error(B200_ERR_TYPE, "use: one (hex ...) per scalar leaf expected");
+    for (size_t l = 0; l < leaves.size(); ++l) {
+      const Sx& h = x.at(3 + l);
+      if (h.head() != "hex") throw Error(B200_ERR_PARSE, "expected (hex DIGITS)");
+      const std::string digits = h.size() > 1 ? h.at(1).s : std::string();
+      const size_t bytes = (size_t)count * ty_bytes[leaves[l]];
+      if (digits.size() != 2 * bytes) throw Error(B200_ERR_TYPE, "use: payload size does not match shape and element type");
+      std::string raw(bytes, '\0');
+      for (size_t i = 0; i < bytes; ++i) raw[i] = (char)(hex_digit(digits[2 * i]) * 16 + hex_digit(digits[2 * i + 1]));
+      n.use_data.push_back(std::move(raw));
+    }
+    outs.push_back({rank, n.elt});
+  } else if (k == "acond") {
+    // (acond EXP (branch ...) (branch ...)): Acond, Interpreter.hs:217-219
+    n.kind = N_ACOND;
+    n.pred = parse_expr(x.at(1), env);
+    if (n.pred->ty.tuple || n.pred->ty.s != U8) throw Error(B200_ERR_TYPE, "acond: the predicate is not a Bool");
+    n.body.push_back(parse_body(p, x.at(2), env, false));
+    n.body.push_back(parse_body(p, x.at(3), env, false));
+    outs = body_result(p, n.body[0]);
+    if (!same_arrays(outs, body_result(p, n.body[1]))) throw Error(B200_ERR_TYPE, "acond: the branches yield different arrays");
+  } else if (k == "awhile") {
+    // (awhile (afun (s..) .. (out c)) (afun (s..) .. (out s'..)) (args a..)): Awhile, Interpreter.hs:221-229
+    n.kind = N_AWHILE;
+    n.body.push_back(parse_body(p, x.at(1), env, true));
+    n.body.push_back(parse_body(p, x.at(2), env, true));
+    const Sx& as = x.at(3);
+    if (as.head() != "args") throw Error(B200_ERR_PARSE, "expected (args ...)");
+    for (size_t j = 1; j < as.size(); ++j) {
+      n.args.push_back(as.k[j].s);
+      outs.push_back(env.array(as.k[j].s));
+    }
+    std::vector<ArrayInfo> c = body_result(p, n.body[0]);
+    if (c.size() != 1 || c[0].rank != 0 || c[0].elt.tuple || c[0].elt.s != U8) throw Error(B200_ERR_TYPE, "awhile: the condition must yield a Scalar Bool");
+    if (!same_arrays(outs, n.body[0].param_info) || !same_arrays(outs, n.body[1].param_info) || !same_arrays(outs, body_result(p, n.body[1])))
+      throw Error(B200_ERR_TYPE, "awhile: condition, step and initial value disagree on the type of the state");
+  } else if (k == "apply") {
+    // (apply (afun (x..) .. (out r..)) (args a..)): Apply, Interpreter.hs:215
+    n.kind = N_APPLY;
+    n.body.push_back(parse_body(p, x.at(1), env, true));
+    const Sx& as = x.at(2);
+    if (as.head() != "args") throw Error(B200_ERR_PARSE, "expected (args ...)");
+    std::vector<ArrayInfo> given;
+    for (size_t j = 1; j < as.size(); ++j) {
+      n.args.push_back(as.k[j].s);
+      given.push_back(env.array(as.k[j].s));
+    }
+    if (!same_arrays(given, n.body[0].param_info)) throw Error(B200_ERR_TYPE, "apply: arguments do not match the function's parameters");
+    outs = body_result(p, n.body[0]);
   } else if (k == "reshape") {
     n.kind = N_RESHAPE;
     n.extent = parse_expr(x.at(1), env);
@@ -559,8 +689,8 @@ void parse_node(ProgramIR& p, const Sx& bind, TEnv& env) {
   if (names.size() != outs.size()) throw Error(B200_ERR_PARSE, "node '" + k + "' defines " + std::to_string(outs.size()) + " array(s)");
   n.outs = names;
   n.out_info = outs;
-  p.nodes.push_back(std::move(n));
-  for (size_t i = 0; i < names.size(); ++i) p.arrays[names[i]] = outs[i];
+  for (size_t i = 0; i < names.size(); ++i) define_array(p, names[i], outs[i]);
+  into.push_back(std::move(n));
 }
 
 void collect_arrays(const Expr& e, std::vector<std::string>& out) {
@@ -577,6 +707,28 @@ void collect_arrays(const Expr& e, std::vector<std::string>& out) {
 
 void free_arrays(const Expr& e, std::vector<std::string>& out) { collect_arrays(e, out); }
 void free_arrays(const Fun& f, std::vector<std::string>& out) { collect_arrays(*f.body, out); }
+
+void node_arrays(const Node& n, std::vector<std::string>& used) {
+  if (n.f) free_arrays(*n.f, used);
+  if (n.g) free_arrays(*n.g, used);
+  if (n.seed) free_arrays(*n.seed, used);
+  if (n.extent) free_arrays(*n.extent, used);
+  if (n.pred) free_arrays(*n.pred, used);
+  for (auto& d : n.d) {
+    if (d.extent) free_arrays(*d.extent, used);
+    if (d.index) free_arrays(*d.index, used);
+  }
+  for (auto& b : n.bnd) {
+    if (b.value) free_arrays(*b.value, used);
+    if (b.fun) free_arrays(*b.fun, used);
+  }
+  if (!n.arr.empty()) used.push_back(n.arr);
+  for (auto& a : n.args) used.push_back(a);
+  for (auto& b : n.body) {
+    for (auto& m : b.nodes) node_arrays(m, used);
+    for (auto& o : b.outs) used.push_back(o);
+  }
+}
 
 std::unique_ptr<ProgramIR> parse_program(const char* text, size_t len) {
   Sx top = parse_sexp(text, len);
@@ -596,7 +748,7 @@ std::unique_ptr<ProgramIR> parse_program(const char* text, size_t len) {
       p->arrays[f.at(1).s] = ai;
       p->inputs.push_back(f.at(1).s);
     } else if (h == "let") {
-      parse_node(*p, f, env);
+      parse_node(*p, p->nodes, f, env);
     } else if (h == "out") {
       for (size_t j = 1; j < f.size(); ++j) {
         env.array(f.k[j].s);

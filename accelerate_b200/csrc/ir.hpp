@@ -123,9 +123,27 @@ struct BoundarySpec {
   std::unique_ptr<Fun> fun;
 };
 
-enum NodeKind { N_GENERATE, N_FOLD, N_FOLDSEG, N_SCAN, N_SCAN2, N_PERMUTE, N_STENCIL, N_STENCIL2, N_RESHAPE };
+// Kernel nodes, and the nodes the reference evaluates on the host (Interpreter.hs:215-231):
+// Use (a constant array embedded in the program), Acond, Awhile and Apply, whose operands are
+// array-level functions (`Body`).
+enum NodeKind { N_GENERATE, N_FOLD, N_FOLDSEG, N_SCAN, N_SCAN2, N_PERMUTE, N_STENCIL, N_STENCIL2, N_RESHAPE,
+                N_USE, N_ACOND, N_AWHILE, N_APPLY };
+struct Node;
+// An array-level function or a branch: parameters (none for branches), nodes, results.
+struct Body {
+  std::vector<std::string> params;
+  std::vector<ArrayInfo> param_info;
+  std::vector<Node> nodes;
+  std::vector<std::string> outs;
+};
 struct Node {
   NodeKind kind = N_GENERATE;
+  int id = -1;                            // position in Program::nodes (unique over all bodies)
+  std::vector<Body> body;                 // acond: then, else; awhile: condition, step; apply: the function
+  std::vector<std::string> args;          // awhile: initial state; apply: arguments
+  std::unique_ptr<Expr> pred;             // acond
+  std::vector<int64_t> use_shape;         // use
+  std::vector<std::string> use_data;      // use: raw bytes of every scalar leaf
   std::string text;                       // the node's own text (hashed into kernel-cache keys)
   std::vector<std::string> outs;          // array variables defined
   std::vector<ArrayInfo> out_info;
@@ -142,6 +160,7 @@ struct Node {
 };
 
 struct ProgramIR {
+  int n_nodes = 0;                         // nodes of all bodies
   std::map<std::string, ArrayInfo> arrays;
   std::vector<std::string> inputs;
   std::vector<Node> nodes;
@@ -154,5 +173,7 @@ std::unique_ptr<ProgramIR> parse_program(const char* text, size_t len);
 // Free array variables of an expression / function (names, in first-use order).
 void free_arrays(const Expr& e, std::vector<std::string>& out);
 void free_arrays(const Fun& f, std::vector<std::string>& out);
+// Every array variable a node mentions, the bodies of control nodes included.
+void node_arrays(const Node& n, std::vector<std::string>& out);
 
 }  // namespace accb200

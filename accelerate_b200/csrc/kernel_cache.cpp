@@ -7,6 +7,7 @@
 #include <sys/stat.h>
 #include <unistd.h>
 
+#include <atomic>
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
@@ -47,6 +48,21 @@ void mkdirs(const std::string& path) {
   }
 }
 
+// A cached file is trusted only if it is a complete ELF image: magic, 64-bit class, and a section
+// header table that lies inside the file (a file cut short by a full disk or a killed writer fails
+// this; so does a file that is not a cubin at all).
+bool plausible_cubin(const std::string& b) {
+  if (b.size() < 64 || memcmp(b.data(), "\x7f" "ELF", 4) != 0 || b[4] != 2) return false;
+  uint64_t shoff;
+  uint16_t shentsize, shnum;
+  memcpy(&shoff, b.data() + 0x28, 8);
+  memcpy(&shentsize, b.data() + 0x3A, 2);
+  memcpy(&shnum, b.data() + 0x3C, 2);
+  return shoff >= 64 && shoff + (uint64_t)shentsize * shnum <= b.size();
+}
+
+std::atomic<unsigned long long> g_tmp_counter{0};
+
 }  // namespace
 
 std::string content_hash(const std::string& s) {
@@ -57,7 +73,7 @@ std::string content_hash(const std::string& s) {
   return buf;
 }
 
-std::string compile_to_cubin(const std::string& source, const std::string& name, CompileStats* stats) {
+std::string compile_to_cubin(const std::string& source, const std::string& name, CompileStats* stats, bool force) {
   int major = 0, minor = 0;
   nvrtcVersion(&major, &minor);
   std::string keytext = source;
@@ -67,16 +83,17 @@ std::string compile_to_cubin(const std::string& source, const std::string& name,
   const bool use_disk = !(getenv("ACCELERATE_B200_NO_DISK_CACHE"));
   const std::string dir = cache_dir();
   const std::string path = dir + "/" + key + ".cubin";
-  if (use_disk && !getenv("ACCELERATE_B200_FORCE_RECOMP")) {
+  if (use_disk && !force && !getenv("ACCELERATE_B200_FORCE_RECOMP")) {
     std::ifstream f(path, std::ios::binary);
     if (f) {
       std::stringstream ss;
       ss << f.rdbuf();
       std::string cubin = ss.str();
-      if (cubin.size() > 64) {
+      if (plausible_cubin(cubin)) {
         if (stats) stats->disk_hits++;
         return cubin;
       }
+      // damaged cache file: fall through, compile, and replace it
     }
   }
   nvrtcProgram prog;
@@ -100,7 +117,8 @@ std::string compile_to_cubin(const std::string& source, const std::string& name,
   if (stats) stats->compiled++;
   if (use_disk) {
     mkdirs(dir);
-    const std::string tmp = path + ".tmp" + std::to_string((long long)getpid());
+    // unique per writer: two contexts or threads of one process may compile the same kernel at once
+    const std::string tmp = path + ".tmp" + std::to_string((long long)getpid()) + "." + std::to_string(g_tmp_counter.fetch_add(1));
     std::ofstream f(tmp, std::ios::binary);
     if (f) {
       f.write(cubin.data(), (std::streamsize)cubin.size());

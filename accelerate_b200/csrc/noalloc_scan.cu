@@ -158,6 +158,7 @@ extern "C" int b200_scanl1_add_i32_noalloc(const int32_t* in, int32_t* out, int6
   acc_scan_i32_noalloc<<<(unsigned)tiles, SCAN_THREADS, 0, stream>>>(p);
   e = cudaGetLastError();
   if (e != cudaSuccess) return fail(B200_ERR_CUDA, std::string("kernel launch: ") + cudaGetErrorString(e));
+  // synchronous by contract: the status word is read back and the stream synchronised before returning
   int err_word = 0;
   e = cudaMemcpyAsync(&err_word, base + 4, sizeof(int), cudaMemcpyDeviceToHost, stream);
   if (e == cudaSuccess) e = cudaStreamSynchronize(stream);

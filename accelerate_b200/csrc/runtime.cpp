@@ -21,7 +21,10 @@ void Driver::load() {
   ModuleLoadData = (decltype(ModuleLoadData))get("cuModuleLoadData");
   ModuleUnload = (decltype(ModuleUnload))get("cuModuleUnload");
   ModuleGetFunction = (decltype(ModuleGetFunction))get("cuModuleGetFunction");
+  ModuleGetGlobal = (decltype(ModuleGetGlobal))get("cuModuleGetGlobal");
   LaunchKernel = (decltype(LaunchKernel))get("cuLaunchKernel");
+  LaunchKernelEx = (decltype(LaunchKernelEx))get("cuLaunchKernelEx");
+  OccupancyMaxActiveClusters = (decltype(OccupancyMaxActiveClusters))get("cuOccupancyMaxActiveClusters");
   FuncSetAttribute = (decltype(FuncSetAttribute))get("cuFuncSetAttribute");
   OccupancyMaxActiveBlocksPerMultiprocessor =
       (decltype(OccupancyMaxActiveBlocksPerMultiprocessor))get("cuOccupancyMaxActiveBlocksPerMultiprocessor");
@@ -115,10 +118,27 @@ CompiledKernel& Ctx::kernel(const std::string& source, const std::string& entry,
     mem_hits++;
     return it->second;
   }
+  const long long hits_before = cstats.disk_hits;
   std::string cubin = compile_to_cubin(source, entry, &cstats);
   CompiledKernel k;
-  check(drv.ModuleLoadData(&k.module, cubin.data()), "cuModuleLoadData");
+  CUresult lr = drv.ModuleLoadData(&k.module, cubin.data());
+  if (lr != CUDA_SUCCESS && cstats.disk_hits != hits_before) {
+    // the image came from the disk cache and the driver rejects it: compile afresh and replace the file
+    cubin = compile_to_cubin(source, entry, &cstats, true);
+    lr = drv.ModuleLoadData(&k.module, cubin.data());
+  }
+  check(lr, "cuModuleLoadData");
   check(drv.ModuleGetFunction(&k.fn, k.module, entry.c_str()), "cuModuleGetFunction");
+  {
+    // scalar helpers that can fail (integer division) report through this context's status word
+    CUdeviceptr slot = 0;
+    size_t slot_bytes = 0;
+    if (drv.ModuleGetGlobal(&slot, &slot_bytes, k.module, "acc_status_word") == CUDA_SUCCESS && slot_bytes == sizeof(void*)) {
+      void* word = d_words;
+      check(cudaMemcpyAsync((void*)slot, &word, sizeof word, cudaMemcpyHostToDevice, stream), "cudaMemcpyAsync");
+      check(cudaStreamSynchronize(stream), "cudaStreamSynchronize");
+    }
+  }
   if (dyn_smem > 32 * 1024)   // static + dynamic shared memory beyond 48 KB needs the opt-in
     check(drv.FuncSetAttribute(k.fn, CU_FUNC_ATTRIBUTE_MAX_DYNAMIC_SHARED_SIZE_BYTES, (int)dyn_smem), "cuFuncSetAttribute");
   int nb = 0;
@@ -127,7 +147,7 @@ CompiledKernel& Ctx::kernel(const std::string& source, const std::string& entry,
   return kernels.emplace(key, k).first->second;
 }
 
-void* Ctx::scan_descriptors(size_t bytes) {
+void* Ctx::scan_descriptors(size_t bytes, const std::string& layout) {
   // status words of a fresh (zeroed) buffer never match an epoch >= 1
   if (bytes > scan_scratch_bytes || scan_epoch >= (1u << 29)) {
     if (scan_scratch) check(cudaFreeAsync(scan_scratch, stream), "cudaFreeAsync");
@@ -136,9 +156,26 @@ void* Ctx::scan_descriptors(size_t bytes) {
     check(cudaMemsetAsync(scan_scratch, 0, want, stream), "cudaMemsetAsync");
     scan_scratch_bytes = want;
     scan_epoch = 0;
+    scan_layout = layout;
+  } else if (layout != scan_layout) {
+    // Epoch tags tell one launch from the next only while status words stay where they are.  Under
+    // another layout (descriptor width or spacing, region offsets) the words this launch polls may
+    // hold an earlier launch's VALUE bits, which can look like a current status: clear them.
+    check(cudaMemsetAsync(scan_scratch, 0, bytes, stream), "cudaMemsetAsync");
+    scan_layout = layout;
   }
   ++scan_epoch;
   return scan_scratch;
+}
+
+// The ring scan kernel fetches whole tiles with cp.async.bulk, which needs 16-byte aligned global
+// addresses.  A tile of row `row` starts at element row*m + q0 (left scans) or row*m + m - q0 - tile
+// (right scans) with q0 a multiple of the tile; tiles are multiples of 16 bytes, so the condition is
+// on the row pitch alone, and only where it enters the address.
+bool scan_ring_aligned(int elt_bytes, int64_t m, int64_t rows, bool right) {
+  if (elt_bytes <= 0) return false;
+  if (rows <= 1 && !right) return true;
+  return (m * elt_bytes) % 16 == 0;
 }
 
 // ---- source assembly -------------------------------------------------------------------------
@@ -202,7 +239,7 @@ void scan_poll_variant(std::map<std::string, std::string>& v, int64_t total_tile
   v["SCAN_BACKOFF_NS"] = e && *e ? std::string(e) : std::to_string(SCAN_BACKOFF_DEFAULT);
 }
 // shape of the shared-memory ring scan kernel (overridable for tuning)
-struct RingShape { int rounds, slots, minb, lbw, redw, look; };
+struct RingShape { int rounds, slots, minb, lbw, redw, look, grab; };
 RingShape scan_ring_shape(int bytes) {
   auto tune = [](const char* name, int dflt) { const char* e = getenv(name); return e && *e ? atoi(e) : dflt; };
   RingShape r;
@@ -212,12 +249,14 @@ RingShape scan_ring_shape(int bytes) {
   r.lbw = std::max(1, tune("ACCELERATE_B200_RING_LB_WARPS", 1));
   r.redw = std::max(1, tune("ACCELERATE_B200_RING_RED_WARPS", 2));
   r.look = std::max(1, tune("ACCELERATE_B200_SCAN_LOOK", 2));
+  r.grab = tune("ACCELERATE_B200_RING_GRAB", 1);
   return r;
 }
 std::map<std::string, std::string> scan_ring_variant(const RingShape& r, int64_t total_tiles) {
   std::map<std::string, std::string> v = {{"SCAN_RING", "1"}, {"SCAN_ROUNDS", std::to_string(r.rounds)}, {"SCAN_SLOTS", std::to_string(r.slots)},
                                           {"SCAN_MIN_BLOCKS", std::to_string(r.minb)}, {"SCAN_LB_WARPS", std::to_string(r.lbw)},
-                                          {"RING_RED_WARPS", std::to_string(r.redw)}, {"SCAN_LOOK", std::to_string(r.look)}};
+                                          {"RING_RED_WARPS", std::to_string(r.redw)}, {"SCAN_LOOK", std::to_string(r.look)},
+                                          {"RING_GRAB_STATE", std::to_string(r.grab)}};
   scan_poll_variant(v, total_tiles);
   return v;
 }
@@ -264,7 +303,14 @@ std::vector<std::pair<std::string, std::map<std::string, std::string>>> default_
     case N_PERMUTE: {
       v.push_back({"permute", {}});
       const std::string& m = g.defines.at("PERMUTE_MODE");
-      if (m.find("ATOMIC") != std::string::npos) v.push_back({"permute", {{"PERMUTE_SMEM", "1"}, {"PERMUTE_THREADS", "1024"}}});
+      if (m.find("ATOMIC") != std::string::npos) {
+        v.push_back({"permute", {{"PERMUTE_SMEM", "1"}, {"PERMUTE_THREADS", "1024"}}});
+        if (m == "PERMUTE_ATOMIC_ADD" && g.defines.at("PERMUTE_BYTES") == "4" && g.defines.at("PERMUTE_FLOAT") == "0")
+          v.push_back({"permute", {{"PERMUTE_SMEM16", "1"}, {"PERMUTE_THREADS", "1024"}}});
+        if (g.defines.at("PERMUTE_BYTES") == "4")
+          for (int lg : {1, 2, 3, 4})
+            v.push_back({"permute", {{"PERMUTE_CLUSTER", std::to_string(1 << lg)}, {"PERMUTE_CLUSTER_LOG2", std::to_string(lg)}, {"PERMUTE_THREADS", "1024"}}});
+      }
       break;
     }
     case N_STENCIL: case N_STENCIL2:
@@ -409,7 +455,7 @@ struct HostEval {
         r.f.assign(sh.i.size(), 0);
         for (size_t d = sh.i.size(); d-- > 0;) {
           if (d == 0) { r.i[0] = i; break; }
-          if (sh.i[d] == 0) throw Error(B200_ERR_BOUNDS, "divide by zero");
+          if (sh.i[d] == 0) throw Error(B200_ERR_ARITH, "divide by zero");
           r.i[d] = i % sh.i[d];
           i /= sh.i[d];
         }
@@ -477,7 +523,7 @@ struct HostEval {
           case P_MIN: return W((sg ? a <= b : (uint64_t)a <= (uint64_t)b) ? a : b);
           case P_MAX: return W((sg ? a <= b : (uint64_t)a <= (uint64_t)b) ? b : a);
           case P_QUOT: case P_REM: case P_IDIV: case P_MOD: {
-            if (b == 0) throw Error(B200_ERR_BOUNDS, "divide by zero");
+            if (b == 0) throw Error(B200_ERR_ARITH, "divide by zero");
             int64_t q, r;
             if (sg) {
               if (b == -1) { q = (int64_t)((uint64_t)0 - (uint64_t)a); r = 0; }
@@ -551,6 +597,29 @@ struct Launcher {
                "cuLaunchKernel");
     ctx->launches++;
   }
+  // `clusters` thread-block clusters of `csize` CTAs each
+  void launch_clusters(CompiledKernel& k, int64_t clusters, int csize, int threads, size_t smem) {
+    if (clusters <= 0) return;
+    std::vector<uint64_t> pb = block();
+    void* args[1] = {pb.data()};
+    CUlaunchAttribute attr;
+    attr.id = CU_LAUNCH_ATTRIBUTE_CLUSTER_DIMENSION;
+    attr.value.clusterDim.x = (unsigned)csize;
+    attr.value.clusterDim.y = 1;
+    attr.value.clusterDim.z = 1;
+    CUlaunchConfig cfg;
+    memset(&cfg, 0, sizeof cfg);
+    cfg.gridDimX = (unsigned)(clusters * csize);
+    cfg.gridDimY = cfg.gridDimZ = 1;
+    cfg.blockDimX = (unsigned)threads;
+    cfg.blockDimY = cfg.blockDimZ = 1;
+    cfg.sharedMemBytes = (unsigned)smem;
+    cfg.hStream = (CUstream)ctx->stream;
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+    ctx->check(ctx->drv.LaunchKernelEx(&cfg, k.fn, args, nullptr), "cuLaunchKernelEx");
+    ctx->launches++;
+  }
   // extent of a delayed operand + whether its streams all have exactly that shape
   void bind_delayed(const std::string& D, const std::vector<int64_t>& ext, size_t k) {
     bool fast = true;
@@ -596,41 +665,65 @@ size_t struct_bytes(const Type& elt) {
 
 // Arrays are released right after their last use, so a chain of nodes (e.g. one
 // hundred stencil iterations) holds two or three arrays at a time, not all of them.
-void Program::analyse_liveness() {
-  std::map<std::string, size_t> last;
-  for (size_t i = 0; i < ir->nodes.size(); ++i) {
-    const Node& n = ir->nodes[i];
+// Inside the body of a control node only the arrays the body defines are released there; a control
+// node counts as a use of every array its bodies mention.
+void Program::liveness_of(const std::vector<Node>& ns, const std::vector<std::string>& keep) {
+  std::map<std::string, int> last;        // array defined in this list -> id of the node that uses it last
+  std::map<std::string, bool> local;
+  for (auto& n : ns)
+    for (auto& o : n.outs) local[o] = true;
+  for (auto& n : ns) {
     std::vector<std::string> used;
-    if (n.f) free_arrays(*n.f, used);
-    if (n.g) free_arrays(*n.g, used);
-    if (n.seed) free_arrays(*n.seed, used);
-    if (n.extent) free_arrays(*n.extent, used);
-    for (auto& d : n.d) {
-      if (d.extent) free_arrays(*d.extent, used);
-      if (d.index) free_arrays(*d.index, used);
-    }
-    for (auto& b : n.bnd) {
-      if (b.value) free_arrays(*b.value, used);
-      if (b.fun) free_arrays(*b.fun, used);
-    }
-    if (!n.arr.empty()) used.push_back(n.arr);
-    for (auto& u : used) last[u] = i;
+    node_arrays(n, used);
+    for (auto& u : used)
+      if (local.count(u)) last[u] = n.id;
     for (auto& o : n.outs)
-      if (!last.count(o)) last[o] = i;  // never read: dies where it is born
+      if (!last.count(o)) last[o] = n.id;  // never read: dies where it is born
+    for (auto& b : n.body) {
+      std::vector<std::string> k = b.outs;
+      liveness_of(b.nodes, k);
+    }
   }
-  dead_after.assign(ir->nodes.size(), {});
   for (auto& kv : last) {
-    bool is_out = false;
-    for (auto& o : ir->outputs) is_out = is_out || o == kv.first;
-    if (!is_out) dead_after[kv.second].push_back(kv.first);
+    bool kept = false;
+    for (auto& o : keep) kept = kept || o == kv.first;
+    if (!kept) dead_after[kv.second].push_back(kv.first);
   }
+}
+
+void Program::analyse_liveness() {
+  dead_after.assign(ir->n_nodes, {});
+  liveness_of(ir->nodes, ir->outputs);
+}
+
+void Program::upload_constants() {
+  std::vector<const Node*> todo;
+  std::vector<const std::vector<Node>*> stack = {&ir->nodes};
+  while (!stack.empty()) {
+    const std::vector<Node>* ns = stack.back();
+    stack.pop_back();
+    for (auto& n : *ns) {
+      if (n.kind == N_USE) todo.push_back(&n);
+      for (auto& b : n.body) stack.push_back(&b.nodes);
+    }
+  }
+  for (const Node* n : todo) {
+    DevArrayP a = ctx->new_array(n->elt, n->use_shape);
+    for (size_t l = 0; l < a->leaf.size(); ++l)
+      if (a->leaf[l]->bytes) {
+        ctx->check(cudaMemcpyAsync(a->leaf[l]->ptr, n->use_data[l].data(), a->leaf[l]->bytes, cudaMemcpyHostToDevice, ctx->stream), "cudaMemcpyAsync(H2D)");
+        ctx->h2d += (long long)a->leaf[l]->bytes;
+      }
+    constants[n->outs[0]] = a;
+  }
+  if (!todo.empty()) ctx->check(cudaStreamSynchronize(ctx->stream), "cudaStreamSynchronize");
 }
 
 void Program::run(const std::vector<DevArrayP>& inputs, std::vector<DevArrayP>& outputs) {
   Ctx& c = *ctx;
-  if (dead_after.size() != ir->nodes.size()) analyse_liveness();
+  if ((int)dead_after.size() != ir->n_nodes) analyse_liveness();
   if (inputs.size() != ir->inputs.size()) throw Error(B200_ERR_ARG, "wrong number of input arrays");
-  std::map<std::string, DevArrayP> env;
+  Env env;
   for (size_t k = 0; k < inputs.size(); ++k) {
     const ArrayInfo& ai = ir->arrays.at(ir->inputs[k]);
     if (!inputs[k] || inputs[k]->elt != ai.elt || (int)inputs[k]->shape.size() != ai.rank)
@@ -638,13 +731,77 @@ void Program::run(const std::vector<DevArrayP>& inputs, std::vector<DevArrayP>& 
     env[ir->inputs[k]] = inputs[k];
   }
   c.runs++;
-  for (size_t ni = 0; ni < ir->nodes.size(); ++ni) {
-    const Node& n = ir->nodes[ni];
+  exec(ir->nodes, env);
+  outputs.clear();
+  for (auto& o : ir->outputs) outputs.push_back(env.at(o));
+}
+
+// Evaluate an array-level function: bind the parameters, run the nodes, collect the results and
+// drop everything the body defined.
+std::vector<DevArrayP> Program::call(const Body& b, const std::vector<DevArrayP>& args, Env& env) {
+  if (args.size() != b.params.size()) throw Error(B200_ERR_ARG, "array function applied to the wrong number of arguments");
+  for (size_t k = 0; k < args.size(); ++k) env[b.params[k]] = args[k];
+  exec(b.nodes, env);
+  std::vector<DevArrayP> r;
+  for (auto& o : b.outs) r.push_back(env.at(o));
+  for (auto& pn : b.params) env.erase(pn);
+  for (auto& n : b.nodes)
+    for (auto& o : n.outs) env.erase(o);
+  return r;
+}
+
+void Program::exec(const std::vector<Node>& ns, Env& env) {
+  Ctx& c = *ctx;
+  for (const Node& n : ns) {
     struct Reaper {
-      std::map<std::string, DevArrayP>& env;
+      Env& env;
       const std::vector<std::string>& dead;
       ~Reaper() { for (auto& d : dead) env.erase(d); }
-    } reaper{env, dead_after[ni]};
+    } reaper{env, dead_after[n.id]};
+    switch (n.kind) {
+      case N_USE: {
+        auto it = constants.find(n.outs[0]);
+        if (it == constants.end()) throw Error(B200_ERR_ARG, "embedded array '" + n.outs[0] + "' was not uploaded");
+        env[n.outs[0]] = it->second;
+        break;
+      }
+      case N_ACOND: {
+        // Interpreter.hs:217-219: the predicate is a scalar expression (it may read arrays)
+        HostEval he{&c, &env, {}};
+        const bool yes = he.eval(*n.pred).i[0] != 0;
+        std::vector<DevArrayP> r = call(n.body[yes ? 0 : 1], {}, env);
+        for (size_t k = 0; k < n.outs.size(); ++k) env[n.outs[k]] = r[k];
+        break;
+      }
+      case N_AWHILE: {
+        // Interpreter.hs:221-229: iterate while the condition's result, read at linear index 0, is True
+        std::vector<DevArrayP> state;
+        for (auto& a : n.args) state.push_back(env.at(a));
+        for (;;) {
+          std::vector<DevArrayP> cnd = call(n.body[0], state, env);
+          HostEval he{&c, &env, {}};
+          if (he.read(*cnd[0], 0).i[0] == 0) break;
+          state = call(n.body[1], state, env);
+        }
+        for (size_t k = 0; k < n.outs.size(); ++k) env[n.outs[k]] = state[k];
+        break;
+      }
+      case N_APPLY: {
+        std::vector<DevArrayP> args;
+        for (auto& a : n.args) args.push_back(env.at(a));
+        std::vector<DevArrayP> r = call(n.body[0], args, env);
+        for (size_t k = 0; k < n.outs.size(); ++k) env[n.outs[k]] = r[k];
+        break;
+      }
+      default: exec_kernel_node(n, env);
+    }
+  }
+}
+
+void Program::exec_kernel_node(const Node& n, Env& env_ref) {
+  Ctx& c = *ctx;
+  Env& env = env_ref;
+  {
     HostEval he{&c, &env, {}};
     if (n.kind == N_RESHAPE) {
       // reshapeOp (Interpreter.hs:293-303): same data, new shape; sizes must agree
@@ -654,9 +811,9 @@ void Program::run(const std::vector<DevArrayP>& inputs, std::vector<DevArrayP>& 
       auto a = std::make_shared<DevArray>(*src);
       a->shape = sh;
       env[n.outs[0]] = a;
-      continue;
+      return;
     }
-    NodeState& st = nodes[ni];
+    NodeState& st = nodes[n.id];
     Launcher L{&c, &env, &st.glue, {}, {}};
     L.named["err"] = (int64_t)(uintptr_t)(c.d_words + 0);
     L.named["spin_limit"] = c.spin_limit;
@@ -769,20 +926,11 @@ void Program::run(const std::vector<DevArrayP>& inputs, std::vector<DevArrayP>& 
         bool out_vec;
         if (mode == 1) out_vec = right ? ((m + 1) % 4 == 0) : (rows == 1 || (m + 1) % 4 == 0);
         else out_vec = right ? (m % 4 == 0) : (rows == 1 || m % 4 == 0);
-        const size_t sb = struct_bytes(n.elt);
-        const size_t status_bytes = ((size_t)total_tiles * 16 * scan_desc_stride(total_tiles) + 255) / 256 * 256;  // packed descriptors take up to 16 bytes
-        const size_t val_bytes = ((size_t)total_tiles * sb + 255) / 256 * 256;
-        char* base = (char*)c.scan_descriptors(status_bytes + 2 * val_bytes);
         L.named["n"] = m;
         L.named["rows"] = rows;
-        L.named["tiles_per_row"] = tiles_per_row;
         L.named["in_vec"] = in_vec;
         L.named["out_vec"] = out_vec;
-        L.named["status"] = (int64_t)(uintptr_t)base;
-        L.named["agg"] = (int64_t)(uintptr_t)(base + status_bytes);
-        L.named["incl"] = (int64_t)(uintptr_t)(base + status_bytes + val_bytes);
         L.named["counter"] = (int64_t)(uintptr_t)(c.d_words + 2);
-        L.named["epoch"] = c.scan_epoch;
         // shared-memory ring kernel: one scalar leaf in, one scalar leaf of the same size out
         {
           const auto& df = st.glue.defines;
@@ -792,7 +940,7 @@ void Program::run(const std::vector<DevArrayP>& inputs, std::vector<DevArrayP>& 
           const int bytes = packed ? atoi(df.at("SCAN_T_BYTES").c_str()) : 0;
           // 8-byte elements halve the elements a ring holds; the register-resident kernel is faster for them
           const bool want = getenv("ACCELERATE_B200_SCAN_RING") ? true : (bytes <= 4 && !small && !getenv("ACCELERATE_B200_SCAN_NO_RING"));
-          if (one_stream && want && L.fast("D0") && in_vec && out_vec) {
+          if (one_stream && want && L.fast("D0") && in_vec && out_vec && scan_ring_aligned(bytes, m, rows, right)) {
             const RingShape rs = scan_ring_shape(bytes);
             const int rounds = rs.rounds, slots = rs.slots, look = rs.look;
             const int64_t rtile = 8 * (int64_t)rounds * 128;
@@ -804,49 +952,35 @@ void Program::run(const std::vector<DevArrayP>& inputs, std::vector<DevArrayP>& 
             const size_t r_status = ((size_t)r_total * 16 * dstride + 255) / 256 * 256;
             const int64_t groups_per_row = (r_tiles_per_row + 32 * look - 1) / (32 * look);
             const size_t g_status = ((size_t)(rows * groups_per_row) * 16 * dstride + 255) / 256 * 256;
-            char* rbase = (char*)c.scan_descriptors(r_status + g_status);
+            char* rbase = (char*)c.scan_descriptors(r_status + g_status, "ring/" + std::to_string(bytes) + "/" + std::to_string(dstride) + "/" + std::to_string(r_status));
             L.named["gstatus"] = (int64_t)(uintptr_t)(rbase + r_status);
             L.named["groups_per_row"] = groups_per_row;
             L.named["tiles_per_row"] = r_tiles_per_row;
             L.named["total_tiles"] = r_total;
             L.named["status"] = (int64_t)(uintptr_t)rbase;
             L.named["epoch"] = c.scan_epoch;
-            std::shared_ptr<Buffer> tbuf;
-            const char* tpath = getenv("ACCELERATE_B200_SCAN_TRACE");
-            if (tpath) {
-              var["SCAN_TRACE"] = "1";
-              tbuf = c.alloc((size_t)r_total * 64);
-              c.check(cudaMemsetAsync(tbuf->ptr, 0, tbuf->bytes, c.stream), "cudaMemsetAsync");
-              L.named["trace"] = (int64_t)(uintptr_t)tbuf->ptr;
-            }
             const int threads = 256 + 32 * rs.redw + 32 * rs.lbw;     // 8 finisher warps, the reducer warps, the look-back warps
             CompiledKernel& k = c.kernel(assemble_source(st.glue, "scan", var), "acc_scan_ring", threads, smem);
             const int64_t grid = std::min<int64_t>(r_total, (int64_t)c.sm_count * k.max_blocks_per_sm);
             L.launch(k, grid, threads, smem);
-            if (tpath) {
-              std::vector<uint64_t> host((size_t)r_total * 8);
-              c.check(cudaMemcpyAsync(host.data(), tbuf->ptr, tbuf->bytes, cudaMemcpyDeviceToHost, c.stream), "cudaMemcpyAsync");
-              c.check(cudaStreamSynchronize(c.stream), "cudaStreamSynchronize");
-              if (FILE* f = fopen(tpath, "wb")) { fwrite(host.data(), 8, host.size(), f); fclose(f); }
-            }
             break;
           }
         }
-        if (const char* tpath = getenv("ACCELERATE_B200_SCAN_TRACE")) {
-          // diagnostic: per-tile phase timestamps written to a file (8 x u64 per tile)
-          auto var = scan_variant(n.elt, small);
-          scan_poll_variant(var, total_tiles);
-          var["SCAN_TRACE"] = "1";
-          auto tbuf = c.alloc((size_t)total_tiles * 64);
-          c.check(cudaMemsetAsync(tbuf->ptr, 0, tbuf->bytes, c.stream), "cudaMemsetAsync");
-          L.named["trace"] = (int64_t)(uintptr_t)tbuf->ptr;
-          CompiledKernel& kt = c.kernel(assemble_source(st.glue, "scan", var), "acc_scan", 256, 0);
-          L.launch(kt, total_tiles, 256, 0);
-          std::vector<uint64_t> host((size_t)total_tiles * 8);
-          c.check(cudaMemcpyAsync(host.data(), tbuf->ptr, tbuf->bytes, cudaMemcpyDeviceToHost, c.stream), "cudaMemcpyAsync");
-          c.check(cudaStreamSynchronize(c.stream), "cudaStreamSynchronize");
-          if (FILE* f = fopen(tpath, "wb")) { fwrite(host.data(), 8, host.size(), f); fclose(f); }
-          break;
+        {
+          const auto& df = st.glue.defines;
+          const bool packed = df.count("SCAN_PACKED") && df.at("SCAN_PACKED") == "1";
+          const int dstride = scan_desc_stride(total_tiles);
+          const size_t sb = struct_bytes(n.elt);
+          const size_t status_bytes = ((size_t)total_tiles * 16 * dstride + 255) / 256 * 256;  // packed descriptors take up to 16 bytes
+          const size_t val_bytes = ((size_t)total_tiles * sb + 255) / 256 * 256;
+          const std::string layout = (packed ? "packed/" + df.at("SCAN_T_BYTES") : "tuple/" + std::to_string(sb)) + "/" + std::to_string(dstride) + "/" +
+                                     std::to_string(status_bytes) + "/" + std::to_string(val_bytes);
+          char* base = (char*)c.scan_descriptors(status_bytes + 2 * val_bytes, layout);
+          L.named["tiles_per_row"] = tiles_per_row;
+          L.named["status"] = (int64_t)(uintptr_t)base;
+          L.named["agg"] = (int64_t)(uintptr_t)(base + status_bytes);
+          L.named["incl"] = (int64_t)(uintptr_t)(base + status_bytes + val_bytes);
+          L.named["epoch"] = c.scan_epoch;
         }
         auto svar = scan_variant(n.elt, small);
         scan_poll_variant(svar, total_tiles);
@@ -883,6 +1017,60 @@ void Program::run(const std::vector<DevArrayP>& inputs, std::vector<DevArrayP>& 
         const int bytes = atomic ? atoi(st.glue.defines.at("PERMUTE_BYTES").c_str()) : 0;
         const int64_t cap = 200 * 1024;
         const char* no_priv = getenv("ACCELERATE_B200_NO_PRIVATISE");
+        int csize = 0;
+        if (const char* e = getenv("ACCELERATE_B200_PERMUTE_CLUSTER")) csize = atoi(e);
+        if (atomic && bytes == 4 && !no_priv && csize >= 2 && (csize & (csize - 1)) == 0 && total >= 8 * out_n && total >= (1 << 16)) {
+          // the target copy is spread over the shared memories of a cluster of `csize` CTAs
+          int lg = 0;
+          while ((1 << lg) < csize) ++lg;
+          int64_t words = cap / bytes;
+          if (const char* e = getenv("ACCELERATE_B200_PERMUTE_CLUSTER_WORDS")) words = atoll(e);
+          const int64_t priv = std::min<int64_t>((out_n + csize - 1) / csize, words);
+          const size_t smem = (size_t)priv * bytes;
+          std::map<std::string, std::string> var = {{"PERMUTE_CLUSTER", std::to_string(csize)}, {"PERMUTE_CLUSTER_LOG2", std::to_string(lg)},
+                                                    {"PERMUTE_THREADS", "1024"}};
+          if (const char* e = getenv("ACCELERATE_B200_PERMUTE_UNROLL")) var["PERMUTE_UNROLL"] = e;
+          CompiledKernel& k = c.kernel(assemble_source(st.glue, "permute", var), "acc_permute", 1024, smem);
+          if (smem > 48 * 1024) c.check(c.drv.FuncSetAttribute(k.fn, CU_FUNC_ATTRIBUTE_MAX_DYNAMIC_SHARED_SIZE_BYTES, (int)smem), "cuFuncSetAttribute");
+          if (csize > 8) c.check(c.drv.FuncSetAttribute(k.fn, CU_FUNC_ATTRIBUTE_NON_PORTABLE_CLUSTER_SIZE_ALLOWED, 1), "cuFuncSetAttribute");
+          CUlaunchAttribute attr;
+          attr.id = CU_LAUNCH_ATTRIBUTE_CLUSTER_DIMENSION;
+          attr.value.clusterDim.x = (unsigned)csize;
+          attr.value.clusterDim.y = attr.value.clusterDim.z = 1;
+          CUlaunchConfig cfg;
+          memset(&cfg, 0, sizeof cfg);
+          cfg.gridDimX = (unsigned)csize; cfg.gridDimY = cfg.gridDimZ = 1;
+          cfg.blockDimX = 1024; cfg.blockDimY = cfg.blockDimZ = 1;
+          cfg.sharedMemBytes = (unsigned)smem;
+          cfg.attrs = &attr;
+          cfg.numAttrs = 1;
+          int nclusters = 0;
+          c.check(c.drv.OccupancyMaxActiveClusters(&nclusters, k.fn, &cfg), "cuOccupancyMaxActiveClusters");
+          if (getenv("ACCELERATE_B200_VERBOSE")) fprintf(stderr, "[accb200] permute: clusters of %d CTAs, %d resident, %lld words per CTA\n", csize, nclusters, (long long)priv);
+          if (nclusters >= 1) {
+            L.named["priv"] = priv;
+            const int64_t work = (total + 3) / 4;
+            const int64_t want = (work + 1024 * csize - 1) / (1024 * csize);
+            L.launch_clusters(k, std::min<int64_t>(want, nclusters), csize, 1024, smem);
+            break;
+          }
+        }
+        const bool int_add32 = mode == "PERMUTE_ATOMIC_ADD" && bytes == 4 && st.glue.defines.at("PERMUTE_FLOAT") == "0";
+        if (int_add32 && !no_priv && out_n > cap / 4 && (out_n + 1) / 2 <= 56 * 1024 && total >= 8 * out_n && !getenv("ACCELERATE_B200_NO_SMEM16")) {
+          // (+) on 32-bit integers, target too large for a CTA-private 32-bit copy but not for 16-bit
+          // fields: every element of the target is private to the CTA, wherever the frequent ones lie
+          const int64_t words = (out_n + 1) / 2;
+          const size_t smem = (size_t)words * 4;
+          std::map<std::string, std::string> var = {{"PERMUTE_SMEM16", "1"}, {"PERMUTE_THREADS", "1024"}};
+          if (const char* e = getenv("ACCELERATE_B200_PERMUTE_UNROLL")) var["PERMUTE_UNROLL"] = e;
+          CompiledKernel& k = c.kernel(assemble_source(st.glue, "permute", var), "acc_permute", 1024, smem);
+          if (smem > 48 * 1024) c.check(c.drv.FuncSetAttribute(k.fn, CU_FUNC_ATTRIBUTE_MAX_DYNAMIC_SHARED_SIZE_BYTES, (int)smem), "cuFuncSetAttribute");
+          L.named["priv"] = words;
+          const int64_t work = (total + 3) / 4;
+          int64_t grid = std::min<int64_t>((work + 1023) / 1024, (int64_t)c.sm_count);
+          L.launch(k, std::max<int64_t>(grid, 1), 1024, smem);
+          break;
+        }
         if (atomic && !no_priv && out_n > 0 && total >= 8 * out_n && total >= (1 << 16)) {
           // CTA-private copy of the first `priv` target elements in shared memory
           const int64_t priv = std::min<int64_t>(out_n, cap / bytes);
@@ -947,11 +1135,9 @@ void Program::run(const std::vector<DevArrayP>& inputs, std::vector<DevArrayP>& 
         L.launch(k, tiles0 * tiles1 * tiles2, t.threads, 0);
         break;
       }
-      case N_RESHAPE: break;
+      default: break;
     }
   }
-  outputs.clear();
-  for (auto& o : ir->outputs) outputs.push_back(env.at(o));
 }
 
 }  // namespace accb200

@@ -23,8 +23,11 @@ struct Driver {
   CUresult (*ModuleLoadData)(CUmodule*, const void*) = nullptr;
   CUresult (*ModuleUnload)(CUmodule) = nullptr;
   CUresult (*ModuleGetFunction)(CUfunction*, CUmodule, const char*) = nullptr;
+  CUresult (*ModuleGetGlobal)(CUdeviceptr*, size_t*, CUmodule, const char*) = nullptr;
   CUresult (*LaunchKernel)(CUfunction, unsigned, unsigned, unsigned, unsigned, unsigned, unsigned, unsigned, CUstream, void**,
                            void**) = nullptr;
+  CUresult (*LaunchKernelEx)(const CUlaunchConfig*, CUfunction, void**, void**) = nullptr;
+  CUresult (*OccupancyMaxActiveClusters)(int*, CUfunction, const CUlaunchConfig*) = nullptr;
   CUresult (*FuncSetAttribute)(CUfunction, CUfunction_attribute, int) = nullptr;
   CUresult (*OccupancyMaxActiveBlocksPerMultiprocessor)(int*, CUfunction, int, size_t) = nullptr;
   CUresult (*GetErrorString)(CUresult, const char**) = nullptr;
@@ -41,7 +44,8 @@ struct CompiledKernel {
 // Compile `source` for sm_100a; returns the cubin.  Throws Error(B200_ERR_COMPILE)
 // with the NVRTC log.  Results are cached on disk by content hash.
 struct CompileStats { std::atomic<long long> compiled{0}, disk_hits{0}; };
-std::string compile_to_cubin(const std::string& source, const std::string& name, CompileStats* stats);
+// `force` skips the disk cache lookup (and replaces the cached file).
+std::string compile_to_cubin(const std::string& source, const std::string& name, CompileStats* stats, bool force = false);
 std::string content_hash(const std::string& s);
 
 // ---- device arrays -------------------------------------------------------------------
@@ -86,6 +90,7 @@ struct Ctx {
   void* scan_scratch = nullptr;
   size_t scan_scratch_bytes = 0;
   uint32_t scan_epoch = 0;
+  std::string scan_layout;      // how the last scan laid its descriptors out in the scratch buffer
   std::map<std::string, CompiledKernel> kernels;  // by content hash of the source
   CompileStats cstats;
   std::atomic<long long> launches{0}, h2d{0}, d2h{0}, mem_hits{0}, allocated{0}, runs{0};
@@ -96,7 +101,7 @@ struct Ctx {
   void check(cudaError_t e, const char* what);
   void check(CUresult e, const char* what);
   CompiledKernel& kernel(const std::string& source, const std::string& entry, int threads, size_t dyn_smem);
-  void* scan_descriptors(size_t bytes);
+  void* scan_descriptors(size_t bytes, const std::string& layout);
 };
 
 // ---- programs ------------------------------------------------------------------------
@@ -107,14 +112,25 @@ struct NodeState {
 struct Program {
   Ctx* ctx = nullptr;
   std::unique_ptr<ProgramIR> ir;
-  std::vector<NodeState> nodes;
-  std::vector<std::vector<std::string>> dead_after;  // arrays whose last use is node i
+  std::vector<NodeState> nodes;                      // by Node::id, the bodies of control nodes included
+  std::vector<std::vector<std::string>> dead_after;  // by Node::id: arrays whose last use is that node
+  std::map<std::string, DevArrayP> constants;        // arrays embedded with (use ...), uploaded at load time
   void analyse_liveness();
+  void upload_constants();                           // needs ctx; called once by b200_program_load
   void run(const std::vector<DevArrayP>& inputs, std::vector<DevArrayP>& outputs);
+
+ private:
+  typedef std::map<std::string, DevArrayP> Env;
+  void liveness_of(const std::vector<Node>& nodes, const std::vector<std::string>& keep);
+  void exec(const std::vector<Node>& nodes, Env& env);
+  void exec_kernel_node(const Node& n, Env& env);
+  std::vector<DevArrayP> call(const Body& b, const std::vector<DevArrayP>& args, Env& env);
 };
 
 // Source text of one kernel variant: prelude, defines, generated code, skeleton.
 std::string assemble_source(const Glue& g, const std::string& skeleton, const std::map<std::string, std::string>& variant);
+// Whether the bulk copies of the ring scan kernel would be 16-byte aligned for rows of m elements.
+bool scan_ring_aligned(int elt_bytes, int64_t m, int64_t rows, bool right);
 // Default variants of a node (used by the build-time compile check).
 std::vector<std::pair<std::string, std::map<std::string, std::string>>> default_variants(const Node& n, const Glue& g);
 

@@ -6,7 +6,12 @@
 //   PERMUTE_ATOMIC_*  f is (+)/min/max/and/or/xor on a 32/64-bit scalar: one
 //                     fire-and-forget reduction (red.global), optionally staged
 //                     through a CTA-private copy of the first `priv` target
-//                     elements in shared memory when the target is small;
+//                     elements in shared memory when the target is small
+//                     (PERMUTE_SMEM), or through a copy of the target that is
+//                     spread over the shared memories of a thread-block cluster
+//                     when it fits there but not in one CTA (PERMUTE_CLUSTER:
+//                     element b lives in CTA b mod C at word b div C; updates
+//                     travel as shared::cluster reductions, never through L2);
 //   PERMUTE_CAS       any other f on a 32/64-bit scalar: compare-and-swap loop;
 //   PERMUTE_STORE     `permute const`: plain store (targets assumed unique);
 //   PERMUTE_LOCK      everything else (tuples, narrow types): one spin lock per
@@ -101,14 +106,97 @@ __device__ __forceinline__ PERMUTE_T permute_identity() {
 }
 #endif
 
-#if PERMUTE_SMEM
+#ifndef PERMUTE_CLUSTER
+#define PERMUTE_CLUSTER 0
+#endif
+#ifndef PERMUTE_SMEM16
+#define PERMUTE_SMEM16 0
+#endif
+#if PERMUTE_SMEM || PERMUTE_CLUSTER || PERMUTE_SMEM16
 extern __shared__ __align__(16) unsigned char permute_smem_raw[];
+#endif
+
+#if PERMUTE_SMEM16
+// (+) on a 32-bit integer target of up to twice as many elements as a CTA has shared-memory words:
+// the CTA keeps the LOW 16 bits of its contribution to every element, two elements per word, and
+// sends everything else straight to the target with red.global:
+//   * the high 16 bits of an addend (zero for counts and other small addends);
+//   * 65536 whenever a 16-bit field wraps.  Every update is one atomicAdd on the word, whose return
+//     value shows exactly whether the addressed field wrapped; a wrap of the lower field also
+//     carries 1 into the upper field, which is taken out again with a second atomic (and if that
+//     carry or its removal wraps the upper field, that too is seen in the returned value and
+//     compensated).  All arithmetic is modulo 2^32 on the target, like the reference's Int32/Word32.
+// At the end the fields are added to the target (permute_flush16).
+__device__ __forceinline__ void permute_add16(const Params& p, i64 dst, u32 v) {
+  u32* sm = reinterpret_cast<u32*>(permute_smem_raw);
+  u32* out = reinterpret_cast<u32*>(p.out0_l0);
+  const u32 hi = v & 0xffff0000u, lo = v & 0xffffu;
+  if (hi) atomicAdd(out + dst, hi);
+  if (!lo) return;
+  u32* w = sm + (dst >> 1);
+  if (dst & 1) {
+    const u32 old = atomicAdd(w, lo << 16);
+    if (((old >> 16) + lo) >> 16) atomicAdd(out + dst, 65536u);
+  } else {
+    const u32 old = atomicAdd(w, lo);
+    if (((old & 0xffffu) + lo) >> 16) {
+      atomicAdd(out + dst, 65536u);
+      if ((old >> 16) == 0xffffu) atomicAdd(out + dst + 1, 65536u);        // the carry wrapped the upper field
+      const u32 old2 = atomicAdd(w, 0xffff0000u);                          // take the carry out again
+      if ((old2 >> 16) == 0u) atomicAdd(out + dst + 1, 0u - 65536u);       // ... which wrapped it downwards
+    }
+  }
+}
+#endif
+
+#if PERMUTE_CLUSTER
+// PERMUTE_CLUSTER = number of CTAs per cluster (a power of two), PERMUTE_CLUSTER_LOG2 its logarithm.
+__device__ __forceinline__ u32 permute_cluster_rank() { u32 r; asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r)); return r; }
+__device__ __forceinline__ void permute_cluster_sync() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// reduction into word `word` of the target copy held by CTA `owner` of this cluster
+__device__ __forceinline__ void permute_cluster_red(u32 owner, u32 word, PERMUTE_T v) {
+  const u32 local = (u32)__cvta_generic_to_shared(permute_smem_raw) + word * (u32)sizeof(PERMUTE_T);
+  u32 remote;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local), "r"(owner));
+#if PERMUTE_MODE == PERMUTE_ATOMIC_ADD && PERMUTE_FLOAT
+  asm volatile("red.relaxed.cluster.shared::cluster.add.f32 [%0], %1;" ::"r"(remote), "f"(v) : "memory");
+#elif PERMUTE_MODE == PERMUTE_ATOMIC_ADD
+  asm volatile("red.relaxed.cluster.shared::cluster.add.u32 [%0], %1;" ::"r"(remote), "r"(permute_bits(v)) : "memory");
+#elif PERMUTE_MODE == PERMUTE_ATOMIC_MIN && PERMUTE_SIGNED
+  asm volatile("red.relaxed.cluster.shared::cluster.min.s32 [%0], %1;" ::"r"(remote), "r"((int)v) : "memory");
+#elif PERMUTE_MODE == PERMUTE_ATOMIC_MIN
+  asm volatile("red.relaxed.cluster.shared::cluster.min.u32 [%0], %1;" ::"r"(remote), "r"(permute_bits(v)) : "memory");
+#elif PERMUTE_MODE == PERMUTE_ATOMIC_MAX && PERMUTE_SIGNED
+  asm volatile("red.relaxed.cluster.shared::cluster.max.s32 [%0], %1;" ::"r"(remote), "r"((int)v) : "memory");
+#elif PERMUTE_MODE == PERMUTE_ATOMIC_MAX
+  asm volatile("red.relaxed.cluster.shared::cluster.max.u32 [%0], %1;" ::"r"(remote), "r"(permute_bits(v)) : "memory");
+#elif PERMUTE_MODE == PERMUTE_ATOMIC_AND
+  asm volatile("red.relaxed.cluster.shared::cluster.and.b32 [%0], %1;" ::"r"(remote), "r"(permute_bits(v)) : "memory");
+#elif PERMUTE_MODE == PERMUTE_ATOMIC_OR
+  asm volatile("red.relaxed.cluster.shared::cluster.or.b32 [%0], %1;" ::"r"(remote), "r"(permute_bits(v)) : "memory");
+#else
+  asm volatile("red.relaxed.cluster.shared::cluster.xor.b32 [%0], %1;" ::"r"(remote), "r"(permute_bits(v)) : "memory");
+#endif
+}
 #endif
 
 __device__ __forceinline__ void permute_update(const Params& p, i64 dst, const elt_t& v) {
 #if PERMUTE_IS_ATOMIC
+#if PERMUTE_SMEM16
+  permute_add16(p, dst, permute_bits(v.l0));
+  return;
+#endif
 #if PERMUTE_SMEM
   if (dst < p.priv) { permute_atomic(reinterpret_cast<PERMUTE_T*>(permute_smem_raw) + dst, v.l0); return; }
+#endif
+#if PERMUTE_CLUSTER
+  // p.priv = words of the target copy per CTA: elements below priv * C are on chip
+  if ((dst >> PERMUTE_CLUSTER_LOG2) < p.priv) {
+    permute_cluster_red((u32)dst & (PERMUTE_CLUSTER - 1), (u32)(dst >> PERMUTE_CLUSTER_LOG2), v.l0);
+    return;
+  }
 #endif
   permute_atomic(p.out0_l0 + dst, v.l0);
 #elif PERMUTE_MODE == PERMUTE_CAS
@@ -142,8 +230,12 @@ __device__ __forceinline__ void permute_update(const Params& p, i64 dst, const e
 }
 
 __device__ __forceinline__ void permute_elem(const Params& p, const pelem_t& e) {
-  // the reference checks the target index (Shape.hs:102-106); here an out-of-range target is dropped
-  if (e.l0 != 0 && (u64)e.l1 < (u64)p.out_n) permute_update(p, e.l1, P_value(e));
+  // the reference checks every component of the target index (indexCheck in toIndex,
+  // Shape.hs:102-106); the generated index function yields -1 for a target outside the array
+  if (e.l0 != 0) {
+    if ((u64)e.l1 < (u64)p.out_n) permute_update(p, e.l1, P_value(e));
+    else acc_fail(p.err, 1003 /* index out of bounds */);
+  }
 }
 
 extern "C" __global__ void __launch_bounds__(PERMUTE_THREADS) acc_permute(const Params p) {
@@ -151,10 +243,22 @@ extern "C" __global__ void __launch_bounds__(PERMUTE_THREADS) acc_permute(const 
   const i64 inner = P_INNER;
   const i64 tid = (i64)blockIdx.x * PERMUTE_THREADS + threadIdx.x;
   const i64 nthreads = (i64)gridDim.x * PERMUTE_THREADS;
-#if PERMUTE_SMEM
+#if PERMUTE_SMEM16
+  {
+    // p.priv = number of 32-bit words (two target elements each)
+    u32* sm16 = reinterpret_cast<u32*>(permute_smem_raw);
+    for (i64 b = threadIdx.x; b < p.priv; b += PERMUTE_THREADS) sm16[b] = 0u;
+    __syncthreads();
+  }
+#endif
+#if PERMUTE_SMEM || PERMUTE_CLUSTER
   PERMUTE_T* sm = reinterpret_cast<PERMUTE_T*>(permute_smem_raw);
   for (i64 b = threadIdx.x; b < p.priv; b += PERMUTE_THREADS) sm[b] = permute_identity();
+#if PERMUTE_CLUSTER
+  permute_cluster_sync();     // no update may reach a CTA that is still clearing its part
+#else
   __syncthreads();
+#endif
 #endif
   i64 done = 0;
   if (p.vec) {
@@ -197,6 +301,29 @@ extern "C" __global__ void __launch_bounds__(PERMUTE_THREADS) acc_permute(const 
   for (i64 b = threadIdx.x; b < p.priv; b += PERMUTE_THREADS) {
     const PERMUTE_T v = sm[b];
     if (permute_bits(v) != permute_bits(permute_identity())) permute_atomic(p.out0_l0 + b, v);
+  }
+#endif
+#if PERMUTE_SMEM16
+  __syncthreads();
+  {
+    const u32* sm16 = reinterpret_cast<const u32*>(permute_smem_raw);
+    u32* out = reinterpret_cast<u32*>(p.out0_l0);
+    for (i64 b = threadIdx.x; b < p.priv; b += PERMUTE_THREADS) {
+      const u32 w = sm16[b];
+      if (w & 0xffffu) atomicAdd(out + 2 * b, w & 0xffffu);
+      if ((w >> 16) && 2 * b + 1 < p.out_n) atomicAdd(out + 2 * b + 1, w >> 16);
+    }
+  }
+#endif
+#if PERMUTE_CLUSTER
+  permute_cluster_sync();     // every CTA of the cluster has sent its last update
+  {
+    const i64 rank = permute_cluster_rank();
+    for (i64 b = threadIdx.x; b < p.priv; b += PERMUTE_THREADS) {
+      const i64 dst = (b << PERMUTE_CLUSTER_LOG2) + rank;
+      const PERMUTE_T v = sm[b];
+      if (dst < p.out_n && permute_bits(v) != permute_bits(permute_identity())) permute_atomic(p.out0_l0 + dst, v);
+    }
   }
 #endif
 }

@@ -28,16 +28,26 @@ template <> struct acc_unsigned<u32> { typedef u32 type; };
 template <> struct acc_unsigned<u64> { typedef u64 type; };
 template <class T> struct acc_is_signed { static const bool value = ((T)-1) < (T)0; };
 
-// quot/rem truncate toward zero; div/mod floor (Interpreter.hs:1328-1344).
-// Division by zero raises an exception in the reference; here it yields 0.
+// Status word of the context that launched the kernel.  Scalar helpers have no parameter block at
+// hand, so the host stores the word's address here when it loads the module (the variable is absent
+// from modules that never raise).  Codes: 1002 divide by zero, 1003 index out of bounds.
+extern "C" { __device__ int* acc_status_word = nullptr; }
+__device__ __forceinline__ void acc_raise(int code) {
+  int* w = acc_status_word;
+  if (w) atomicCAS(w, 0, code);
+}
+
+// quot/rem truncate toward zero; div/mod floor (Interpreter.hs:1328-1344).  Division by zero raises
+// an exception in the reference (GHC's DivideByZero); here it is recorded in the status word (the
+// call that next synchronises reports B200_ERR_ARITH) and the operation yields 0.
 template <class T> __device__ __forceinline__ T acc_quot(T a, T b) {
   typedef typename acc_unsigned<T>::type U;
-  if (b == 0) return 0;
+  if (b == 0) { acc_raise(1002); return 0; }
   if (acc_is_signed<T>::value && b == (T)-1) return (T)((U)0 - (U)a);
   return (T)(a / b);
 }
 template <class T> __device__ __forceinline__ T acc_rem(T a, T b) {
-  if (b == 0) return 0;
+  if (b == 0) { acc_raise(1002); return 0; }
   if (acc_is_signed<T>::value && b == (T)-1) return 0;
   return (T)(a % b);
 }

@@ -36,19 +36,6 @@
 #ifndef SCAN_LOOK
 #define SCAN_LOOK 2
 #endif
-// SCAN_TRACE: diagnostic build that records, per tile, nanosecond timestamps of its phases
-// (8 words per tile at the address in the named parameter `trace`).
-#ifndef SCAN_TRACE
-#define SCAN_TRACE 0
-#endif
-#if SCAN_TRACE
-__device__ __forceinline__ u64 scan_now() { u64 t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); return t; }
-#define SCAN_MARK(T, K) do { if (threadIdx.x == 0) reinterpret_cast<u64*>(p.trace)[(T) * 8 + (K)] = scan_now(); } while (0)
-#define SCAN_MARK_VAL(T, K, V) do { if (threadIdx.x == 0) reinterpret_cast<u64*>(p.trace)[(T) * 8 + (K)] = (u64)(V); } while (0)
-#else
-#define SCAN_MARK(T, K) do { } while (0)
-#define SCAN_MARK_VAL(T, K, V) do { } while (0)
-#endif
 #define SCAN_ST_AGG 1u
 #define SCAN_ST_PREFIX 2u
 
@@ -177,7 +164,6 @@ __device__ __forceinline__ void scan_tile_body(const Params& p, const i64 T, con
   const i64 tile_q0 = tt * SCAN_TILE;
   const i64 warp_q0 = tile_q0 + (i64)warp * SCAN_WARP_ELEMS;
   const bool out_vec = p.out_vec != 0;
-  SCAN_MARK(T, 1);   // the tile's elements have been requested
   elt_t tot[SCAN_ROUNDS];
   bool htot[SCAN_ROUNDS];
 #pragma unroll
@@ -222,7 +208,6 @@ __device__ __forceinline__ void scan_tile_body(const Params& p, const i64 T, con
   // carry now holds the warp's total
   if (lane == 0) { sm_v[warp] = carry; sm_h[warp] = hcarry; }
   SCAN_SYNC();
-  SCAN_MARK(T, 2);   // local scans done
 
   // ---- tile aggregate, look-back (warp 0), tile exclusive prefix ---------------
   if (warp == 0) {
@@ -255,7 +240,6 @@ __device__ __forceinline__ void scan_tile_body(const Params& p, const i64 T, con
       }
       const i64 row_first = T - tt;
       i64 look = T - 1;
-      int windows = 0;
       // Each lane inspects SCAN_LOOK consecutive predecessors per step (distance
       // SCAN_LOOK*lane + j from `look`), so one L2 round trip covers 32*SCAN_LOOK tiles: the
       // rate at which prefixes propagate, not bandwidth, is what limits a single-pass scan.
@@ -321,8 +305,6 @@ __device__ __forceinline__ void scan_tile_body(const Params& p, const i64 T, con
           if (lane + d < 32) scan_join_front(p, o, oh != 0, c, hc);
         }
         scan_join_front(p, c, hc, excl, hexcl);  // meaningful in lane 0
-        ++windows;
-        SCAN_MARK_VAL(T, 6, windows);
         if (pm != 0 || look - 32 * SCAN_LOOK < row_first) break;
         look -= 32 * SCAN_LOOK;
       }
@@ -362,7 +344,6 @@ __device__ __forceinline__ void scan_tile_body(const Params& p, const i64 T, con
     }
   }
   SCAN_SYNC();
-  SCAN_MARK(T, 3);   // exclusive prefix known
   if (sm_flag[1]) return;
 
   // ---- per-thread prefixes and stores ----------------------------------------------
@@ -421,7 +402,6 @@ __device__ __forceinline__ void scan_tile_body(const Params& p, const i64 T, con
       }
     }
   }
-  SCAN_MARK(T, 4);   // stores issued
 }
 
 template <bool FULL>
@@ -432,7 +412,6 @@ __device__ __forceinline__ void scan_tile(const Params& p, const i64 T, const i6
   const i64 tile_q0 = tt * SCAN_TILE;
   const i64 warp_q0 = tile_q0 + (i64)warp * SCAN_WARP_ELEMS;
   const bool in_vec = p.in_vec != 0;
-  SCAN_MARK(T, 0);   // tile started
 
   // ---- load; thread-local inclusive scan of each group of four ----------------
   elt_t item[SCAN_ROUNDS][4];
@@ -487,10 +466,14 @@ extern "C" __global__ void __launch_bounds__(SCAN_THREADS, SCAN_MIN_BLOCKS) acc_
 // acc_scan_ring: persistent CTAs that keep SCAN_SLOTS tiles each in a shared-memory
 // ring.  A tile is bulk-copied in (cp.async.bulk + mbarrier); reducer warps publish
 // its aggregate the moment it has arrived; a look-back warp finds its exclusive
-// prefix; finisher warps then scan the tile straight out of shared memory, store it
-// and hand the slot to the next ticket.  Unlike acc_scan, tile data does not occupy
-// registers while the look-back is pending, so a SM keeps several times more
-// elements in flight and the look-back latency idles the memory system much less.
+// prefix.  The finisher warps take the oldest tile whose aggregate is out into
+// registers, scan it there and hand its slot to the next ticket at once; they add the
+// exclusive prefix and store when the look-back has delivered it.  A CTA therefore has
+// SCAN_SLOTS tiles in shared memory plus one in registers in flight, and the look-back
+// latency idles the memory system much less than in acc_scan, where a tile occupies
+// registers from its load to its store.  Bookkeeping is per ring position (RING_META
+// entries), separate from the data slots, because a slot is reused while the tile it
+// held is still waiting for its prefix.
 // Requirements (checked by the host): one scalar leaf (SCAN_PACKED), exactly one stream
 // leaf of the same size, fast layout, in_vec and out_vec.  Partial tiles (the last of a
 // row) are handled by scan_tile<false> inside the same kernel.
@@ -500,6 +483,7 @@ extern "C" __global__ void __launch_bounds__(SCAN_THREADS, SCAN_MIN_BLOCKS) acc_
 #ifndef SCAN_SLOTS
 #define SCAN_SLOTS 6
 #endif
+#define RING_META (SCAN_SLOTS + 1)
 #define RING_SLOT_BYTES (SCAN_TILE * SCAN_T_BYTES)
 #define RING_GROUP (32 * SCAN_LOOK)
 #define RING_PH_OWN 0
@@ -547,6 +531,12 @@ template <class T> __device__ __forceinline__ void ring_stv(T* p, T v) { *reinte
 #define RING_RED_WARPS 2
 #endif
 #define RING_THREADS (SCAN_THREADS + 32 * RING_RED_WARPS + 32 * SCAN_LB_WARPS)
+// state a tile must have reached before the finishers take it out of its slot: SCANNED (its
+// aggregate is out; the default) or RESOLVED (its prefix is known: the tile then stays in its slot
+// for the whole look-back)
+#ifndef RING_GRAB_STATE
+#define RING_GRAB_STATE RING_SCANNED
+#endif
 #define RING_ACT_SCAN 1
 #define RING_ACT_FIN 2
 #define RING_ACT_EXIT 4
@@ -563,11 +553,12 @@ extern "C" __global__ void __launch_bounds__(RING_THREADS, SCAN_MIN_BLOCKS) acc_
   __shared__ elt_t sm_excl1;
   __shared__ int sm_flag1[2];
   __shared__ __align__(8) u64 full_bar[SCAN_SLOTS];
-  __shared__ i64 slot_tile[SCAN_SLOTS], slot_pos[SCAN_SLOTS];
-  __shared__ u32 slot_parity[SCAN_SLOTS], slot_uses[SCAN_SLOTS];
-  __shared__ int slot_direct[SCAN_SLOTS], slot_state[SCAN_SLOTS], slot_hexcl[SCAN_SLOTS];
-  __shared__ elt_t slot_agg[SCAN_SLOTS], slot_excl[SCAN_SLOTS];
-  __shared__ int ctl_act, sh_fail;
+  // data slots: full_bar, slot_uses; ring positions (index pos % RING_META): everything else
+  __shared__ i64 slot_tile[RING_META], slot_pos[RING_META];
+  __shared__ u32 slot_parity[RING_META], slot_uses[SCAN_SLOTS];
+  __shared__ int slot_direct[RING_META], slot_state[RING_META], slot_hexcl[RING_META];
+  __shared__ elt_t slot_agg[RING_META], slot_excl[RING_META];
+  __shared__ int ctl_act, ctl_act2, sh_fail;   // thread 0's verdicts after the two waits of an iteration
   __shared__ elt_t red_v[2][RING_RED_WARPS];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const i64 n = p.n;
@@ -576,19 +567,20 @@ extern "C" __global__ void __launch_bounds__(RING_THREADS, SCAN_MIN_BLOCKS) acc_
   unsigned* counter = reinterpret_cast<unsigned*>(p.counter);
   unsigned* exits = counter + 1;
 
-  // worker thread 0: next ticket into slot s for ring position `pos`
-  auto fetch = [&](int s, i64 pos) {
+  // worker thread 0: next ticket for ring position `pos`, whose data go to slot pos % SCAN_SLOTS
+  auto fetch = [&](i64 pos) {
+    const int s = (int)(pos % SCAN_SLOTS), m = (int)(pos % RING_META);
     const i64 T = (i64)atomicAdd(counter, 1u);
-    slot_tile[s] = T;
-    slot_direct[s] = 1;
-    slot_state[s] = RING_LOADING;
+    slot_tile[m] = T;
+    slot_direct[m] = 1;
+    slot_state[m] = RING_LOADING;
     if (T < total_tiles) {
       const i64 row = T / p.tiles_per_row;
       const i64 tt = T - row * p.tiles_per_row;
       const i64 q0 = tt * SCAN_TILE;
       if (q0 + SCAN_TILE <= n) {
-        slot_direct[s] = 0;
-        slot_parity[s] = slot_uses[s] & 1u;
+        slot_direct[m] = 0;
+        slot_parity[m] = slot_uses[s] & 1u;
         slot_uses[s] += 1;
 #if ACC_RIGHT
         const i64 src = row * n + (n - q0 - SCAN_TILE);
@@ -596,24 +588,24 @@ extern "C" __global__ void __launch_bounds__(RING_THREADS, SCAN_MIN_BLOCKS) acc_
         const i64 src = row * n + q0;
 #endif
         unsigned char* base = scan_ring_smem + (size_t)s * RING_SLOT_BYTES;
-        SCAN_MARK(T, 0);   // requested
         ring_mbar_expect(&full_bar[s], (u32)RING_SLOT_BYTES);
         D0_BULK_ISSUE(base, &full_bar[s], src)
       }
     }
     __threadfence_block();
-    ring_stv(&slot_pos[s], pos);          // the look-back warp may now look at the slot
+    ring_stv(&slot_pos[m], pos);          // reducers and the look-back warp may now look at the entry
   };
 
   if (tid == 0) {
-    for (int s = 0; s < SCAN_SLOTS; ++s) { ring_mbar_init(&full_bar[s], 1); slot_uses[s] = 0; slot_pos[s] = -1; }
+    for (int s = 0; s < SCAN_SLOTS; ++s) { ring_mbar_init(&full_bar[s], 1); slot_uses[s] = 0; }
+    for (int m = 0; m < RING_META; ++m) { slot_pos[m] = -1; slot_tile[m] = total_tiles; slot_direct[m] = 1; slot_state[m] = RING_DONE; }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     ctl_act = 0;
     sh_fail = 0;
   }
   __syncthreads();
   if (tid == 0)
-    for (int s = 0; s < SCAN_SLOTS; ++s) fetch(s, s);
+    for (int s = 0; s < SCAN_SLOTS; ++s) fetch(s);
   __syncthreads();
 
   if (warp >= SCAN_WARPS + RING_RED_WARPS) {
@@ -624,7 +616,7 @@ extern "C" __global__ void __launch_bounds__(RING_THREADS, SCAN_MIN_BLOCKS) acc_
     // yet from its tile descriptors and publishes the summary for every later walker.
     int lb_failed = 0;
     for (i64 r = warp - SCAN_WARPS - RING_RED_WARPS;; r += SCAN_LB_WARPS) {
-      const int s = (int)(r % SCAN_SLOTS);
+      const int s = (int)(r % RING_META);
       i64 spins = 0;
       int failed = 0;
       while (ring_ldv(&slot_pos[s]) != r) {
@@ -655,10 +647,8 @@ extern "C" __global__ void __launch_bounds__(RING_THREADS, SCAN_MIN_BLOCKS) acc_
       int phase = (tt % RING_GROUP == 0) ? RING_PH_GROUPS : RING_PH_OWN;
       i64 g = gid - 1;
       i64 polls = 0;
-      int steps = 0;
       bool done = false;
       while (!done) {
-        ++steps;
         if (phase == RING_PH_GROUPS) {
           const i64 gi = g - lane;
           const bool in = gi >= 0;
@@ -748,10 +738,6 @@ extern "C" __global__ void __launch_bounds__(RING_THREADS, SCAN_MIN_BLOCKS) acc_
           scan_desc_store(p.gstatus, group_base + gid, (epoch << 2) | SCAN_ST_PREFIX, inc.l0);
         slot_excl[s] = excl;
         slot_hexcl[s] = hexcl ? 1 : 0;
-#if SCAN_TRACE
-        reinterpret_cast<u64*>(p.trace)[T * 8 + 3] = scan_now();   // prefix known
-        reinterpret_cast<u64*>(p.trace)[T * 8 + 6] = (u64)steps;
-#endif
         __threadfence_block();
         ring_stv(&slot_state[s], RING_RESOLVED);
       }
@@ -766,7 +752,7 @@ extern "C" __global__ void __launch_bounds__(RING_THREADS, SCAN_MIN_BLOCKS) acc_
     const int rt = tid - SCAN_THREADS, rw = warp - SCAN_WARPS;
     int red_failed = 0;
     for (i64 r = 0;; ++r) {
-      const int s = (int)(r % SCAN_SLOTS);
+      const int s = (int)(r % RING_META), ds = (int)(r % SCAN_SLOTS);
       i64 spins = 0;
       while (ring_ldv(&slot_pos[s]) != r) {
         if (++spins > p.spin_limit || ring_ldv(&sh_fail)) { red_failed = 1; break; }
@@ -778,16 +764,13 @@ extern "C" __global__ void __launch_bounds__(RING_THREADS, SCAN_MIN_BLOCKS) acc_
       if (T >= total_tiles) break;
       if (slot_direct[s]) continue;                 // partial tile: the finishers do it start to finish
       spins = 0;
-      while (!ring_mbar_try_wait(&full_bar[s], slot_parity[s])) {
+      while (!ring_mbar_try_wait(&full_bar[ds], slot_parity[s])) {
         if (++spins > p.spin_limit || ring_ldv(&sh_fail)) { red_failed = 1; break; }
       }
       if (red_failed) break;
       const i64 row = T / p.tiles_per_row;
       const i64 tt = T - row * p.tiles_per_row;
-      const unsigned char* base = scan_ring_smem + (size_t)s * RING_SLOT_BYTES;
-#if SCAN_TRACE
-      if (rt == 0) reinterpret_cast<u64*>(p.trace)[T * 8 + 1] = scan_now();   // arrived
-#endif
+      const unsigned char* base = scan_ring_smem + (size_t)ds * RING_SLOT_BYTES;
       // warp rw reduces elements [rw, rw + 1) * SCAN_TILE / RING_RED_WARPS in rounds of 128
       constexpr int RED_ROUNDS = SCAN_TILE / (128 * RING_RED_WARPS);
       elt_t tot;
@@ -838,9 +821,6 @@ extern "C" __global__ void __launch_bounds__(RING_THREADS, SCAN_MIN_BLOCKS) acc_
         elt_t agg = red_v[r & 1][0];
         for (int w = 1; w < RING_RED_WARPS; ++w) agg = scan_op(p, agg, red_v[r & 1][w]);
         slot_agg[s] = agg;
-#if SCAN_TRACE
-        reinterpret_cast<u64*>(p.trace)[T * 8 + 2] = scan_now();   // aggregate published
-#endif
         if (tt == 0) {
           // first tile of a row: its exclusive prefix is the seed (or nothing)
           elt_t inc = agg;
@@ -865,24 +845,29 @@ extern "C" __global__ void __launch_bounds__(RING_THREADS, SCAN_MIN_BLOCKS) acc_
     if (red_failed && lane == 0) ring_stv(&sh_fail, 1);
   } else {
     // ================= finishers ========================================================
-    // Slots are finished in ring order: once a slot knows its exclusive prefix, the tile is scanned
-    // straight out of shared memory and stored, and the slot is handed to the next ticket.
+    // Ring positions are finished in order.  As soon as the tile's aggregate is out (the reducers
+    // are done with the slot) the tile is read into registers and scanned there, and its slot is
+    // handed to the next ticket; prefix and stores follow when the look-back has resolved the tile.
     i64 idle = 0;                          // thread 0: consecutive polls without anything to do
     for (i64 r = 0;; ++r) {
-      const int fs = (int)(r % SCAN_SLOTS);
-      const i64 T = slot_tile[fs];         // written by thread 0 before a SCAN_SYNC
+      const int fs = (int)(r % SCAN_SLOTS), fm = (int)(r % RING_META);
+      const i64 T = slot_tile[fm];         // written by thread 0 before a SCAN_SYNC
       if (T >= total_tiles) break;
       const i64 row = T / p.tiles_per_row;
       const i64 tt = T - row * p.tiles_per_row;
-      if (slot_direct[fs]) {
+      if (slot_direct[fm]) {
         ring_partial_tile(p, T, row, tt, sm_v, sm_h, &sm_excl1, sm_flag1);    // partial tile: start to finish
         SCAN_SYNC();
-        if (tid == 0 && sm_flag1[1]) ring_stv(&sh_fail, 1);
+        if (tid == 0) {
+          if (sm_flag1[1]) ring_stv(&sh_fail, 1);
+          fetch(r + SCAN_SLOTS);
+        }
+        SCAN_SYNC();                     // the next tile of this slot is known to every finisher
       } else {
         if (tid == 0) {
           idle = 0;
-          while (ring_ldv(&slot_state[fs]) < RING_RESOLVED) {
-            if (++idle > p.spin_limit) ring_stv(&sh_fail, 1);     // the prefix never arrived: give up
+          while (ring_ldv(&slot_state[fm]) < RING_GRAB_STATE) {
+            if (++idle > p.spin_limit) ring_stv(&sh_fail, 1);     // the aggregate never arrived: give up
             if (ring_ldv(&sh_fail)) break;
             __nanosleep(40);
           }
@@ -893,11 +878,8 @@ extern "C" __global__ void __launch_bounds__(RING_THREADS, SCAN_MIN_BLOCKS) acc_
         // (the data was seen complete by the reducers, whose state change this thread observed
         // through thread 0 and the barrier; testing the barrier again costs nothing and makes the
         // bulk copy's writes visible to this thread in its own right)
-        ring_mbar_try_wait(&full_bar[fs], slot_parity[fs]);
-        SCAN_MARK(T, 5);   // finish starts
+        ring_mbar_try_wait(&full_bar[fs], slot_parity[fm]);
         const unsigned char* base = scan_ring_smem + (size_t)fs * RING_SLOT_BYTES;
-        const elt_t excl = slot_excl[fs];
-        const bool hexcl = slot_hexcl[fs] != 0;
 #if ACC_SCAN_MODE == 1
         const i64 out_row = row * (n + 1);
 #else
@@ -937,7 +919,21 @@ extern "C" __global__ void __launch_bounds__(RING_THREADS, SCAN_MIN_BLOCKS) acc_
           else carry = scan_op(p, carry, rtot);
         }
         if (lane == 0) sm_v[warp] = carry;
+        SCAN_SYNC();                     // every finisher has the slot's data in registers
+        if (tid == 0) {
+          fetch(r + SCAN_SLOTS);         // the slot takes the next ticket while this tile waits for its prefix
+          idle = 0;
+          while (ring_ldv(&slot_state[fm]) < RING_RESOLVED) {
+            if (++idle > p.spin_limit) ring_stv(&sh_fail, 1);     // the prefix never arrived: give up
+            if (ring_ldv(&sh_fail)) break;
+            __nanosleep(20);
+          }
+          ctl_act2 = ring_ldv(&sh_fail) ? RING_ACT_EXIT : RING_ACT_FIN;
+        }
         SCAN_SYNC();
+        if (ctl_act2 == RING_ACT_EXIT) break;
+        const elt_t excl = slot_excl[fm];
+        const bool hexcl = slot_hexcl[fm] != 0;
         elt_t wbase = excl;             // everything before this warp's part: tile prefix, then earlier warps
         bool hwb = hexcl;
         for (int w = 0; w < warp; ++w) scan_join(p, wbase, hwb, sm_v[w], true);
@@ -975,7 +971,7 @@ extern "C" __global__ void __launch_bounds__(RING_THREADS, SCAN_MIN_BLOCKS) acc_
         }
 #if ACC_SCAN_MODE != 0
         if (tid == 0 && tt == p.tiles_per_row - 1) {
-          const elt_t tot = scan_op(p, excl, slot_agg[fs]);
+          const elt_t tot = scan_op(p, excl, slot_agg[fm]);
 #if ACC_SCAN_MODE == 1
 #if ACC_RIGHT
           OUT0_store(p, row * (n + 1), tot);
@@ -987,23 +983,23 @@ extern "C" __global__ void __launch_bounds__(RING_THREADS, SCAN_MIN_BLOCKS) acc_
 #endif
         }
 #endif
-        SCAN_MARK(T, 4);   // stores issued
+        // (sm_v, ctl_act and this entry's bookkeeping are next written after the barriers of
+        // the following iteration, which every finisher reaches only after its reads above)
       }
-      SCAN_SYNC();                     // everyone is done reading the slot (and sm_v)
-      if (tid == 0) fetch(fs, r + SCAN_SLOTS);
-      SCAN_SYNC();                     // the slot's next tile is known to every finisher
     }
   }
   // everybody meets here; the look-back warp leaves its loop when it sees a tile past the end,
   // a failure flag, or an expired wait (in which case it raises the flag itself)
   __syncthreads();
   if (tid == 0) {
-    // wait (bounded) for bulk copies still in flight into this CTA's shared memory
-    for (int s = 0; s < SCAN_SLOTS; ++s) {
-      if (slot_tile[s] < total_tiles && !slot_direct[s] && slot_state[s] == RING_LOADING) {
+    // Wait for bulk copies still in flight into this CTA's shared memory (only after a failure can
+    // there be any).  A bulk copy completes without the help of any other CTA, so this wait gets a
+    // bound of its own, far above the time a copy can take.
+    for (int m = 0; m < RING_META; ++m) {
+      if (slot_pos[m] >= 0 && slot_tile[m] < total_tiles && !slot_direct[m] && slot_state[m] == RING_LOADING) {
         i64 spins = 0;
-        while (!ring_mbar_try_wait(&full_bar[s], slot_parity[s]))
-          if (++spins > p.spin_limit) break;
+        while (!ring_mbar_try_wait(&full_bar[slot_pos[m] % SCAN_SLOTS], slot_parity[m]))
+          if (++spins > ((i64)1 << 26)) break;
       }
     }
     if (sh_fail) acc_fail(p.err, 110 /* ETIMEDOUT */);

@@ -19,6 +19,7 @@ B200 backend (``accelerate_b200.backend``) and the CPU oracle accept.
 from __future__ import annotations
 
 import itertools
+import re
 import numpy as np
 
 # ----------------------------------------------------------------------------
@@ -715,10 +716,95 @@ class Program:
         self.outputs = outputs        # list of (rank, elt)
 
 
-def build_program(results):
-    """Collect every node the results depend on, in dependency order."""
-    results = [compute(use(r)) for r in (results if isinstance(results, (list, tuple)) else [results])]
-    order, seen = [], set()
+_NAME = re.compile(r"(?<![\w.+-])([av])(\d+)(?![\w.])")
+
+
+def _canonical_names(text):
+    """Rename array (a<k>) and scalar (v<k>) variables in order of first appearance.  Generated
+    names come from a process-wide counter; the kernel cache is keyed on the generated source, so
+    the same program built twice must yield the same text."""
+    table = {}
+
+    def sub(m):
+        old = m.group(0)
+        if old not in table:
+            table[old] = m.group(1) + str(sum(1 for k in table if k[0] == m.group(1)))
+        return table[old]
+    return _NAME.sub(sub, text)
+
+
+# ----------------------------------------------------------------------------
+# Array-level control flow (evaluated on the host by every backend:
+# Interpreter.hs:215-231).  The operands are array-level functions; their nodes
+# are serialised inside the control node, except what does not depend on the
+# function's parameters (hoisted in front of it, as the reference's let-floating
+# does) and what several bodies share.
+# ----------------------------------------------------------------------------
+def _as_list(x):
+    return list(x) if isinstance(x, (list, tuple)) else [x]
+
+
+def _avars(like):
+    return [Acc(a.rank, a.elt, node=Node("avar", a.rank, a.elt)) for a in like]
+
+
+def _control(kind, outs_like, deps, bodies, pred=None, args=()):
+    node = Node(kind, outs_like[0].rank, outs_like[0].elt, deps=deps, nouts=len(outs_like))
+    node.out_ranks, node.out_elts = [a.rank for a in outs_like], [a.elt for a in outs_like]
+    node.bodies, node.pred, node.args = bodies, pred, list(args)
+    return [Acc(a.rank, a.elt, node=node, out=k) for k, a in enumerate(outs_like)]
+
+
+def acond(p, t, e):
+    """``acond`` (Language.hs:396; evaluated as Interpreter.hs:217-219): only the chosen branch runs."""
+    p = p if isinstance(p, Exp) else lift(p, BOOL)
+    single = not isinstance(t, (list, tuple))
+    ts, es = [compute(use(x)) for x in _as_list(t)], [compute(use(x)) for x in _as_list(e)]
+    if [(a.rank, a.elt) for a in ts] != [(a.rank, a.elt) for a in es]:
+        raise TypeError("acond: the branches yield different arrays")
+    out = _control("acond", ts, list(p.deps), [([], ts), ([], es)], pred=p)
+    return out[0] if single else tuple(out)
+
+
+def awhile(cond_f, step_f, init):
+    """``awhile`` (Language.hs:409; Interpreter.hs:221-229): apply ``step_f`` while ``cond_f`` yields True
+    (a ``Scalar Bool``, read at linear index 0).  The state is one array or a tuple of arrays."""
+    single = not isinstance(init, (list, tuple))
+    st = [compute(use(x)) for x in _as_list(init)]
+    pc, ps = _avars(st), _avars(st)
+    c = compute(use(cond_f(pc[0] if single else tuple(pc))))
+    nxt = [compute(use(x)) for x in _as_list(step_f(ps[0] if single else tuple(ps)))]
+    if (c.rank, c.elt) != (0, BOOL):
+        raise TypeError("awhile: the condition must yield a Scalar Bool")
+    if [(a.rank, a.elt) for a in nxt] != [(a.rank, a.elt) for a in st]:
+        raise TypeError("awhile: the step changes the type of the state")
+    out = _control("awhile", st, [a.node for a in st], [(pc, [c]), (ps, nxt)], args=st)
+    return out[0] if single else tuple(out)
+
+
+def apply(f, *args):
+    """``Apply`` of an array-level function (AST.hs:268; Interpreter.hs:215)."""
+    xs = [compute(use(x)) for x in args]
+    ps = _avars(xs)
+    r = f(*ps)
+    single = not isinstance(r, (list, tuple))
+    rs = [compute(use(x)) for x in _as_list(r)]
+    out = _control("apply", rs, [a.node for a in xs], [(ps, rs)], args=xs)
+    return out[0] if single else tuple(out)
+
+
+def pipe(f, g):
+    """``f >-> g`` (Language.hs:365-372): two computations kept apart, the second applied to the first's result."""
+    return lambda *xs: apply(g, *_as_list(apply(f, *xs)))
+
+
+def _is_control(n):
+    return n.kind in ("acond", "awhile", "apply")
+
+
+def _reach(roots, stop=()):
+    """Nodes reachable through ``deps`` (bodies of control nodes are not entered), dependencies first."""
+    order, seen = [], set(id(s) for s in stop)
 
     def visit(n):
         if id(n) in seen:
@@ -727,16 +813,127 @@ def build_program(results):
         for d in n.deps:
             visit(d)
         order.append(n)
-    for r in results:
-        visit(r.node)
-    inputs = [n for n in order if n.kind == "in"]
+    for r in roots:
+        visit(r)
+    return order
+
+
+def _all_inputs(roots):
+    """Every program input below ``roots``, the bodies of control nodes included, in first-use order."""
+    ins, seen = [], set()
+
+    def visit(n):
+        if id(n) in seen:
+            return
+        seen.add(id(n))
+        for d in n.deps:
+            visit(d)
+        if _is_control(n):
+            for _, res in n.bodies:
+                for r in res:
+                    visit(r.node)
+        if n.kind == "in":
+            ins.append(n)
+    for r in roots:
+        visit(r)
+    return ins
+
+
+def _depends_on(n, params, memo):
+    """Whether node ``n`` needs one of the ``params`` (directly, or inside the body of a control node)."""
+    if id(n) in memo:
+        return memo[id(n)]
+    memo[id(n)] = False
+    r = any(n is q for q in params) or any(_depends_on(d, params, memo) for d in n.deps)
+    if not r and _is_control(n):
+        r = any(_depends_on(x.node, params, memo) for _, res in n.bodies for x in res)
+    memo[id(n)] = r
+    return r
+
+
+class _Emitter:
+    def __init__(self, embed):
+        self.embed = embed
+
+    def hex_use(self, n):
+        sh, leaves = n.data
+        body = " ".join("(hex " + np.ascontiguousarray(x).tobytes().hex() + ")" for x in leaves)
+        return f"(use (array {n.rank} {ty_sx(n.elt)}) (shape{''.join(' ' + str(d) for d in sh)}) {body})"
+
+    def level(self, roots, emitted, lines, indent):
+        """Emit, into ``lines``, every node the ``roots`` need that is not in ``emitted`` yet."""
+        skip = lambda n: id(n) in emitted or n.kind in ("in", "avar")  # noqa: E731
+        hoisted = {}                                   # id(control node) -> nodes to emit in front of it
+        while True:
+            order = []
+            seen = set()
+
+            def visit(n):
+                if id(n) in seen:
+                    return
+                seen.add(id(n))
+                for d in list(n.deps) + hoisted.get(id(n), []):
+                    visit(d)
+                order.append(n)
+            for r in roots:
+                visit(r)
+            here = set(id(n) for n in order)
+            count, more = {}, False
+            for c in order:
+                if not _is_control(c) or skip(c):
+                    continue
+                for params, res in c.bodies:
+                    memo = {}
+                    for n in _reach([r.node for r in res]):
+                        if skip(n) or id(n) in here:
+                            continue
+                        free = c.kind != "acond" and not _depends_on(n, [q.node for q in params], memo)
+                        count[id(n)] = count.get(id(n), 0) + 1
+                        if free or count[id(n)] > 1:
+                            hoisted.setdefault(id(c), []).append(n)
+                            more = True
+            if not more:
+                break
+        pad = "  " * indent
+        for n in order:
+            if skip(n):
+                continue
+            lhs = n.names[0] if n.nouts == 1 else "(" + " ".join(n.names) + ")"
+            if _is_control(n):
+                inner = set(emitted)
+                parts = []
+                for params, res in n.bodies:
+                    sub = []
+                    self.level([r.node for r in res], inner | set(id(q.node) for q in params), sub, indent + 2)
+                    head = "(branch" if n.kind == "acond" else "(afun (" + " ".join(f"({q.name} (array {q.rank} {ty_sx(q.elt)}))" for q in params) + ")"
+                    parts.append("\n".join([pad + "    " + head] + sub + [pad + "      (out " + " ".join(r.name for r in res) + "))"]))
+                args = "(args " + " ".join(a.name for a in n.args) + ")"
+                if n.kind == "acond":
+                    text = f"(acond {n.pred.sx}\n" + "\n".join(parts) + ")"
+                else:
+                    text = f"({n.kind}\n" + "\n".join(parts) + f"\n{pad}    {args})"
+                lines.append(f"{pad}(let {lhs} {text})")
+            else:
+                lines.append(f"{pad}(let {lhs} {n.sx})")
+            emitted.add(id(n))
+
+
+def build_program(results, embed=False):
+    """Serialise everything the results depend on, in dependency order.  With ``embed`` the host
+    arrays given to ``use`` travel inside the program text as ``(use ...)`` nodes (the reference's
+    ``Use``, Interpreter.hs:231) instead of being program inputs."""
+    results = [compute(use(r)) for r in (results if isinstance(results, (list, tuple)) else [results])]
+    roots = [r.node for r in results]
+    ins = _all_inputs(roots)
+    inputs = [n for n in ins if not (embed and n.data is not None)]
     lines = ["(program"]
     for n in inputs:
         lines.append(f"  (in {n.names[0]} (array {n.rank} {ty_sx(n.elt)}))")
-    for n in order:
-        if n.kind == "in":
-            continue
-        lhs = n.names[0] if n.nouts == 1 else "(" + " ".join(n.names) + ")"
-        lines.append(f"  (let {lhs} {n.sx})")
+    em = _Emitter(embed)
+    if embed:
+        for n in ins:
+            if n.data is not None:
+                lines.append(f"  (let {n.names[0]} {em.hex_use(n)})")
+    em.level(roots, set(), lines, 1)
     lines.append("  (out " + " ".join(r.name for r in results) + "))")
-    return Program("\n".join(lines), inputs, [(r.rank, r.elt) for r in results])
+    return Program(_canonical_names("\n".join(lines)), inputs, [(r.rank, r.elt) for r in results])

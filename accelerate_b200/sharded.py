@@ -28,18 +28,46 @@ import torch.distributed as dist
 from . import language as L
 
 
-class GpuExecutor:
-    """Runs terms on this rank's GPU; arrays are ``backend.DeviceArray``."""
+def closure_key(obj, depth=0):
+    """A hashable description of what a builder function will build: its code and, recursively,
+    everything it closes over (functions by code and closure, constants by value, other objects by
+    identity).  Two lambdas written at the same place that capture different functions, shapes or
+    constants get different keys; re-creating the same lambda with the same captures does not."""
+    if depth > 6:
+        return ("deep", id(obj))
+    if isinstance(obj, (int, float, str, bytes, bool, type(None), np.generic)):
+        return (type(obj).__name__, repr(obj))
+    if isinstance(obj, (tuple, list)):
+        return (type(obj).__name__,) + tuple(closure_key(x, depth + 1) for x in obj)
+    if isinstance(obj, dict):
+        return ("dict",) + tuple((repr(k), closure_key(v, depth + 1)) for k, v in sorted(obj.items(), key=lambda kv: repr(kv[0])))
+    code = getattr(obj, "__code__", None)
+    if code is not None:
+        cells = tuple(closure_key(c.cell_contents, depth + 1) for c in (obj.__closure__ or ()))
+        dflt = tuple(closure_key(d, depth + 1) for d in (obj.__defaults__ or ()))
+        return ("fn", code.co_filename, code.co_firstlineno, _code_key(code), cells, dflt)
+    func = getattr(obj, "__func__", None)
+    if func is not None:                      # bound method
+        return ("method", closure_key(func, depth + 1), id(getattr(obj, "__self__", None)))
+    if hasattr(obj, "elt") and hasattr(obj, "shape"):     # an array: builders only look at its type and shape
+        return ("array", repr(obj.elt), tuple(obj.shape))
+    return (type(obj).__name__, id(obj))
 
-    def __init__(self, ctx):
-        from . import backend
-        self.backend, self.ctx = backend, ctx
-        self.stream = torch.cuda.ExternalStream(ctx.stream(), device=torch.device("cuda", ctx.device))
+
+def _code_key(code):
+    """Instructions, names and constants of a code object (nested lambdas are constants of it)."""
+    consts = tuple(_code_key(c) if hasattr(c, "co_code") else repr(c) for c in code.co_consts)
+    return (code.co_code, code.co_names, consts)
+
+
+class ProgramCache:
+    """Built programs by call-site key, input signature and builder identity."""
+
+    def __init__(self):
         self._progs = {}
 
-    def run(self, key, build, inputs):
-        """``build(*params)`` -> term(s); cached under ``key`` + input signature."""
-        sig = (key, tuple((a.elt if L.is_scalar(a.elt) else tuple(a.elt), len(a.shape)) for a in inputs))
+    def get(self, key, build, inputs):
+        sig = (key, tuple((a.elt if L.is_scalar(a.elt) else tuple(a.elt), len(a.shape)) for a in inputs), closure_key(build))
         ent = self._progs.get(sig)
         if ent is None:
             L.reset_names()
@@ -48,8 +76,25 @@ class GpuExecutor:
             single = not isinstance(res, (list, tuple))
             prog = L.build_program(res)
             order = [next(i for i, q in enumerate(params) if q.node is n) for n in prog.inputs]
-            ent = self._progs[sig] = (prog, order, single)
-        prog, order, single = ent
+            # `build` is kept so that objects its key names by identity stay alive as long as the entry
+            ent = self._progs[sig] = (prog, order, single, build)
+        return ent[:3]
+
+
+class GpuExecutor:
+    """Runs terms on this rank's GPU; arrays are ``backend.DeviceArray``."""
+
+    def __init__(self, ctx):
+        from . import backend
+        self.backend, self.ctx = backend, ctx
+        self.stream = torch.cuda.ExternalStream(ctx.stream(), device=torch.device("cuda", ctx.device))
+        self._progs = ProgramCache()
+
+    def run(self, key, build, inputs):
+        """``build(*params)`` -> term(s).  The built program is cached under the input signature
+        and the builder's own identity (its code and everything it captures: ``closure_key``);
+        ``key`` only keeps unrelated call sites apart."""
+        prog, order, single = self._progs.get(key, build, inputs)
         outs = self.ctx.execute(prog.text, [inputs[k] for k in order], len(prog.outputs))
         for o, (_, elt) in zip(outs, prog.outputs):
             o.elt = elt
@@ -230,6 +275,8 @@ class Sharded:
         ``build_source(*inputs)`` are given the rank's input shards."""
         f = {"add": lambda a, b: a + b, "min": L.min_, "max": L.max_}[op]
         elt = defaults.elt
+        if not L.is_scalar(elt):
+            raise ValueError("sharded permute reduces one scalar leaf; tuple element types are not supported")
         if self.rank == 0:
             start = defaults
         else:

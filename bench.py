@@ -67,19 +67,30 @@ def tiled(gen, n, dtype):
     return np.tile(b, (n + BLOCK - 1) // BLOCK)[:n]
 
 
-def zipf_keys(rng, n, bins, s=1.1):
-    """Zipf(s) over ranks 1..bins by inverse CDF on a 2^24-entry quantile table; bin = rank-1."""
+def zipf_keys(rng, n, bins, s=1.1, shuffle=False):
+    """Zipf(s) over ranks 1..bins by inverse CDF on a 2^24-entry quantile table; bin = rank-1, or,
+    with ``shuffle``, a fixed (seeded) permutation of the bins applied to rank-1, so that the
+    frequent keys are scattered over the whole target instead of sitting at its start."""
     p = 1.0 / np.arange(1, bins + 1, dtype=np.float64) ** s
     cdf = np.cumsum(p / p.sum())
     table = np.searchsorted(cdf, (np.arange(1 << 24) + 0.5) / (1 << 24)).astype(np.int32)
     table = np.minimum(table, bins - 1)
+    if shuffle:
+        table = np.random.default_rng(7).permutation(bins).astype(np.int32)[table]
     return tiled(lambda m: table[rng.integers(0, 1 << 24, size=m)], n, np.int32)
 
 
+def make_grid(seed2, rank, side, side_c):
+    """Rank `rank`'s (side x side_c) slab of the stencil input with seed `seed2`."""
+    g = np.random.default_rng(seed2 + 1000 * rank)
+    return tiled(lambda m: g.random(size=m, dtype=np.float32), side * side_c, np.float32).reshape(side, side_c)
+
+
 class Workload:
-    def __init__(self, name, config, inputs, build, elements, alg_bytes, kernel, launches):
+    def __init__(self, name, config, inputs, build, elements, alg_bytes, kernel, launches, in_value=True):
         self.name, self.config, self.inputs, self.build = name, config, inputs, build
         self.elements, self.alg_bytes, self.kernel, self.launches = elements, alg_bytes, kernel, launches
+        self.in_value = in_value      # False: reported beside the suite, not part of `value`
 
 
 def suite(scale=0, seed=42, rank=0):
@@ -133,8 +144,7 @@ def suite(scale=0, seed=42, rank=0):
                       n30, 8 * n30, "acc_permute", 2))
 
     def grid(seed2):
-        g = np.random.default_rng(seed2 + 1000 * rank)
-        return lambda: tiled(lambda m: g.random(size=m, dtype=np.float32), side * side_c, np.float32).reshape(side, side_c)
+        return lambda: make_grid(seed2, rank, side, side_c)
 
     def jac(m):
         for _ in range(iters):
@@ -143,8 +153,13 @@ def suite(scale=0, seed=42, rank=0):
     W.append(Workload("jacobi5_clamp_x100_f32", "configs[4]", [grid(seed)], jac, side * side_c * iters, 8 * side * side_c * iters, "acc_stencil2d", iters))
     W.append(Workload("stencil2_gauss_mirror_f32", "configs[4]", [grid(seed), grid(seed + 1)],
                       lambda a, b: A.stencil2(gauss2, A.mirror, a, A.mirror, b), side * side_c, 12 * side * side_c, "acc_stencil2d", 1))
+    # the same histogram with the bins shuffled (reported beside the suite; `value` keeps the rank-1 layout)
+    hist_build = W[5].build
+    W.append(Workload("permute_hist_i32_shuffled", "configs[3]", [lambda: zipf_keys(np.random.default_rng(seed + 77 + 1000 * rank), n30, bins16, shuffle=True)],
+                      hist_build, n30, 4 * n30, "acc_permute", 2, in_value=False))
     for w in W:
-        w.bins = bins16 if w.name == "permute_hist_i32" else bins20
+        w.bins = bins16 if w.name.startswith("permute_hist_i32") else bins20
+        w.iters, w.side, w.scale, w.seed = iters, (side, side_c), scale, seed
     return W
 
 
@@ -191,7 +206,7 @@ class ShardedBound:
         ex = self.sh.ex
         self.dev = [ex.from_host(h) for h in self.host]
         name = self.w.name
-        if name == "permute_hist_i32":
+        if name.startswith("permute_hist_i32"):
             self.aux["defaults"] = ex.from_host(np.zeros(self.w.bins, np.int32))
         if name == "permute_add_f32":
             self.aux["defaults"] = ex.from_host(np.zeros(self.w.bins, np.float32))
@@ -229,7 +244,7 @@ class ShardedBound:
             return sh.scan1d("scanl'", add, 0.0, d[0], key="c2b")
         if name == "scanr1_max_i64":
             return sh.scan1d("scanr1", A.max_, None, d[0], key="c2c")
-        if name == "permute_hist_i32":
+        if name.startswith("permute_hist_i32"):
             return sh.permute("add", self.aux["defaults"], lambda ix, k: A.Just_(A.index(A.from_integral(k[ix], "i64"))), d,
                               lambda k: A.fill(k.shape, A.constant(np.int32(1))), key="c3a")
         if name == "permute_add_f32":
@@ -242,6 +257,128 @@ class ShardedBound:
         if name == "stencil2_gauss_mirror_f32":
             return sh.stencil2(gauss2, A.mirror, d[0], A.mirror, d[1], key="c4b")
         raise KeyError(name)
+
+
+# ---------------------------------------------------------------------------------
+# parity of what was timed: every rank checks its part of every result against NumPy
+# (integers bit-exact; Float sums within 1e-5 * sqrt(n) relative; stencils bit-exact on
+# blocks that include the array's corners and the rows either side of every slab edge)
+# ---------------------------------------------------------------------------------
+def _gather(x, rank, world, dist, dtype):
+    """Every rank's scalar `x` as a NumPy vector."""
+    if world == 1:
+        return np.array([x], dtype)
+    import torch
+    t = torch.zeros(world, dtype=torch.float64 if np.dtype(dtype).kind == "f" else torch.int64, device="cuda")
+    t[rank] = float(x) if np.dtype(dtype).kind == "f" else int(x)
+    dist.all_reduce(t)
+    return t.cpu().numpy().astype(dtype)
+
+
+def _allreduce_np(a, world, dist):
+    if world == 1:
+        return a
+    import torch
+    t = torch.from_numpy(np.ascontiguousarray(a)).cuda()
+    dist.all_reduce(t)
+    return t.cpu().numpy()
+
+
+def _stencil_blocks(w, rank, world, got, apply_np, mode, seeds, iters, radius=1):
+    """Compare blocks of this rank's result slab with NumPy.  The expected block is computed from the
+    input window `iters * radius` wider on every side (taken from the neighbouring ranks' slabs where
+    it crosses a slab edge): after `iters` applications everything further than that from a window
+    edge that is not an edge of the whole array is exact."""
+    side, side_c = w.side
+    grids = {}
+
+    def rows(seed2, lo, hi):
+        parts = []
+        for r in range(lo // side, (hi - 1) // side + 1):
+            if (seed2, r) not in grids:
+                grids[(seed2, r)] = make_grid(seed2, r, side, side_c)
+            parts.append(grids[(seed2, r)][max(lo - r * side, 0):min(hi - r * side, side)])
+        return np.concatenate(parts, axis=0)
+
+    H, B, halo = world * side, min(64, side // 2), iters * radius
+    base = rank * side
+    blocks = [(base, 0), (base + side - B, side_c - B), (base + side // 2, side_c // 2 - B // 2)]
+    for (r0, c0) in blocks:
+        lo, hi = max(r0 - halo, 0), min(r0 + B + halo, H)
+        cl, ch = max(c0 - halo, 0), min(c0 + B + halo, side_c)
+        wins = [rows(sd, lo, hi)[:, cl:ch].copy() for sd in seeds]
+        for _ in range(iters):
+            wins = [apply_np(*[np.pad(x, radius, mode=mode) for x in wins])] + wins[1:]
+        want = wins[0][r0 - lo:r0 - lo + B, c0 - cl:c0 - cl + B]
+        have = got[r0 - base:r0 - base + B, c0:c0 + B]
+        if not np.array_equal(want, have):
+            return False
+    return True
+
+
+def _jacobi_np(p):
+    return np.float32(0.25) * (((p[:-2, 1:-1] + p[2:, 1:-1]) + p[1:-1, :-2]) + p[1:-1, 2:])
+
+
+def _gauss2_np(p, q):
+    acc = np.zeros((p.shape[0] - 2, p.shape[1] - 2), np.float32)
+    for i in range(3):
+        for j in range(3):
+            acc = acc + np.float32(GAUSS[i][j] / 16.0) * (p[i:p.shape[0] - 2 + i, j:p.shape[1] - 2 + j] + q[i:q.shape[0] - 2 + i, j:q.shape[1] - 2 + j])
+    return acc
+
+
+def verify(w, host, outs, rank, world, dist):
+    """True if this rank's part of workload `w`'s result (`outs`: host arrays) is right."""
+    name = w.name
+    if name == "fold1seg_add_i32":
+        vals, lens = host
+        offs = np.concatenate([[0], np.cumsum(lens, dtype=np.int64)[:-1]])
+        return np.array_equal(outs[0], np.add.reduceat(vals.astype(np.int64), offs).astype(np.int32))
+    if name == "fold_max_rows_f32":
+        return np.array_equal(outs[0], host[0].max(axis=1))
+    if name == "scanl1_add_i32":
+        x = host[0]
+        tot = _gather(int(x.sum(dtype=np.int64)), rank, world, dist, np.int64)
+        carry = np.uint32(int(tot[:rank].sum()) & 0xffffffff)
+        want = (np.cumsum(x.view(np.uint32), dtype=np.uint32) + carry).view(np.int32)
+        return np.array_equal(outs[0], want)
+    if name == "scanl_prime_add_f32":
+        x = host[0]
+        tot = _gather(float(x.sum(dtype=np.float64)), rank, world, dist, np.float64)
+        c = np.cumsum(x, dtype=np.float64)
+        want = c - x + tot[:rank].sum()
+        tol = min(1e-5 * np.sqrt(float(x.size) * world), 1e-4)      # the specification's bound, capped: a tree scan is far inside it
+        ok = bool(np.all(np.abs(outs[0] - want) <= tol * np.maximum(np.abs(want), 1.0)))
+        return ok and abs(float(outs[1]) - tot.sum()) <= tol * tot.sum()
+    if name == "scanr1_max_i64":
+        x = host[0]
+        mx = _gather(int(x.max()), rank, world, dist, np.int64)
+        want = np.maximum.accumulate(x[::-1])[::-1]
+        if rank + 1 < world:
+            want = np.maximum(want, mx[rank + 1:].max())
+        return np.array_equal(outs[0], want)
+    if name.startswith("permute_hist_i32"):
+        k = host[0]
+        want = np.zeros(w.bins, np.int64)
+        for a in range(0, k.size, 1 << 26):
+            want += np.bincount(k[a:a + (1 << 26)], minlength=w.bins)
+        return np.array_equal(outs[0], _allreduce_np(want, world, dist).astype(np.int32))
+    if name == "permute_add_f32":
+        k, v = host
+        want = np.zeros(w.bins, np.float64)
+        for a in range(0, k.size, 1 << 26):
+            kk, vv = k[a:a + (1 << 26)], v[a:a + (1 << 26)]
+            keep = kk >= 0
+            want += np.bincount(kk[keep] % w.bins, weights=vv[keep].astype(np.float64), minlength=w.bins)
+        want = _allreduce_np(want, world, dist)
+        tol = 1e-5 * np.sqrt(max(float(k.size) * world / w.bins, 1.0))
+        return bool(np.all(np.abs(outs[0] - want) <= tol * np.maximum(np.abs(want), 1.0)))
+    if name == "jacobi5_clamp_x100_f32":
+        return _stencil_blocks(w, rank, world, outs[0], _jacobi_np, "edge", [w.seed], w.iters)
+    if name == "stencil2_gauss_mirror_f32":
+        return _stencil_blocks(w, rank, world, outs[0], _gauss2_np, "reflect", [w.seed, w.seed + 1], 1)
+    raise KeyError(name)
 
 
 class ClockSampler:
@@ -293,54 +430,79 @@ def measured_peaks():
     return 6650.0, "fallback"
 
 
-def cpu_baseline(scale_hint=0, budget_s=20.0):
-    """The oracle (CPU restatement of the reference interpreter, 1 thread) on a
-    bounded sample of every workload."""
+NOMINAL_HBM_GBS = 8000.0       # the nominal HBM3e figure the benchmark specification quotes
+
+
+def _cpu_one(args):
+    """One workload on the CPU oracle (runs in a worker process); returns (name, elements, seconds)."""
+    k, shrink = args
     from oracle import oracle
-    shrink = 8    # every size / 2^8: 2^20..2^22 elements per skeleton; two of the 100 Jacobi iterations
-    ws = suite(scale=shrink)
-    total_e, total_t, per = 0, 0.0, {}
-    for w in ws:
-        host = [f() for f in w.inputs]
-        build = w.build
-        elements = w.elements
-        if w.name.startswith("jacobi"):
-            build = lambda m: A.stencil(jacobi, A.clamp, A.stencil(jacobi, A.clamp, m))  # noqa: E731  (2 of the 100 iterations)
-            elements = w.elements // 50
-        term = build(*[A.use(h) for h in host])
-        t0 = time.perf_counter()
-        oracle.run(term)
-        dt = time.perf_counter() - t0
-        per[w.name] = elements / dt
-        total_e += elements
-        total_t += dt
-        if total_t > budget_s * 3:
-            break
-    return {"value": total_e / total_t, "unit": "elements/s", "cores": 1, "kind": "port",
-            "sample": f"every workload at 1/{1 << shrink} of its size (Jacobi: 2 iterations), {total_t:.1f} s of CPU work",
-            "per_skeleton": per}
+    ws = [w for w in suite(scale=shrink) if w.in_value]
+    # the shared generator is consumed in suite order: draw the earlier workloads' inputs too
+    for w in ws[:k]:
+        for f in w.inputs:
+            f()
+    w = ws[k]
+    host = [f() for f in w.inputs]
+    build, elements = w.build, w.elements
+    if w.name.startswith("jacobi"):
+        build = lambda m: A.stencil(jacobi, A.clamp, A.stencil(jacobi, A.clamp, m))  # noqa: E731  (2 of the 100 iterations)
+        elements = w.elements // 50
+    term = build(*[A.use(h) for h in host])
+    t0 = time.perf_counter()
+    oracle.run(term)
+    return w.name, elements, time.perf_counter() - t0
+
+
+def cpu_baseline(shrink=8, workers=1):
+    """The oracle (CPU restatement of the reference interpreter) on a bounded sample of every
+    workload: every size / 2^shrink, two of the 100 Jacobi iterations.  The interpreter is
+    sequential; with `workers` > 1 the workloads of the suite run side by side, one per host
+    thread, and the step takes as long as the slowest of them."""
+    from oracle import oracle
+    oracle.build()
+    n = len([w for w in suite(scale=shrink) if w.in_value])
+    jobs = [(k, shrink) for k in range(n)]
+    if workers > 1:
+        import multiprocessing as mp
+        with mp.get_context("fork").Pool(min(workers, n)) as pool:
+            res = pool.map(_cpu_one, jobs, chunksize=1)
+        step_s = max(r[2] for r in res)
+        cores = min(workers, n)
+    else:
+        res = [_cpu_one(j) for j in jobs]
+        step_s = sum(r[2] for r in res)
+        cores = 1
+    total_e = sum(r[1] for r in res)
+    return {"value": total_e / step_s, "unit": "elements/s", "cores": cores, "kind": "port",
+            "sample": f"every workload at 1/{1 << shrink} of its size (Jacobi: 2 iterations), {sum(r[2] for r in res):.1f} s of CPU work"
+                      + (f" spread over {cores} host threads (one workload each)" if cores > 1 else ""),
+            "per_skeleton": {r[0]: r[1] / r[2] for r in res}, "step_s": step_s}
 
 
 def reference_arm(args):
+    """The reference's CPU path: the oracle port (the Haskell interpreter cannot be built here), every
+    workload of the suite on its own host thread.  Runs the warm-up and the steps it is asked for."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
     t0 = time.perf_counter()
-    vals = []
-    cb = None
-    step_ms = []
-    for _ in range(max(1, min(args.steps, 2))):
-        t1 = time.perf_counter()
-        cb = cpu_baseline()
-        step_ms.append((time.perf_counter() - t1) * 1e3)
+    workers = min(9, os.cpu_count() or 1)
+    shrink = 9
+    for _ in range(args.warmup):
+        cb = cpu_baseline(shrink, workers)
+    vals, step_ms = [], []
+    for _ in range(max(1, args.steps)):
+        cb = cpu_baseline(shrink, workers)
+        step_ms.append(cb["step_s"] * 1e3)
         vals.append(cb["value"])
     v = float(np.mean(vals))
     cb["value"] = v
     line = {"impl": "reference", "metric": "elements/s over the configs[1-4] skeleton suite", "value": v, "unit": "elements/s",
-            "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": float(np.mean(step_ms)), "higher_is_better": True,
+            "n_gpus": args.gpus, "steps": max(1, args.steps), "warmup": args.warmup, "ms_per_step": float(np.mean(step_ms)), "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "i32/i64/f32", "data": "synthetic",
             "config": {"workload": "configs[1-4] skeleton suite", "sample": cb["sample"],
-                       "note": "CPU restatement of Data.Array.Accelerate.Interpreter (oracle/), 1 thread like the interpreter; the Haskell reference cannot be built here"},
+                       "note": "CPU restatement of Data.Array.Accelerate.Interpreter (oracle/); the Haskell reference cannot be built here"},
             "cpu_baseline": {k: cb[k] for k in ("value", "unit", "cores", "kind", "sample")},
             "e2e": {"value": v, "unit": "elements/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
             "wall_s": time.perf_counter() - t0}
@@ -356,6 +518,7 @@ def main():
     ap.add_argument("--impl", default="b200")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--no-verify", action="store_true")
     ap.add_argument("--only", default="")
     args = ap.parse_args()
     if args.impl == "reference":
@@ -373,21 +536,24 @@ def main():
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     ctx = backend.Context(local)
     stream = torch.cuda.ExternalStream(ctx.stream(), device=torch.device("cuda", local))
-    ws = suite(args.scale, rank=rank)
+    ws_all = suite(args.scale, rank=rank)
     if args.only:
-        ws = [w for w in ws if any(s in w.name for s in args.only.split(","))]
+        ws_all = [w for w in ws_all if any(s in w.name for s in args.only.split(","))]
     t_gen = time.perf_counter()
-    bound = []
+    bound_all = []
     sharded = None
     if world > 1:
         from accelerate_b200.sharded import GpuExecutor, Sharded
         sharded = Sharded(GpuExecutor(ctx))
-    for w in ws:
+    for w in ws_all:
         b = ShardedBound(sharded, w, [f() for f in w.inputs]) if sharded else Bound(ctx, w, [f() for f in w.inputs])
         b.upload()
-        bound.append(b)
+        bound_all.append(b)
     ctx.sync()
     t_gen = time.perf_counter() - t_gen
+    ws = [w for w in ws_all if w.in_value]
+    bound = [b for b in bound_all if b.w.in_value]
+    extra = [b for b in bound_all if not b.w.in_value]
 
     def barrier():
         ctx.sync()
@@ -400,7 +566,7 @@ def main():
     sampler = ClockSampler(local)
     sampler.start()
     for _ in range(max(args.warmup, 1)):
-        for b in bound:
+        for b in bound_all:
             b.run()
     barrier()
     l0 = ctx.stats()["launches"]
@@ -418,37 +584,80 @@ def main():
     barrier()
     clocks = sampler.stop()
     launches = ctx.stats()["launches"] - l0
-    total_ms = e_start.elapsed_time(e_end)
+    total_ms = e_start.elapsed_time(e_end) if bound else 0.0
     if dist is not None:
         t = torch.tensor([total_ms], device="cuda")
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         total_ms = float(t.item())
     per_ms = [float(np.mean([ev[s][k][0].elapsed_time(ev[s][k][1]) for s in range(args.steps)])) for k in range(len(bound))]
     per_ms_min = [float(np.min([ev[s][k][0].elapsed_time(ev[s][k][1]) for s in range(args.steps)])) for k in range(len(bound))]
+    # workloads reported beside the suite (not part of `value`): timed the same way, after it
+    ex_ms, ex_min = [], []
+    for b in extra:
+        evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
+        barrier()
+        for s in range(args.steps):
+            evs[s][0].record(stream)
+            b.run()
+            evs[s][1].record(stream)
+        barrier()
+        ts = [a.elapsed_time(z) for a, z in evs]
+        if dist is not None:
+            t = torch.tensor(ts, device="cuda")
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ts = [float(x) for x in t.tolist()]
+        ex_ms.append(float(np.mean(ts)))
+        ex_min.append(float(np.min(ts)))
     elements_step = sum(w.elements for w in ws) * world
-    value = elements_step * args.steps / (total_ms * 1e-3)
+    value = elements_step * args.steps / (total_ms * 1e-3) if bound else 0.0
     peak, peak_kind = measured_peaks()
     per = {}
-    for w, ms, ms_min in zip(ws, per_ms, per_ms_min):
+    for w, ms, ms_min in list(zip(ws, per_ms, per_ms_min)) + list(zip([b.w for b in extra], ex_ms, ex_min)):
         gbs = w.alg_bytes / (ms * 1e-3) / 1e9
         per[w.name] = {"ms": round(ms, 4), "ms_fastest_step": round(ms_min, 4), "elements_per_s": w.elements / (ms * 1e-3), "achieved_gbs": round(gbs, 1),
-                       "frac_of_hbm_peak": round(gbs / peak, 4), "config": w.config}
-    # dominant kernel: the one with the largest share of the step
-    dom = int(np.argmax(per_ms))
-    wd = ws[dom]
-    many = wd.launches > 3        # the Jacobi workload is 100 launches of the same kernel
-    launch_ms = per_ms[dom] / wd.launches if many else per_ms[dom]
-    achieved = wd.alg_bytes / (wd.launches if many else 1) / (launch_ms * 1e-3) / 1e9
-    # DRAM bytes per launch of the Jacobi kernel from the ncu capture summarised in
-    # profiles/acc_stencil2d_jacobi5_clamp.md (8192^2 case: 493.4 MB; traffic grows with the points: x4 at 16384^2)
-    traffic = 493.4e6 * 4 if (wd.name.startswith("jacobi") and args.scale == 0) else None
-    roofline = {"bound": "hbm", "kernel": wd.kernel, "workload": wd.name, "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s",
-                "frac": round(achieved / peak, 4), "peak_kind": f"of {peak_kind}", "traffic": traffic,
-                "launch_ms": round(launch_ms, 4)}
+                       "frac_of_hbm_peak": round(gbs / peak, 4), "frac_of_nominal_8tbs": round(gbs / NOMINAL_HBM_GBS, 4), "config": w.config,
+                       "in_value": w.in_value}
+    roofline = None
+    if bound:
+        # dominant kernel: the one with the largest share of the step
+        dom = int(np.argmax(per_ms))
+        wd = ws[dom]
+        many = wd.launches > 3        # the Jacobi workload is 100 launches of the same kernel
+        launch_ms = per_ms[dom] / wd.launches if many else per_ms[dom]
+        achieved = wd.alg_bytes / (wd.launches if many else 1) / (launch_ms * 1e-3) / 1e9
+        # DRAM bytes per launch of the Jacobi kernel, scaled from an ncu capture of the 8192^2 case
+        # (493.4 MB per launch there; traffic grows with the number of points: x4 at 16384^2)
+        jac_full = wd.name.startswith("jacobi") and args.scale == 0
+        roofline = {"bound": "hbm", "kernel": wd.kernel, "workload": wd.name, "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s",
+                    "frac": round(achieved / peak, 4), "peak_kind": f"of {peak_kind}", "frac_of_nominal_8tbs": round(achieved / NOMINAL_HBM_GBS, 4),
+                    "traffic": 493.4e6 * 4 if jac_full else None, "traffic_from": "ncu capture of the 8192^2 case x4 (scaled, not measured at this size)" if jac_full else None,
+                    "launch_ms": round(launch_ms, 4)}
+
+    # parity of what was just timed: one more run of every workload, checked against NumPy on every rank
+    parity_ok, parity_failed = None, []
+    if not args.no_verify:
+        for b in bound_all:
+            r = b.run()
+            outs = [o.download() for o in (list(r) if isinstance(r, (list, tuple)) else [r])]
+            ctx.sync()
+            good = bool(verify(b.w, b.host, outs, rank, world, dist))
+            if dist is not None:
+                t = torch.tensor([0 if good else 1], device="cuda")
+                dist.all_reduce(t)
+                good = int(t.item()) == 0
+            if not good:
+                parity_failed.append(b.w.name)
+            del outs, r
+        parity_ok = not parity_failed
 
     # end to end: pinned host buffers in, results back to pinned host buffers
     e2e = None
-    if not args.no_e2e:
+    if not args.no_e2e and bound:
+        for b in extra:
+            for d in (b.dev or []):
+                if hasattr(d, "free"):
+                    d.free()
+            b.dev = None
         h2d = d2h = 0
         pinned_in, outs_buf = [], []
         for b in bound:
@@ -523,7 +732,7 @@ def main():
             ms = ea.elapsed_time(eb) / reps
             gbs = 8 * n / (ms * 1e-3) / 1e9
             c0[f"dotp_f32_2^{n.bit_length() - 1}"] = {"ms": round(ms, 4), "elements_per_s": n / (ms * 1e-3), "achieved_gbs": round(gbs, 1),
-                                                   "frac_of_hbm_peak": round(gbs / peak, 4),
+                                                   "frac_of_hbm_peak": round(gbs / peak, 4), "frac_of_nominal_8tbs": round(gbs / NOMINAL_HBM_GBS, 4),
                                                    "note": "8 MiB of input: L2-resident and launch-latency bound" if n == 1 << 20 else "2 GiB of input"}
             for d in b0.dev:
                 d.free()
@@ -540,8 +749,10 @@ def main():
                 "dtype": "i32/i64/f32", "data": "synthetic (seeded 2^24-element blocks tiled to size)",
                 "config": {"workload": "configs[1-4] skeleton suite" + (f" / 2^{args.scale}" if args.scale else ""),
                            "l2": "every input is larger than L2 (126 MB); no flush", "per_gpu_elements_per_step": sum(w.elements for w in ws),
+                           "histogram_bins": "value uses bin = Zipf rank - 1; per_skeleton.permute_hist_i32_shuffled is the same histogram with the bins shuffled",
                            "parallelism": f"dp{world}", "setup_s": round(t_gen, 1)},
-                "roofline": roofline, "per_skeleton": per, "gpu_launches": int(launches), "clocks": clocks, "e2e": e2e, "cpu_baseline": cb,
+                "roofline": roofline, "per_skeleton": per, "gpu_launches": int(launches), "clocks": clocks,
+                "parity_ok": parity_ok, "parity_failed": parity_failed, "e2e": e2e, "cpu_baseline": cb,
                 "config0_dotp": c0}
         print(json.dumps(line))
     if dist is not None:

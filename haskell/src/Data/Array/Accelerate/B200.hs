@@ -55,7 +55,7 @@ import Data.Array.Accelerate.Type
 import qualified Data.Array.Accelerate.Smart                        as Smart
 import qualified Data.Array.Accelerate.Sugar.Array                  as Sugar
 
-import Control.Exception                                            ( throwIO, ErrorCall(..) )
+import Control.Exception                                            ( throwIO, ErrorCall(..), ArithException(..) )
 import Control.Monad
 import Data.Int
 import Data.IORef
@@ -99,8 +99,10 @@ check :: CInt -> IO ()
 check 0  = return ()
 check rc = do
   msg <- peekCString =<< c_lastError
-  -- B200_ERR_BOUNDS (5) corresponds to the reference's boundsCheck failures (Error.hs:52-63)
-  throwIO (ErrorCall ("accelerate-b200 [" ++ show rc ++ "]: " ++ msg))
+  -- B200_ERR_BOUNDS (5) corresponds to the reference's boundsCheck failures (Error.hs:52-63);
+  -- B200_ERR_ARITH (9) is what GHC raises from quot/rem/div/mod by zero
+  if rc == 9 then throwIO DivideByZero
+             else throwIO (ErrorCall ("accelerate-b200 [" ++ show rc ++ "]: " ++ msg))
 
 -- | Open a context on the given CUDA device.
 createB200 :: Int -> IO B200

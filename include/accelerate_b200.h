@@ -32,11 +32,13 @@ enum {
   B200_ERR_TYPE = 2,        /* ill-typed program */
   B200_ERR_COMPILE = 3,     /* NVRTC rejected a generated kernel (internal error) */
   B200_ERR_CUDA = 4,        /* a CUDA call failed, or the CUDA driver is missing */
-  B200_ERR_BOUNDS = 5,      /* the reference's boundsCheck failures: "empty array",
-                               "empty segment", "shape mismatch" (Error.hs:52-63) */
+  B200_ERR_BOUNDS = 5,      /* the reference's boundsCheck failures: "empty array", "empty segment",
+                               "shape mismatch", "index out of bounds" (Error.hs:52-63) */
   B200_ERR_UNSUPPORTED = 6,
   B200_ERR_ARG = 7,
-  B200_ERR_TIMEOUT = 8      /* a bounded device-side wait gave up */
+  B200_ERR_TIMEOUT = 8,     /* a bounded device-side wait gave up */
+  B200_ERR_ARITH = 9        /* integer division by zero (GHC's ArithException DivideByZero, raised by
+                               quot/rem/div/mod in Interpreter.hs:1328-1344) */
 };
 
 /* Message of the last failure on this thread (valid until the next call). */
@@ -119,6 +121,12 @@ int b200_compile_check(const char* text, size_t len, char* log, size_t log_len);
 /* Generated CUDA source of node `node` (default variant), for inspection. */
 int b200_kernel_source(const char* text, size_t len, int node, char* out, size_t out_len);
 
+/* Diagnostic (no counterpart in the reference; used by the host-side tests): 1 when a scan along
+ * rows of `n` elements of `elt_bytes` bytes each (`rows` rows, right-to-left if `right`) meets the
+ * 16-byte alignment rule of the bulk copies in the shared-memory ring kernel, 0 when it has to take
+ * the register kernel. */
+int b200_scan_ring_aligned(int elt_bytes, int64_t n, int64_t rows, int right);
+
 /* Inclusive prefix sum (scanl1 (+)) of `n` Int32 values, device to device,
  * WITHOUT allocating anything.  It has no counterpart in the reference: it
  * exists for callers that may not allocate device memory themselves nor let
@@ -126,9 +134,13 @@ int b200_kernel_source(const char* text, size_t len, int node, char* out, size_t
  * and lends out only the input and output buffers, or a caller on a path where
  * cudaMalloc's implicit device synchronisation is unacceptable.
  *
- * `in` and `out` are device pointers on the current device (they may not
- * overlap); `stream` is a cudaStream_t (NULL = default stream).  The call
- * returns after the result is complete.  The look-back descriptors of the scan
+ * `in` and `out` are device pointers on the current device, 4-byte aligned
+ * (16-byte alignment of both enables the vector path).  They may not overlap,
+ * and in == out is not allowed either: tiles are read through the read-only
+ * data path while other tiles are being written.  `stream` is a cudaStream_t
+ * (NULL = default stream).  The call is synchronous: it blocks the calling host
+ * thread until the result is complete (it copies a status word back and
+ * synchronises `stream`).  The look-back descriptors of the scan
  * live in a fixed __device__ array of about 1 MB that every GPU using this
  * library holds until the process exits, hence:
  *   - n may not exceed B200_NOALLOC_SCAN_MAX_ELEMS; more is refused (B200_ERR_ARG);

@@ -836,9 +836,20 @@ struct Delayed {
   std::unique_ptr<Fun> index;
 };
 
+struct Node;
+// An array-level function (Awhile's condition and step, Apply's function) or a branch of Acond.
+struct Body {
+  std::vector<int> params;
+  std::vector<Node> nodes;
+  std::vector<int> outs;
+};
+
 struct Node {
   std::string kind;
   std::vector<int> outs;  // array slots defined
+  std::vector<Body> body;              // acond: then, else; awhile: condition, step; apply: function
+  std::vector<int> args;               // awhile: initial state; apply: arguments
+  ArrayP use_val;                      // use: the embedded array
   std::vector<std::unique_ptr<Fun>> f;
   std::vector<std::unique_ptr<Exp>> x;
   std::vector<Delayed> d;
@@ -927,7 +938,35 @@ std::vector<int> parse_stencilr(const Sx& x) {
 //   (stencil ELT stencilr fun bnd D)
 //   (stencil2 ELT stencilr1 stencilr2 fun bnd1 D1 bnd2 D2)
 //   (reshape sh a)
-void parse_node(Program& p, const Sx& bind, Scope& sc) {
+void parse_node(Program& p, std::vector<Node>& into, const Sx& bind, Scope& sc);
+
+// (afun ((p (array R T)) ...) (let ..)* (out ..))  |  (branch (let ..)* (out ..))
+Body parse_body(Program& p, const Sx& x, Scope& sc, bool with_params) {
+  if (x.head() != (with_params ? "afun" : "branch")) throw std::runtime_error("expected an array function");
+  Body b;
+  size_t i = 1;
+  if (with_params) {
+    for (auto& q : x[1].k) b.params.push_back(def_array(p, q[0].s));
+    i = 2;
+  }
+  for (; i < x.size(); ++i) {
+    const Sx& f = x.k[i];
+    if (f.head() == "let") parse_node(p, b.nodes, f, sc);
+    else if (f.head() == "out") for (size_t j = 1; j < f.size(); ++j) b.outs.push_back(sc.array(f.k[j].s));
+    else throw std::runtime_error("unknown form in an array function");
+  }
+  if (b.outs.empty()) throw std::runtime_error("array function has no (out ...)");
+  return b;
+}
+
+int hex_val(char c) {
+  if (c >= '0' && c <= '9') return c - '0';
+  if (c >= 'a' && c <= 'f') return c - 'a' + 10;
+  if (c >= 'A' && c <= 'F') return c - 'A' + 10;
+  throw std::runtime_error("bad hexadecimal digit");
+}
+
+void parse_node(Program& p, std::vector<Node>& into, const Sx& bind, Scope& sc) {
   const Sx& lhs = bind[1];
   const Sx& x = bind[2];
   Node n;
@@ -973,6 +1012,30 @@ void parse_node(Program& p, const Sx& bind, Scope& sc) {
   } else if (k == "reshape") {
     n.x.push_back(parse_exp(x[1], sc));
     n.arr = sc.array(x[2].s);
+  } else if (k == "use") {
+    // (use (array R ELT) (shape d..) (hex LEAF)...): Use, Interp:231
+    EltTy elt = parse_elt(x[1][2]);
+    std::vector<int64_t> sh;
+    for (size_t d = 1; d < x[2].size(); ++d) sh.push_back(atoll(x[2].k[d].s.c_str()));
+    n.use_val = new_array(elt, sh);
+    if (x.size() != 3 + n.use_val->leaf.size()) throw std::runtime_error("use: one (hex ...) per leaf expected");
+    for (size_t l = 0; l < n.use_val->leaf.size(); ++l) {
+      const std::string digits = x[3 + l].size() > 1 ? x[3 + l][1].s : std::string();
+      auto& buf = n.use_val->leaf[l];
+      if (digits.size() != 2 * buf.size()) throw std::runtime_error("use: payload size mismatch");
+      for (size_t b = 0; b < buf.size(); ++b) buf[b] = (unsigned char)(hex_val(digits[2 * b]) * 16 + hex_val(digits[2 * b + 1]));
+    }
+  } else if (k == "acond") {
+    n.x.push_back(parse_exp(x[1], sc));
+    n.body.push_back(parse_body(p, x[2], sc, false));
+    n.body.push_back(parse_body(p, x[3], sc, false));
+  } else if (k == "awhile") {
+    n.body.push_back(parse_body(p, x[1], sc, true));
+    n.body.push_back(parse_body(p, x[2], sc, true));
+    for (size_t j = 1; j < x[3].size(); ++j) n.args.push_back(sc.array(x[3].k[j].s));
+  } else if (k == "apply") {
+    n.body.push_back(parse_body(p, x[1], sc, true));
+    for (size_t j = 1; j < x[2].size(); ++j) n.args.push_back(sc.array(x[2].k[j].s));
   } else {
     throw std::runtime_error("unknown array node '" + k + "'");
   }
@@ -980,7 +1043,7 @@ void parse_node(Program& p, const Sx& bind, Scope& sc) {
   // define outputs after parsing operands (no recursive bindings)
   if (lhs.atom) n.outs.push_back(def_array(p, lhs.s));
   else for (auto& nm : lhs.k) n.outs.push_back(def_array(p, nm.s));
-  p.nodes.push_back(std::move(n));
+  into.push_back(std::move(n));
 }
 
 Program* parse_program(const std::string& text) {
@@ -1000,7 +1063,7 @@ Program* parse_program(const std::string& text) {
       p->input_rank.push_back(atoi(f[2][1].s.c_str()));
       p->input_elt.push_back(parse_elt(f[2][2]));
     } else if (h == "let") {
-      parse_node(*p, f, sc);
+      parse_node(*p, p->nodes, f, sc);
     } else if (h == "out") {
       for (size_t j = 1; j < f.size(); ++j) p->outputs.push_back(sc.array(f.k[j].s));
     } else {
@@ -1069,10 +1132,45 @@ Value fold_range(const Fun& f, Env& env, const Value* seed, int64_t n, const std
   return r;
 }
 
+void run_node(Program& p, const Node& n, Env& env);
+
+// Evaluate an array-level function on the given arrays (evalOpenAfun, Interp:144-156)
+std::vector<ArrayP> call_body(Program& p, const Body& b, const std::vector<ArrayP>& args, Env& env) {
+  if (args.size() != b.params.size()) throw std::runtime_error("array function: wrong number of arguments");
+  for (size_t k = 0; k < args.size(); ++k) p.vals[b.params[k]] = args[k];
+  for (auto& m : b.nodes) run_node(p, m, env);
+  std::vector<ArrayP> r;
+  for (int o : b.outs) r.push_back(p.vals[o]);
+  return r;
+}
+
 void run_node(Program& p, const Node& n, Env& env) {
   const std::string& k = n.kind;
   auto& vals = p.vals;
-  if (k == "generate") {
+  if (k == "use") {
+    vals[n.outs[0]] = n.use_val;                                   // Interp:231
+  } else if (k == "acond") {
+    // Interp:217-219
+    const bool yes = eval(*n.x[0], env).s.i != 0;
+    std::vector<ArrayP> r = call_body(p, n.body[yes ? 0 : 1], {}, env);
+    for (size_t i = 0; i < n.outs.size(); ++i) vals[n.outs[i]] = r[i];
+  } else if (k == "awhile") {
+    // Interp:221-229: go a = if cond a `linearIndex` 0 then go (body a) else a
+    std::vector<ArrayP> st;
+    for (int a : n.args) st.push_back(vals[a]);
+    for (;;) {
+      std::vector<ArrayP> c = call_body(p, n.body[0], st, env);
+      if (read_value(*c[0], 0).s.i == 0) break;
+      st = call_body(p, n.body[1], st, env);
+    }
+    for (size_t i = 0; i < n.outs.size(); ++i) vals[n.outs[i]] = st[i];
+  } else if (k == "apply") {
+    // Interp:215
+    std::vector<ArrayP> as;
+    for (int a : n.args) as.push_back(vals[a]);
+    std::vector<ArrayP> r = call_body(p, n.body[0], as, env);
+    for (size_t i = 0; i < n.outs.size(); ++i) vals[n.outs[i]] = r[i];
+  } else if (k == "generate") {
     // generateOp Interp:269-275 via fromFunctionM (Representation/Array.hs:109-122)
     auto sh = value_shape(eval(*n.x[0], env));
     ArrayP out = new_array(n.elt[0], sh);

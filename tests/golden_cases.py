@@ -154,6 +154,17 @@ def extra_cases():
     efl = (np.full(100, 1.01, np.float32), np.zeros(100, np.float32))
     exp = (np.array([1.01 * k for k in range(1, 101)], np.float32), np.zeros(100, np.float32))
     out["issue114_ref2"] = (A.scanl1(_efloat_add, efl), exp)
+    # Test/NoFib/Misc/Cache.hs:43-73: two kernels that differ only in the expression computing their
+    # extent (host-side, not part of the kernel) and in which arrays that expression mentions; a kernel
+    # cache that ignores the extent must still pass the right parameters to each
+    a10 = A.use(np.arange(10, dtype=np.float32))
+    b10 = A.use(np.arange(10, 20, dtype=np.float32))
+    c = A.compute(A.generate(A.index(a10.shape[0] + b10.shape[0]), lambda ix: a10[A.index(A.rem(ix[0], 10))]))
+    d = A.compute(A.generate(A.index(3 * a10.shape[0]), lambda ix: a10[A.index(A.rem(ix[0], 10))]))
+    out["misc_cache_generate"] = (A.zipWith(add, A.sum_(c), A.sum_(d)), np.array(5 * 45, np.float32))
+    c = A.compute(A.backpermute(A.index(A.min_(a10.shape[0], b10.shape[0])), lambda ix: ix, a10))
+    d = A.compute(A.backpermute(A.index(a10.shape[0]), lambda ix: ix, a10))
+    out["misc_cache_backpermute"] = (A.zipWith(add, A.sum_(c), A.sum_(d)), np.array(2 * 45, np.float32))
     # Test/NoFib/Issues/Issue93.hs:30-37
     xs = np.array([[5]], I)
     out["issue93"] = (A.permute(lambda c, _: c, A.fill(A.use(xs).shape, A.constant(0)), lambda ix: A.Just_(ix), xs), xs)

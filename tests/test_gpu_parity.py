@@ -9,6 +9,7 @@ import numpy as np
 import pytest
 
 import accelerate_b200 as A
+from accelerate_b200.backend import run as backend_run
 from tests.util import check
 
 pytestmark = pytest.mark.gpu
@@ -265,6 +266,85 @@ def test_scan_wraps_int32(scan_path):
     check(A.scanl1(add, x))
 
 
+@pytest.mark.parametrize("ty", ["i8", "u8", "i16", "u16"])
+@pytest.mark.parametrize("shape", [(40000,), (16384 + 16,), (3, 16400), (3, 16396), (1, 8196), (2, 8196)])
+def test_scans_narrow_types_on_both_kernels(ty, shape, monkeypatch):
+    # Long rows of 1- and 2-byte elements: shapes whose row pitch is a multiple of 16 bytes take the
+    # shared-memory ring (bulk copies), the others must fall back to the register kernel.
+    monkeypatch.setenv("ACCELERATE_B200_SCAN_NO_SMALL", "1")
+    dt = A.NP_OF[ty]
+    m = rng.integers(0, 3, size=shape).astype(dt)
+    check(A.scanl1(add, m))
+    check(A.scanr1(add, m))
+    check(A.scanr(A.max_, 1, m))
+    check(list(A.scanl_prime(add, 1, m)))
+
+
+def test_scan_descriptor_layouts_do_not_leak_into_each_other():
+    # All scans of a context share one scratch buffer of look-back descriptors, told apart by an
+    # epoch tag.  Packed 8-byte descriptors, packed 16-byte descriptors and the status/value arrays
+    # of tuple scans lay the buffer out differently, so a scan must not take value bits a previous
+    # scan left behind for a status word of its own epoch.  The first scan leaves the tile prefixes
+    # 1, 2, 3, ... (every small status value among them) in the buffer.
+    from accelerate_b200 import backend, language as L
+    ctx = backend.Context(0)
+    try:
+        def run(build, *hosts):
+            L.reset_names()
+            ps = [L.param(h[0].ndim if isinstance(h, tuple) else h.ndim,
+                          tuple(L.TY_OF_NP[x.dtype] for x in h) if isinstance(h, tuple) else L.TY_OF_NP[h.dtype]) for h in hosts]
+            prog = A.build_program(build(*ps))
+            outs = ctx.execute(prog.text, [ctx.from_host(h) for h in hosts], len(prog.outputs))
+            return [o.download() for o in outs]
+        tiles = 700
+        x = np.zeros(tiles * 8192, np.int32)
+        x[::8192] = 1                                            # one per tile: tile prefixes 1..700
+        for _ in range(3):
+            got, = run(lambda a: A.scanl1(add, a), x)
+            assert np.array_equal(got, np.cumsum(x, dtype=np.int32))
+            n = 3_000_000
+            a, b = ints(n, np.int64), ints(n, np.int64)
+            got, = run(lambda p: A.scanl1(_interval, p), (a, b))     # tuple scan: u32 status array
+            assert np.array_equal(got[0], np.full(n, a[0])) and np.array_equal(got[1], b)
+            big = rng.integers(-1 << 40, 1 << 40, size=2_500_000, dtype=np.int64)
+            got, = run(lambda p: A.scanr1(A.max_, p), big)           # 16-byte descriptors
+            assert np.array_equal(got, np.maximum.accumulate(big[::-1])[::-1])
+            small = ints(70000, np.int32, 0, 3)
+            got, = run(lambda p: A.scanl1(add, p), small)            # short rows: small tiles, dense descriptors
+            assert np.array_equal(got, np.cumsum(small, dtype=np.int32))
+    finally:
+        ctx.close()
+
+
+# ---- errors the reference raises from scalar code ------------------------------------------
+def test_integer_division_by_zero_is_reported():
+    # quot/rem/div/mod by zero throw DivideByZero in the reference (Interpreter.hs:1328-1344)
+    from accelerate_b200.backend import B200Error
+    x = ints(1000, np.int32, 1, 50)
+    y = x.copy()
+    y[777] = 0
+    for f in (lambda a, b: a // b, lambda a, b: a % b, lambda a, b: A.quot(a, b), lambda a, b: A.rem(a, b)):
+        with pytest.raises(B200Error) as e:
+            backend_run(A.zipWith(f, x, y))
+        assert e.value.code == 9, e.value
+        check(A.zipWith(f, x, x))                                 # the context keeps working
+    # a division the scalar code never reaches raises nothing
+    check(A.zipWith(lambda a, b: A.cond(b.eq(0), a, a // b), x, y))
+
+
+def test_permute_target_out_of_bounds_is_reported():
+    # toIndex checks every component of the target index (Shape.hs:102-106)
+    from accelerate_b200.backend import B200Error
+    src = ints(64, np.int32)
+    with pytest.raises(B200Error) as e:
+        backend_run(A.permute(add, A.fill(10, A.constant(np.int32(0))), lambda ix: A.Just_(A.index(ix[0] % 11)), src))
+    assert e.value.code == 5 and "out of bounds" in str(e.value)
+    with pytest.raises(B200Error) as e:
+        backend_run(A.permute(add, A.fill(A.index(4, 4), A.constant(np.int32(0))), lambda ix: A.Just_(A.index(ix[0] % 4, 1 + ix[0] % 4)), src))
+    assert e.value.code == 5                                       # (r, 4) is a valid linear offset but not a valid index
+    check(A.permute(add, A.fill(A.index(4, 4), A.constant(np.int32(0))), lambda ix: A.Just_(A.index(ix[0] % 4, ix[0] % 3)), src))
+
+
 # ---- permute -----------------------------------------------------------------------
 @pytest.mark.parametrize("n,bins", [(0, 4), (1, 1), (20, 10), (5000, 37), (100000, 1000), (200000, 70000)])
 def test_histogram(n, bins):
@@ -272,6 +352,31 @@ def test_histogram(n, bins):
     k = A.use(keys)
     check(A.permute(add, A.fill(bins, A.constant(np.int32(0))), lambda ix: A.Just_(A.index(A.from_integral(k[ix], "i64"))),
                     A.fill(k.shape, A.constant(np.int32(1)))))
+
+
+@pytest.mark.parametrize("bins", [70001, 65536, 100000])
+@pytest.mark.parametrize("vals", ["ones", "mixed"])
+def test_permute_add_int32_large_target_packed_fields(bins, vals):
+    # (+) into an Int32 target of 51 201 .. 114 688 elements: the kernel keeps 16-bit fields per CTA and
+    # compensates every wrap of a field.  Two neighbouring elements receive most of the updates (so
+    # their fields wrap many times, the lower one carrying into the upper one), the addends include
+    # values above 16 bits and negative ones, and the last element of an odd-sized target is hit too.
+    n = 3_000_000
+    g = np.random.default_rng(bins)
+    keys = g.integers(0, bins, size=n).astype(np.int32)
+    hot = g.random(n)
+    keys[hot < 0.30] = 12344
+    keys[(hot >= 0.30) & (hot < 0.55)] = 12345
+    keys[(hot >= 0.55) & (hot < 0.60)] = bins - 1
+    if vals == "ones":
+        v = np.ones(n, np.int32)
+    else:
+        v = g.choice(np.array([1, 65535, 70000, -3, 2_000_000_000, 0], np.int32), size=n)
+    want = np.zeros(bins, np.int64)
+    np.add.at(want, keys, v.astype(np.int64))
+    ku = A.use(keys)
+    got = backend_run(A.permute(add, A.fill(bins, A.constant(np.int32(5))), lambda ix: A.Just_(A.index(A.from_integral(ku[ix], "i64"))), v))
+    assert np.array_equal(got, (want + 5).astype(np.int32))
 
 
 def test_permute_float_dropped():

@@ -45,6 +45,23 @@ def _check(text):
     return backend.compile_check(text)
 
 
+def test_ring_scan_alignment_rule(lib_built):
+    """The ring scan kernel copies whole tiles with cp.async.bulk (16-byte aligned sources): rows whose
+    pitch in bytes is not a multiple of 16 must take the register kernel whenever the pitch enters a
+    tile's address (several rows, or a right-to-left scan)."""
+    lib = ctypes.CDLL(lib_built)
+    f = lib.b200_scan_ring_aligned
+    f.argtypes = [ctypes.c_int, ctypes.c_int64, ctypes.c_int64, ctypes.c_int]
+    assert f(4, 1 << 20, 1, 0) == 1 and f(4, 1 << 20, 1, 1) == 1
+    assert f(4, 8196, 300, 0) == 1            # 4-byte elements, n % 4 == 0: always aligned
+    assert f(2, 8196, 1, 0) == 1              # one row, left to right: tiles start at multiples of the tile
+    assert f(2, 8196, 1, 1) == 0              # right to left: tiles start at n - k*tile -> 8 mod 16
+    assert f(2, 8196, 300, 0) == 0            # rows start at row * 16392 bytes
+    assert f(2, 8200, 300, 1) == 1
+    assert f(1, 8196, 2, 0) == 0 and f(1, 8208, 2, 1) == 1
+    assert f(8, 4098, 2, 0) == 1 and f(8, 4097, 2, 0) == 0
+
+
 def test_parse_and_type_errors_have_codes(lib_built):
     with pytest.raises(backend.B200Error) as e:
         _check("(program (in a (array 1 i32)) (out a")
@@ -126,3 +143,56 @@ def test_program_text_as_the_haskell_module_writes_it(lib_built):
     assert float(res) == 140.0
     assert "ok fold" in backend.compile_check(HASKELL_DIALECT)
     assert "acc_ld4(p.a0_l0" in backend.kernel_source(HASKELL_DIALECT, 0)
+
+
+def test_sharded_program_cache_tells_builders_apart():
+    """The executor of the sharded skeletons caches built programs.  Builders are closures: the same
+    call site with another function, shape or constant must not get the first call's program."""
+    from accelerate_b200 import language as L
+    from accelerate_b200.sharded import ProgramCache
+
+    class Arr:
+        def __init__(self, elt, shape):
+            self.elt, self.shape = elt, shape
+    cache = ProgramCache()
+    x = Arr("i32", (10,))
+
+    def fold_all(f):
+        return cache.get(("fold_all", "local"), lambda a: L.fold1(f, a), [x])[0].text
+    t_add, t_max = fold_all(add), fold_all(L.max_)
+    assert "add" in t_add and "max" in t_max and t_add != t_max
+    assert fold_all(lambda a, b: a + b) == t_add                          # same code, same captures: one entry
+    n_before = len(cache._progs)
+    fold_all(add)
+    assert len(cache._progs) == n_before
+
+    def extend(rows):
+        return cache.get("halo", lambda a: L.generate(L.index(rows + 2, 4), lambda ix: a[L.index(L.min_(ix[0], rows - 1), ix[1])], "i32"),
+                         [Arr("i32", (rows, 4))])[0].text
+    assert extend(6) != extend(8)                                          # the extent is baked into the program
+    assert cache.get("k", lambda a: L.map_(lambda v: v + 1, a), [x])[0].text != cache.get("k", lambda a: L.map_(lambda v: v + 2, a), [x])[0].text
+
+
+def test_kernel_cache_disk_hit_force_recompile_and_damaged_files(lib_built, tmp_path, monkeypatch):
+    """The on-disk kernel cache: a second compilation of the same source is served from the cache,
+    ACCELERATE_B200_FORCE_RECOMP bypasses it, and a cache file that is cut short or is not a cubin
+    is recompiled and replaced instead of being loaded."""
+    monkeypatch.setenv("ACCELERATE_B200_CACHE_DIR", str(tmp_path))
+    text = A.build_program(A.map(lambda v: v * 7 + 3, np.zeros(8, np.int32))).text
+    log = _check(text)
+    assert log.count("compiled") == 1 and "disk cache" not in log
+    files = sorted(tmp_path.glob("*.cubin"))
+    assert len(files) == 1 and not list(tmp_path.glob("*.tmp*"))
+    good = files[0].read_bytes()
+    assert good[:4] == b"\x7fELF"
+    assert "from the disk cache" in _check(text)
+    monkeypatch.setenv("ACCELERATE_B200_FORCE_RECOMP", "1")
+    assert "compiled" in _check(text)
+    monkeypatch.delenv("ACCELERATE_B200_FORCE_RECOMP")
+    for damaged in (good[:len(good) // 2], b"not a cubin at all " * 40, b""):
+        files[0].write_bytes(damaged)
+        assert "compiled" in _check(text)
+        assert files[0].read_bytes()[:4] == b"\x7fELF" and len(files[0].read_bytes()) == len(good)
+    # another scalar body is another kernel; another array SIZE is not (shapes are kernel parameters)
+    assert "compiled" in _check(A.build_program(A.map(lambda v: v * 7 + 4, np.zeros(8, np.int32))).text)
+    assert "from the disk cache" in _check(A.build_program(A.map(lambda v: v * 7 + 3, np.zeros(100000, np.int32))).text)

@@ -2,6 +2,7 @@
 reference's property tests (Test/NoFib/Prelude/{Fold,Scan,Permute,Stencil}.hs:
 random shapes and arrays, result compared with a sequential list reference)."""
 import numpy as np
+import pytest
 from hypothesis import given, settings, strategies as st
 
 import accelerate_b200 as A
@@ -69,3 +70,70 @@ def test_stencil_3x3_matches_padded_reference(shape, bnd, seed):
     b = {"clamp": A.clamp, "mirror": A.mirror, "wrap": A.wrap}[bnd]
     got = oracle.run(A.stencil(lambda s: sum((s[i][j] * (3 * i + j + 1) for i in range(3) for j in range(3)), A.constant(0)), b, m))
     assert np.array_equal(got, want)
+
+
+# ---- stencils against the reference suite's own list-based references ------------------------
+# Every shape Test/NoFib/Prelude/Stencil.hs:48-97 lists, at its sizes (:112, :130, :148, :166,
+# :186-188 ...), with a random tap pattern and a random boundary out of clamp / mirror / wrap /
+# constant, the latter written as `function (\_ -> constant x)` as the reference's tests do (:118).
+from tests import stencil_ref as SR  # noqa: E402
+
+STENCIL_SHAPES = [((3,), 2, 256), ((5,), 3, 256), ((7,), 4, 256), ((9,), 5, 256),
+                  ((3, 3), 2, 96), ((5, 5), 3, 96), ((7, 7), 4, 96), ((9, 9), 5, 96), ((3, 3, 3), 2, 32)]
+
+
+def _boundary(kind, value, as_function=True):
+    if kind == "constant":
+        return ("constant", value), (A.function(lambda _ix: A.constant(value)) if as_function else A.constant_boundary(value))
+    return kind, {"clamp": A.clamp, "mirror": A.mirror, "wrap": A.wrap}[kind]
+
+
+def _examples(extent):
+    return 12 if len(extent) == 1 else (5 if max(extent) <= 5 else 3)
+
+
+@pytest.mark.parametrize("extent,lo,hi", STENCIL_SHAPES, ids=["x".join(map(str, e)) for e, _, _ in STENCIL_SHAPES])
+@pytest.mark.parametrize("dtype", [np.int32, np.float64])
+def test_stencil_matches_list_reference(extent, lo, hi, dtype):
+    import random
+    rnd = random.Random(hash((extent, str(dtype))) & 0xffff)
+    for _ in range(_examples(extent)):
+        sh = tuple(rnd.randint(lo, min(hi, 96 if len(extent) == 2 else (24 if len(extent) == 3 else hi))) for _ in extent)
+        g = np.random.default_rng(rnd.randrange(1 << 30))
+        xs = g.integers(-100, 100, size=sh).astype(dtype) if dtype == np.int32 else g.uniform(-1, 1, size=sh)
+        cval = dtype(g.integers(-9, 9))
+        kind = rnd.choice(["clamp", "mirror", "wrap", "constant"])
+        ref_b, acc_b = _boundary(kind, cval.item(), as_function=rnd.random() < 0.7)
+        pat = SR.random_pattern(rnd, extent)
+        zero = dtype(0)
+        want = np.array(SR.stencil_ref(lambda nb: SR.apply_pattern(pat, nb, zero, len(extent)), ref_b, xs.tolist(), sh, extent), dtype=dtype).reshape(sh)
+        got = oracle.run(A.stencil(lambda s: SR.apply_pattern(pat, s, A.constant(zero), len(extent)), acc_b, xs, extent=extent))
+        if dtype == np.int32:
+            assert np.array_equal(got, want), (extent, sh, kind, pat)
+        else:
+            assert np.allclose(got, want, rtol=1e-12, atol=1e-12), (extent, sh, kind, pat)
+
+
+@pytest.mark.parametrize("ext1,ext2", [((3,), (5,)), ((3, 3), (3, 3)), ((5, 3), (3, 7)), ((3, 3, 3), (3, 3, 3))])
+def test_stencil2_matches_two_list_references(ext1, ext2):
+    # stencil2 has no results test in the reference; its definition (Interpreter.hs:652-668) is two
+    # stencil accesses with their own boundaries over the intersection of the shapes, which is what
+    # two list-based references side by side compute
+    import random
+    rnd = random.Random(len(ext1) * 131 + sum(ext2))
+    for _ in range(5):
+        cap = {1: 60, 2: 24, 3: 10}[len(ext1)]
+        sh1 = tuple(rnd.randint(max(e // 2 + 1, 2), cap) for e in ext1)
+        sh2 = tuple(rnd.randint(max(e // 2 + 1, 2), cap) for e in ext2)
+        g = np.random.default_rng(rnd.randrange(1 << 30))
+        a, b = g.integers(-50, 50, size=sh1).astype(np.int64), g.integers(-50, 50, size=sh2).astype(np.int64)
+        k1, k2 = rnd.choice(["clamp", "mirror", "wrap", "constant"]), rnd.choice(["clamp", "mirror", "wrap", "constant"])
+        (r1, b1), (r2, b2) = _boundary(k1, 7), _boundary(k2, -3)
+        p1, p2 = SR.random_pattern(rnd, ext1), SR.random_pattern(rnd, ext2)
+        d = len(ext1)
+        f_ref = lambda s, t: SR.apply_pattern(p1, s, 0, d) * 3 - SR.apply_pattern(p2, t, 0, d)  # noqa: E731
+        f_acc = lambda s, t: SR.apply_pattern(p1, s, A.constant(0), d) * 3 - SR.apply_pattern(p2, t, A.constant(0), d)  # noqa: E731
+        want = np.array(SR.stencil2_ref(f_ref, r1, a.tolist(), sh1, ext1, r2, b.tolist(), sh2, ext2), dtype=np.int64)
+        got = oracle.run(A.stencil2(f_acc, b1, a, b2, b, extent1=ext1, extent2=ext2))
+        assert got.shape == tuple(min(x, y) for x, y in zip(sh1, sh2))
+        assert np.array_equal(got, want.reshape(got.shape)), (ext1, ext2, sh1, sh2, k1, k2)

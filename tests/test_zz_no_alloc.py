@@ -61,3 +61,25 @@ def test_noalloc_scan_rejects_oversize_and_accepts_empty(gpu_ctx):
     assert rc == 7                                                   # B200_ERR_ARG
     assert b"B200_NOALLOC_SCAN_MAX_ELEMS" in lib.b200_last_error()
     assert lib.b200_scanl1_add_i32_noalloc(None, None, 0, gpu_ctx.stream()) == 0
+
+
+def test_noalloc_scan_at_the_size_limit_and_on_unaligned_pointers(gpu_ctx):
+    """The largest input the fixed scratch array can describe (exactly B200_NOALLOC_SCAN_MAX_ELEMS), and
+    an input/output pair that is only 4-byte aligned, which takes the scalar instead of the 128-bit path."""
+    lib = backend.lib()
+    lib.b200_scanl1_add_i32_noalloc.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int64, ctypes.c_void_p]
+    lib.b200_scanl1_add_i32_noalloc.restype = ctypes.c_int
+    n = 1 << 28
+    block = np.random.default_rng(11).integers(0, 100, size=1 << 22).astype(np.int32)
+    host = np.tile(block, n >> 22)
+    got = _noalloc_scan(gpu_ctx, host)
+    assert np.array_equal(got, np.cumsum(host, dtype=np.int32))
+    del got, host
+    # 4 bytes past a 16-byte boundary on both sides
+    m = 3 * 4096 + 77
+    host = np.random.default_rng(12).integers(-1000, 1000, size=m + 1).astype(np.int32)
+    src = gpu_ctx.from_host(host)
+    dst = gpu_ctx.array("i32", (m + 1,))
+    rc = lib.b200_scanl1_add_i32_noalloc(src.devptr(0) + 4, dst.devptr(0) + 4, m, gpu_ctx.stream())
+    assert rc == 0, lib.b200_last_error().decode()
+    assert np.array_equal(dst.download()[1:], np.cumsum(host[1:], dtype=np.int32))

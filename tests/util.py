@@ -34,10 +34,10 @@ def similar(got, want, rtol=0.0, atol=0.0):
                 raise AssertionError(f"integer mismatch at {bad.tolist()}: got {g[g != w][:5]}, want {w[g != w][:5]}")
 
 
-def check(acc, rtol=0.0, atol=0.0):
+def check(acc, rtol=0.0, atol=0.0, embed=False):
     """Evaluate on GPU and oracle; compare; return the GPU result."""
     multi = isinstance(acc, (list, tuple))
-    got = backend.run(list(acc) if multi else acc)
+    got = backend.run(list(acc) if multi else acc, embed=embed)
     want = oracle.run(list(acc) if multi else acc)
     if multi:
         for g, w in zip(got, want):
