@@ -49,6 +49,8 @@ def lib():
         l.b200_array_adopt_host.argtypes = [vp, ctypes.c_uint64, ctypes.c_int, vp, ctypes.c_size_t]
         l.b200_array_download_async.argtypes = [vp, ctypes.c_uint64, ctypes.c_int, vp, ctypes.c_size_t]
         l.b200_array_free.argtypes = [vp, ctypes.c_uint64]
+        l.b200_array_intern.argtypes = [vp, ctypes.c_uint64, cp, ctypes.c_int, i64p, ctypes.POINTER(vp), u64p]
+        l.b200_array_forget.argtypes = [vp, ctypes.c_uint64]
         l.b200_array_rank.argtypes = [vp, ctypes.c_uint64, ctypes.POINTER(ctypes.c_int)]
         l.b200_array_shape.argtypes = [vp, ctypes.c_uint64, i64p]
         l.b200_array_num_leaves.argtypes = [vp, ctypes.c_uint64, ctypes.POINTER(ctypes.c_int)]
@@ -60,6 +62,16 @@ def lib():
         l.b200_program_num_inputs.argtypes = [vp, ctypes.POINTER(ctypes.c_int)]
         l.b200_program_num_outputs.argtypes = [vp, ctypes.POINTER(ctypes.c_int)]
         l.b200_program_run.argtypes = [vp, u64p, ctypes.c_int, u64p, ctypes.c_int]
+        l.b200_program_run_rows.argtypes = [vp, u64p, ctypes.c_int, ctypes.c_uint64, ctypes.c_int64, ctypes.c_int64]
+        l.b200_group_unique_id.argtypes = [ctypes.c_char_p]
+        l.b200_group_create.argtypes = [vp, ctypes.c_char_p, ctypes.c_int, ctypes.c_int, ctypes.c_double, ctypes.POINTER(vp)]
+        l.b200_group_destroy.argtypes = [vp]
+        l.b200_group_destroy.restype = None
+        l.b200_group_all_gather.argtypes = [vp, ctypes.c_uint64, u64p]
+        l.b200_group_all_reduce.argtypes = [vp, ctypes.c_uint64, ctypes.c_int]
+        l.b200_group_halo_exchange.argtypes = [vp, ctypes.c_uint64, ctypes.c_int64, ctypes.c_int64, ctypes.c_int64, ctypes.c_int64,
+                                               ctypes.c_int, ctypes.c_int, ctypes.c_int]
+        l.b200_group_halo_wait.argtypes = [vp]
         l.b200_sync.argtypes = [vp]
         l.b200_stats.argtypes = [vp, i64p]
         l.b200_ctx_stream.argtypes = [vp, ctypes.POINTER(vp)]
@@ -172,6 +184,7 @@ class Context:
         self.device = device
         self._programs = {}
         self._inflight = []          # views with an asynchronous download under way (kept alive until sync)
+        self._interned = {}          # host payloads registered in the memory table, by key
 
     def close(self):
         if self.h:
@@ -204,6 +217,28 @@ class Context:
             elt = tuple(L.TY_OF_NP[x.dtype] for x in leaves) if isinstance(a, (tuple, list)) else L.TY_OF_NP[leaves[0].dtype]
         return self.array(elt, leaves[0].shape).adopt_host(leaves)
 
+    def intern(self, key, a, elt=None):
+        """The device copy of host array ``a`` under the caller's unique ``key`` (the memory table,
+        ``b200_array_intern``): uploaded at most once however often it is asked for.  The caller
+        guarantees that ``a`` is not modified while the key is registered."""
+        leaves = [np.ascontiguousarray(x) for x in (a if isinstance(a, (tuple, list)) else [a])]
+        leaves = [x.view(np.uint8) if x.dtype == np.bool_ else x for x in leaves]
+        if elt is None:
+            elt = tuple(L.TY_OF_NP[x.dtype] for x in leaves) if isinstance(a, (tuple, list)) else L.TY_OF_NP[leaves[0].dtype]
+        shape = leaves[0].shape
+        ident = ctypes.c_uint64()
+        sh = (ctypes.c_int64 * max(1, len(shape)))(*shape)
+        ptrs = (ctypes.c_void_p * len(leaves))(*[x.ctypes.data for x in leaves])
+        _check(lib().b200_array_intern(self.h, key, L.ty_sx(elt).encode(), len(shape), sh, ptrs, ctypes.byref(ident)))
+        d = DeviceArray(self, ident.value, elt)
+        d._adopted = leaves
+        self._interned.setdefault(key, leaves)      # the payload stays alive while the key is registered
+        return d
+
+    def forget(self, key):
+        _check(lib().b200_array_forget(self.h, key))
+        self._interned.pop(key, None)
+
     def wrap(self, elt, shape, ptrs):
         """Adopt caller-owned device memory (one pointer per leaf)."""
         ident = ctypes.c_uint64()
@@ -230,6 +265,12 @@ class Context:
         _check(lib().b200_program_run(p, ins, len(inputs), outs, n_out))
         return [DeviceArray(self, outs[k]) for k in range(n_out)]
 
+    def run_rows(self, text, inputs, out, row_lo, row_hi):
+        """Rows [row_lo, row_hi) of a one-stencil-node program's result, into the existing array ``out``."""
+        p = self.load(text)
+        ins = (ctypes.c_uint64 * max(1, len(inputs)))(*[a.id for a in inputs])
+        _check(lib().b200_program_run_rows(p, ins, len(inputs), out.id, row_lo, row_hi))
+
     def sync(self):
         try:
             _check(lib().b200_sync(self.h))
@@ -246,6 +287,44 @@ class Context:
         s = ctypes.c_void_p()
         _check(lib().b200_ctx_stream(self.h, ctypes.byref(s)))
         return s.value or 0
+
+
+class Group:
+    """This context's GPU as one rank of a group of GPUs (``b200_group_*``): the exchange steps of
+    the sharded skeletons, enqueued on the context's streams."""
+
+    OPS = {"add": 0, "min": 1, "max": 2, "mul": 3}
+
+    @staticmethod
+    def unique_id():
+        buf = ctypes.create_string_buffer(128)
+        _check(lib().b200_group_unique_id(buf))
+        return buf.raw
+
+    def __init__(self, ctx, unique_id, rank, world, deadline_s=60.0):
+        self.ctx, self.rank, self.world = ctx, rank, world
+        self.h = ctypes.c_void_p()
+        _check(lib().b200_group_create(ctx.h, unique_id, rank, world, deadline_s, ctypes.byref(self.h)))
+
+    def close(self):
+        if self.h:
+            lib().b200_group_destroy(self.h)
+            self.h = ctypes.c_void_p()
+
+    def all_gather(self, a):
+        out = ctypes.c_uint64()
+        _check(lib().b200_group_all_gather(self.h, a.id, ctypes.byref(out)))
+        return DeviceArray(self.ctx, out.value, a.elt)
+
+    def all_reduce(self, a, op):
+        _check(lib().b200_group_all_reduce(self.h, a.id, self.OPS[op]))
+
+    def halo_exchange(self, a, top, rows, bot, radius, up, down, overlap=False):
+        _check(lib().b200_group_halo_exchange(self.h, a.id, top, rows, bot, radius, -1 if up is None else up, -1 if down is None else down,
+                                              1 if overlap else 0))
+
+    def halo_wait(self):
+        _check(lib().b200_group_halo_wait(self.h))
 
 
 _default = None

@@ -7,9 +7,6 @@
 
 using namespace accb200;
 
-struct b200_ctx { Ctx c; };
-struct b200_program { Program p; };
-
 namespace {
 thread_local std::string g_error;
 
@@ -110,6 +107,7 @@ void b200_ctx_destroy(b200_ctx* ctx) {
   {
     std::lock_guard<std::mutex> g(c.mu);
     c.arrays.clear();
+    c.table.clear();
     c.reap(true);
     for (auto& k : c.kernels)
       if (k.second.module) c.drv.ModuleUnload(k.second.module);
@@ -267,6 +265,46 @@ int b200_array_download_async(b200_ctx* ctx, uint64_t id, int leaf, void* host, 
   B200_END
 }
 
+int b200_array_intern(b200_ctx* ctx, uint64_t key, const char* elt_type, int rank, const int64_t* shape,
+                      const void* const* host_leaves, uint64_t* id) {
+  B200_TRY
+  if (!ctx || !elt_type || !id || rank < 0 || (rank > 0 && !shape)) throw Error(B200_ERR_ARG, "bad argument");
+  Ctx& c = ctx->c;
+  std::lock_guard<std::mutex> g(c.mu);
+  const Type elt = parse_type_text(elt_type);
+  const std::vector<int64_t> sh(shape, shape + rank);
+  auto it = c.table.find(key);
+  DevArrayP a;
+  if (it != c.table.end()) {
+    a = it->second;
+    if (a->elt != elt || a->shape != sh) throw Error(B200_ERR_ARG, "array key " + std::to_string(key) + " was registered with another type or shape");
+  } else {
+    c.check(cudaSetDevice(c.device), "cudaSetDevice");
+    a = c.new_array(elt, sh);
+    if (a->size() > 0) {
+      if (!host_leaves) throw Error(B200_ERR_ARG, "null host pointer");
+      a->pending.assign(a->leaf.size(), nullptr);
+      for (size_t l = 0; l < a->leaf.size(); ++l) {
+        if (!host_leaves[l]) throw Error(B200_ERR_ARG, "null host pointer");
+        a->pending[l] = host_leaves[l];
+      }
+    }
+    c.table[key] = a;
+  }
+  *id = c.next_id++;
+  c.arrays[*id] = a;
+  B200_END
+}
+
+int b200_array_forget(b200_ctx* ctx, uint64_t key) {
+  B200_TRY
+  if (!ctx) throw Error(B200_ERR_ARG, "null context");
+  Ctx& c = ctx->c;
+  std::lock_guard<std::mutex> g(c.mu);
+  c.table.erase(key);
+  B200_END
+}
+
 int b200_array_free(b200_ctx* ctx, uint64_t id) {
   B200_TRY
   if (!ctx) throw Error(B200_ERR_ARG, "null context");
@@ -358,6 +396,19 @@ int b200_program_run(b200_program* prog, const uint64_t* in_ids, int n_in, uint6
     out_ids[k] = c.next_id++;
     c.arrays[out_ids[k]] = outs[k];
   }
+  B200_END
+}
+
+int b200_program_run_rows(b200_program* prog, const uint64_t* in_ids, int n_in, uint64_t out_id, int64_t row_lo, int64_t row_hi) {
+  B200_TRY
+  if (!prog) throw Error(B200_ERR_ARG, "null program");
+  Ctx& c = *prog->p.ctx;
+  std::lock_guard<std::mutex> g(c.mu);
+  c.check(cudaSetDevice(c.device), "cudaSetDevice");
+  std::vector<DevArrayP> ins;
+  for (int k = 0; k < n_in; ++k) ins.push_back(lookup(c, in_ids[k]));
+  for (auto& a : ins) materialise(c, *a);
+  prog->p.run_rows(ins, lookup(c, out_id), row_lo, row_hi);
   B200_END
 }
 

@@ -767,6 +767,9 @@ Glue build_glue(const Node& n, const std::map<std::string, ArrayInfo>& arrays) {
         def["PERMUTE_BYTES"] = std::to_string(ty_bytes[l[0]]);
         def["PERMUTE_SIGNED"] = ty_is_signed(l[0]) ? "1" : "0";
         def["PERMUTE_FLOAT"] = ty_is_float(l[0]) ? "1" : "0";
+        // every source element is the literal 1 (the histogram idiom, `permute (+) zeros ix (fill sh 1)`)
+        const Expr& src = *n.d[0].index->body;
+        def["PERMUTE_UNIT"] = (!n.d[0].manifest && src.kind == X_CONST && ty_is_int(l[0]) && src.lit == "1") ? "1" : "0";
       }
       break;
     }
@@ -960,10 +963,10 @@ Glue build_glue(const Node& n, const std::map<std::string, ArrayInfo>& arrays) {
     case N_FOLD: named = {"n", "rows", "row", "vec", "scratch", "flags", "counter"}; break;
     case N_FOLDSEG: named = {"segs", "rows", "vec", "err"}; break;
     case N_SCAN: case N_SCAN2:
-      named = {"n", "rows", "tiles_per_row", "total_tiles", "in_vec", "out_vec", "status", "agg", "incl", "gstatus", "groups_per_row", "counter", "epoch", "err", "spin_limit"};
+      named = {"n", "rows", "tiles_per_row", "total_tiles", "batches_per_row", "total_batches", "in_vec", "out_vec", "status", "agg", "incl", "gstatus", "groups_per_row", "counter", "epoch", "err", "spin_limit"};
       break;
-    case N_PERMUTE: named = {"n", "vec", "out_n", "priv", "locks", "err", "spin_limit"}; break;
-    case N_STENCIL: case N_STENCIL2: named = {"o0", "o1", "o2", "tiles1", "tiles2", "vec"}; break;
+    case N_PERMUTE: named = {"n", "vec", "out_n", "priv", "priv16", "choice", "locks", "err", "spin_limit"}; break;
+    case N_STENCIL: case N_STENCIL2: named = {"o0", "o1", "o2", "row0", "row1", "tiles1", "tiles2", "vec"}; break;
     default: break;
   }
   for (auto& nm : named) b.ps.use_named(nm);

@@ -23,8 +23,6 @@ void Driver::load() {
   ModuleGetFunction = (decltype(ModuleGetFunction))get("cuModuleGetFunction");
   ModuleGetGlobal = (decltype(ModuleGetGlobal))get("cuModuleGetGlobal");
   LaunchKernel = (decltype(LaunchKernel))get("cuLaunchKernel");
-  LaunchKernelEx = (decltype(LaunchKernelEx))get("cuLaunchKernelEx");
-  OccupancyMaxActiveClusters = (decltype(OccupancyMaxActiveClusters))get("cuOccupancyMaxActiveClusters");
   FuncSetAttribute = (decltype(FuncSetAttribute))get("cuFuncSetAttribute");
   OccupancyMaxActiveBlocksPerMultiprocessor =
       (decltype(OccupancyMaxActiveBlocksPerMultiprocessor))get("cuOccupancyMaxActiveBlocksPerMultiprocessor");
@@ -224,6 +222,7 @@ std::map<std::string, std::string> scan_variant(const Type& elt, bool small = fa
   if (const char* e = getenv("ACCELERATE_B200_SCAN_MIN_BLOCKS")) minb = e;
   std::map<std::string, std::string> v = {{"SCAN_MIN_BLOCKS", minb}, {"SCAN_ROUNDS", std::to_string(rounds)}};
   if (const char* e = getenv("ACCELERATE_B200_SCAN_LOOK")) v["SCAN_LOOK"] = e;
+  if (const char* e = getenv("ACCELERATE_B200_SCAN_DESC_SPLIT")) v["SCAN_DESC_SPLIT"] = e;
   return v;
 }
 // Spacing of look-back descriptors (in descriptors) and pause after an unsuccessful poll.
@@ -239,7 +238,7 @@ void scan_poll_variant(std::map<std::string, std::string>& v, int64_t total_tile
   v["SCAN_BACKOFF_NS"] = e && *e ? std::string(e) : std::to_string(SCAN_BACKOFF_DEFAULT);
 }
 // shape of the shared-memory ring scan kernel (overridable for tuning)
-struct RingShape { int rounds, slots, minb, lbw, redw, look, grab; };
+struct RingShape { int rounds, slots, minb, lbw, redw, look, grab, batch; };
 RingShape scan_ring_shape(int bytes) {
   auto tune = [](const char* name, int dflt) { const char* e = getenv(name); return e && *e ? atoi(e) : dflt; };
   RingShape r;
@@ -247,16 +246,18 @@ RingShape scan_ring_shape(int bytes) {
   r.slots = tune("ACCELERATE_B200_RING_SLOTS", 3);
   r.minb = tune("ACCELERATE_B200_RING_MIN_BLOCKS", 2);
   r.lbw = std::max(1, tune("ACCELERATE_B200_RING_LB_WARPS", 1));
-  r.redw = std::max(1, tune("ACCELERATE_B200_RING_RED_WARPS", 2));
-  r.look = std::max(1, tune("ACCELERATE_B200_SCAN_LOOK", 2));
+  r.redw = std::max(1, tune("ACCELERATE_B200_RING_RED_WARPS", 1));
+  r.look = std::max(1, tune("ACCELERATE_B200_SCAN_LOOK", 4));
   r.grab = tune("ACCELERATE_B200_RING_GRAB", 1);
+  r.batch = std::max(1, tune("ACCELERATE_B200_RING_BATCH", 2));
   return r;
 }
 std::map<std::string, std::string> scan_ring_variant(const RingShape& r, int64_t total_tiles) {
   std::map<std::string, std::string> v = {{"SCAN_RING", "1"}, {"SCAN_ROUNDS", std::to_string(r.rounds)}, {"SCAN_SLOTS", std::to_string(r.slots)},
                                           {"SCAN_MIN_BLOCKS", std::to_string(r.minb)}, {"SCAN_LB_WARPS", std::to_string(r.lbw)},
                                           {"RING_RED_WARPS", std::to_string(r.redw)}, {"SCAN_LOOK", std::to_string(r.look)},
-                                          {"RING_GRAB_STATE", std::to_string(r.grab)}};
+                                          {"RING_GRAB_STATE", std::to_string(r.grab)}, {"RING_BATCH", std::to_string(r.batch)}};
+  if (const char* e = getenv("ACCELERATE_B200_SCAN_DESC_SPLIT")) v["SCAN_DESC_SPLIT"] = e;
   scan_poll_variant(v, total_tiles);
   return v;
 }
@@ -306,10 +307,10 @@ std::vector<std::pair<std::string, std::map<std::string, std::string>>> default_
       if (m.find("ATOMIC") != std::string::npos) {
         v.push_back({"permute", {{"PERMUTE_SMEM", "1"}, {"PERMUTE_THREADS", "1024"}}});
         if (m == "PERMUTE_ATOMIC_ADD" && g.defines.at("PERMUTE_BYTES") == "4" && g.defines.at("PERMUTE_FLOAT") == "0")
-          v.push_back({"permute", {{"PERMUTE_SMEM16", "1"}, {"PERMUTE_THREADS", "1024"}}});
-        if (g.defines.at("PERMUTE_BYTES") == "4")
-          for (int lg : {1, 2, 3, 4})
-            v.push_back({"permute", {{"PERMUTE_CLUSTER", std::to_string(1 << lg)}, {"PERMUTE_CLUSTER_LOG2", std::to_string(lg)}, {"PERMUTE_THREADS", "1024"}}});
+        {
+          v.push_back({"permute", {{"PERMUTE_SMEM16", "1"}, {"PERMUTE_THREADS", "1024"}, {"PERMUTE_CHOICE_ID", "1"}}});
+          v.push_back({"permute", {{"PERMUTE_SAMPLE", "1"}}});
+        }
       }
       break;
     }
@@ -597,29 +598,6 @@ struct Launcher {
                "cuLaunchKernel");
     ctx->launches++;
   }
-  // `clusters` thread-block clusters of `csize` CTAs each
-  void launch_clusters(CompiledKernel& k, int64_t clusters, int csize, int threads, size_t smem) {
-    if (clusters <= 0) return;
-    std::vector<uint64_t> pb = block();
-    void* args[1] = {pb.data()};
-    CUlaunchAttribute attr;
-    attr.id = CU_LAUNCH_ATTRIBUTE_CLUSTER_DIMENSION;
-    attr.value.clusterDim.x = (unsigned)csize;
-    attr.value.clusterDim.y = 1;
-    attr.value.clusterDim.z = 1;
-    CUlaunchConfig cfg;
-    memset(&cfg, 0, sizeof cfg);
-    cfg.gridDimX = (unsigned)(clusters * csize);
-    cfg.gridDimY = cfg.gridDimZ = 1;
-    cfg.blockDimX = (unsigned)threads;
-    cfg.blockDimY = cfg.blockDimZ = 1;
-    cfg.sharedMemBytes = (unsigned)smem;
-    cfg.hStream = (CUstream)ctx->stream;
-    cfg.attrs = &attr;
-    cfg.numAttrs = 1;
-    ctx->check(ctx->drv.LaunchKernelEx(&cfg, k.fn, args, nullptr), "cuLaunchKernelEx");
-    ctx->launches++;
-  }
   // extent of a delayed operand + whether its streams all have exactly that shape
   void bind_delayed(const std::string& D, const std::vector<int64_t>& ext, size_t k) {
     bool fast = true;
@@ -734,6 +712,18 @@ void Program::run(const std::vector<DevArrayP>& inputs, std::vector<DevArrayP>& 
   exec(ir->nodes, env);
   outputs.clear();
   for (auto& o : ir->outputs) outputs.push_back(env.at(o));
+}
+
+void Program::run_rows(const std::vector<DevArrayP>& inputs, const DevArrayP& out, int64_t row_lo, int64_t row_hi) {
+  if (ir->nodes.size() != 1 || (ir->nodes[0].kind != N_STENCIL && ir->nodes[0].kind != N_STENCIL2) || ir->outputs.size() != 1 ||
+      ir->outputs[0] != ir->nodes[0].outs[0])
+    throw Error(B200_ERR_ARG, "a row window needs a program that is exactly one stencil node");
+  if (!out) throw Error(B200_ERR_ARG, "null output array");
+  Window w{out, row_lo, row_hi};
+  struct Guard { const Window*& slot; ~Guard() { slot = nullptr; } } guard{window};
+  window = &w;
+  std::vector<DevArrayP> outs;
+  run(inputs, outs);
 }
 
 // Evaluate an array-level function: bind the parameters, run the nodes, collect the results and
@@ -947,21 +937,26 @@ void Program::exec_kernel_node(const Node& n, Env& env_ref) {
             const int64_t r_tiles_per_row = std::max<int64_t>(1, (m + rtile - 1) / rtile);
             const int64_t r_total = rows * r_tiles_per_row;
             const size_t smem = (size_t)slots * rtile * bytes;
-            std::map<std::string, std::string> var = scan_ring_variant(rs, r_total);
-            const int dstride = scan_desc_stride(r_total);
-            const size_t r_status = ((size_t)r_total * 16 * dstride + 255) / 256 * 256;
-            const int64_t groups_per_row = (r_tiles_per_row + 32 * look - 1) / (32 * look);
+            // look-back descriptors describe batches of rs.batch consecutive tiles of a row
+            const int64_t batches_per_row = (r_tiles_per_row + rs.batch - 1) / rs.batch;
+            const int64_t total_batches = rows * batches_per_row;
+            std::map<std::string, std::string> var = scan_ring_variant(rs, total_batches);
+            const int dstride = scan_desc_stride(total_batches);
+            const size_t r_status = ((size_t)total_batches * 16 * dstride + 255) / 256 * 256;
+            const int64_t groups_per_row = (batches_per_row + 32 * look - 1) / (32 * look);
             const size_t g_status = ((size_t)(rows * groups_per_row) * 16 * dstride + 255) / 256 * 256;
             char* rbase = (char*)c.scan_descriptors(r_status + g_status, "ring/" + std::to_string(bytes) + "/" + std::to_string(dstride) + "/" + std::to_string(r_status));
             L.named["gstatus"] = (int64_t)(uintptr_t)(rbase + r_status);
             L.named["groups_per_row"] = groups_per_row;
             L.named["tiles_per_row"] = r_tiles_per_row;
             L.named["total_tiles"] = r_total;
+            L.named["batches_per_row"] = batches_per_row;
+            L.named["total_batches"] = total_batches;
             L.named["status"] = (int64_t)(uintptr_t)rbase;
             L.named["epoch"] = c.scan_epoch;
             const int threads = 256 + 32 * rs.redw + 32 * rs.lbw;     // 8 finisher warps, the reducer warps, the look-back warps
             CompiledKernel& k = c.kernel(assemble_source(st.glue, "scan", var), "acc_scan_ring", threads, smem);
-            const int64_t grid = std::min<int64_t>(r_total, (int64_t)c.sm_count * k.max_blocks_per_sm);
+            const int64_t grid = std::min<int64_t>(total_batches, (int64_t)c.sm_count * k.max_blocks_per_sm);
             L.launch(k, grid, threads, smem);
             break;
           }
@@ -1017,59 +1012,30 @@ void Program::exec_kernel_node(const Node& n, Env& env_ref) {
         const int bytes = atomic ? atoi(st.glue.defines.at("PERMUTE_BYTES").c_str()) : 0;
         const int64_t cap = 200 * 1024;
         const char* no_priv = getenv("ACCELERATE_B200_NO_PRIVATISE");
-        int csize = 0;
-        if (const char* e = getenv("ACCELERATE_B200_PERMUTE_CLUSTER")) csize = atoi(e);
-        if (atomic && bytes == 4 && !no_priv && csize >= 2 && (csize & (csize - 1)) == 0 && total >= 8 * out_n && total >= (1 << 16)) {
-          // the target copy is spread over the shared memories of a cluster of `csize` CTAs
-          int lg = 0;
-          while ((1 << lg) < csize) ++lg;
-          int64_t words = cap / bytes;
-          if (const char* e = getenv("ACCELERATE_B200_PERMUTE_CLUSTER_WORDS")) words = atoll(e);
-          const int64_t priv = std::min<int64_t>((out_n + csize - 1) / csize, words);
-          const size_t smem = (size_t)priv * bytes;
-          std::map<std::string, std::string> var = {{"PERMUTE_CLUSTER", std::to_string(csize)}, {"PERMUTE_CLUSTER_LOG2", std::to_string(lg)},
-                                                    {"PERMUTE_THREADS", "1024"}};
-          if (const char* e = getenv("ACCELERATE_B200_PERMUTE_UNROLL")) var["PERMUTE_UNROLL"] = e;
-          CompiledKernel& k = c.kernel(assemble_source(st.glue, "permute", var), "acc_permute", 1024, smem);
-          if (smem > 48 * 1024) c.check(c.drv.FuncSetAttribute(k.fn, CU_FUNC_ATTRIBUTE_MAX_DYNAMIC_SHARED_SIZE_BYTES, (int)smem), "cuFuncSetAttribute");
-          if (csize > 8) c.check(c.drv.FuncSetAttribute(k.fn, CU_FUNC_ATTRIBUTE_NON_PORTABLE_CLUSTER_SIZE_ALLOWED, 1), "cuFuncSetAttribute");
-          CUlaunchAttribute attr;
-          attr.id = CU_LAUNCH_ATTRIBUTE_CLUSTER_DIMENSION;
-          attr.value.clusterDim.x = (unsigned)csize;
-          attr.value.clusterDim.y = attr.value.clusterDim.z = 1;
-          CUlaunchConfig cfg;
-          memset(&cfg, 0, sizeof cfg);
-          cfg.gridDimX = (unsigned)csize; cfg.gridDimY = cfg.gridDimZ = 1;
-          cfg.blockDimX = 1024; cfg.blockDimY = cfg.blockDimZ = 1;
-          cfg.sharedMemBytes = (unsigned)smem;
-          cfg.attrs = &attr;
-          cfg.numAttrs = 1;
-          int nclusters = 0;
-          c.check(c.drv.OccupancyMaxActiveClusters(&nclusters, k.fn, &cfg), "cuOccupancyMaxActiveClusters");
-          if (getenv("ACCELERATE_B200_VERBOSE")) fprintf(stderr, "[accb200] permute: clusters of %d CTAs, %d resident, %lld words per CTA\n", csize, nclusters, (long long)priv);
-          if (nclusters >= 1) {
-            L.named["priv"] = priv;
-            const int64_t work = (total + 3) / 4;
-            const int64_t want = (work + 1024 * csize - 1) / (1024 * csize);
-            L.launch_clusters(k, std::min<int64_t>(want, nclusters), csize, 1024, smem);
-            break;
-          }
-        }
         const bool int_add32 = mode == "PERMUTE_ATOMIC_ADD" && bytes == 4 && st.glue.defines.at("PERMUTE_FLOAT") == "0";
-        if (int_add32 && !no_priv && out_n > cap / 4 && (out_n + 1) / 2 <= 56 * 1024 && total >= 8 * out_n && !getenv("ACCELERATE_B200_NO_SMEM16")) {
+        const bool fields16 = int_add32 && !no_priv && out_n > cap / 4 && (out_n + 1) / 2 <= 56 * 1024 && total >= 8 * out_n &&
+                              !getenv("ACCELERATE_B200_NO_SMEM16");
+        L.named["choice"] = 0;
+        if (fields16) {
           // (+) on 32-bit integers, target too large for a CTA-private 32-bit copy but not for 16-bit
-          // fields: every element of the target is private to the CTA, wherever the frequent ones lie
-          const int64_t words = (out_n + 1) / 2;
-          const size_t smem = (size_t)words * 4;
-          std::map<std::string, std::string> var = {{"PERMUTE_SMEM16", "1"}, {"PERMUTE_THREADS", "1024"}};
-          if (const char* e = getenv("ACCELERATE_B200_PERMUTE_UNROLL")) var["PERMUTE_UNROLL"] = e;
+          // fields.  A sample of the input decides on the device between that kernel and the faster
+          // partial 32-bit copy below (see acc_permute_sample); both are launched.
+          int* choice = c.d_words + 4;
+          L.named["choice"] = (int64_t)(uintptr_t)choice;
+          L.named["priv"] = std::min<int64_t>(out_n, cap / bytes);
+          L.named["priv16"] = 0;
+          CompiledKernel& ks = c.kernel(assemble_source(st.glue, "permute", {{"PERMUTE_SAMPLE", "1"}}), "acc_permute_sample", 1024, 0);
+          L.launch(ks, 1, 1024, 0);
+          const int64_t words16 = (out_n + 1) / 2;
+          const size_t smem = (size_t)words16 * 4;
+          std::map<std::string, std::string> var = {{"PERMUTE_SMEM16", "1"}, {"PERMUTE_THREADS", "1024"}, {"PERMUTE_CHOICE_ID", "1"}};
           CompiledKernel& k = c.kernel(assemble_source(st.glue, "permute", var), "acc_permute", 1024, smem);
           if (smem > 48 * 1024) c.check(c.drv.FuncSetAttribute(k.fn, CU_FUNC_ATTRIBUTE_MAX_DYNAMIC_SHARED_SIZE_BYTES, (int)smem), "cuFuncSetAttribute");
-          L.named["priv"] = words;
+          L.named["priv16"] = words16;
           const int64_t work = (total + 3) / 4;
           int64_t grid = std::min<int64_t>((work + 1023) / 1024, (int64_t)c.sm_count);
           L.launch(k, std::max<int64_t>(grid, 1), 1024, smem);
-          break;
+          // (falls through to the partial 32-bit copy, which runs only if the sample chose it)
         }
         if (atomic && !no_priv && out_n > 0 && total >= 8 * out_n && total >= (1 << 16)) {
           // CTA-private copy of the first `priv` target elements in shared memory
@@ -1103,10 +1069,12 @@ void Program::exec_kernel_node(const Node& n, Env& env_ref) {
         std::vector<int64_t> osh = ext[0];
         for (size_t a = 1; a < ext.size(); ++a)
           for (int d = 0; d < rank; ++d) osh[d] = std::min(osh[d], ext[a][d]);  // Shape.hs:81-91
-        DevArrayP out = c.new_array(n.elt, osh);
+        if (window && (rank != 2 || window->out->shape != osh || window->out->elt != n.elt || window->lo < 0 || window->hi > osh[0] || window->lo > window->hi))
+          throw Error(B200_ERR_ARG, "row window: the output array does not have the shape and type of the stencil's result, or the rows lie outside it");
+        DevArrayP out = window ? window->out : c.new_array(n.elt, osh);
         L.outs = {out};
         env[n.outs[0]] = out;
-        if (size_of(osh) == 0) break;
+        if (size_of(osh) == 0 || (window && window->lo == window->hi)) break;
         for (size_t a = 0; a < ext.size(); ++a) L.bind_delayed("D" + std::to_string(a), ext[a], a);
         int64_t o[3] = {1, 1, 1};
         for (int d = 0; d < rank; ++d) o[d + 3 - rank] = osh[d];
@@ -1118,11 +1086,14 @@ void Program::exec_kernel_node(const Node& n, Env& env_ref) {
         L.named["tiles1"] = tiles1;
         L.named["tiles2"] = tiles2;
         L.named["vec"] = (o[2] % 4 == 0 && out->aligned16()) ? 1 : 0;
-        if (rank == 2 && o[1] < 2000000000 && o[2] < 2000000000 && !getenv("ACCELERATE_B200_STENCIL_SMEM")) {
+        const int64_t row0 = window ? window->lo : 0, row1 = window ? window->hi : o[1];
+        L.named["row0"] = row0;
+        L.named["row1"] = row1;
+        if (rank == 2 && o[1] < 2000000000 && o[2] < 2000000000 && (window || !getenv("ACCELERATE_B200_STENCIL_SMEM"))) {
           // register-window kernel: warp tasks of 128 columns x ST2_ROWS (32) rows
           const Stencil2dShape shp = stencil2d_shape();
           const int warps = shp.warps, rows = shp.rows;
-          const int64_t strips = (o[2] + 119) / 120, rowblocks = (o[1] + rows - 1) / rows;  // 120 output columns per warp
+          const int64_t strips = (o[2] + 119) / 120, rowblocks = (row1 - row0 + rows - 1) / rows;  // 120 output columns per warp
           L.named["tiles1"] = rowblocks;
           L.named["tiles2"] = strips;
           const std::map<std::string, std::string> var = stencil2d_variant();

@@ -26,8 +26,6 @@ struct Driver {
   CUresult (*ModuleGetGlobal)(CUdeviceptr*, size_t*, CUmodule, const char*) = nullptr;
   CUresult (*LaunchKernel)(CUfunction, unsigned, unsigned, unsigned, unsigned, unsigned, unsigned, unsigned, CUstream, void**,
                            void**) = nullptr;
-  CUresult (*LaunchKernelEx)(const CUlaunchConfig*, CUfunction, void**, void**) = nullptr;
-  CUresult (*OccupancyMaxActiveClusters)(int*, CUfunction, const CUlaunchConfig*) = nullptr;
   CUresult (*FuncSetAttribute)(CUfunction, CUfunction_attribute, int) = nullptr;
   CUresult (*OccupancyMaxActiveBlocksPerMultiprocessor)(int*, CUfunction, int, size_t) = nullptr;
   CUresult (*GetErrorString)(CUresult, const char**) = nullptr;
@@ -84,7 +82,8 @@ struct Ctx {
   std::mutex mu;
   std::map<uint64_t, DevArrayP> arrays;
   uint64_t next_id = 1;
-  // device words: [0] error status, [1] fold ticket counter, [2] scan ticket counter
+  std::map<uint64_t, DevArrayP> table;   // device copies of host arrays by the host array's unique id
+  // device words: [0] error status, [1] fold ticket counter, [2] scan ticket counter, [3] scan exit counter, [4] permute kernel choice
   int* d_words = nullptr;
   // scan descriptors (persistent, epoch-tagged)
   void* scan_scratch = nullptr;
@@ -118,8 +117,13 @@ struct Program {
   void analyse_liveness();
   void upload_constants();                           // needs ctx; called once by b200_program_load
   void run(const std::vector<DevArrayP>& inputs, std::vector<DevArrayP>& outputs);
+  // A program that is one rank-2 stencil (or stencil2) node: produce rows [row_lo, row_hi) of its
+  // result in the existing array `out` (same shape and element type as the result).
+  void run_rows(const std::vector<DevArrayP>& inputs, const DevArrayP& out, int64_t row_lo, int64_t row_hi);
 
  private:
+  struct Window { DevArrayP out; int64_t lo, hi; };
+  const Window* window = nullptr;
   typedef std::map<std::string, DevArrayP> Env;
   void liveness_of(const std::vector<Node>& nodes, const std::vector<std::string>& keep);
   void exec(const std::vector<Node>& nodes, Env& env);
@@ -135,3 +139,7 @@ bool scan_ring_aligned(int elt_bytes, int64_t m, int64_t rows, bool right);
 std::vector<std::pair<std::string, std::map<std::string, std::string>>> default_variants(const Node& n, const Glue& g);
 
 }  // namespace accb200
+
+// the handles of the C ABI
+struct b200_ctx { accb200::Ctx c; };
+struct b200_program { accb200::Program p; };

@@ -7,11 +7,8 @@
 //                     fire-and-forget reduction (red.global), optionally staged
 //                     through a CTA-private copy of the first `priv` target
 //                     elements in shared memory when the target is small
-//                     (PERMUTE_SMEM), or through a copy of the target that is
-//                     spread over the shared memories of a thread-block cluster
-//                     when it fits there but not in one CTA (PERMUTE_CLUSTER:
-//                     element b lives in CTA b mod C at word b div C; updates
-//                     travel as shared::cluster reductions, never through L2);
+//                     (PERMUTE_SMEM); for (+) on 32-bit integers a private copy of
+//                     16-bit fields covers targets twice that size (PERMUTE_SMEM16);
 //   PERMUTE_CAS       any other f on a 32/64-bit scalar: compare-and-swap loop;
 //   PERMUTE_STORE     `permute const`: plain store (targets assumed unique);
 //   PERMUTE_LOCK      everything else (tuples, narrow types): one spin lock per
@@ -106,81 +103,56 @@ __device__ __forceinline__ PERMUTE_T permute_identity() {
 }
 #endif
 
-#ifndef PERMUTE_CLUSTER
-#define PERMUTE_CLUSTER 0
-#endif
 #ifndef PERMUTE_SMEM16
 #define PERMUTE_SMEM16 0
 #endif
-#if PERMUTE_SMEM || PERMUTE_CLUSTER || PERMUTE_SMEM16
+#ifndef PERMUTE_UNIT
+#define PERMUTE_UNIT 0
+#endif
+#if PERMUTE_SMEM || PERMUTE_SMEM16
 extern __shared__ __align__(16) unsigned char permute_smem_raw[];
 #endif
 
 #if PERMUTE_SMEM16
-// (+) on a 32-bit integer target of up to twice as many elements as a CTA has shared-memory words:
-// the CTA keeps the LOW 16 bits of its contribution to every element, two elements per word, and
-// sends everything else straight to the target with red.global:
+// (+) on a 32-bit integer target of up to twice as many elements as a CTA has shared-memory words.
+// The CTA has a private copy of EVERY element, wherever the frequent ones lie: it keeps the LOW 16
+// bits of its contribution, two elements per word, and sends everything else straight to the
+// target with red.global:
 //   * the high 16 bits of an addend (zero for counts and other small addends);
 //   * 65536 whenever a 16-bit field wraps.  Every update is one atomicAdd on the word, whose return
 //     value shows exactly whether the addressed field wrapped; a wrap of the lower field also
 //     carries 1 into the upper field, which is taken out again with a second atomic (and if that
 //     carry or its removal wraps the upper field, that too is seen in the returned value and
 //     compensated).  All arithmetic is modulo 2^32 on the target, like the reference's Int32/Word32.
-// At the end the fields are added to the target (permute_flush16).
-__device__ __forceinline__ void permute_add16(const Params& p, i64 dst, u32 v) {
-  u32* sm = reinterpret_cast<u32*>(permute_smem_raw);
+// At the end the fields are added to the target.
+// The update is split in two so that a thread can have the atomics of all its elements in flight
+// before it looks at any of their results: permute_issue16 performs the atomic and hands back the
+// word it found, permute_settle16 does what that word demands.
+__device__ __forceinline__ u32* permute_fields16(const Params& p) { (void)p; return reinterpret_cast<u32*>(permute_smem_raw); }
+__device__ __forceinline__ u32 permute_issue16(const Params& p, i64 dst, u32 v) {
+  const i64 f = dst;
+  const u32 lo = v & 0xffffu;
+  return atomicAdd(permute_fields16(p) + (f >> 1), (f & 1) ? (lo << 16) : lo);
+}
+__device__ __forceinline__ void permute_settle16(const Params& p, i64 dst, u32 v, u32 old) {
+  const i64 f = dst;
   u32* out = reinterpret_cast<u32*>(p.out0_l0);
   const u32 hi = v & 0xffff0000u, lo = v & 0xffffu;
   if (hi) atomicAdd(out + dst, hi);
-  if (!lo) return;
-  u32* w = sm + (dst >> 1);
-  if (dst & 1) {
-    const u32 old = atomicAdd(w, lo << 16);
+  if (f & 1) {
     if (((old >> 16) + lo) >> 16) atomicAdd(out + dst, 65536u);
-  } else {
-    const u32 old = atomicAdd(w, lo);
-    if (((old & 0xffffu) + lo) >> 16) {
-      atomicAdd(out + dst, 65536u);
-      if ((old >> 16) == 0xffffu) atomicAdd(out + dst + 1, 65536u);        // the carry wrapped the upper field
-      const u32 old2 = atomicAdd(w, 0xffff0000u);                          // take the carry out again
-      if ((old2 >> 16) == 0u) atomicAdd(out + dst + 1, 0u - 65536u);       // ... which wrapped it downwards
-    }
+  } else if (((old & 0xffffu) + lo) >> 16) {
+    atomicAdd(out + dst, 65536u);
+    if ((old >> 16) == 0xffffu) atomicAdd(out + dst + 1, 65536u);        // the carry wrapped the upper field
+    const u32 old2 = atomicAdd(permute_fields16(p) + (f >> 1), 0xffff0000u);   // take the carry out again
+    if ((old2 >> 16) == 0u) atomicAdd(out + dst + 1, 0u - 65536u);       // ... which wrapped it downwards
   }
+}
+__device__ __forceinline__ void permute_add16(const Params& p, i64 dst, u32 v) {
+  permute_settle16(p, dst, v, permute_issue16(p, dst, v));
 }
 #endif
 
-#if PERMUTE_CLUSTER
-// PERMUTE_CLUSTER = number of CTAs per cluster (a power of two), PERMUTE_CLUSTER_LOG2 its logarithm.
-__device__ __forceinline__ u32 permute_cluster_rank() { u32 r; asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r)); return r; }
-__device__ __forceinline__ void permute_cluster_sync() {
-  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
-}
-// reduction into word `word` of the target copy held by CTA `owner` of this cluster
-__device__ __forceinline__ void permute_cluster_red(u32 owner, u32 word, PERMUTE_T v) {
-  const u32 local = (u32)__cvta_generic_to_shared(permute_smem_raw) + word * (u32)sizeof(PERMUTE_T);
-  u32 remote;
-  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local), "r"(owner));
-#if PERMUTE_MODE == PERMUTE_ATOMIC_ADD && PERMUTE_FLOAT
-  asm volatile("red.relaxed.cluster.shared::cluster.add.f32 [%0], %1;" ::"r"(remote), "f"(v) : "memory");
-#elif PERMUTE_MODE == PERMUTE_ATOMIC_ADD
-  asm volatile("red.relaxed.cluster.shared::cluster.add.u32 [%0], %1;" ::"r"(remote), "r"(permute_bits(v)) : "memory");
-#elif PERMUTE_MODE == PERMUTE_ATOMIC_MIN && PERMUTE_SIGNED
-  asm volatile("red.relaxed.cluster.shared::cluster.min.s32 [%0], %1;" ::"r"(remote), "r"((int)v) : "memory");
-#elif PERMUTE_MODE == PERMUTE_ATOMIC_MIN
-  asm volatile("red.relaxed.cluster.shared::cluster.min.u32 [%0], %1;" ::"r"(remote), "r"(permute_bits(v)) : "memory");
-#elif PERMUTE_MODE == PERMUTE_ATOMIC_MAX && PERMUTE_SIGNED
-  asm volatile("red.relaxed.cluster.shared::cluster.max.s32 [%0], %1;" ::"r"(remote), "r"((int)v) : "memory");
-#elif PERMUTE_MODE == PERMUTE_ATOMIC_MAX
-  asm volatile("red.relaxed.cluster.shared::cluster.max.u32 [%0], %1;" ::"r"(remote), "r"(permute_bits(v)) : "memory");
-#elif PERMUTE_MODE == PERMUTE_ATOMIC_AND
-  asm volatile("red.relaxed.cluster.shared::cluster.and.b32 [%0], %1;" ::"r"(remote), "r"(permute_bits(v)) : "memory");
-#elif PERMUTE_MODE == PERMUTE_ATOMIC_OR
-  asm volatile("red.relaxed.cluster.shared::cluster.or.b32 [%0], %1;" ::"r"(remote), "r"(permute_bits(v)) : "memory");
-#else
-  asm volatile("red.relaxed.cluster.shared::cluster.xor.b32 [%0], %1;" ::"r"(remote), "r"(permute_bits(v)) : "memory");
-#endif
-}
-#endif
 
 __device__ __forceinline__ void permute_update(const Params& p, i64 dst, const elt_t& v) {
 #if PERMUTE_IS_ATOMIC
@@ -190,13 +162,6 @@ __device__ __forceinline__ void permute_update(const Params& p, i64 dst, const e
 #endif
 #if PERMUTE_SMEM
   if (dst < p.priv) { permute_atomic(reinterpret_cast<PERMUTE_T*>(permute_smem_raw) + dst, v.l0); return; }
-#endif
-#if PERMUTE_CLUSTER
-  // p.priv = words of the target copy per CTA: elements below priv * C are on chip
-  if ((dst >> PERMUTE_CLUSTER_LOG2) < p.priv) {
-    permute_cluster_red((u32)dst & (PERMUTE_CLUSTER - 1), (u32)(dst >> PERMUTE_CLUSTER_LOG2), v.l0);
-    return;
-  }
 #endif
   permute_atomic(p.out0_l0 + dst, v.l0);
 #elif PERMUTE_MODE == PERMUTE_CAS
@@ -238,27 +203,56 @@ __device__ __forceinline__ void permute_elem(const Params& p, const pelem_t& e) 
   }
 }
 
+// Which of two kernels handles a target that the 32-bit private copy covers only in part?  The copy
+// of the first `priv` elements is the faster one as long as almost every update lands inside it;
+// updates outside go to the target one by one, and a frequent element out there serialises them.
+// The copy of 16-bit fields covers everything but pays for updates whose result it must inspect.
+// acc_permute_sample looks at 65 536 source elements spread over the input and writes 1 to
+// *choice if more than 1 in 64 of their targets lie outside the first `priv` elements, else 0; both
+// kernels are launched behind it and the one that is not chosen returns at once (no host round trip).
+#if defined(PERMUTE_SAMPLE) && PERMUTE_SAMPLE
+extern "C" __global__ void __launch_bounds__(1024) acc_permute_sample(const Params p) {
+  __shared__ u32 outside;
+  const i64 n = p.n, inner = P_INNER;
+  if (threadIdx.x == 0) outside = 0u;
+  __syncthreads();
+  const i64 samples = n < 65536 ? n : 65536;
+  const i64 step = n / samples;
+  u32 mine = 0;
+  for (i64 k = threadIdx.x; k < samples; k += 1024) {
+    const i64 i = k * step;
+    i64 row = 0, j = i;
+    if (inner != n) { row = i / inner; j = i - row * inner; }
+    const pelem_t e = P_get(p, row, j);
+    if (e.l0 != 0 && e.l1 >= p.priv) ++mine;
+  }
+  atomicAdd(&outside, mine);
+  __syncthreads();
+  if (threadIdx.x == 0) *reinterpret_cast<int*>(p.choice) = (i64)outside * 64 > samples ? 1 : 0;
+}
+#endif
+#ifndef PERMUTE_CHOICE_ID
+#define PERMUTE_CHOICE_ID 0
+#endif
+
 extern "C" __global__ void __launch_bounds__(PERMUTE_THREADS) acc_permute(const Params p) {
+  if (p.choice != 0 && *reinterpret_cast<const volatile int*>(p.choice) != PERMUTE_CHOICE_ID) return;
   const i64 n = p.n;
   const i64 inner = P_INNER;
   const i64 tid = (i64)blockIdx.x * PERMUTE_THREADS + threadIdx.x;
   const i64 nthreads = (i64)gridDim.x * PERMUTE_THREADS;
 #if PERMUTE_SMEM16
   {
-    // p.priv = number of 32-bit words (two target elements each)
+    // p.priv16 words of two 16-bit fields each
     u32* sm16 = reinterpret_cast<u32*>(permute_smem_raw);
-    for (i64 b = threadIdx.x; b < p.priv; b += PERMUTE_THREADS) sm16[b] = 0u;
+    for (i64 b = threadIdx.x; b < p.priv16; b += PERMUTE_THREADS) sm16[b] = 0u;
     __syncthreads();
   }
 #endif
-#if PERMUTE_SMEM || PERMUTE_CLUSTER
+#if PERMUTE_SMEM
   PERMUTE_T* sm = reinterpret_cast<PERMUTE_T*>(permute_smem_raw);
   for (i64 b = threadIdx.x; b < p.priv; b += PERMUTE_THREADS) sm[b] = permute_identity();
-#if PERMUTE_CLUSTER
-  permute_cluster_sync();     // no update may reach a CTA that is still clearing its part
-#else
   __syncthreads();
-#endif
 #endif
   i64 done = 0;
   if (p.vec) {
@@ -274,11 +268,34 @@ extern "C" __global__ void __launch_bounds__(PERMUTE_THREADS) acc_permute(const 
         if (inner != n) { row = i / inner; j = i - row * inner; }
         P_get4(p, row, j, x[u]);
       }
+#if PERMUTE_SMEM16
+      u32 found[PERMUTE_UNROLL][4];
+#pragma unroll
+      for (int u = 0; u < PERMUTE_UNROLL; ++u) {
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          const pelem_t& e = x[u][k];
+          if (e.l0 != 0 && (u64)e.l1 < (u64)p.out_n) found[u][k] = permute_issue16(p, e.l1, permute_bits(P_value(e).l0));
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < PERMUTE_UNROLL; ++u) {
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          const pelem_t& e = x[u][k];
+          if (e.l0 != 0) {
+            if ((u64)e.l1 >= (u64)p.out_n) acc_fail(p.err, 1003 /* index out of bounds */);
+            else permute_settle16(p, e.l1, permute_bits(P_value(e).l0), found[u][k]);
+          }
+        }
+      }
+#else
 #pragma unroll
       for (int u = 0; u < PERMUTE_UNROLL; ++u) {
 #pragma unroll
         for (int k = 0; k < 4; ++k) permute_elem(p, x[u][k]);
       }
+#endif
     }
     for (; v < nv; v += nthreads) {
       const i64 i = v << 2;
@@ -306,24 +323,15 @@ extern "C" __global__ void __launch_bounds__(PERMUTE_THREADS) acc_permute(const 
 #if PERMUTE_SMEM16
   __syncthreads();
   {
-    const u32* sm16 = reinterpret_cast<const u32*>(permute_smem_raw);
+    const u32* sm16 = permute_fields16(p);
     u32* out = reinterpret_cast<u32*>(p.out0_l0);
-    for (i64 b = threadIdx.x; b < p.priv; b += PERMUTE_THREADS) {
+    for (i64 b = threadIdx.x; b < p.priv16; b += PERMUTE_THREADS) {
       const u32 w = sm16[b];
-      if (w & 0xffffu) atomicAdd(out + 2 * b, w & 0xffffu);
-      if ((w >> 16) && 2 * b + 1 < p.out_n) atomicAdd(out + 2 * b + 1, w >> 16);
-    }
-  }
-#endif
-#if PERMUTE_CLUSTER
-  permute_cluster_sync();     // every CTA of the cluster has sent its last update
-  {
-    const i64 rank = permute_cluster_rank();
-    for (i64 b = threadIdx.x; b < p.priv; b += PERMUTE_THREADS) {
-      const i64 dst = (b << PERMUTE_CLUSTER_LOG2) + rank;
-      const PERMUTE_T v = sm[b];
-      if (dst < p.out_n && permute_bits(v) != permute_bits(permute_identity())) permute_atomic(p.out0_l0 + dst, v);
+      const i64 dst = 2 * b;
+      if (w & 0xffffu) atomicAdd(out + dst, w & 0xffffu);
+      if ((w >> 16) && dst + 1 < p.out_n) atomicAdd(out + dst + 1, w >> 16);
     }
   }
 #endif
 }
+

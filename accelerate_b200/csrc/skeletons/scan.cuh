@@ -92,6 +92,26 @@ __device__ __forceinline__ u32 scan_desc_load(i64 base, i64 idx, SCAN_T& v) {
   memcpy(&v, &bits, sizeof(SCAN_T));
   return (u32)(w >> 32);
 }
+#elif defined(SCAN_DESC_SPLIT) && SCAN_DESC_SPLIT
+// 8-byte values as two independent 8-byte words {status, low half} {status, high half}: each word is
+// written and read with one 64-bit access; a reader takes the descriptor only if both words carry
+// the same status (a torn view reads as "not there yet").
+__device__ __forceinline__ void scan_desc_store(i64 base, i64 idx, u32 status, SCAN_T v) {
+  u64 bits = 0;
+  memcpy(&bits, &v, sizeof(SCAN_T));
+  u64* w = reinterpret_cast<u64*>(base) + 2 * idx * SCAN_DESC_STRIDE;
+  asm volatile("st.relaxed.gpu.global.u64 [%0], %1;" ::"l"(w), "l"(((u64)status << 32) | (bits & 0xffffffffull)) : "memory");
+  asm volatile("st.relaxed.gpu.global.u64 [%0], %1;" ::"l"(w + 1), "l"(((u64)status << 32) | (bits >> 32)) : "memory");
+}
+__device__ __forceinline__ u32 scan_desc_load(i64 base, i64 idx, SCAN_T& v) {
+  u64 a, b;
+  const u64* w = reinterpret_cast<const u64*>(base) + 2 * idx * SCAN_DESC_STRIDE;
+  asm volatile("ld.relaxed.gpu.global.u64 %0, [%1];" : "=l"(a) : "l"(w) : "memory");
+  asm volatile("ld.relaxed.gpu.global.u64 %0, [%1];" : "=l"(b) : "l"(w + 1) : "memory");
+  const u64 bits = (a & 0xffffffffull) | (b << 32);
+  memcpy(&v, &bits, sizeof(SCAN_T));
+  return (u32)(a >> 32) == (u32)(b >> 32) ? (u32)(a >> 32) : 0u;
+}
 #else
 // 16-byte descriptor {value bits, status}: one aligned 128-bit access
 __device__ __forceinline__ void scan_desc_store(i64 base, i64 idx, u32 status, SCAN_T v) {
@@ -155,10 +175,12 @@ __device__ __forceinline__ i64 scan_phys(i64 n, i64 q) {
 }
 
 // Everything after the tile's elements are in registers: local scans, aggregate,
-// look-back, per-thread prefixes, stores.
-template <bool FULL>
+// look-back, per-thread prefixes, stores.  With GIVEN the caller already knows the tile's exclusive
+// prefix (*given, if has_given): no descriptor is read or written.
+template <bool FULL, bool GIVEN>
 __device__ __forceinline__ void scan_tile_body(const Params& p, const i64 T, const i64 row, const i64 tt, elt_t (&item)[SCAN_ROUNDS][4],
-                                               bool (&valid)[SCAN_ROUNDS][4], elt_t* sm_v, int* sm_h, elt_t* sm_excl, int* sm_flag) {
+                                               bool (&valid)[SCAN_ROUNDS][4], elt_t* sm_v, int* sm_h, elt_t* sm_excl, int* sm_flag,
+                                               const elt_t* given, bool has_given) {
   const i64 n = p.n;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const i64 tile_q0 = tt * SCAN_TILE;
@@ -222,7 +244,9 @@ __device__ __forceinline__ void scan_tile_body(const Params& p, const i64 T, con
     elt_t* d_incl = reinterpret_cast<elt_t*>(p.incl);
     const u32 epoch = (u32)p.epoch;
     int failed = 0;
-    if (tt == 0) {
+    if (GIVEN) {
+      if (has_given) { excl = *given; hexcl = true; }
+    } else if (tt == 0) {
 #if ACC_SEEDED
       excl = F_seed(p);
       hexcl = true;
@@ -316,13 +340,15 @@ __device__ __forceinline__ void scan_tile_body(const Params& p, const i64 T, con
         elt_t inc = excl;
         bool hinc = hexcl;
         scan_join(p, inc, hinc, agg, hagg);
+        if (!GIVEN) {
 #if SCAN_PACKED
-        scan_desc_store(p.status, T, (epoch << 2) | SCAN_ST_PREFIX, inc.l0);
+          scan_desc_store(p.status, T, (epoch << 2) | SCAN_ST_PREFIX, inc.l0);
 #else
-        if (hinc) d_incl[T] = inc;
-        __threadfence();
-        status[T] = (epoch << 2) | SCAN_ST_PREFIX;
+          if (hinc) d_incl[T] = inc;
+          __threadfence();
+          status[T] = (epoch << 2) | SCAN_ST_PREFIX;
 #endif
+        }
 #if ACC_SCAN_MODE != 0
         if (tt == p.tiles_per_row - 1) {
           // the row's total (seed included)
@@ -404,9 +430,9 @@ __device__ __forceinline__ void scan_tile_body(const Params& p, const i64 T, con
   }
 }
 
-template <bool FULL>
+template <bool FULL, bool GIVEN>
 __device__ __forceinline__ void scan_tile(const Params& p, const i64 T, const i64 row, const i64 tt, elt_t* sm_v, int* sm_h,
-                                          elt_t* sm_excl, int* sm_flag) {
+                                          elt_t* sm_excl, int* sm_flag, const elt_t* given, bool has_given) {
   const i64 n = p.n;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const i64 tile_q0 = tt * SCAN_TILE;
@@ -438,7 +464,7 @@ __device__ __forceinline__ void scan_tile(const Params& p, const i64 T, const i6
       }
     }
   }
-  scan_tile_body<FULL>(p, T, row, tt, item, valid, sm_v, sm_h, sm_excl, sm_flag);
+  scan_tile_body<FULL, GIVEN>(p, T, row, tt, item, valid, sm_v, sm_h, sm_excl, sm_flag, given, has_given);
 }
 
 extern "C" __global__ void __launch_bounds__(SCAN_THREADS, SCAN_MIN_BLOCKS) acc_scan(const Params p) {
@@ -458,8 +484,8 @@ extern "C" __global__ void __launch_bounds__(SCAN_THREADS, SCAN_MIN_BLOCKS) acc_
   const i64 row = T / p.tiles_per_row;
   const i64 tt = T - row * p.tiles_per_row;
   const bool full = (tt + 1) * SCAN_TILE <= p.n;
-  if (full) scan_tile<true>(p, T, row, tt, sm_v, sm_h, &sm_excl, sm_flag);
-  else scan_tile<false>(p, T, row, tt, sm_v, sm_h, &sm_excl, sm_flag);
+  if (full) scan_tile<true, false>(p, T, row, tt, sm_v, sm_h, &sm_excl, sm_flag, nullptr, false);
+  else scan_tile<false, false>(p, T, row, tt, sm_v, sm_h, &sm_excl, sm_flag, nullptr, false);
 }
 
 // ---------------------------------------------------------------------------------
@@ -477,7 +503,8 @@ extern "C" __global__ void __launch_bounds__(SCAN_THREADS, SCAN_MIN_BLOCKS) acc_
 // Requirements (checked by the host): one scalar leaf (SCAN_PACKED), exactly one stream
 // leaf of the same size, fast layout, in_vec and out_vec.  Partial tiles (the last of a
 // row) are handled by scan_tile<false> inside the same kernel.
-// Extra named parameters: total_tiles, gstatus, groups_per_row.
+// Extra named parameters: total_tiles, total_batches, batches_per_row, gstatus, groups_per_row
+// (`status` and `gstatus` hold one descriptor per batch and per group of batches).
 // ---------------------------------------------------------------------------------
 #if defined(SCAN_RING) && SCAN_RING
 #ifndef SCAN_SLOTS
@@ -541,11 +568,22 @@ template <class T> __device__ __forceinline__ void ring_stv(T* p, T v) { *reinte
 #define RING_ACT_FIN 2
 #define RING_ACT_EXIT 4
 
-// The partial tile at the end of a row is rare and register-hungry (it carries its own look-back):
-// kept out of line so that it does not set the register budget of the common path.
-__device__ __noinline__ void ring_partial_tile(const Params& p, i64 T, i64 row, i64 tt, elt_t* sm_v, int* sm_h, elt_t* sm_excl, int* sm_flag) {
-  scan_tile<false>(p, T, row, tt, sm_v, sm_h, sm_excl, sm_flag);
+// The partial tile at the end of a row is rare and register-hungry: kept out of line so that it
+// does not set the register budget of the common path.  Its exclusive prefix is handed in.
+__device__ __noinline__ void ring_partial_tile(const Params& p, i64 T, i64 row, i64 tt, elt_t* sm_v, int* sm_h, elt_t* sm_excl, int* sm_flag,
+                                               const elt_t* given, bool has_given) {
+  scan_tile<false, true>(p, T, row, tt, sm_v, sm_h, sm_excl, sm_flag, given, has_given);
 }
+
+// Tickets hand out BATCHES of RING_BATCH consecutive tiles of a row.  Look-back descriptors
+// describe batches: a CTA chains the tiles of its batch through shared memory (the exclusive
+// prefix of tile j+1 is that of tile j combined with tile j's aggregate) and walks the global
+// descriptors once per batch.  That divides the polling traffic and the number of descriptors by
+// RING_BATCH; the price is that a batch's aggregate is published when its last tile has arrived.
+#ifndef RING_BATCH
+#define RING_BATCH SCAN_SLOTS
+#endif
+#define RING_VOID ((i64)-2)            // position past the last tile of its row (rows need not be whole batches)
 
 extern "C" __global__ void __launch_bounds__(RING_THREADS, SCAN_MIN_BLOCKS) acc_scan_ring(const Params p) {
   __shared__ elt_t sm_v[SCAN_WARPS];
@@ -554,44 +592,55 @@ extern "C" __global__ void __launch_bounds__(RING_THREADS, SCAN_MIN_BLOCKS) acc_
   __shared__ int sm_flag1[2];
   __shared__ __align__(8) u64 full_bar[SCAN_SLOTS];
   // data slots: full_bar, slot_uses; ring positions (index pos % RING_META): everything else
-  __shared__ i64 slot_tile[RING_META], slot_pos[RING_META];
+  __shared__ i64 slot_tile[RING_META], slot_pos[RING_META], slot_batch[RING_META];
   __shared__ u32 slot_parity[RING_META], slot_uses[SCAN_SLOTS];
   __shared__ int slot_direct[RING_META], slot_state[RING_META], slot_hexcl[RING_META];
   __shared__ elt_t slot_agg[RING_META], slot_excl[RING_META];
   __shared__ int ctl_act, ctl_act2, sh_fail;   // thread 0's verdicts after the two waits of an iteration
+  __shared__ i64 cur_batch;
   __shared__ elt_t red_v[2][RING_RED_WARPS];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const i64 n = p.n;
   const i64 total_tiles = p.total_tiles;
+  const i64 total_batches = p.total_batches;
   const u32 epoch = (u32)p.epoch;
   unsigned* counter = reinterpret_cast<unsigned*>(p.counter);
   unsigned* exits = counter + 1;
 
-  // worker thread 0: next ticket for ring position `pos`, whose data go to slot pos % SCAN_SLOTS
+  // worker thread 0: the tile of ring position `pos` (tile pos % RING_BATCH of the CTA's current
+  // batch; a new batch is drawn at every multiple of RING_BATCH); its data go to slot pos % SCAN_SLOTS
   auto fetch = [&](i64 pos) {
-    const int s = (int)(pos % SCAN_SLOTS), m = (int)(pos % RING_META);
-    const i64 T = (i64)atomicAdd(counter, 1u);
-    slot_tile[m] = T;
+    const int s = (int)(pos % SCAN_SLOTS), m = (int)(pos % RING_META), j = (int)(pos % RING_BATCH);
+    if (j == 0) cur_batch = (i64)atomicAdd(counter, 1u);
+    const i64 K = cur_batch;
+    i64 T = total_tiles;                                   // past the end: every role leaves its loop
+    slot_batch[m] = K;
     slot_direct[m] = 1;
     slot_state[m] = RING_LOADING;
-    if (T < total_tiles) {
-      const i64 row = T / p.tiles_per_row;
-      const i64 tt = T - row * p.tiles_per_row;
-      const i64 q0 = tt * SCAN_TILE;
-      if (q0 + SCAN_TILE <= n) {
-        slot_direct[m] = 0;
-        slot_parity[m] = slot_uses[s] & 1u;
-        slot_uses[s] += 1;
+    if (K < total_batches) {
+      const i64 row = K / p.batches_per_row;
+      const i64 tt = (K - row * p.batches_per_row) * RING_BATCH + j;
+      if (tt >= p.tiles_per_row) {
+        T = RING_VOID;
+      } else {
+        T = row * p.tiles_per_row + tt;
+        const i64 q0 = tt * SCAN_TILE;
+        if (q0 + SCAN_TILE <= n) {
+          slot_direct[m] = 0;
+          slot_parity[m] = slot_uses[s] & 1u;
+          slot_uses[s] += 1;
 #if ACC_RIGHT
-        const i64 src = row * n + (n - q0 - SCAN_TILE);
+          const i64 src = row * n + (n - q0 - SCAN_TILE);
 #else
-        const i64 src = row * n + q0;
+          const i64 src = row * n + q0;
 #endif
-        unsigned char* base = scan_ring_smem + (size_t)s * RING_SLOT_BYTES;
-        ring_mbar_expect(&full_bar[s], (u32)RING_SLOT_BYTES);
-        D0_BULK_ISSUE(base, &full_bar[s], src)
+          unsigned char* base = scan_ring_smem + (size_t)s * RING_SLOT_BYTES;
+          ring_mbar_expect(&full_bar[s], (u32)RING_SLOT_BYTES);
+          D0_BULK_ISSUE(base, &full_bar[s], src)
+        }
       }
     }
+    slot_tile[m] = T;
     __threadfence_block();
     ring_stv(&slot_pos[m], pos);          // reducers and the look-back warp may now look at the entry
   };
@@ -601,7 +650,9 @@ extern "C" __global__ void __launch_bounds__(RING_THREADS, SCAN_MIN_BLOCKS) acc_
     for (int m = 0; m < RING_META; ++m) { slot_pos[m] = -1; slot_tile[m] = total_tiles; slot_direct[m] = 1; slot_state[m] = RING_DONE; }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     ctl_act = 0;
+    ctl_act2 = 0;
     sh_fail = 0;
+    cur_batch = total_batches;
   }
   __syncthreads();
   if (tid == 0)
@@ -609,137 +660,173 @@ extern "C" __global__ void __launch_bounds__(RING_THREADS, SCAN_MIN_BLOCKS) acc_
   __syncthreads();
 
   if (warp >= SCAN_WARPS + RING_RED_WARPS) {
-    // ================= look-back warps =================================================
-    // Hierarchical walk: tiles of a row are grouped by RING_GROUP.  Phase OWN reads the earlier
-    // tiles of the own group; phase GROUPS reads 32 group descriptors per step (aggregate or
-    // inclusive prefix of a whole group); phase COMPUTE summarises a group nobody has summarised
-    // yet from its tile descriptors and publishes the summary for every later walker.
+    // ================= look-back warp ==================================================
+    // One walk per batch, started as soon as the batch is drawn (its own data need not have
+    // arrived).  Hierarchical: batches of a row are grouped by RING_GROUP.  Phase OWN reads the
+    // earlier batches of the own group; phase GROUPS reads 32 group descriptors per step (aggregate
+    // or inclusive prefix of a whole group); phase COMPUTE summarises a group nobody has summarised
+    // yet from its batch descriptors and publishes the summary for every later walker.  The tiles of
+    // the batch are then resolved in order from the batch's prefix and their aggregates.
     int lb_failed = 0;
-    for (i64 r = warp - SCAN_WARPS - RING_RED_WARPS;; r += SCAN_LB_WARPS) {
-      const int s = (int)(r % RING_META);
+    for (i64 r0 = 0; !lb_failed; r0 += RING_BATCH) {
+      const int m0 = (int)(r0 % RING_META);
       i64 spins = 0;
-      int failed = 0;
-      while (ring_ldv(&slot_pos[s]) != r) {
-        if (++spins > p.spin_limit || ring_ldv(&sh_fail)) { failed = 1; break; }
+      while (ring_ldv(&slot_pos[m0]) != r0) {
+        if (++spins > p.spin_limit || ring_ldv(&sh_fail)) { lb_failed = 1; break; }
         __nanosleep(40);                             // leave the issue slots to the workers
       }
-      if (failed) { lb_failed = 1; break; }
+      if (lb_failed) break;
       __threadfence_block();
-      const i64 T = slot_tile[s];
-      if (T >= total_tiles) break;
-      if (slot_direct[s]) continue;                 // partial tile: the finishers do it start to finish
-      int st0;
-      spins = 0;
-      while ((st0 = ring_ldv(&slot_state[s])) < RING_SCANNED) {
-        if (++spins > p.spin_limit || ring_ldv(&sh_fail)) { failed = 1; break; }
-        __nanosleep(40);
-      }
-      if (failed) { lb_failed = 1; break; }
-      __threadfence_block();
-      if (st0 >= RING_RESOLVED) continue;           // first tile of a row: nothing to do
-      const i64 row = T / p.tiles_per_row;
-      const i64 tt = T - row * p.tiles_per_row;
-      const i64 row_first = T - tt;
-      const i64 gid = tt / RING_GROUP;
+      const i64 K = slot_batch[m0];
+      if (K >= total_batches) break;
+      const i64 row = K / p.batches_per_row;
+      const i64 kb = K - row * p.batches_per_row;
+      const i64 row_first = K - kb;
+      const i64 gid = kb / RING_GROUP;
       const i64 group_base = row * p.groups_per_row;
       elt_t excl;
       bool hexcl = false;
-      int phase = (tt % RING_GROUP == 0) ? RING_PH_GROUPS : RING_PH_OWN;
-      i64 g = gid - 1;
-      i64 polls = 0;
-      bool done = false;
-      while (!done) {
-        if (phase == RING_PH_GROUPS) {
-          const i64 gi = g - lane;
-          const bool in = gi >= 0;
-          u32 st = 0;
-          elt_t v;
-          if (in) st = scan_desc_load(p.gstatus, group_base + gi, v.l0);
-          const bool ready = in && (st >> 2) == epoch;
-          const unsigned pm = __ballot_sync(ACC_FULL_MASK, ready && (st & 3u) == SCAN_ST_PREFIX);
-          const unsigned em = __ballot_sync(ACC_FULL_MASK, in && !ready);
-          const int lp = pm ? (__ffs((int)pm) - 1) : 32;
-          const int lm = em ? (__ffs((int)em) - 1) : 32;
-          elt_t c = v;
-          bool hc = in && (lp < lm ? lane <= lp : lane < lm);
+      int failed = 0;
+      if (kb == 0) {
+#if ACC_SEEDED
+        excl = F_seed(p);
+        hexcl = true;
+#endif
+      } else {
+        int phase = (kb % RING_GROUP == 0) ? RING_PH_GROUPS : RING_PH_OWN;
+        i64 g = gid - 1;
+        i64 polls = 0;
+        bool done = false;
+        while (!done) {
+          if (phase == RING_PH_GROUPS) {
+            const i64 gi = g - lane;
+            const bool in = gi >= 0;
+            u32 st = 0;
+            elt_t v;
+            if (in) st = scan_desc_load(p.gstatus, group_base + gi, v.l0);
+            const bool ready = in && (st >> 2) == epoch;
+            const unsigned pm = __ballot_sync(ACC_FULL_MASK, ready && (st & 3u) == SCAN_ST_PREFIX);
+            const unsigned em = __ballot_sync(ACC_FULL_MASK, in && !ready);
+            const int lp = pm ? (__ffs((int)pm) - 1) : 32;
+            const int lm = em ? (__ffs((int)em) - 1) : 32;
+            elt_t c = v;
+            bool hc = in && (lp < lm ? lane <= lp : lane < lm);
 #pragma unroll
-          for (int d = 1; d < 32; d <<= 1) {
-            const elt_t o = acc_shfl_down(c, d);
-            const int oh = __shfl_down_sync(ACC_FULL_MASK, (int)hc, d);
-            if (lane + d < 32) scan_join_front(p, o, oh != 0, c, hc);
-          }
-          scan_join_front(p, c, hc, excl, hexcl);           // meaningful in lane 0
-          if (lp < lm) done = true;
-          else if (lm < 32) { g -= lm; phase = RING_PH_COMPUTE; }
-          else { g -= 32; if (g < 0) done = true; }         // (group 0 is never a plain aggregate: not reached)
-        } else {
-          // tiles hi, hi-1, ..., lo of the row (at most RING_GROUP = 32 * SCAN_LOOK of them)
-          const i64 hi = phase == RING_PH_OWN ? tt - 1 : g * RING_GROUP + RING_GROUP - 1;
-          const i64 lo = phase == RING_PH_OWN ? gid * RING_GROUP : g * RING_GROUP;
-          u32 st[SCAN_LOOK];
-          elt_t v[SCAN_LOOK];
-          bool in[SCAN_LOOK], ready[SCAN_LOOK];
+            for (int d = 1; d < 32; d <<= 1) {
+              const elt_t o = acc_shfl_down(c, d);
+              const int oh = __shfl_down_sync(ACC_FULL_MASK, (int)hc, d);
+              if (lane + d < 32) scan_join_front(p, o, oh != 0, c, hc);
+            }
+            scan_join_front(p, c, hc, excl, hexcl);           // meaningful in lane 0
+            if (lp < lm) done = true;
+            else if (lm < 32) { g -= lm; phase = RING_PH_COMPUTE; }
+            else { g -= 32; if (g < 0) done = true; }         // (group 0 is never a plain aggregate: not reached)
+          } else {
+            // batches hi, hi-1, ..., lo of the row (at most RING_GROUP = 32 * SCAN_LOOK of them)
+            const i64 hi = phase == RING_PH_OWN ? kb - 1 : g * RING_GROUP + RING_GROUP - 1;
+            const i64 lo = phase == RING_PH_OWN ? gid * RING_GROUP : g * RING_GROUP;
+            u32 st[SCAN_LOOK];
+            elt_t v[SCAN_LOOK];
+            bool in[SCAN_LOOK], ready[SCAN_LOOK];
 #pragma unroll
-          for (int j = 0; j < SCAN_LOOK; ++j) {
-            in[j] = hi - (i64)(SCAN_LOOK * lane + j) >= lo;
-            ready[j] = !in[j];
-            st[j] = 0;
-          }
-          for (;;) {                                  // entries found ready are not read again
-            bool all = true;
+            for (int j = 0; j < SCAN_LOOK; ++j) {
+              in[j] = hi - (i64)(SCAN_LOOK * lane + j) >= lo;
+              ready[j] = !in[j];
+              st[j] = 0;
+            }
+            for (;;) {                                  // entries found ready are not read again
+              bool all = true;
 #pragma unroll
-            for (int j = 0; j < SCAN_LOOK; ++j)
-              if (!ready[j]) {
-                st[j] = scan_desc_load(p.status, row_first + hi - (i64)(SCAN_LOOK * lane + j), v[j].l0);
-                ready[j] = (st[j] >> 2) == epoch;
-                all = all && ready[j];
-              }
-            if (__all_sync(ACC_FULL_MASK, all)) break;
-            if (++polls > p.spin_limit || ring_ldv(&sh_fail)) { failed = 1; break; }
-            scan_backoff();
-          }
-          if (failed) break;
-          int jp = SCAN_LOOK;
+              for (int j = 0; j < SCAN_LOOK; ++j)
+                if (!ready[j]) {
+                  st[j] = scan_desc_load(p.status, row_first + hi - (i64)(SCAN_LOOK * lane + j), v[j].l0);
+                  ready[j] = (st[j] >> 2) == epoch;
+                  all = all && ready[j];
+                }
+              if (__all_sync(ACC_FULL_MASK, all)) break;
+              if (++polls > p.spin_limit || ring_ldv(&sh_fail)) { failed = 1; break; }
+              scan_backoff();
+            }
+            if (failed) break;
+            int jp = SCAN_LOOK;
 #pragma unroll
-          for (int j = SCAN_LOOK - 1; j >= 0; --j)
-            if (in[j] && (st[j] & 3u) == SCAN_ST_PREFIX) jp = j;
-          const unsigned pm = __ballot_sync(ACC_FULL_MASK, jp < SCAN_LOOK);
-          const int lstar = pm ? (__ffs((int)pm) - 1) : 32;
-          const int last = lane < lstar ? SCAN_LOOK - 1 : (lane == lstar ? jp : -1);
-          elt_t c;
-          bool hc = false;
+            for (int j = SCAN_LOOK - 1; j >= 0; --j)
+              if (in[j] && (st[j] & 3u) == SCAN_ST_PREFIX) jp = j;
+            const unsigned pm = __ballot_sync(ACC_FULL_MASK, jp < SCAN_LOOK);
+            const int lstar = pm ? (__ffs((int)pm) - 1) : 32;
+            const int last = lane < lstar ? SCAN_LOOK - 1 : (lane == lstar ? jp : -1);
+            elt_t c;
+            bool hc = false;
 #pragma unroll
-          for (int j = SCAN_LOOK - 1; j >= 0; --j)
-            if (in[j] && j <= last) scan_join(p, c, hc, v[j], true);
+            for (int j = SCAN_LOOK - 1; j >= 0; --j)
+              if (in[j] && j <= last) scan_join(p, c, hc, v[j], true);
 #pragma unroll
-          for (int d = 1; d < 32; d <<= 1) {
-            const elt_t o = acc_shfl_down(c, d);
-            const int oh = __shfl_down_sync(ACC_FULL_MASK, (int)hc, d);
-            if (lane + d < 32) scan_join_front(p, o, oh != 0, c, hc);
-          }
-          if (phase == RING_PH_COMPUTE && lane == 0 && hc)     // summary of group g, for every later walker
-            scan_desc_store(p.gstatus, group_base + g, (epoch << 2) | (pm ? SCAN_ST_PREFIX : SCAN_ST_AGG), c.l0);
-          scan_join_front(p, c, hc, excl, hexcl);             // meaningful in lane 0
-          if (pm != 0) done = true;
-          else {
-            g = (phase == RING_PH_OWN) ? gid - 1 : g - 1;
-            phase = RING_PH_GROUPS;
-            if (g < 0) done = true;                           // start of the row reached
+            for (int d = 1; d < 32; d <<= 1) {
+              const elt_t o = acc_shfl_down(c, d);
+              const int oh = __shfl_down_sync(ACC_FULL_MASK, (int)hc, d);
+              if (lane + d < 32) scan_join_front(p, o, oh != 0, c, hc);
+            }
+            if (phase == RING_PH_COMPUTE && lane == 0 && hc)     // summary of group g, for every later walker
+              scan_desc_store(p.gstatus, group_base + g, (epoch << 2) | (pm ? SCAN_ST_PREFIX : SCAN_ST_AGG), c.l0);
+            scan_join_front(p, c, hc, excl, hexcl);             // meaningful in lane 0
+            if (pm != 0) done = true;
+            else {
+              g = (phase == RING_PH_OWN) ? gid - 1 : g - 1;
+              phase = RING_PH_GROUPS;
+              if (g < 0) done = true;                           // start of the row reached
+            }
           }
         }
       }
       if (failed) { lb_failed = 1; break; }
-      if (lane == 0) {
-        elt_t inc = excl;
-        bool hinc = hexcl;
-        scan_join(p, inc, hinc, slot_agg[s], true);
-        scan_desc_store(p.status, T, (epoch << 2) | SCAN_ST_PREFIX, inc.l0);
-        if ((tt % RING_GROUP) == RING_GROUP - 1)              // also the inclusive prefix of its whole group
-          scan_desc_store(p.gstatus, group_base + gid, (epoch << 2) | SCAN_ST_PREFIX, inc.l0);
-        slot_excl[s] = excl;
-        slot_hexcl[s] = hexcl ? 1 : 0;
+      // resolve the batch's tiles in order (lane 0 holds the running prefix)
+      bool whole = true;                                         // all RING_BATCH tiles present and full
+      for (int j = 0; j < RING_BATCH; ++j) {
+        const i64 r = r0 + j;
+        const int m = (int)(r % RING_META);
+        spins = 0;
+        while (ring_ldv(&slot_pos[m]) != r) {
+          if (++spins > p.spin_limit || ring_ldv(&sh_fail)) { failed = 1; break; }
+          __nanosleep(40);
+        }
+        if (failed) break;
         __threadfence_block();
-        ring_stv(&slot_state[s], RING_RESOLVED);
+        const i64 T = slot_tile[m];
+        if (T == RING_VOID) { whole = false; break; }             // the row ended inside this batch
+        if (slot_direct[m]) {
+          // partial tile, the last of its row: the finishers scan it from global memory with this prefix
+          if (lane == 0) {
+            slot_excl[m] = excl;
+            slot_hexcl[m] = hexcl ? 1 : 0;
+            __threadfence_block();
+            ring_stv(&slot_state[m], RING_RESOLVED);
+          }
+          whole = false;
+          break;
+        }
+        spins = 0;
+        while (ring_ldv(&slot_state[m]) < RING_SCANNED) {
+          if (++spins > p.spin_limit || ring_ldv(&sh_fail)) { failed = 1; break; }
+          __nanosleep(40);
+        }
+        if (failed) break;
+        __threadfence_block();
+        if (lane == 0) {
+          const elt_t agg = slot_agg[m];
+          slot_excl[m] = excl;
+          slot_hexcl[m] = hexcl ? 1 : 0;
+          __threadfence_block();
+          ring_stv(&slot_state[m], RING_RESOLVED);
+          scan_join(p, excl, hexcl, agg, true);                   // prefix of the next tile
+        }
+        __syncwarp();
+      }
+      if (failed) { lb_failed = 1; break; }
+      if (whole && lane == 0) {
+        // excl is now the inclusive prefix of the whole batch
+        scan_desc_store(p.status, K, (epoch << 2) | SCAN_ST_PREFIX, excl.l0);
+        if ((kb % RING_GROUP) == RING_GROUP - 1)                  // also the inclusive prefix of its whole group
+          scan_desc_store(p.gstatus, group_base + gid, (epoch << 2) | SCAN_ST_PREFIX, excl.l0);
       }
       __syncwarp();
     }
@@ -747,12 +834,14 @@ extern "C" __global__ void __launch_bounds__(RING_THREADS, SCAN_MIN_BLOCKS) acc_
     if (lb_failed && lane == 0) ring_stv(&sh_fail, 1);
   } else if (warp >= SCAN_WARPS) {
     // ================= reducers ========================================================
-    // Every later tile of the row waits for this tile's aggregate, so it is computed by warps that
-    // do nothing else, the moment the data has arrived; the scan itself is left to the finishers.
+    // Every later batch of the row waits for this batch's aggregate, so tile aggregates are computed
+    // by warps that do nothing else, the moment the data has arrived; the scan itself is left to
+    // the finishers.  The batch's aggregate is published with its last tile.
     const int rt = tid - SCAN_THREADS, rw = warp - SCAN_WARPS;
     int red_failed = 0;
+    elt_t bacc;                                      // thread rt == 0: aggregate of the batch so far
     for (i64 r = 0;; ++r) {
-      const int s = (int)(r % RING_META), ds = (int)(r % SCAN_SLOTS);
+      const int s = (int)(r % RING_META), ds = (int)(r % SCAN_SLOTS), j = (int)(r % RING_BATCH);
       i64 spins = 0;
       while (ring_ldv(&slot_pos[s]) != r) {
         if (++spins > p.spin_limit || ring_ldv(&sh_fail)) { red_failed = 1; break; }
@@ -762,7 +851,7 @@ extern "C" __global__ void __launch_bounds__(RING_THREADS, SCAN_MIN_BLOCKS) acc_
       __threadfence_block();
       const i64 T = slot_tile[s];
       if (T >= total_tiles) break;
-      if (slot_direct[s]) continue;                 // partial tile: the finishers do it start to finish
+      if (T == RING_VOID || slot_direct[s]) continue;           // nothing to reduce: the row ends here, nobody needs this batch's aggregate
       spins = 0;
       while (!ring_mbar_try_wait(&full_bar[ds], slot_parity[s])) {
         if (++spins > p.spin_limit || ring_ldv(&sh_fail)) { red_failed = 1; break; }
@@ -820,25 +909,23 @@ extern "C" __global__ void __launch_bounds__(RING_THREADS, SCAN_MIN_BLOCKS) acc_
       if (rt == 0) {
         elt_t agg = red_v[r & 1][0];
         for (int w = 1; w < RING_RED_WARPS; ++w) agg = scan_op(p, agg, red_v[r & 1][w]);
+        const i64 K = slot_batch[s];     // (read before the state change below lets the entry move on)
         slot_agg[s] = agg;
-        if (tt == 0) {
-          // first tile of a row: its exclusive prefix is the seed (or nothing)
-          elt_t inc = agg;
+        __threadfence_block();
+        ring_stv(&slot_state[s], RING_SCANNED);
+        if (j == 0) bacc = agg;
+        else bacc = scan_op(p, bacc, agg);
+        if (j == RING_BATCH - 1) {
+          // the batch is complete (a batch cut short by the end of its row has no successor)
+          if (K % p.batches_per_row == 0) {
 #if ACC_SEEDED
-          const elt_t z = F_seed(p);
-          inc = scan_op(p, z, agg);
-          slot_excl[s] = z;
-          slot_hexcl[s] = 1;
+            scan_desc_store(p.status, K, (epoch << 2) | SCAN_ST_PREFIX, scan_op(p, F_seed(p), bacc).l0);
 #else
-          slot_hexcl[s] = 0;
+            scan_desc_store(p.status, K, (epoch << 2) | SCAN_ST_PREFIX, bacc.l0);
 #endif
-          scan_desc_store(p.status, T, (epoch << 2) | SCAN_ST_PREFIX, inc.l0);
-          __threadfence_block();
-          ring_stv(&slot_state[s], RING_RESOLVED);
-        } else {
-          scan_desc_store(p.status, T, (epoch << 2) | SCAN_ST_AGG, agg.l0);
-          __threadfence_block();
-          ring_stv(&slot_state[s], RING_SCANNED);
+          } else {
+            scan_desc_store(p.status, K, (epoch << 2) | SCAN_ST_AGG, bacc.l0);
+          }
         }
       }
     }
@@ -847,21 +934,37 @@ extern "C" __global__ void __launch_bounds__(RING_THREADS, SCAN_MIN_BLOCKS) acc_
     // ================= finishers ========================================================
     // Ring positions are finished in order.  As soon as the tile's aggregate is out (the reducers
     // are done with the slot) the tile is read into registers and scanned there, and its slot is
-    // handed to the next ticket; prefix and stores follow when the look-back has resolved the tile.
+    // handed to the next tile; prefix and stores follow when the look-back warp has resolved the tile.
     i64 idle = 0;                          // thread 0: consecutive polls without anything to do
     for (i64 r = 0;; ++r) {
       const int fs = (int)(r % SCAN_SLOTS), fm = (int)(r % RING_META);
       const i64 T = slot_tile[fm];         // written by thread 0 before a SCAN_SYNC
       if (T >= total_tiles) break;
+      if (T == RING_VOID) {
+        SCAN_SYNC();
+        if (tid == 0) fetch(r + SCAN_SLOTS);
+        SCAN_SYNC();
+        continue;
+      }
       const i64 row = T / p.tiles_per_row;
       const i64 tt = T - row * p.tiles_per_row;
       if (slot_direct[fm]) {
-        ring_partial_tile(p, T, row, tt, sm_v, sm_h, &sm_excl1, sm_flag1);    // partial tile: start to finish
-        SCAN_SYNC();
+        // partial tile: wait for its prefix, then start to finish from global memory
         if (tid == 0) {
-          if (sm_flag1[1]) ring_stv(&sh_fail, 1);
-          fetch(r + SCAN_SLOTS);
+          idle = 0;
+          while (ring_ldv(&slot_state[fm]) < RING_RESOLVED) {
+            if (++idle > p.spin_limit) ring_stv(&sh_fail, 1);
+            if (ring_ldv(&sh_fail)) break;
+            __nanosleep(40);
+          }
+          ctl_act = ring_ldv(&sh_fail) ? RING_ACT_EXIT : RING_ACT_FIN;
         }
+        SCAN_SYNC();
+        if (ctl_act == RING_ACT_EXIT) break;
+        const elt_t gexcl = slot_excl[fm];
+        ring_partial_tile(p, T, row, tt, sm_v, sm_h, &sm_excl1, sm_flag1, &gexcl, slot_hexcl[fm] != 0);
+        SCAN_SYNC();
+        if (tid == 0) fetch(r + SCAN_SLOTS);
         SCAN_SYNC();                     // the next tile of this slot is known to every finisher
       } else {
         if (tid == 0) {
@@ -921,7 +1024,7 @@ extern "C" __global__ void __launch_bounds__(RING_THREADS, SCAN_MIN_BLOCKS) acc_
         if (lane == 0) sm_v[warp] = carry;
         SCAN_SYNC();                     // every finisher has the slot's data in registers
         if (tid == 0) {
-          fetch(r + SCAN_SLOTS);         // the slot takes the next ticket while this tile waits for its prefix
+          fetch(r + SCAN_SLOTS);         // the slot takes the next tile while this one waits for its prefix
           idle = 0;
           while (ring_ldv(&slot_state[fm]) < RING_RESOLVED) {
             if (++idle > p.spin_limit) ring_stv(&sh_fail, 1);     // the prefix never arrived: give up
@@ -988,7 +1091,7 @@ extern "C" __global__ void __launch_bounds__(RING_THREADS, SCAN_MIN_BLOCKS) acc_
       }
     }
   }
-  // everybody meets here; the look-back warp leaves its loop when it sees a tile past the end,
+  // everybody meets here; the look-back warp leaves its loop when it sees a batch past the end,
   // a failure flag, or an expired wait (in which case it raises the flag itself)
   __syncthreads();
   if (tid == 0) {
@@ -996,7 +1099,7 @@ extern "C" __global__ void __launch_bounds__(RING_THREADS, SCAN_MIN_BLOCKS) acc_
     // there be any).  A bulk copy completes without the help of any other CTA, so this wait gets a
     // bound of its own, far above the time a copy can take.
     for (int m = 0; m < RING_META; ++m) {
-      if (slot_pos[m] >= 0 && slot_tile[m] < total_tiles && !slot_direct[m] && slot_state[m] == RING_LOADING) {
+      if (slot_pos[m] >= 0 && slot_tile[m] >= 0 && slot_tile[m] < total_tiles && !slot_direct[m] && slot_state[m] == RING_LOADING) {
         i64 spins = 0;
         while (!ring_mbar_try_wait(&full_bar[slot_pos[m] % SCAN_SLOTS], slot_parity[m]))
           if (++spins > ((i64)1 << 26)) break;

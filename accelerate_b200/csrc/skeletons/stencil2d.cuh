@@ -17,8 +17,9 @@
 // HBM traffic: one read per input point and one write per output point, plus
 // 2*ry halo rows per ST2_ROWS rows.
 //
-// Named parameters: o1, o2 (output rows, columns), tiles1 (row blocks),
-// tiles2 (strips of 120 output columns), vec (o2 % 4 == 0, 16-byte aligned output).
+// Named parameters: o1, o2 (output rows, columns), row0, row1 (the rows to produce: all of them, or a
+// window of an existing output array), tiles1 (row blocks of the window), tiles2 (strips of 120
+// output columns), vec (o2 % 4 == 0, 16-byte aligned output).
 // One warp per task: grid = ceil(tiles1 * tiles2 / ST2_WARPS).
 
 #ifndef ST2_WARPS
@@ -84,8 +85,9 @@ extern "C" __global__ void __launch_bounds__(ST2_THREADS, ST2_MIN_BLOCKS) acc_st
   const int rb = (int)(task / p.tiles2);
   const int strip = (int)(task - (i64)rb * p.tiles2);
   const int gx0 = strip * ST2_STRIP - 4 + lane * 4;
-  const int y0 = rb * ST2_ROWS;
-  const int y1 = min(y0 + ST2_ROWS, o1);
+  const int y0 = (int)p.row0 + rb * ST2_ROWS;
+  const int y1 = min(y0 + ST2_ROWS, (int)p.row1);
+  (void)o1;
   // lanes 1..30 produce output; the strip's columns beyond the array produce none
   const bool writer = lane >= 1 && lane <= 30 && gx0 < o2;
   const bool st_vec = p.vec != 0 && gx0 + 4 <= o2;

@@ -704,6 +704,174 @@ def maximum(a): return fold1(max_, a)
 def minimum(a): return fold1(min_, a)
 
 
+# segmented scans (Prelude.hs:950-1420): built from the skeletons above -----------------
+def _outer_inner(sh, rank):
+    """(outer components, innermost extent) of a shape expression."""
+    return [sh[d] for d in range(rank - 1)], sh[rank - 1]
+
+
+def _null(a):
+    return use(a).size().eq(0)
+
+
+def _take_inner(n, a):
+    """The first ``n`` elements along the innermost dimension (``take``, Prelude.hs:1531-1540)."""
+    a = use(a)
+    outer, sz = _outer_inner(a.shape, a.rank)
+    return backpermute(index(*outer, min_(max_(lift(n, INT), 0), sz)), lambda ix: ix, a)
+
+
+def _drop_inner(n, a):
+    """All but the first ``n`` elements along the innermost dimension (``drop``, Prelude.hs:1556-1567)."""
+    a = use(a)
+    outer, sz = _outer_inner(a.shape, a.rank)
+    n = max_(lift(n, INT), 0)
+    return backpermute(index(*outer, max_(sz - n, 0)), lambda ix: index(*[ix[d] for d in range(a.rank - 1)], ix[a.rank - 1] + n), a)
+
+
+def _init1(a):
+    """``init`` of a vector (Prelude.hs:1582-1591)."""
+    a = use(a)
+    return backpermute(index(max_(a.shape[0] - 1, 0)), lambda ix: ix, a)
+
+
+def mkHeadFlags(seg):
+    """Head flags of a segment descriptor for left scans: non-zero where a segment starts; a value
+    above one stands for that many segments starting there (empty ones) (Prelude.hs:1364-1375)."""
+    seg = use(seg)
+    offset, ln = scanl_prime(lambda x, y: x + y, lift(0, seg.elt), seg)
+    zeros = fill(index(from_integral(the(ln), INT) + 1), lift(0, seg.elt))
+    ones = fill(index(offset.size()), lift(1, seg.elt))
+    return _init1(permute(lambda x, y: x + y, zeros, lambda ix: Just_(index(from_integral(offset[ix], INT))), ones))
+
+
+def mkTailFlags(seg):
+    """Tail flags for right scans: the flag sits on the last place of each segment (Prelude.hs:1379-1390)."""
+    seg = use(seg)
+    offset, ln = scanr_prime(lambda x, y: x + y, lift(0, seg.elt), seg)
+    zeros = fill(index(from_integral(the(ln), INT) + 1), lift(0, seg.elt))
+    ones = fill(index(offset.size()), lift(1, seg.elt))
+    return _init1(permute(lambda x, y: x + y, zeros, lambda ix: Just_(index(from_integral(the(ln) - 1 - offset[ix], INT))), ones))
+
+
+def segmentedL(f):
+    """Segmented version of ``f`` on (flag, value) pairs (Sengupta et al.; Prelude.hs:1395-1401)."""
+    return lambda a, b: tup(a[0] | b[0], cond(b[0].ne(0), b[1], f(a[1], b[1])))
+
+
+def segmentedR(f):
+    """Prelude.hs:1403-1407"""
+    g = segmentedL(lambda x, y: f(y, x))
+    return lambda y, x: g(x, y)
+
+
+def _with_flags(flags, arr):
+    """``zip (replicate (indexTail (shape arr) :. All) flags) arr``"""
+    arr, flags = use(arr), compute(use(flags))
+    outer, sz = _outer_inner(arr.shape, arr.rank)
+    return generate(index(*outer, min_(sz, flags.shape[0])), lambda ix: tup(flags[index(ix[arr.rank - 1])], arr[ix]))
+
+
+def scanl1Seg(f, arr, seg):
+    """Prelude.hs:1138-1148"""
+    return map_(lambda t: t[1], scanl1(segmentedL(f), _with_flags(mkHeadFlags(seg), arr)))
+
+
+def scanr1Seg(f, arr, seg):
+    """Prelude.hs:1315-1325"""
+    return map_(lambda t: t[1], scanr1(segmentedR(f), _with_flags(mkTailFlags(seg), arr)))
+
+
+def scanlSeg(f, z, arr, seg):
+    """Segmented exclusive scan: the seed is injected at the head of every segment, then a
+    segmented inclusive scan runs over the longer array (Prelude.hs:979-1013)."""
+    arr, seg = use(arr), use(seg)
+    z = lift(z, arr.elt)
+    outer, sz = _outer_inner(arr.shape, arr.rank)
+    flags = compute(mkHeadFlags(seg))
+    inc = compute(scanl1(lambda x, y: x + y, flags))
+    full = index(*outer, sz + seg.shape[0])
+    last = arr.rank - 1
+    arr2 = permute(lambda new, old: new, fill(full, z),
+                   lambda ix: Just_(index(*[ix[d] for d in range(last)], ix[last] + from_integral(inc[index(ix[last])], INT))),
+                   _take_inner(flags.shape[0], arr))
+    seg2 = map_(lambda v: v + 1, seg)
+    return acond(lor(_null(arr), _null(flags)), fill(full, z), scanl1Seg(f, arr2, seg2))
+
+
+def scanl_primeSeg(f, z, arr, seg):
+    """``scanl'Seg`` (Prelude.hs:1052-1105): the segmented exclusive scan taken apart into the
+    scan bodies and the per-segment totals."""
+    arr, seg = use(arr), use(seg)
+    z = lift(z, arr.elt)
+    outer, sz = _outer_inner(arr.shape, arr.rank)
+    last = arr.rank - 1
+    arr2 = compute(scanlSeg(f, z, arr, seg))
+    add = lambda x, y: x + y  # noqa: E731
+    seg2 = map_(lambda v: v + 1, seg)
+    tails = compute(zipWith(add, seg, scanl_prime(add, lift(0, seg.elt), seg2)[0]))
+    sums = backpermute(index(*outer, seg.shape[0]), lambda ix: index(*[ix[d] for d in range(last)], from_integral(tails[index(ix[last])], INT)), arr2)
+    offset = compute(scanl1(add, seg))
+    inc = compute(scanl1(add, permute(add, fill(index(arr.size() + 1), lift(0, seg.elt)), lambda ix: Just_(index(from_integral(offset[ix], INT))),
+                                      fill(seg.shape, lift(1, seg.elt)))))
+    ln = offset[index(offset.shape[0] - 1)]
+    body = backpermute(index(*outer, from_integral(ln, INT)),
+                       lambda ix: index(*[ix[d] for d in range(last)], ix[last] + from_integral(inc[index(ix[last])], INT)), arr2)
+    empty_sums = fill(index(*outer, seg.shape[0]), z)
+    return acond(_null(arr), (compute(arr), empty_sums), (body, sums))
+
+
+def scanrSeg(f, z, arr, seg):
+    """Prelude.hs:1200-1226"""
+    arr, seg = use(arr), use(seg)
+    z = lift(z, arr.elt)
+    outer, sz = _outer_inner(arr.shape, arr.rank)
+    flags = compute(mkHeadFlags(seg))
+    inc = compute(scanl1(lambda x, y: x + y, flags))
+    full = index(*outer, sz + seg.shape[0])
+    last = arr.rank - 1
+    arr2 = permute(lambda new, old: new, fill(full, z),
+                   lambda ix: Just_(index(*[ix[d] for d in range(last)], ix[last] + from_integral(inc.linear(ix[last]), INT) - 1)),
+                   _drop_inner(sz - flags.shape[0], arr))
+    seg2 = map_(lambda v: v + 1, seg)
+    return acond(lor(_null(arr), _null(flags)), fill(full, z), scanr1Seg(f, arr2, seg2))
+
+
+def scanr_primeSeg(f, z, arr, seg):
+    """``scanr'Seg`` (Prelude.hs:1259-1290)"""
+    arr, seg = use(arr), use(seg)
+    z = lift(z, arr.elt)
+    outer, sz = _outer_inner(arr.shape, arr.rank)
+    last = arr.rank - 1
+    add = lambda x, y: x + y  # noqa: E731
+    arr2 = compute(scanrSeg(f, z, arr, seg))
+    seg2 = map_(lambda v: v + 1, seg)
+    heads = compute(scanl_prime(add, lift(0, seg.elt), seg2)[0])
+    sums = backpermute(index(*outer, seg.shape[0]), lambda ix: index(*[ix[d] for d in range(last)], from_integral(heads[index(ix[last])], INT)), arr2)
+    flags = compute(mkHeadFlags(seg))
+    inc = compute(scanl1(add, flags))
+    body = backpermute(index(*outer, flags.shape[0]),
+                       lambda ix: index(*[ix[d] for d in range(last)], ix[last] + from_integral(inc[index(ix[last])], INT)), arr2)
+    empty_sums = fill(index(*outer, seg.shape[0]), z)
+    return acond(_null(arr), (compute(arr), empty_sums), (body, sums))
+
+
+def prescanlSeg(f, z, arr, seg): return scanl_primeSeg(f, z, arr, seg)[0]      # Prelude.hs:1152-1162
+def prescanrSeg(f, z, arr, seg): return scanr_primeSeg(f, z, arr, seg)[0]      # Prelude.hs:1329-1339
+
+
+def postscanlSeg(f, z, arr, seg):
+    """Prelude.hs:1166-1176"""
+    z = lift(z, use(arr).elt)
+    return map_(lambda v: f(z, v), scanl1Seg(f, arr, seg))
+
+
+def postscanrSeg(f, z, arr, seg):
+    """Prelude.hs:1343-1353"""
+    z = lift(z, use(arr).elt)
+    return map_(lambda v: f(v, z), scanr1Seg(f, arr, seg))
+
+
 # ----------------------------------------------------------------------------
 # Program assembly
 # ----------------------------------------------------------------------------

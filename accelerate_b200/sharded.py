@@ -84,11 +84,30 @@ class ProgramCache:
 class GpuExecutor:
     """Runs terms on this rank's GPU; arrays are ``backend.DeviceArray``."""
 
-    def __init__(self, ctx):
+    def __init__(self, ctx, group=None):
+        """``group``: a ``backend.Group`` (the library's own NCCL communicator); without one the
+        exchange steps go through ``torch.distributed`` on views of the device arrays."""
         from . import backend
-        self.backend, self.ctx = backend, ctx
+        self.backend, self.ctx, self.group = backend, ctx, group
         self.stream = torch.cuda.ExternalStream(ctx.stream(), device=torch.device("cuda", ctx.device))
         self._progs = ProgramCache()
+
+    @classmethod
+    def with_group(cls, ctx, deadline_s=60.0):
+        """Executor whose exchange steps run inside the C-ABI library: rank 0 creates the rendezvous
+        id and the ranks of the default process group receive it over ``torch.distributed``."""
+        from . import backend
+        rank, world = dist.get_rank(), dist.get_world_size()
+        box = [backend.Group.unique_id() if rank == 0 else None]
+        dist.broadcast_object_list(box, src=0)
+        return cls(ctx, backend.Group(ctx, box[0], rank, world, deadline_s))
+
+    def program(self, key, build, inputs):
+        """Text of the (cached) program ``build`` yields for these inputs."""
+        return self._progs.get(key, build, inputs)[0].text
+
+    def run_rows(self, text, inputs, out, row_lo, row_hi):
+        self.ctx.run_rows(text, inputs, out, row_lo, row_hi)
 
     def run(self, key, build, inputs):
         """``build(*params)`` -> term(s).  The built program is cached under the input signature
@@ -191,6 +210,8 @@ class Sharded:
 
     def _gathered_array(self, arr):
         """All ranks' scalars as one local array of shape (world,) (element type kept)."""
+        if getattr(self.ex, "group", None) is not None:
+            return self.ex.group.all_gather(arr)
         leaves = self._all_gather_scalars(arr)
         if len(leaves) == 1:
             return self.ex.wrap(leaves[0], arr.elt)
@@ -285,6 +306,9 @@ class Sharded:
             start = self.ex.run((key, "ident", op), lambda d: L.fill(d.shape, ident), [defaults])
         out = self.ex.run((key, op), lambda d, *xs: L.permute(f, d, lambda ix: index_fn(ix, *xs), build_source(*xs)), [start] + list(inputs))
         if self.world > 1:
+            if getattr(self.ex, "group", None) is not None:
+                self.ex.group.all_reduce(out, op)
+                return out
             t = self.ex.tensor(out)
             with self.ex.collective():
                 dist.all_reduce(t, op={"add": dist.ReduceOp.SUM, "min": dist.ReduceOp.MIN, "max": dist.ReduceOp.MAX}[op], group=self.group)
@@ -329,6 +353,30 @@ class Sharded:
         up, down = self._neighbours(boundary)
         ext = h.ext
         cols = ext.shape[1]
+        g = getattr(self.ex, "group", None)
+        if g is not None and iterations > 0 and h.rows >= 4 * radius and (h.top or h.bot):
+            # Exchange and kernels overlap: the rows that need no halo rows are computed while the
+            # halo rows of the current grid are still in flight (second stream), the `radius` rows at
+            # either edge of the slab after they have arrived; the edges of the new grid then travel
+            # while the next application's interior runs.  Two grids in the halo layout alternate.
+            text = self.ex.program((key, "it"), lambda x: L.stencil(f, boundary, x), [ext])
+            spare = [self.ex.empty(ext.elt, ext.shape) for _ in range(min(iterations, 2))]      # the caller's grid is only read
+            lo, hi = h.top, h.top + h.rows
+            ilo, ihi = lo + (radius if h.top else 0), hi - (radius if h.bot else 0)
+            g.halo_exchange(ext, h.top, h.rows, h.bot, radius, up, down, overlap=True)
+            src = ext
+            for k in range(iterations):
+                dst = spare[k % 2]
+                self.ex.run_rows(text, [src], dst, ilo, ihi)
+                g.halo_wait()
+                if ilo > lo:
+                    self.ex.run_rows(text, [src], dst, lo, ilo)
+                if ihi < hi:
+                    self.ex.run_rows(text, [src], dst, ihi, hi)
+                if k + 1 < iterations:
+                    g.halo_exchange(dst, h.top, h.rows, h.bot, radius, up, down, overlap=True)
+                src = dst
+            return self.ex.rows_view(src, h.top, h.top + h.rows)
         for _ in range(iterations):
             self._exchange_halos(ext, h.rows, cols, h.top, h.bot, up, down, radius)
             ext = self.ex.run((key, "it"), lambda x: L.stencil(f, boundary, x), [ext])
@@ -349,6 +397,10 @@ class Sharded:
         return self.ex.rows_view(out, hs[0].top, hs[0].top + hs[0].rows)
 
     def _exchange_halos(self, ext, rows, cols, top, bot, up, down, radius):
+        if getattr(self.ex, "group", None) is not None:
+            if up is not None or down is not None:
+                self.ex.group.halo_exchange(ext, top, rows, bot, radius, up, down, overlap=False)
+            return
         t = self.ex.tensor(ext)
         ops = []
         # sends first (up, down), then receives (from down, from up): with two ranks and a wrap

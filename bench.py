@@ -544,7 +544,7 @@ def main():
     sharded = None
     if world > 1:
         from accelerate_b200.sharded import GpuExecutor, Sharded
-        sharded = Sharded(GpuExecutor(ctx))
+        sharded = Sharded(GpuExecutor.with_group(ctx))     # exchange steps inside the C-ABI library (NCCL)
     for w in ws_all:
         b = ShardedBound(sharded, w, [f() for f in w.inputs]) if sharded else Bound(ctx, w, [f() for f in w.inputs])
         b.upload()

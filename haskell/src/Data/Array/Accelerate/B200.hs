@@ -42,7 +42,7 @@ import Data.Array.Accelerate.AST.Idx
 import Data.Array.Accelerate.AST.LeftHandSide
 import Data.Array.Accelerate.AST.Var
 import Data.Array.Accelerate.Array.Data                             ( ArrayData, GArrayDataR )
-import Data.Array.Accelerate.Array.Unique                           ( unsafeUniqueArrayPtr )
+import Data.Array.Accelerate.Array.Unique                           ( unsafeUniqueArrayPtr, getUniqueId )
 import Data.Array.Accelerate.Error
 import Data.Array.Accelerate.Representation.Array
 import Data.Array.Accelerate.Representation.Shape
@@ -67,7 +67,7 @@ import Foreign.Marshal.Alloc
 import Foreign.Marshal.Array
 import Foreign.Ptr
 import Foreign.Storable
-import Numeric                                                      ( showHFloat )
+import Numeric                                                      ( showHFloat, showHex )
 import System.IO.Unsafe                                             ( unsafePerformIO )
 
 
@@ -87,6 +87,8 @@ foreign import ccall safe "b200_array_download_async" c_arrayDownloadAsync :: Pt
 -- (touchArrayData) until the call that uses the array has returned
 foreign import ccall safe "b200_array_adopt_host" c_arrayAdoptHost :: Ptr Ctx -> Word64 -> CInt -> Ptr () -> CSize -> IO CInt
 foreign import ccall safe "b200_array_free"     c_arrayFree    :: Ptr Ctx -> Word64 -> IO CInt
+foreign import ccall safe "b200_array_intern"   c_arrayIntern  :: Ptr Ctx -> Word64 -> CString -> CInt -> Ptr Int64 -> Ptr (Ptr ()) -> Ptr Word64 -> IO CInt
+foreign import ccall safe "b200_array_forget"   c_arrayForget  :: Ptr Ctx -> Word64 -> IO CInt
 foreign import ccall safe "b200_array_rank"     c_arrayRank    :: Ptr Ctx -> Word64 -> Ptr CInt -> IO CInt
 foreign import ccall safe "b200_array_shape"    c_arrayShape   :: Ptr Ctx -> Word64 -> Ptr Int64 -> IO CInt
 foreign import ccall safe "b200_program_load"   c_programLoad  :: Ptr Ctx -> CString -> CSize -> Ptr (Ptr Prog) -> IO CInt
@@ -187,11 +189,17 @@ uploadArrays ctx (TupRpair ra rb) (a, b) = (++) <$> uploadArrays ctx ra a <*> up
 uploadArrays ctx (TupRsingle (ArrayR shr tp)) (Array sh adata) = do
   let dims = map fromIntegral (shapeToList shr sh) :: [Int64]
       n    = size shr sh
-  ident <- withCString (typeText tp) $ \ty -> withArrayLen (reverse dims) $ \r pd -> alloca $ \pid -> do
-    check =<< c_arrayNew ctx ty (fromIntegral r) pd pid      -- shapeToList is innermost-first
+  -- The device copy is keyed by the unique id of the array's first leaf (Array/Unique.hs:48-51), as in
+  -- the reference's memory table (Array/Remote/Table.hs:89-100): an array passed to several runs is
+  -- uploaded once.  (A finalizer on the array calls b200_array_forget: Array/Remote/Table.hs:271-284.)
+  ptrs <- newIORef []
+  _ <- forLeaves tp adata 0 $ \_ _ ptr -> modifyIORef ptrs (ptr :)
+  leaves <- reverse <$> readIORef ptrs
+  let _ = n
+  ident <- withCString (typeText tp) $ \ty -> withArrayLen (reverse dims) $ \r pd ->
+           withArray leaves $ \pl -> alloca $ \pid -> do
+    check =<< c_arrayIntern ctx (arrayKey tp adata) ty (fromIntegral r) pd pl pid      -- shapeToList is innermost-first
     peek pid
-  forLeaves tp adata 0 $ \leaf bytesPer ptr ->
-    check =<< c_arrayUpload ctx ident (fromIntegral leaf) ptr (fromIntegral (n * bytesPer))
   return [ident]
 
 downloadArrays :: Ptr Ctx -> ArraysR a -> IORef [Word64] -> IO a
@@ -207,6 +215,13 @@ downloadArrays ctx (TupRsingle repr@(ArrayR shr tp)) ref = do
     check =<< c_arrayDownload ctx ident (fromIntegral leaf) ptr (fromIntegral (size shr sh * bytesPer))
   _ <- c_arrayFree ctx ident
   return arr
+
+-- | Key of an array in the memory table: the unique id of its first scalar leaf (every leaf of a
+-- struct-of-arrays payload is allocated together and dies together).
+arrayKey :: TypeR e -> ArrayData e -> Word64
+arrayKey TupRunit        ()     = 0
+arrayKey (TupRpair ta _) (a, _) = arrayKey ta a
+arrayKey (TupRsingle t)  ad     = fromIntegral (unsafePerformIO (scalarUniqueId t ad))
 
 -- | Visit the payload pointer of every scalar leaf, left to right.
 forLeaves :: TypeR e -> ArrayData e -> Int -> (Int -> Int -> Ptr () -> IO ()) -> IO Int
@@ -231,6 +246,18 @@ scalarPayload (SingleScalarType (NumSingleType nt)) ad = case nt of
     TypeHalf   -> unsupported "Half arrays"
 scalarPayload VectorScalarType{} _ = unsupported "SIMD vector element types"
 
+-- 'getUniqueId' of the leaf's 'UniqueArray' (Array/Unique.hs:48-51, 66-69).
+scalarUniqueId :: ScalarType t -> ArrayData t -> IO Int
+scalarUniqueId (SingleScalarType (NumSingleType nt)) ad = case nt of
+  IntegralNumType it -> case it of
+    TypeInt    -> getUniqueId ad; TypeInt8   -> getUniqueId ad; TypeInt16  -> getUniqueId ad; TypeInt32  -> getUniqueId ad
+    TypeInt64  -> getUniqueId ad; TypeWord   -> getUniqueId ad; TypeWord8  -> getUniqueId ad; TypeWord16 -> getUniqueId ad
+    TypeWord32 -> getUniqueId ad; TypeWord64 -> getUniqueId ad
+  FloatingNumType ft -> case ft of
+    TypeFloat  -> getUniqueId ad; TypeDouble -> getUniqueId ad
+    TypeHalf   -> unsupported "Half arrays"
+scalarUniqueId VectorScalarType{} _ = unsupported "SIMD vector element types"
+
 unsupported :: String -> a
 unsupported what = error ("accelerate-b200: " ++ what ++ " are not supported by this backend")
 
@@ -244,6 +271,11 @@ unsupported what = error ("accelerate-b200: " ++ what ++ " are not supported by 
 --            | (scanl|scanr ELT fun [seed] D) | (scanl'|scanr' ELT fun seed D)
 --            | (permute ELT fun DEFAULTS ixfun D) | (stencil ELT stencilr fun bnd D)
 --            | (stencil2 ELT stencilr stencilr fun bnd D bnd D) | (reshape sh NAME)
+--            | (use (array RANK ELT) (shape d..) (hex BYTES)+)        -- Use: one (hex ..) per scalar leaf
+--            | (acond exp (branch BODY) (branch BODY))                 -- Acond
+--            | (awhile AFUN AFUN (args NAME*)) | (apply AFUN (args NAME*))
+--   AFUN    := (afun ((NAME (array RANK ELT))*) BODY)
+--   BODY    := (let LHS NODE)* (out NAME+)
 --   D       := (manifest NAME) | (delayed extent fun)
 --
 -- Tuples are the representation's snoc lists: Nil = (tup), Pair l r = (snoc l r).
@@ -302,7 +334,12 @@ bindNames lhs xs ns = fst (go lhs xs ns)
 -- One executable node = one (let ...) line.
 emitNode :: PreOpenAcc DelayedOpenAcc aenv a -> Names aenv -> S -> ([String], S)
 emitNode pacc ns s0 =
-  let nouts       = case pacc of Scan'{} -> 2; _ -> 1
+  let nouts       = case pacc of
+                      Scan'{}  -> 2
+                      Acond{}  -> countArrays (arraysR pacc)
+                      Awhile{} -> countArrays (arraysR pacc)
+                      Apply{}  -> countArrays (arraysR pacc)
+                      _        -> 1
       names       = [ "a" ++ show (fresh s0 + k) | k <- [0 .. nouts - 1] ]
       s1          = s0 { fresh = fresh s0 + nouts }
       (body, s2)  = nodeText pacc ns s1
@@ -311,7 +348,10 @@ emitNode pacc ns s0 =
 
 nodeText :: PreOpenAcc DelayedOpenAcc aenv a -> Names aenv -> S -> (String, S)
 nodeText pacc ns s = case pacc of
-  Use{}                        -> unsupported "embedded (use) arrays inside runN bodies; pass them as arguments"
+  Use (ArrayR shr tp) (Array sh adata)
+                               -> let dims = reverse (shapeToList shr sh)          -- shapeToList is innermost-first
+                                  in  (sx (["use", "(array " ++ show (rank shr) ++ " " ++ typeText tp ++ ")", sx ("shape" : map show dims)]
+                                           ++ hexLeaves tp adata (size shr sh)), s)
   Unit tp e                    -> (sx ["generate", typeText tp, "(tup)", lam1 "(tup)" (\_ -> expText ns [] e)], s)
   Generate (ArrayR _ tp) sh f  -> (sx ["generate", typeText tp, expText ns [] sh, funText ns f], s)
   Map tp f a                   -> let (d, s') = operand a ns s
@@ -338,9 +378,17 @@ nodeText pacc ns s = case pacc of
                                -> let (d1, sa) = operand a1 ns s; (d2, sb) = operand a2 ns sa
                                   in  (sx ["stencil2", typeText tp, stencilText s1r, stencilText s2r, funText ns f,
                                            boundaryText ns (arrayR a1) b1, operandText d1, boundaryText ns (arrayR a2) b2, operandText d2], sb)
-  Acond{}                      -> unsupported "array-level conditionals (evaluate the predicate on the host and call runN per branch)"
-  Awhile{}                     -> unsupported "array-level loops (iterate runN on the host)"
-  Apply{}                      -> unsupported "array-level function application"
+  -- evaluated on the host by the library, as by every backend (Interpreter.hs:215-229)
+  Acond p t e                  -> let (tb, s1) = subBody "branch" (manifestArrays t ns) s
+                                      (eb, s2) = subBody "branch" (manifestArrays e ns) s1
+                                  in  (sx ["acond", expText ns [] p, tb, eb], s2)
+  Awhile c f a                 -> let (xs, s1) = manifestArrays a ns s
+                                      (cb, s2) = afunText c ns s1
+                                      (fb, s3) = afunText f ns s2
+                                  in  (sx ["awhile", cb, fb, sx ("args" : xs)], s3)
+  Apply _ f a                  -> let (xs, s1) = manifestArrays a ns s
+                                      (fb, s2) = afunText f ns s1
+                                  in  (sx ["apply", fb, sx ("args" : xs)], s2)
   Aforeign{}                   -> unsupported "foreign functions"
   Atrace{}                     -> unsupported "atrace"
   _                            -> internalError "node should have been fused away (Fusion.hs:198-200)"
@@ -350,6 +398,38 @@ nodeText pacc ns s = case pacc of
     eltOf a = typeText (arrayRtype (arrayR a))
     scanName LeftToRight p = if p then "scanl'" else "scanl"
     scanName RightToLeft p = if p then "scanr'" else "scanr"
+
+-- The nodes of a branch or of an array-level function, serialised on their own and wrapped.
+subBody :: String -> (S -> ([String], S)) -> S -> (String, S)
+subBody hd k s =
+  let (outs, s') = k s { lets = [] }
+  in  ("(" ++ hd ++ " " ++ unwords (reverse (lets s')) ++ " (out " ++ unwords outs ++ "))", s' { lets = lets s })
+
+-- (afun ((p (array R T)) ...) (let ..)* (out ..)) for a unary array-level function
+afunText :: DelayedOpenAfun aenv f -> Names aenv -> S -> (String, S)
+afunText (Alam lhs (Abody b)) ns s =
+  let (ns', ps, s1) = bindParams lhs ns s
+  in  subBody ("afun (" ++ unwords ps ++ ")") (manifestArrays b ns') s1
+afunText _ _ _ = internalError "array-level function of unexpected arity"
+
+bindParams :: ALeftHandSide a aenv aenv' -> Names aenv -> S -> (Names aenv', [String], S)
+bindParams (LeftHandSideWildcard _) ns s = (ns, [], s)
+bindParams (LeftHandSidePair a b)   ns s =
+  let (ns1, p1, s1) = bindParams a ns s; (ns2, p2, s2) = bindParams b ns1 s1 in (ns2, p1 ++ p2, s2)
+bindParams (LeftHandSideSingle (ArrayR shr tp)) ns s =
+  let nm = "a" ++ show (fresh s)
+  in  (push ns nm, ["(" ++ nm ++ " (array " ++ show (rank shr) ++ " " ++ typeText tp ++ "))"], s { fresh = fresh s + 1 })
+
+-- Payload of an embedded array: the bytes of every scalar leaf as hexadecimal text.
+hexLeaves :: TypeR e -> ArrayData e -> Int -> [String]
+hexLeaves tp ad n = unsafePerformIO $ do
+  ref <- newIORef []
+  _ <- forLeaves tp ad 0 $ \_ bytesPer ptr -> do
+         bytes <- peekArray (n * bytesPer) (castPtr ptr :: Ptr Word8)
+         modifyIORef ref (("(hex " ++ concatMap (\b -> showHex2 b) bytes ++ ")") :)
+  reverse <$> readIORef ref
+  where
+    showHex2 b = let h = showHex b "" in if length h == 1 then '0' : h else h
 
 -- An operand is either a manifest array (by name) or a delayed array.
 data Operand = OManifest String Int | ODelayed String String     -- extent text, index function text

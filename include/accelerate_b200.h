@@ -25,6 +25,7 @@ extern "C" {
 
 typedef struct b200_ctx b200_ctx;
 typedef struct b200_program b200_program;
+typedef struct b200_group b200_group;
 
 enum {
   B200_OK = 0,
@@ -78,6 +79,18 @@ int b200_array_download_async(b200_ctx* ctx, uint64_t id, int leaf, void* host, 
  * Haskell side keeps it alive with touchArrayData, Array/Data.hs:250-255).  An explicit
  * b200_array_upload of the same leaf replaces it. */
 int b200_array_adopt_host(b200_ctx* ctx, uint64_t id, int leaf, const void* host, size_t bytes);
+/* The memory table (Array/Remote/Table.hs:89-100, LRU.hs:140-199): the device copy of a host array,
+ * keyed by the array's unique id (Array/Unique.hs:48-51), so that an array passed to several runs is
+ * uploaded once.  The first call for a key creates the device array and adopts the host payload
+ * (one pointer per scalar leaf; copied at first use, as with b200_array_adopt_host, so the payload
+ * must stay valid and unchanged until then); later calls with the same key return a new id for the
+ * SAME device array without touching the host pointers.  Ids are released with b200_array_free as
+ * usual; the table's own reference lives until b200_array_forget (the host array's finalizer,
+ * Array/Remote/Table.hs:271-284) or b200_ctx_destroy.  A key seen again with another type or shape
+ * is an error (B200_ERR_ARG). */
+int b200_array_intern(b200_ctx* ctx, uint64_t key, const char* elt_type, int rank, const int64_t* shape,
+                      const void* const* host_leaves, uint64_t* id);
+int b200_array_forget(b200_ctx* ctx, uint64_t key);
 /* Release (callable from any thread, e.g. a GHC finalizer; Array/Remote/Table.hs:271-284). */
 int b200_array_free(b200_ctx* ctx, uint64_t id);
 int b200_array_rank(b200_ctx* ctx, uint64_t id, int* rank);
@@ -102,6 +115,14 @@ int b200_program_num_outputs(b200_program* prog, int* n);
  * download. */
 int b200_program_run(b200_program* prog, const uint64_t* in_ids, int n_in, uint64_t* out_ids, int n_out);
 
+/* For a program that is exactly one rank-2 stencil or stencil2 node: compute only rows
+ * [row_lo, row_hi) of its result, into the existing array `out_id` (same shape and element type as
+ * the result; the other rows are left alone).  This is how a caller splits one stencil application
+ * into the rows that need freshly exchanged halo rows and the rows that do not (stencilOp,
+ * Interpreter.hs:637-649, restricted to a range of its index space). */
+int b200_program_run_rows(b200_program* prog, const uint64_t* in_ids, int n_in, uint64_t out_id, int64_t row_lo,
+                          int64_t row_hi);
+
 /* Wait for all work of the context (asynchronous downloads included) and report device-side failures. */
 int b200_sync(b200_ctx* ctx);
 
@@ -114,6 +135,37 @@ int b200_stats(b200_ctx* ctx, int64_t out[8]);
 /* The CUDA stream the context launches on (a cudaStream_t), for callers that
  * time kernels with their own events. */
 int b200_ctx_stream(b200_ctx* ctx, void** stream);
+
+/* ---- several GPUs -----------------------------------------------------------------------------
+ * The reference has no multi-device backend; these entry points carry the exchange steps of the
+ * data-parallel skeletons split over several GPUs (one context per GPU; contexts may live in one
+ * process or in several).  Arrays are split along their outermost dimension and stay resident.
+ * A group owns an NCCL communicator (NCCL is loaded at run time; B200_ERR_UNSUPPORTED if it is
+ * missing).  All exchanges are enqueued on the context's streams and do not synchronise the host.
+ * Every call is collective: all ranks of the group make it, in the same order.  A rank that does not
+ * arrive within `deadline_s` seconds (60 if <= 0) makes the call fail with B200_ERR_TIMEOUT on the
+ * others and aborts the group. */
+#define B200_GROUP_ID_BYTES 128
+/* A fresh rendezvous id: one rank creates it and hands the bytes to the others by any host channel. */
+int b200_group_unique_id(uint8_t out[B200_GROUP_ID_BYTES]);
+int b200_group_create(b200_ctx* ctx, const uint8_t id[B200_GROUP_ID_BYTES], int rank, int world, double deadline_s,
+                      b200_group** out);
+void b200_group_destroy(b200_group* group);
+int b200_group_rank(b200_group* group, int* rank, int* world);
+/* Folds and scan carries: every rank's array `src` (n elements, any rank, same n everywhere) becomes
+ * elements [r*n, (r+1)*n) of a new vector of world*n elements, in rank order, on every rank. */
+int b200_group_all_gather(b200_group* group, uint64_t src, uint64_t* dst);
+/* Permute: element-wise reduction of `arr` over the ranks, in place.  op: 0 (+), 1 min, 2 max, 3 (*). */
+int b200_group_all_reduce(b200_group* group, uint64_t arr, int op);
+/* Stencils: `arr` is a (top + rows + bot) x cols row slab with `top`/`bot` spare rows for the
+ * neighbours' rows.  Sends this rank's first and last `radius` rows to ranks `up` / `down` (-1 = no such
+ * neighbour) and receives theirs into the spare rows.  With `overlap` the exchange runs on a second
+ * stream, after everything submitted so far and beside whatever is submitted next;
+ * b200_group_halo_wait makes the context's stream wait for it (call it before launching work that
+ * reads the spare rows). */
+int b200_group_halo_exchange(b200_group* group, uint64_t arr, int64_t top, int64_t rows, int64_t bot, int64_t radius,
+                             int up, int down, int overlap);
+int b200_group_halo_wait(b200_group* group);
 
 /* Generate and NVRTC-compile every kernel of a program for sm_100a without
  * touching a GPU (build-time check).  `log` receives diagnostics. */

@@ -101,6 +101,14 @@ def main(ref):
             ("maximum_mat", "run $ maximum (use mat)", 1),
             ("gather", "run $ gather (use from) (use input)", 1),
             ("scatter", "run $ scatter (use to) (fill (constant (Z:.10)) 0) (use input)", 1),
+            ("scanlSeg_mat", "run $ scanlSeg (+) 0 (use mat) (use seg)", 1),
+            ("scanl_primeSeg_res", "res", 1),
+            ("scanl_primeSeg_sums", "sums", 1),
+            ("scanl1Seg_mat", "run $ scanl1Seg (+) (use mat) (use seg)", 1),
+            ("scanrSeg_mat", "run $ scanrSeg (+) 0 (use mat) (use seg)", 1),
+            ("scanr_primeSeg_res", "res", 2),
+            ("scanr_primeSeg_sums", "sums", 2),
+            ("scanr1Seg_mat", "run $ scanr1Seg (+) (use mat) (use seg)", 1),
         ],
     }
     for fname, cases in doc_cases.items():

@@ -79,6 +79,9 @@ def cases():
     mp, ms = A.scanl_prime(add, 0, mat4x10)
     t4 = np.arange(10, dtype=I)
     efl = (np.full(100, 1.01, np.float32), np.zeros(100, np.float32))
+    seg4 = np.array([1, 4, 0, 3], I)
+    spr, sps = A.scanl_primeSeg(add, 0, mat5x10, seg4)
+    rpr, rps = A.scanr_primeSeg(add, 0, mat5x10, seg4)
     c = {
         "generate_plus1": A.generate(A.index(10), lambda ix: ix[0] + 1),                              # Language.hs:288
         "map_plus1": A.map(lambda x: x + 1, vec10),                                                   # Language.hs:412-416
@@ -95,6 +98,12 @@ def cases():
                                       A.fill(A.index(5), A.constant(1))),                             # Language.hs:734-743
         "backpermute_transpose": A.backpermute(A.index(matu.shape[1], matu.shape[0]), lambda ix: A.index(ix[1], ix[0]), matu),
         "foldSeg_mat": A.foldSeg(add, 0, mat5x10, np.array([1, 4, 0, 3], I)),                         # Prelude.hs:689-702
+        "scanlSeg_mat": A.scanlSeg(add, 0, mat5x10, seg4),                                            # Prelude.hs:954-977
+        "scanl_primeSeg_res": spr, "scanl_primeSeg_sums": sps,                                        # Prelude.hs:1023-1050
+        "scanl1Seg_mat": A.scanl1Seg(add, mat5x10, seg4),                                             # Prelude.hs:1121-1136
+        "scanrSeg_mat": A.scanrSeg(add, 0, mat5x10, seg4),                                            # Prelude.hs:1183-1198
+        "scanr_primeSeg_res": rpr, "scanr_primeSeg_sums": rps,                                        # Prelude.hs:1232-1257
+        "scanr1Seg_mat": A.scanr1Seg(add, mat5x10, seg4),                                             # Prelude.hs:1296-1313
         "sum_mat": A.sum(np.arange(10, dtype=I).reshape(2, 5)),                                       # Prelude.hs:822-823
         "minimum_mat": A.minimum(m34), "maximum_mat": A.maximum(m34),                                 # Prelude.hs:849-877
         "gather": A.gather(frm, in9),                                                                 # Prelude.hs:1696-1698

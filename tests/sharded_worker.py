@@ -75,7 +75,9 @@ def main(rank, world, port):
         from accelerate_b200.sharded import GpuExecutor
         torch.cuda.set_device(rank)
         dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
-        ex = GpuExecutor(backend.Context(rank))
+        # "gpu": the exchange steps run inside the C-ABI library (its own NCCL communicator);
+        # "gpu-torch": through torch.distributed on views of the device arrays
+        ex = GpuExecutor.with_group(backend.Context(rank), deadline_s=120.0) if sys.argv[4] == "gpu" else GpuExecutor(backend.Context(rank))
     else:
         dist.init_process_group("gloo", rank=rank, world_size=world)
         ex = OracleExecutor()
@@ -164,7 +166,7 @@ def main(rank, world, port):
     sys.exit(0)
 
 
-GPU = len(sys.argv) > 4 and sys.argv[4] == "gpu"
+GPU = len(sys.argv) > 4 and sys.argv[4].startswith("gpu")
 
 if __name__ == "__main__":
     main(int(sys.argv[1]), int(sys.argv[2]), int(sys.argv[3]))

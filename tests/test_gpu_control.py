@@ -66,3 +66,30 @@ def test_gpu_kernel_cache_hits_across_sizes(gpu_ctx):
     s1 = gpu_ctx.stats()
     assert s1["compiled"] == s0["compiled"] and s1["disk_hits"] == s0["disk_hits"]
     assert s1["mem_hits"] > s0["mem_hits"]
+
+
+def test_gpu_memory_table_uploads_a_host_array_once(gpu_ctx):
+    # the reference's memory table (Array/Remote/Table.hs:89-100): arrays are keyed by their unique id, so
+    # a host array that several runs use travels to the device once
+    from accelerate_b200 import language as L
+    x = np.arange(1 << 16, dtype=np.int32)
+    L.reset_names()
+    prog = A.build_program(A.map(lambda v: v + 1, L.param(1, "i32")))
+    key = 0xABCDEF01
+    s0 = gpu_ctx.stats()["h2d_bytes"]
+    for _ in range(3):
+        d = gpu_ctx.intern(key, x)
+        out, = gpu_ctx.execute(prog.text, [d], 1)
+        assert np.array_equal(out.download(), x + 1)
+        d.free()                                     # the id goes, the table keeps the device copy
+        out.free()
+    assert gpu_ctx.stats()["h2d_bytes"] - s0 == x.nbytes
+    with pytest.raises(backend.B200Error) as e:
+        gpu_ctx.intern(key, x[:100])
+    assert e.value.code == 7
+    gpu_ctx.forget(key)
+    d = gpu_ctx.intern(key, x)
+    out, = gpu_ctx.execute(prog.text, [d], 1)
+    assert np.array_equal(out.download(), x + 1)
+    assert gpu_ctx.stats()["h2d_bytes"] - s0 == 2 * x.nbytes
+    gpu_ctx.forget(key)

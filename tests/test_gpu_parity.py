@@ -357,17 +357,21 @@ def test_histogram(n, bins):
 @pytest.mark.parametrize("bins", [70001, 65536, 100000])
 @pytest.mark.parametrize("vals", ["ones", "mixed"])
 def test_permute_add_int32_large_target_packed_fields(bins, vals):
-    # (+) into an Int32 target of 51 201 .. 114 688 elements: the kernel keeps 16-bit fields per CTA and
-    # compensates every wrap of a field.  Two neighbouring elements receive most of the updates (so
-    # their fields wrap many times, the lower one carrying into the upper one), the addends include
-    # values above 16 bits and negative ones, and the last element of an odd-sized target is hit too.
+    # (+) into an Int32 target of 51 201 .. 114 688 elements: every element is private to the CTA, the
+    # leading ones as 32-bit words, the others as 16-bit fields whose wraps are compensated.  Neighbouring
+    # elements of the second kind receive most of the updates (so their fields wrap many times, lower
+    # ones carrying into upper ones), the addends include values above 16 bits and negative ones, and
+    # the last element of an odd-sized target is hit too.
     n = 3_000_000
     g = np.random.default_rng(bins)
     keys = g.integers(0, bins, size=n).astype(np.int32)
     hot = g.random(n)
-    keys[hot < 0.30] = 12344
-    keys[(hot >= 0.30) & (hot < 0.55)] = 12345
+    # four neighbouring elements near the end (16-bit fields of both parities), the last element, and one
+    # element near the start (which has a 32-bit word of its own)
+    for k, (lo, hi) in enumerate([(0.0, 0.15), (0.15, 0.30), (0.30, 0.42), (0.42, 0.55)]):
+        keys[(hot >= lo) & (hot < hi)] = bins - 6 + k
     keys[(hot >= 0.55) & (hot < 0.60)] = bins - 1
+    keys[(hot >= 0.60) & (hot < 0.70)] = 12344
     if vals == "ones":
         v = np.ones(n, np.int32)
     else:

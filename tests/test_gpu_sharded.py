@@ -11,7 +11,8 @@ pytestmark = pytest.mark.gpu
 HERE = os.path.dirname(os.path.abspath(__file__))
 
 
-def test_two_gpu_sharded_run_matches_oracle():
+@pytest.mark.parametrize("mode", ["gpu", "gpu-torch"])
+def test_two_gpu_sharded_run_matches_oracle(mode):
     import torch
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
@@ -20,7 +21,7 @@ def test_two_gpu_sharded_run_matches_oracle():
     port = s.getsockname()[1]
     s.close()
     env = dict(os.environ, NCCL_NVLS_ENABLE="0")
-    procs = [subprocess.Popen([sys.executable, os.path.join(HERE, "sharded_worker.py"), str(r), "2", str(port), "gpu"],
+    procs = [subprocess.Popen([sys.executable, os.path.join(HERE, "sharded_worker.py"), str(r), "2", str(port), mode],
                               stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True, env=env) for r in range(2)]
     outs = [p.communicate(timeout=600)[0] for p in procs]
     assert all(p.returncode == 0 for p in procs), "\n".join(outs)

@@ -137,3 +137,64 @@ def test_stencil2_matches_two_list_references(ext1, ext2):
         got = oracle.run(A.stencil2(f_acc, b1, a, b2, b, extent1=ext1, extent2=ext2))
         assert got.shape == tuple(min(x, y) for x, y in zip(sh1, sh2))
         assert np.array_equal(got, want.reshape(got.shape)), (ext1, ext2, sh1, sh2, k1, k2)
+
+
+# ---- segmented scans against list references (Test/NoFib/Prelude/Scan.hs:263-468, 850-946) --------
+def _segments(rnd, total_cap):
+    seg = []
+    while sum(seg) < total_cap and len(seg) < 12:
+        seg.append(rnd.choice([0, 0, 1, 2, 3, 5, 9]))
+    return seg
+
+
+@pytest.mark.parametrize("seed", range(12))
+def test_segmented_scans_match_list_references(seed):
+    import random
+    rnd = random.Random(seed)
+    seg = _segments(rnd, rnd.randint(0, 40)) if seed else []
+    n = sum(seg)
+    rows = rnd.randint(1, 3)
+    m = np.random.default_rng(seed).integers(-20, 20, size=(rows, n)).astype(np.int64)
+    sg = np.array(seg, np.int64)
+    f = lambda a, b: a * 2 + b                                     # noqa: E731  (not commutative: order of operands shows)
+    pf = lambda a, b: 2 * a + b                                    # noqa: E731
+    z = 3
+    parts = lambda row: np.split(row, np.cumsum(seg)[:-1]) if seg else []   # noqa: E731
+
+    def lscan(xs, seeded):
+        out, acc = [], (z if seeded else None)
+        if seeded:
+            out.append(acc)
+        for x in xs:
+            acc = int(x) if acc is None else pf(acc, int(x))
+            out.append(acc)
+        return out
+
+    def rscan(xs, seeded):
+        out, acc = [], (z if seeded else None)
+        if seeded:
+            out.append(acc)
+        for x in reversed(xs):
+            acc = int(x) if acc is None else pf(int(x), acc)
+            out.append(acc)
+        return out[::-1]
+
+    def rows_of(fn):
+        return np.array([sum((fn(list(p)) for p in parts(r)), []) for r in m], np.int64).reshape(rows, -1)
+    if n > 0:
+        assert np.array_equal(oracle.run(A.scanl1Seg(f, m, sg)), rows_of(lambda p: lscan(p, False)))
+        if seg[0] == 0:
+            # mkTailFlags (Prelude.hs:1379-1390) puts the flag of a leading empty segment at index -1:
+            # the reference's own permute raises its bounds error there, and so does the restatement
+            with pytest.raises(oracle.OracleError, match="out of bounds"):
+                oracle.run(A.scanr1Seg(f, m, sg))
+        else:
+            assert np.array_equal(oracle.run(A.scanr1Seg(f, m, sg)), rows_of(lambda p: rscan(p, False)))
+    assert np.array_equal(oracle.run(A.scanlSeg(f, z, m, sg)), rows_of(lambda p: lscan(p, True)))
+    assert np.array_equal(oracle.run(A.scanrSeg(f, z, m, sg)), rows_of(lambda p: rscan(p, True)))
+    body, sums = oracle.run(list(A.scanl_primeSeg(f, z, m, sg)))
+    assert np.array_equal(body, rows_of(lambda p: lscan(p, True)[:-1]))
+    assert np.array_equal(sums, rows_of(lambda p: lscan(p, True)[-1:]))
+    body, sums = oracle.run(list(A.scanr_primeSeg(f, z, m, sg)))
+    assert np.array_equal(body, rows_of(lambda p: rscan(p, True)[1:]))
+    assert np.array_equal(sums, rows_of(lambda p: rscan(p, True)[:1]))
