@@ -767,9 +767,6 @@ Glue build_glue(const Node& n, const std::map<std::string, ArrayInfo>& arrays) {
         def["PERMUTE_BYTES"] = std::to_string(ty_bytes[l[0]]);
         def["PERMUTE_SIGNED"] = ty_is_signed(l[0]) ? "1" : "0";
         def["PERMUTE_FLOAT"] = ty_is_float(l[0]) ? "1" : "0";
-        // every source element is the literal 1 (the histogram idiom, `permute (+) zeros ix (fill sh 1)`)
-        const Expr& src = *n.d[0].index->body;
-        def["PERMUTE_UNIT"] = (!n.d[0].manifest && src.kind == X_CONST && ty_is_int(l[0]) && src.lit == "1") ? "1" : "0";
       }
       break;
     }

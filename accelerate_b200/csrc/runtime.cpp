@@ -203,71 +203,50 @@ constexpr int SCAN_BACKOFF_DEFAULT = 0;
 int scan_rounds(const Type& elt) {
   size_t bytes = 0;
   for (Ty t : elt.leaves()) bytes += ty_bytes[t];
-  int r = bytes <= 8 ? 8 : 4;
-  if (const char* e = getenv("ACCELERATE_B200_SCAN_ROUNDS")) r = std::max(1, atoi(e));
-  return r;
+  return bytes <= 8 ? 8 : 4;
 }
 // Short rows: the kernel's time is the latency of one tile plus the look-back chain, so many small
 // tiles that all start at once beat few large ones.
 constexpr int64_t SCAN_SMALL_ELEMS = 1 << 21;
 constexpr int SCAN_SMALL_ROUNDS = 2;
 bool scan_is_small(int64_t total_elems) {
-  return total_elems <= SCAN_SMALL_ELEMS && !getenv("ACCELERATE_B200_SCAN_ROUNDS") && !getenv("ACCELERATE_B200_SCAN_NO_SMALL");
+  // ACCELERATE_B200_SCAN_NO_SMALL lets tests reach the long-row kernels with inputs a CPU check finishes quickly
+  return total_elems <= SCAN_SMALL_ELEMS && !getenv("ACCELERATE_B200_SCAN_NO_SMALL");
 }
 std::map<std::string, std::string> scan_variant(const Type& elt, bool small = false) {
   size_t bytes = 0;
   for (Ty t : elt.leaves()) bytes += ty_bytes[t];
   const int rounds = small ? std::min(scan_rounds(elt), SCAN_SMALL_ROUNDS) : scan_rounds(elt);
-  std::string minb = bytes * rounds <= 16 ? "4" : (bytes * rounds <= 64 ? "2" : "1");
-  if (const char* e = getenv("ACCELERATE_B200_SCAN_MIN_BLOCKS")) minb = e;
-  std::map<std::string, std::string> v = {{"SCAN_MIN_BLOCKS", minb}, {"SCAN_ROUNDS", std::to_string(rounds)}};
-  if (const char* e = getenv("ACCELERATE_B200_SCAN_LOOK")) v["SCAN_LOOK"] = e;
-  if (const char* e = getenv("ACCELERATE_B200_SCAN_DESC_SPLIT")) v["SCAN_DESC_SPLIT"] = e;
-  return v;
+  const std::string minb = bytes * rounds <= 16 ? "4" : (bytes * rounds <= 64 ? "2" : "1");
+  return {{"SCAN_MIN_BLOCKS", minb}, {"SCAN_ROUNDS", std::to_string(rounds)}};
 }
 // Spacing of look-back descriptors (in descriptors) and pause after an unsuccessful poll.
 // Spread descriptors cost total_tiles * 16 * stride bytes of scratch, so long lists of tiles stay dense.
 int scan_desc_stride(int64_t total_tiles) {
-  if (const char* e = getenv("ACCELERATE_B200_SCAN_DESC_STRIDE")) return std::max(1, atoi(e));
   // at most 64 MiB of descriptors
   return total_tiles <= 262144 ? SCAN_DESC_STRIDE_DEFAULT : (total_tiles <= 1048576 ? 4 : 1);
 }
 void scan_poll_variant(std::map<std::string, std::string>& v, int64_t total_tiles) {
   v["SCAN_DESC_STRIDE"] = std::to_string(scan_desc_stride(total_tiles));
-  const char* e = getenv("ACCELERATE_B200_SCAN_BACKOFF");
-  v["SCAN_BACKOFF_NS"] = e && *e ? std::string(e) : std::to_string(SCAN_BACKOFF_DEFAULT);
+  v["SCAN_BACKOFF_NS"] = std::to_string(SCAN_BACKOFF_DEFAULT);
 }
-// shape of the shared-memory ring scan kernel (overridable for tuning)
+// Shape of the shared-memory ring scan kernel: tiles of 1024*rounds elements, `slots` tiles in flight per
+// CTA, `minb` CTAs per SM, one look-back and one reducer warp, `look` descriptors polled per lane step,
+// finishers take a slot once it is scanned (grab 1), one look-back descriptor per `batch` tiles.
 struct RingShape { int rounds, slots, minb, lbw, redw, look, grab, batch; };
-RingShape scan_ring_shape(int bytes) {
-  auto tune = [](const char* name, int dflt) { const char* e = getenv(name); return e && *e ? atoi(e) : dflt; };
-  RingShape r;
-  r.rounds = tune("ACCELERATE_B200_RING_ROUNDS", bytes <= 4 ? 8 : 4);
-  r.slots = tune("ACCELERATE_B200_RING_SLOTS", 3);
-  r.minb = tune("ACCELERATE_B200_RING_MIN_BLOCKS", 2);
-  r.lbw = std::max(1, tune("ACCELERATE_B200_RING_LB_WARPS", 1));
-  r.redw = std::max(1, tune("ACCELERATE_B200_RING_RED_WARPS", 1));
-  r.look = std::max(1, tune("ACCELERATE_B200_SCAN_LOOK", 4));
-  r.grab = tune("ACCELERATE_B200_RING_GRAB", 1);
-  r.batch = std::max(1, tune("ACCELERATE_B200_RING_BATCH", 2));
-  return r;
-}
+RingShape scan_ring_shape(int bytes) { return {bytes <= 4 ? 8 : 4, 3, 2, 1, 1, 4, 1, 2}; }
 std::map<std::string, std::string> scan_ring_variant(const RingShape& r, int64_t total_tiles) {
   std::map<std::string, std::string> v = {{"SCAN_RING", "1"}, {"SCAN_ROUNDS", std::to_string(r.rounds)}, {"SCAN_SLOTS", std::to_string(r.slots)},
                                           {"SCAN_MIN_BLOCKS", std::to_string(r.minb)}, {"SCAN_LB_WARPS", std::to_string(r.lbw)},
                                           {"RING_RED_WARPS", std::to_string(r.redw)}, {"SCAN_LOOK", std::to_string(r.look)},
                                           {"RING_GRAB_STATE", std::to_string(r.grab)}, {"RING_BATCH", std::to_string(r.batch)}};
-  if (const char* e = getenv("ACCELERATE_B200_SCAN_DESC_SPLIT")) v["SCAN_DESC_SPLIT"] = e;
   scan_poll_variant(v, total_tiles);
   return v;
 }
-// launch shape of the register-window rank-2 stencil kernel (overridable for tuning)
+// launch shape of the register-window rank-2 stencil kernel: warps per CTA, rows per warp task,
+// CTAs per SM asked of the compiler, rows loaded ahead
 struct Stencil2dShape { int warps, rows, minb, depth; };
-Stencil2dShape stencil2d_shape() {
-  auto tune = [](const char* name, int dflt) { const char* e = getenv(name); return e && *e ? atoi(e) : dflt; };
-  return {tune("ACCELERATE_B200_ST2_WARPS", 4), tune("ACCELERATE_B200_ST2_ROWS", 32), tune("ACCELERATE_B200_ST2_MIN_BLOCKS", 1),
-          tune("ACCELERATE_B200_ST2_DEPTH", 4)};
-}
+Stencil2dShape stencil2d_shape() { return {4, 32, 1, 4}; }
 std::map<std::string, std::string> stencil2d_variant() {
   Stencil2dShape s = stencil2d_shape();
   return {{"ST2_WARPS", std::to_string(s.warps)}, {"ST2_ROWS", std::to_string(s.rows)}, {"ST2_MIN_BLOCKS", std::to_string(s.minb)},
@@ -929,7 +908,7 @@ void Program::exec_kernel_node(const Node& n, Env& env_ref) {
                                   df.at("D0_STREAM_BYTES") == df.at("SCAN_T_BYTES");
           const int bytes = packed ? atoi(df.at("SCAN_T_BYTES").c_str()) : 0;
           // 8-byte elements halve the elements a ring holds; the register-resident kernel is faster for them
-          const bool want = getenv("ACCELERATE_B200_SCAN_RING") ? true : (bytes <= 4 && !small && !getenv("ACCELERATE_B200_SCAN_NO_RING"));
+          const bool want = bytes <= 4 && !small;
           if (one_stream && want && L.fast("D0") && in_vec && out_vec && scan_ring_aligned(bytes, m, rows, right)) {
             const RingShape rs = scan_ring_shape(bytes);
             const int rounds = rs.rounds, slots = rs.slots, look = rs.look;
@@ -1011,10 +990,8 @@ void Program::exec_kernel_node(const Node& n, Env& env_ref) {
         const bool atomic = mode.find("ATOMIC") != std::string::npos;
         const int bytes = atomic ? atoi(st.glue.defines.at("PERMUTE_BYTES").c_str()) : 0;
         const int64_t cap = 200 * 1024;
-        const char* no_priv = getenv("ACCELERATE_B200_NO_PRIVATISE");
         const bool int_add32 = mode == "PERMUTE_ATOMIC_ADD" && bytes == 4 && st.glue.defines.at("PERMUTE_FLOAT") == "0";
-        const bool fields16 = int_add32 && !no_priv && out_n > cap / 4 && (out_n + 1) / 2 <= 56 * 1024 && total >= 8 * out_n &&
-                              !getenv("ACCELERATE_B200_NO_SMEM16");
+        const bool fields16 = int_add32 && out_n > cap / 4 && (out_n + 1) / 2 <= 56 * 1024 && total >= 8 * out_n;
         L.named["choice"] = 0;
         if (fields16) {
           // (+) on 32-bit integers, target too large for a CTA-private 32-bit copy but not for 16-bit
@@ -1037,12 +1014,11 @@ void Program::exec_kernel_node(const Node& n, Env& env_ref) {
           L.launch(k, std::max<int64_t>(grid, 1), 1024, smem);
           // (falls through to the partial 32-bit copy, which runs only if the sample chose it)
         }
-        if (atomic && !no_priv && out_n > 0 && total >= 8 * out_n && total >= (1 << 16)) {
+        if (atomic && out_n > 0 && total >= 8 * out_n && total >= (1 << 16)) {
           // CTA-private copy of the first `priv` target elements in shared memory
           const int64_t priv = std::min<int64_t>(out_n, cap / bytes);
           const size_t smem = (size_t)priv * bytes;
           std::map<std::string, std::string> var = {{"PERMUTE_SMEM", "1"}, {"PERMUTE_THREADS", "1024"}};
-          if (const char* e = getenv("ACCELERATE_B200_PERMUTE_UNROLL")) var["PERMUTE_UNROLL"] = e;
           CompiledKernel& k = c.kernel(assemble_source(st.glue, "permute", var), "acc_permute", 1024, smem);
           if (smem > 48 * 1024) c.check(c.drv.FuncSetAttribute(k.fn, CU_FUNC_ATTRIBUTE_MAX_DYNAMIC_SHARED_SIZE_BYTES, (int)smem), "cuFuncSetAttribute");
           int nb = 1;
@@ -1053,9 +1029,7 @@ void Program::exec_kernel_node(const Node& n, Env& env_ref) {
           L.launch(k, std::max<int64_t>(grid, 1), 1024, smem);
         } else {
           L.named["priv"] = 0;
-          std::map<std::string, std::string> pvar;
-          if (const char* e = getenv("ACCELERATE_B200_PERMUTE_UNROLL")) pvar["PERMUTE_UNROLL"] = e;
-          CompiledKernel& k = c.kernel(assemble_source(st.glue, "permute", pvar), "acc_permute", 512, 0);
+          CompiledKernel& k = c.kernel(assemble_source(st.glue, "permute", {}), "acc_permute", 512, 0);
           const int64_t work = L.named["vec"] ? (total + 3) / 4 : total;
           int64_t grid = std::min<int64_t>((work + 511) / 512, (int64_t)c.sm_count * k.max_blocks_per_sm * 2);
           L.launch(k, std::max<int64_t>(grid, 1), 512, 0);
@@ -1089,7 +1063,7 @@ void Program::exec_kernel_node(const Node& n, Env& env_ref) {
         const int64_t row0 = window ? window->lo : 0, row1 = window ? window->hi : o[1];
         L.named["row0"] = row0;
         L.named["row1"] = row1;
-        if (rank == 2 && o[1] < 2000000000 && o[2] < 2000000000 && (window || !getenv("ACCELERATE_B200_STENCIL_SMEM"))) {
+        if (rank == 2 && o[1] < 2000000000 && o[2] < 2000000000) {
           // register-window kernel: warp tasks of 128 columns x ST2_ROWS (32) rows
           const Stencil2dShape shp = stencil2d_shape();
           const int warps = shp.warps, rows = shp.rows;

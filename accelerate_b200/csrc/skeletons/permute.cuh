@@ -106,9 +106,6 @@ __device__ __forceinline__ PERMUTE_T permute_identity() {
 #ifndef PERMUTE_SMEM16
 #define PERMUTE_SMEM16 0
 #endif
-#ifndef PERMUTE_UNIT
-#define PERMUTE_UNIT 0
-#endif
 #if PERMUTE_SMEM || PERMUTE_SMEM16
 extern __shared__ __align__(16) unsigned char permute_smem_raw[];
 #endif

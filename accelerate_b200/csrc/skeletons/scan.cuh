@@ -92,26 +92,6 @@ __device__ __forceinline__ u32 scan_desc_load(i64 base, i64 idx, SCAN_T& v) {
   memcpy(&v, &bits, sizeof(SCAN_T));
   return (u32)(w >> 32);
 }
-#elif defined(SCAN_DESC_SPLIT) && SCAN_DESC_SPLIT
-// 8-byte values as two independent 8-byte words {status, low half} {status, high half}: each word is
-// written and read with one 64-bit access; a reader takes the descriptor only if both words carry
-// the same status (a torn view reads as "not there yet").
-__device__ __forceinline__ void scan_desc_store(i64 base, i64 idx, u32 status, SCAN_T v) {
-  u64 bits = 0;
-  memcpy(&bits, &v, sizeof(SCAN_T));
-  u64* w = reinterpret_cast<u64*>(base) + 2 * idx * SCAN_DESC_STRIDE;
-  asm volatile("st.relaxed.gpu.global.u64 [%0], %1;" ::"l"(w), "l"(((u64)status << 32) | (bits & 0xffffffffull)) : "memory");
-  asm volatile("st.relaxed.gpu.global.u64 [%0], %1;" ::"l"(w + 1), "l"(((u64)status << 32) | (bits >> 32)) : "memory");
-}
-__device__ __forceinline__ u32 scan_desc_load(i64 base, i64 idx, SCAN_T& v) {
-  u64 a, b;
-  const u64* w = reinterpret_cast<const u64*>(base) + 2 * idx * SCAN_DESC_STRIDE;
-  asm volatile("ld.relaxed.gpu.global.u64 %0, [%1];" : "=l"(a) : "l"(w) : "memory");
-  asm volatile("ld.relaxed.gpu.global.u64 %0, [%1];" : "=l"(b) : "l"(w + 1) : "memory");
-  const u64 bits = (a & 0xffffffffull) | (b << 32);
-  memcpy(&v, &bits, sizeof(SCAN_T));
-  return (u32)(a >> 32) == (u32)(b >> 32) ? (u32)(a >> 32) : 0u;
-}
 #else
 // 16-byte descriptor {value bits, status}: one aligned 128-bit access
 __device__ __forceinline__ void scan_desc_store(i64 base, i64 idx, u32 status, SCAN_T v) {
