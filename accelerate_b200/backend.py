@@ -74,6 +74,8 @@ def lib():
         l.b200_group_halo_wait.argtypes = [vp]
         l.b200_sync.argtypes = [vp]
         l.b200_stats.argtypes = [vp, i64p]
+        l.b200_memory_stats.argtypes = [vp, i64p]
+        l.b200_ctx_purge.argtypes = [vp]
         l.b200_ctx_stream.argtypes = [vp, ctypes.POINTER(vp)]
         l.b200_compile_check.argtypes = [cp, ctypes.c_size_t, ctypes.c_char_p, ctypes.c_size_t]
         l.b200_kernel_source.argtypes = [cp, ctypes.c_size_t, ctypes.c_int, ctypes.c_char_p, ctypes.c_size_t]
@@ -282,6 +284,16 @@ class Context:
         _check(lib().b200_stats(self.h, out))
         keys = ["launches", "h2d_bytes", "d2h_bytes", "compiled", "mem_hits", "disk_hits", "allocated_bytes", "runs"]
         return dict(zip(keys, [int(v) for v in out]))
+
+    def memory_stats(self):
+        """Live bytes, and the freed buffers kept for reuse (the nursery): bytes, count, allocations served."""
+        out = (ctypes.c_int64 * 5)()
+        _check(lib().b200_memory_stats(self.h, out))
+        return dict(zip(["live_bytes", "nursery_bytes", "nursery_blocks", "nursery_hits", "inplace_permutes"], [int(v) for v in out]))
+
+    def purge(self):
+        """Hand the kept buffers back to the driver."""
+        _check(lib().b200_ctx_purge(self.h))
 
     def stream(self):
         s = ctypes.c_void_p()

@@ -91,6 +91,11 @@ int b200_ctx_create(int device, uint32_t flags, b200_ctx** out) {
   c.check(cudaDeviceGetDefaultMemPool(&pool, device), "cudaDeviceGetDefaultMemPool");
   uint64_t threshold = ~0ull;
   c.check(cudaMemPoolSetAttribute(pool, cudaMemPoolAttrReleaseThreshold, &threshold), "cudaMemPoolSetAttribute");
+  {
+    size_t free_b = 0, total_b = 0;
+    c.check(cudaMemGetInfo(&free_b, &total_b), "cudaMemGetInfo");
+    c.nursery.limit = total_b / 2;
+  }
   c.check(cudaMalloc((void**)&c.d_words, 64), "cudaMalloc");
   c.check(cudaMemset(c.d_words, 0, 64), "cudaMemset");
   if (const char* s = getenv("ACCELERATE_B200_SPIN_LIMIT")) c.spin_limit = atoll(s);
@@ -109,6 +114,7 @@ void b200_ctx_destroy(b200_ctx* ctx) {
     c.arrays.clear();
     c.table.clear();
     c.reap(true);
+    c.purge();
     for (auto& k : c.kernels)
       if (k.second.module) c.drv.ModuleUnload(k.second.module);
     c.kernels.clear();
@@ -435,6 +441,26 @@ int b200_stats(b200_ctx* ctx, int64_t out[8]) {
   out[5] = c.cstats.disk_hits;
   out[6] = c.allocated;
   out[7] = c.runs;
+  B200_END
+}
+
+int b200_memory_stats(b200_ctx* ctx, int64_t out[5]) {
+  B200_TRY
+  Ctx& c = ctx->c;
+  std::lock_guard<std::mutex> g(c.nursery.mu);
+  out[0] = c.allocated;
+  out[1] = (int64_t)c.nursery.bytes;
+  out[2] = (int64_t)c.nursery.blocks.size();
+  out[3] = c.nursery.hits;
+  out[4] = c.inplace_permutes;
+  B200_END
+}
+
+int b200_ctx_purge(b200_ctx* ctx) {
+  B200_TRY
+  Ctx& c = ctx->c;
+  c.check(cudaSetDevice(c.device), "cudaSetDevice");
+  c.purge();
   B200_END
 }
 

@@ -639,10 +639,21 @@ struct GlueBuilder {
         glue.slots.push_back({Slot::OUT_LEAF, "", (int)(k * 64 + i)});
       }
     }
+    // Names that start with '?' are wanted by some variants of the node's kernels only: they come last
+    // (the host always passes them) and are declared when the variant defines ACC_OPT_PARAMS.  A kernel
+    // that does not use them keeps the parameter block, and with it the code the compiler generates,
+    // unchanged when such a field is added.
+    bool opt = false;
     for (auto& n : ps.named) {
-      pb << "  i64 " << n << ";\n";
-      glue.slots.push_back({Slot::NAMED, n, 0});
+      const bool o = !n.empty() && n[0] == '?';
+      if (opt && !o) throw Error(B200_ERR_ARG, "optional kernel parameters must come last");
+      if (o && !opt) pb << "#if defined(ACC_OPT_PARAMS) && ACC_OPT_PARAMS\n";
+      opt = opt || o;
+      const std::string field = o ? n.substr(1) : n;
+      pb << "  i64 " << field << ";\n";
+      glue.slots.push_back({Slot::NAMED, field, 0});
     }
+    if (opt) pb << "#endif\n";
     pb << "};\n";
     // element structs do not depend on Params; functions do
     glue.code = ps.struct_code + pb.str() + fns.str();
@@ -873,6 +884,10 @@ Glue build_glue(const Node& n, const std::map<std::string, ArrayInfo>& arrays) {
           def["ST_RYMAX"] = std::to_string(rymax);
           def["ST_H"] = std::to_string(2 * rymax + 1);
           std::string win_decl, win_params, win_args, issue_all, commit_all, lane_fast, issue_fast, all_fast, min_e0;
+          // shared-memory staging of input rows (acc_stencil2d_bulk): every input must be read through streams
+          // whose leaves are at least 4 bytes wide (a row segment then starts on a 16-byte boundary)
+          std::string take_all, bulk_all, stage_off = "0";
+          bool bulk_ok = true;
           for (size_t a = 0; a < nin; ++a) {
             const std::string A = std::to_string(a);
             const int rx = n.st_extent[a][1] / 2;
@@ -922,6 +937,24 @@ Glue build_glue(const Node& n, const std::map<std::string, ArrayInfo>& arrays) {
             for (size_t i = 0; i < l.size(); ++i)
               b.fns << "  _Pragma(\"unroll\") for (int k = 0; k < 4; ++k) w" << A << "_l" << i << "[SLOT][" << rx << " + k] = own[k].l" << i << ";\n";
             b.fns << "}\n";
+            size_t min_leaf = 16;
+            for (auto& sn : b.glue.streams[a])
+              for (Ty t : b.ps.array(sn).elt.leaves()) min_leaf = std::min(min_leaf, (size_t)ty_bytes[t]);
+            if (def.count("D" + A + "_STREAM_NLEAVES") && min_leaf >= 4) {
+              // the same row out of its staged copy: `seg` points at this input's part of the row slot
+              b.fns << "#if defined(ST2_BULK) && ST2_BULK\n"
+                    << "template <int SLOT> __device__ __forceinline__ void ST2_take" << A << "(const Params& p, const unsigned char* seg, int gy, int gx0, int lane" << wp << ") {\n"
+                    << "  " << S << " own[4];\n"
+                    << "  D" << A << "_get4_sm(p, gy, gx0, seg, lane * 4, own);\n";
+              for (size_t i = 0; i < l.size(); ++i)
+                b.fns << "  _Pragma(\"unroll\") for (int k = 0; k < 4; ++k) w" << A << "_l" << i << "[SLOT][" << rx << " + k] = own[k].l" << i << ";\n";
+              b.fns << "}\n#endif\n";
+              take_all += "ST2_take" + A + "<SLOT>(p, (ROWBASE) + (" + stage_off + "), GY, gx0, lane" + wa + "); ";
+              bulk_all += "D" + A + "_BULK_ISSUE((ROWBASE) + (" + stage_off + "), BAR, (i64)(GY) * (i64)(int)" + e1 + " + (i64)(GX0)) ";
+              stage_off += " + D" + A + "_STAGE_BYTES";
+            } else {
+              bulk_ok = false;
+            }
             b.fns << "template <int SLOT> __device__ __forceinline__ void ST2_commit" << A << "(int lane" << wp << ") {\n  (void)lane;\n";
             for (int j = 1; j <= rx; ++j) {
               for (size_t i = 0; i < l.size(); ++i) {
@@ -941,6 +974,12 @@ Glue build_glue(const Node& n, const std::map<std::string, ArrayInfo>& arrays) {
           def["ST2_ISSUE_ALL_FAST(SLOT, GY)"] = issue_fast;
           def["ST2_ALL_LANE_FAST"] = "(" + all_fast + ")";
           def["ST2_MIN_E0"] = "(" + min_e0 + ")";
+          def["ST2_BULK_OK"] = bulk_ok ? "1" : "0";
+          if (bulk_ok) {
+            def["ST2_TAKE_ALL(SLOT, ROWBASE, GY)"] = take_all;
+            def["ST2_BULK_ISSUE_ALL(ROWBASE, BAR, GY, GX0)"] = bulk_all;
+            def["ST2_STAGE_BYTES"] = "(" + stage_off + ")";
+          }
           b.fns << "template <int K, int PH> __device__ __forceinline__ " << E << " ST2_apply(const Params& p, ST2_WIN_PARAMS) {\n" << g.out.str()
                 << b.ret_struct(E, r) << "}\n";
         }
@@ -963,7 +1002,7 @@ Glue build_glue(const Node& n, const std::map<std::string, ArrayInfo>& arrays) {
       named = {"n", "rows", "tiles_per_row", "total_tiles", "batches_per_row", "total_batches", "in_vec", "out_vec", "status", "agg", "incl", "gstatus", "groups_per_row", "counter", "epoch", "err", "spin_limit"};
       break;
     case N_PERMUTE: named = {"n", "vec", "out_n", "priv", "priv16", "choice", "locks", "err", "spin_limit"}; break;
-    case N_STENCIL: case N_STENCIL2: named = {"o0", "o1", "o2", "row0", "row1", "tiles1", "tiles2", "vec"}; break;
+    case N_STENCIL: case N_STENCIL2: named = {"o0", "o1", "o2", "row0", "row1", "tiles1", "tiles2", "vec", "?fr_strips", "?fr_r0", "?fr_r1", "?strip0", "?err", "?spin_limit"}; break;
     default: break;
   }
   for (auto& nm : named) b.ps.use_named(nm);

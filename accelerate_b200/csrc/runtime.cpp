@@ -46,16 +46,35 @@ Buffer::~Buffer() {
   if (busy) {
     cudaSetDevice(ctx->device);
     if (owned && ptr && cudaEventQuery(busy) != cudaSuccess) {
-      ctx->deferred.push_back({ptr, bytes, busy});     // a download is still reading the buffer
+      ctx->deferred.push_back({ptr, bytes, capacity, busy});     // a download is still reading the buffer
       return;
     }
     cudaEventDestroy(busy);
   }
   if (owned && ptr) {
     cudaSetDevice(ctx->device);
-    cudaFreeAsync(ptr, ctx->stream);
+    ctx->release(ptr, capacity);
     ctx->allocated -= (long long)bytes;
   }
+}
+
+void Ctx::release(void* ptr, size_t capacity) {
+  {
+    std::lock_guard<std::mutex> g(nursery.mu);
+    if (capacity && nursery.bytes + capacity <= nursery.limit) {
+      nursery.blocks.emplace(capacity, ptr);
+      nursery.bytes += capacity;
+      return;
+    }
+  }
+  cudaFreeAsync(ptr, stream);
+}
+
+void Ctx::purge() {
+  std::lock_guard<std::mutex> g(nursery.mu);
+  for (auto& b : nursery.blocks) cudaFreeAsync(b.second, stream);
+  nursery.blocks.clear();
+  nursery.bytes = 0;
 }
 
 void Ctx::reap(bool wait) {
@@ -64,7 +83,7 @@ void Ctx::reap(bool wait) {
     if (wait) cudaEventSynchronize(d.done);
     if (cudaEventQuery(d.done) == cudaSuccess) {
       cudaEventDestroy(d.done);
-      cudaFreeAsync(d.ptr, stream);
+      release(d.ptr, d.capacity);
       allocated -= (long long)d.bytes;
     } else {
       deferred[kept++] = d;
@@ -79,7 +98,29 @@ std::shared_ptr<Buffer> Ctx::alloc(size_t bytes) {
   b->bytes = bytes;
   if (bytes) {
     if (!deferred.empty()) reap(false);
-    check(cudaMallocAsync(&b->ptr, bytes, stream), "cudaMallocAsync");
+    const size_t cap = (bytes + kChunk - 1) / kChunk * kChunk;
+    b->capacity = cap;
+    {
+      std::lock_guard<std::mutex> g(nursery.mu);
+      auto it = nursery.blocks.find(cap);
+      if (it != nursery.blocks.end()) {
+        b->ptr = it->second;
+        nursery.blocks.erase(it);
+        nursery.bytes -= cap;
+        nursery.hits++;
+      }
+    }
+    if (!b->ptr) {
+      cudaError_t e = cudaMallocAsync(&b->ptr, cap, stream);
+      if (e == cudaErrorMemoryAllocation) {
+        // out of memory: give the nursery back and try once more (Table.hs:199-204)
+        cudaGetLastError();
+        purge();
+        check(cudaStreamSynchronize(stream), "cudaStreamSynchronize");
+        e = cudaMallocAsync(&b->ptr, cap, stream);
+      }
+      check(e, "cudaMallocAsync");
+    }
     allocated += (long long)bytes;
   }
   return b;
@@ -247,6 +288,14 @@ std::map<std::string, std::string> scan_ring_variant(const RingShape& r, int64_t
 // CTAs per SM asked of the compiler, rows loaded ahead
 struct Stencil2dShape { int warps, rows, minb, depth; };
 Stencil2dShape stencil2d_shape() { return {4, 32, 1, 4}; }
+// acc_stencil2d_bulk: warps per CTA, CTAs per SM asked of the compiler, row slots per warp, rows per warp
+// task, and the bytes per point (all inputs) from which it replaces the register kernel
+struct Stencil2dBulkShape { int warps, minb, slots, rows, min_point_bytes; };
+Stencil2dBulkShape stencil2d_bulk_shape() { return {4, 4, 8, 64, 8}; }
+std::map<std::string, std::string> stencil2d_bulk_variant(const Stencil2dBulkShape& bs) {
+  return {{"ST2_BULK", "1"}, {"ACC_OPT_PARAMS", "1"}, {"ST2_DEPTH", "0"}, {"SCAN_TILE", "128"}, {"ST2_WARPS", std::to_string(bs.warps)},
+          {"ST2_MIN_BLOCKS", std::to_string(bs.minb)}, {"ST2B_SLOTS", std::to_string(bs.slots)}, {"ST2B_ROWS", std::to_string(bs.rows)}};
+}
 std::map<std::string, std::string> stencil2d_variant() {
   Stencil2dShape s = stencil2d_shape();
   return {{"ST2_WARPS", std::to_string(s.warps)}, {"ST2_ROWS", std::to_string(s.rows)}, {"ST2_MIN_BLOCKS", std::to_string(s.minb)},
@@ -295,7 +344,16 @@ std::vector<std::pair<std::string, std::map<std::string, std::string>>> default_
     }
     case N_STENCIL: case N_STENCIL2:
       v.push_back({"stencil", stencil_variant(n.d[0].rank)});
-      if (n.d[0].rank == 2) v.push_back({"stencil2d", stencil2d_variant()});
+      if (n.d[0].rank == 2) {
+        v.push_back({"stencil2d", stencil2d_variant()});
+        if (g.defines.count("ST2_BULK_OK") && g.defines.at("ST2_BULK_OK") == "1") {
+          v.push_back({"stencil2d", stencil2d_bulk_variant(stencil2d_bulk_shape())});
+          auto fv = stencil2d_variant();
+          fv["ST2_FRAME"] = "1";
+          fv["ACC_OPT_PARAMS"] = "1";
+          v.push_back({"stencil2d", fv});
+        }
+      }
       break;
     case N_RESHAPE: break;
   }
@@ -907,15 +965,15 @@ void Program::exec_kernel_node(const Node& n, Env& env_ref) {
           const bool one_stream = df.count("D0_STREAM_NLEAVES") && df.at("D0_STREAM_NLEAVES") == "1" && packed &&
                                   df.at("D0_STREAM_BYTES") == df.at("SCAN_T_BYTES");
           const int bytes = packed ? atoi(df.at("SCAN_T_BYTES").c_str()) : 0;
-          // 8-byte elements halve the elements a ring holds; the register-resident kernel is faster for them
-          const bool want = bytes <= 4 && !small;
+          const bool want = bytes <= 8 && !small;
           if (one_stream && want && L.fast("D0") && in_vec && out_vec && scan_ring_aligned(bytes, m, rows, right)) {
             const RingShape rs = scan_ring_shape(bytes);
             const int rounds = rs.rounds, slots = rs.slots, look = rs.look;
             const int64_t rtile = 8 * (int64_t)rounds * 128;
             const int64_t r_tiles_per_row = std::max<int64_t>(1, (m + rtile - 1) / rtile);
             const int64_t r_total = rows * r_tiles_per_row;
-            const size_t smem = (size_t)slots * rtile * bytes;
+            // (8-byte elements: one more kilobyte per finisher warp, through which results are transposed for the stores)
+            const size_t smem = (size_t)slots * rtile * bytes + (bytes == 8 ? 8 * 1024 : 0);
             // look-back descriptors describe batches of rs.batch consecutive tiles of a row
             const int64_t batches_per_row = (r_tiles_per_row + rs.batch - 1) / rs.batch;
             const int64_t total_batches = rows * batches_per_row;
@@ -966,10 +1024,25 @@ void Program::exec_kernel_node(const Node& n, Env& env_ref) {
         DevArrayP def = env.at(n.arr);
         std::vector<int64_t> ext = he.eval(*n.d[0].extent).i;
         const int64_t total = size_of(ext);
-        DevArrayP out = c.new_array(n.elt, def->shape);
-        for (size_t l = 0; l < out->leaf.size(); ++l)
-          if (out->leaf[l]->bytes)
-            c.check(cudaMemcpyAsync(out->leaf[l]->ptr, def->leaf[l]->ptr, out->leaf[l]->bytes, cudaMemcpyDeviceToDevice, c.stream), "cudaMemcpyAsync");
+        // "If the array of default values is only used once, it will be updated in-place" (Language.hs:764-765):
+        // the defaults are a temporary of this run that nobody else holds (no caller's handle, no embedded
+        // constant, no reshaped view, no second name), this node is its last use, and the node's scalar code
+        // does not read it.  Otherwise the permutation works on a copy.
+        bool in_place = def.use_count() == 2;      // the environment's reference and this one
+        {
+          const std::vector<std::string>& dead = dead_after[n.id];
+          in_place = in_place && std::find(dead.begin(), dead.end(), n.arr) != dead.end();
+          for (auto& b : def->leaf) in_place = in_place && b->owned && b.use_count() == 1;
+          for (auto& sl : st.glue.slots)
+            if ((sl.kind == Slot::ARR_LEAF || sl.kind == Slot::ARR_DIM) && sl.name == n.arr) in_place = false;
+          for (auto& pend : def->pending) in_place = in_place && pend == nullptr;
+        }
+        DevArrayP out = in_place ? def : c.new_array(n.elt, def->shape);
+        if (!in_place)
+          for (size_t l = 0; l < out->leaf.size(); ++l)
+            if (out->leaf[l]->bytes)
+              c.check(cudaMemcpyAsync(out->leaf[l]->ptr, def->leaf[l]->ptr, out->leaf[l]->bytes, cudaMemcpyDeviceToDevice, c.stream), "cudaMemcpyAsync");
+        if (in_place) c.inplace_permutes++;
         L.outs = {out};
         env[n.outs[0]] = out;
         if (total == 0) break;
@@ -1072,6 +1145,51 @@ void Program::exec_kernel_node(const Node& n, Env& env_ref) {
           L.named["tiles2"] = strips;
           const std::map<std::string, std::string> var = stencil2d_variant();
           CompiledKernel& k2 = c.kernel(assemble_source(st.glue, "stencil2d", var), "acc_stencil2d", warps * 32, 0);
+          // Rows staged through shared memory (acc_stencil2d_bulk) for the middle of the arrays, when the
+          // register windows of acc_stencil2d are wide (8 bytes or more per point over all inputs: they
+          // then leave too few registers for rows requested ahead); acc_stencil2d computes the frame.
+          const auto& df = st.glue.defines;
+          const Stencil2dBulkShape bs = stencil2d_bulk_shape();
+          int64_t point_bytes = 0, min_e1 = o[2];
+          bool staged = !window && df.count("ST2_BULK_OK") && df.at("ST2_BULK_OK") == "1" && L.named["vec"] == 1;
+          for (size_t a = 0; a < ext.size() && staged; ++a) {
+            const std::string D = "D" + std::to_string(a);
+            staged = L.fast(D) && ext[a][1] % 4 == 0 && df.count(D + "_STREAM_BYTES");
+            if (staged) point_bytes += atoi(df.at(D + "_STREAM_BYTES").c_str());
+            min_e1 = std::min(min_e1, ext[a][1]);
+          }
+          const int64_t ry = atoi(df.at("ST_RYMAX").c_str());
+          const int64_t mid_strips = staged ? std::min<int64_t>(std::max<int64_t>((min_e1 - 124) / 120, 0), strips - 1) : 0;
+          const int64_t mid_r0 = ry, mid_r1 = o[1] - ry;
+          if (staged && point_bytes >= bs.min_point_bytes && mid_strips > 0 && mid_r1 - mid_r0 >= bs.rows) {
+            const std::map<std::string, std::string> bvar = stencil2d_bulk_variant(bs);
+            const size_t smem = (size_t)bs.warps * bs.slots * 128 * point_bytes;
+            CompiledKernel& kb = c.kernel(assemble_source(st.glue, "stencil2d", bvar), "acc_stencil2d_bulk", bs.warps * 32, smem);
+            const int64_t mid_blocks = (mid_r1 - mid_r0 + bs.rows - 1) / bs.rows;
+            L.named["row0"] = mid_r0;
+            L.named["row1"] = mid_r1;
+            L.named["strip0"] = 1;
+            L.named["tiles1"] = mid_blocks;
+            L.named["tiles2"] = mid_strips;
+            L.launch(kb, (mid_strips * mid_blocks + bs.warps - 1) / bs.warps, bs.warps * 32, smem);
+            // the frame: strip 0 and the strips after the middle ones over all rows, the rows above and below
+            // the middle of the middle strips
+            const int64_t ra = (o[1] + rows - 1) / rows, rc = (mid_r0 + rows - 1) / rows, rd = (o[1] - mid_r1 + rows - 1) / rows;
+            const int64_t frame_tasks = (strips - mid_strips) * ra + mid_strips * (rc + rd);
+            L.named["row0"] = 0;
+            L.named["row1"] = o[1];
+            L.named["tiles1"] = ra;
+            L.named["tiles2"] = strips;
+            L.named["fr_strips"] = mid_strips;
+            L.named["fr_r0"] = mid_r0;
+            L.named["fr_r1"] = mid_r1;
+            std::map<std::string, std::string> fvar = var;
+            fvar["ST2_FRAME"] = "1";
+            fvar["ACC_OPT_PARAMS"] = "1";
+            CompiledKernel& kf = c.kernel(assemble_source(st.glue, "stencil2d", fvar), "acc_stencil2d", warps * 32, 0);
+            L.launch(kf, (frame_tasks + warps - 1) / warps, warps * 32, 0);
+            break;
+          }
           const int64_t ctas = (strips * rowblocks + warps - 1) / warps;
           L.launch(k2, ctas, warps * 32, 0);  // one warp per task; the hardware scheduler balances the tail
           break;

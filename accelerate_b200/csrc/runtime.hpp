@@ -52,6 +52,7 @@ struct Buffer {
   Ctx* ctx = nullptr;
   void* ptr = nullptr;
   size_t bytes = 0;
+  size_t capacity = 0;          // what was asked of the allocator (bytes rounded up to the nursery's chunk)
   bool owned = true;
   cudaEvent_t busy = nullptr;   // last asynchronous download of this buffer (on the copy-out stream)
   ~Buffer();
@@ -75,9 +76,25 @@ struct Ctx {
   cudaStream_t d2h_stream = nullptr;   // asynchronous downloads run here, beside kernels and uploads
   // buffers released while a download was still reading them: freed once that copy has completed,
   // without making the main stream wait for it
-  struct Deferred { void* ptr; size_t bytes; cudaEvent_t done; };
+  struct Deferred { void* ptr; size_t bytes, capacity; cudaEvent_t done; };
   std::vector<Deferred> deferred;
   void reap(bool wait);
+  // Freed buffers wait here, by size, for the next allocation of the same size (the reference's
+  // nursery, Array/Remote/Nursery.hs:55-108, searched by exact size after rounding requests up to a
+  // chunk, Array/Remote/Table.hs:176-205).  A block handed back to the driver's pool may be split,
+  // and getting a large block out of the pool again after a synchronisation has been seen to stall
+  // the host for milliseconds; a block kept here is reused as it is.  Everything that uses a block
+  // runs on `stream` (downloads on the other stream are waited for before a block gets here), so
+  // reuse needs no further ordering.
+  struct Nursery {
+    std::mutex mu;
+    std::multimap<size_t, void*> blocks;
+    size_t bytes = 0, limit = 0;
+    long long hits = 0;
+  } nursery;
+  static constexpr size_t kChunk = 512;
+  void release(void* ptr, size_t capacity);   // into the nursery, or back to the driver when it is full
+  void purge();                               // everything in the nursery back to the driver
   Driver drv;
   std::mutex mu;
   std::map<uint64_t, DevArrayP> arrays;
@@ -92,7 +109,7 @@ struct Ctx {
   std::string scan_layout;      // how the last scan laid its descriptors out in the scratch buffer
   std::map<std::string, CompiledKernel> kernels;  // by content hash of the source
   CompileStats cstats;
-  std::atomic<long long> launches{0}, h2d{0}, d2h{0}, mem_hits{0}, allocated{0}, runs{0};
+  std::atomic<long long> launches{0}, h2d{0}, d2h{0}, mem_hits{0}, allocated{0}, runs{0}, inplace_permutes{0};
   long long spin_limit = 1 << 22;
 
   DevArrayP new_array(const Type& elt, const std::vector<int64_t>& shape);

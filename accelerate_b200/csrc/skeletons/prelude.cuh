@@ -179,11 +179,27 @@ template <class T> __device__ __forceinline__ void acc_ld4(const T* p, T (&o)[4]
 template <class T> __device__ __forceinline__ void acc_st4(T* p, const T (&o)[4]) { acc_vec4<T, (int)sizeof(T)>::st(p, o); }
 
 // four consecutive elements from shared memory (address aligned to 4 * sizeof(T))
-template <class T> __device__ __forceinline__ void acc_lds4(const T* p, T (&o)[4]) {
-  struct __align__(sizeof(T) * 4) quad { T v[4]; };
-  const quad q = *reinterpret_cast<const quad*>(p);
-  _Pragma("unroll") for (int k = 0; k < 4; ++k) o[k] = q.v[k];
-}
+template <class T, int BYTES> struct acc_lds4_impl {
+  static __device__ __forceinline__ void ld(const T* p, T (&o)[4]) {
+    struct __align__(sizeof(T) * 4) quad { T v[4]; };
+    const quad q = *reinterpret_cast<const quad*>(p);
+    _Pragma("unroll") for (int k = 0; k < 4; ++k) o[k] = q.v[k];
+  }
+};
+// 8-byte elements: neighbouring lanes are 32 bytes apart, so two plain 16-byte reads per lane would hit every
+// bank twice.  The two halves are read in an order that alternates every four lanes: the eight lanes that are
+// served together then cover all 32 banks once.  (Callers pass addresses that grow or shrink by 32 bytes per lane.)
+template <class T> struct acc_lds4_impl<T, 8> {
+  static __device__ __forceinline__ void ld(const T* p, T (&o)[4]) {
+    const uint4* q = reinterpret_cast<const uint4*>(p);
+    const int h = (threadIdx.x >> 2) & 1;
+    const uint4 a = q[h], b = q[h ^ 1];
+    const uint4 lo = h ? b : a, hi = h ? a : b;
+    memcpy(&o[0], &lo, 16);
+    memcpy(&o[2], &hi, 16);
+  }
+};
+template <class T> __device__ __forceinline__ void acc_lds4(const T* p, T (&o)[4]) { acc_lds4_impl<T, (int)sizeof(T)>::ld(p, o); }
 
 // Record the first device-side failure (a bounded wait that gave up, ...).
 __device__ __forceinline__ void acc_fail(i64 err_ptr, int code) {

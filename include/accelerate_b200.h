@@ -132,6 +132,17 @@ int b200_sync(b200_ctx* ctx);
  * [6] device bytes currently allocated, [7] programs run. */
 int b200_stats(b200_ctx* ctx, int64_t out[8]);
 
+/* The context's device memory: [0] bytes in live arrays, [1] bytes of freed buffers kept for reuse (the
+ * reference's nursery, Array/Remote/Nursery.hs:55-117: a freed buffer is handed to the next allocation of the
+ * same size, sizes being rounded up to a chunk as in Array/Remote/Table.hs:176-205), [2] buffers kept,
+ * [3] allocations served from them so far, [4] permutations that updated their defaults array in place
+ * because it was a temporary used only there (Language.hs:764-765). */
+int b200_memory_stats(b200_ctx* ctx, int64_t out[5]);
+
+/* Hand every kept buffer back to the driver (Table.hs:342-344, `purge`).  Done by itself when an allocation
+ * fails for lack of memory. */
+int b200_ctx_purge(b200_ctx* ctx);
+
 /* The CUDA stream the context launches on (a cudaStream_t), for callers that
  * time kernels with their own events. */
 int b200_ctx_stream(b200_ctx* ctx, void** stream);

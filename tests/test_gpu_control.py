@@ -93,3 +93,66 @@ def test_gpu_memory_table_uploads_a_host_array_once(gpu_ctx):
     assert np.array_equal(out.download(), x + 1)
     assert gpu_ctx.stats()["h2d_bytes"] - s0 == 2 * x.nbytes
     gpu_ctx.forget(key)
+
+
+def test_gpu_freed_buffers_are_reused_by_size(gpu_ctx):
+    # the reference's nursery (Array/Remote/Nursery.hs:55-108; Table.hs:176-205): a freed device buffer is kept
+    # and handed to the next allocation of the same (chunk-rounded) size; `purge` gives everything back
+    gpu_ctx.sync()
+    gpu_ctx.purge()
+    n = 300_001                                       # 1 200 004 bytes: not a multiple of the chunk
+    a = gpu_ctx.from_host(np.arange(n, dtype=np.int32))
+    p = a.devptr()
+    m0 = gpu_ctx.memory_stats()
+    assert m0["live_bytes"] >= 4 * n
+    a.free()
+    m1 = gpu_ctx.memory_stats()
+    assert m1["nursery_blocks"] == m0["nursery_blocks"] + 1 and m1["nursery_bytes"] - m0["nursery_bytes"] >= 4 * n
+    b = gpu_ctx.from_host(np.arange(n - 1, dtype=np.int32) * 3)        # rounds up to the same size
+    assert b.devptr() == p
+    m2 = gpu_ctx.memory_stats()
+    assert m2["nursery_hits"] == m1["nursery_hits"] + 1 and m2["nursery_blocks"] == m0["nursery_blocks"]
+    assert np.array_equal(b.download(), np.arange(n - 1, dtype=np.int32) * 3)
+    c = gpu_ctx.from_host(np.zeros(17, dtype=np.int64))                # another size: no hit
+    assert gpu_ctx.memory_stats()["nursery_hits"] == m2["nursery_hits"]
+    b.free(); c.free()
+    gpu_ctx.purge()
+    m3 = gpu_ctx.memory_stats()
+    assert m3["nursery_blocks"] == 0 and m3["nursery_bytes"] == 0
+    # results of a program come out of the nursery too
+    x = np.arange(1 << 12, dtype=np.float32)
+    h0 = gpu_ctx.memory_stats()["nursery_hits"]
+    for _ in range(3):
+        out = backend.run(A.map(lambda v: v * 2, x), gpu_ctx)
+        assert np.array_equal(out, x * 2)
+    assert gpu_ctx.memory_stats()["nursery_hits"] > h0
+
+
+def test_gpu_permute_updates_unshared_defaults_in_place(gpu_ctx):
+    # Language.hs:764-765: defaults that are used only by the permutation are updated in place; defaults that
+    # are an input, are used again, or are read by the permutation's own source are copied first
+    add = lambda a, b: a + b  # noqa: E731
+    k = (np.arange(5000, dtype=np.int64) * 7) % 64
+    ones = np.ones(5000, dtype=np.int32)
+    want = np.bincount(k, minlength=64).astype(np.int32)
+    ix = lambda i: A.Just_(A.index(A.use(k)[i]))  # noqa: E731
+    m0 = gpu_ctx.memory_stats()["inplace_permutes"]
+    got = backend.run(A.permute(add, A.fill(64, A.constant(np.int32(0))), ix, ones), gpu_ctx)
+    assert np.array_equal(got, want)
+    assert gpu_ctx.memory_stats()["inplace_permutes"] == m0 + 1
+    base = np.arange(64, dtype=np.int32)
+    got = backend.run(A.permute(add, base, ix, ones), gpu_ctx)                 # an input: not touched
+    assert np.array_equal(got, want + base) and np.array_equal(base, np.arange(64, dtype=np.int32))
+    assert gpu_ctx.memory_stats()["inplace_permutes"] == m0 + 1
+    d = A.scanl1(add, base)                                                     # a temporary used twice
+    h = A.permute(add, d, ix, ones)
+    got = backend.run(A.zipWith(add, h, d), gpu_ctx)
+    assert np.array_equal(got, want + 2 * np.cumsum(base, dtype=np.int32))
+    assert gpu_ctx.memory_stats()["inplace_permutes"] == m0 + 1
+    d2 = A.scanl1(add, base)                                                    # a temporary that the permutation's index and source read
+    got = backend.run(A.permute(add, d2, lambda i: A.Just_(A.index(A.from_integral(d2[i] % 64, "i64"))), A.map(lambda v: v * 3, d2)), gpu_ctx)
+    c = np.cumsum(base, dtype=np.int32)
+    w = c.copy()
+    np.add.at(w, c % 64, 3 * c)
+    assert np.array_equal(got, w)
+    assert gpu_ctx.memory_stats()["inplace_permutes"] == m0 + 1

@@ -470,6 +470,41 @@ def test_stencil2_gaussian_mirror():
     check(A.stencil2(f, A.mirror, a, A.mirror, b))
 
 
+@pytest.mark.parametrize("case", ["stencil2_f32", "stencil2_ragged", "f64_3x3", "zipped_5x5", "f32_odd_width", "i64_wrap_7x3"])
+def test_stencil_2d_rows_staged_through_shared_memory(case):
+    # arrays wide and tall enough for the kernel that stages input rows in shared memory (at least 8 bytes per
+    # point over all inputs, 244 columns, 64 rows besides the halo); the frame around its part comes from the
+    # register-window kernel, so every boundary kind is exercised along the seams too
+    w = [[1, 2, 1], [2, 4, 2], [1, 2, 1]]
+    g2 = lambda s, t: sum((np.float32(w[i][j] / 16.0) * (s[i][j] + t[i][j]) for i in range(3) for j in range(3)), A.constant(np.float32(0)))  # noqa: E731
+    if case == "stencil2_f32":
+        a = rng.uniform(0, 1, (200, 488)).astype(np.float32)
+        b = rng.uniform(0, 1, (200, 488)).astype(np.float32)
+        for bnd in BOUNDARIES[:3]:
+            check(A.stencil2(g2, bnd, a, A.mirror, b))
+    elif case == "stencil2_ragged":
+        a = rng.uniform(0, 1, (150, 500)).astype(np.float32)
+        b = rng.uniform(0, 1, (131, 488)).astype(np.float32)
+        check(A.stencil2(g2, A.clamp, a, A.wrap, b))
+        check(A.stencil2(g2, A.function(lambda ix: A.constant(np.float32(7.5))), a, A.clamp, b))
+    elif case == "f64_3x3":
+        m = rng.uniform(0, 1, (130, 400))
+        for bnd in BOUNDARIES[:3]:
+            check(A.stencil(lambda s: sum((s[i][j] * float(i * 3 + j + 1) for i in range(3) for j in range(3)), A.constant(np.float64(0))), bnd, m))
+    elif case == "zipped_5x5":
+        x = rng.uniform(0, 1, (150, 372)).astype(np.float32)
+        y = rng.uniform(0, 1, (150, 372)).astype(np.float32)
+        z = A.zipWith(lambda u, v: u * 2.0 + v, x, y)
+        check(A.stencil(lambda s: sum((s[i][j] * float(i * 5 + j) for i in range(5) for j in range(5)), A.constant(np.float32(0))), A.wrap, z,
+                        extent=(5, 5)))
+    elif case == "f32_odd_width":
+        a = rng.uniform(0, 1, (100, 487)).astype(np.float32)       # rows that are no multiple of four elements: not staged
+        check(A.stencil2(g2, A.mirror, a, A.mirror, a))
+    else:
+        m = ints((140, 368), np.int64, -1000, 1000)
+        check(A.stencil(lambda s: sum((s[i][j] * (i * 3 + j) for i in range(7) for j in range(3)), A.constant(np.int64(0))), A.wrap, m, extent=(7, 3)))
+
+
 def test_stencil_delayed_input_and_jacobi_iterated():
     m = rng.uniform(0, 1, (50, 200)).astype(np.float32)
     jac = lambda s: 0.25 * (s[0][1] + s[2][1] + s[1][0] + s[1][2])  # noqa: E731
