@@ -86,6 +86,13 @@ int b200_ctx_create(int device, uint32_t flags, b200_ctx** out) {
   c.sm_count = prop.multiProcessorCount;
   c.check(cudaStreamCreateWithFlags(&c.stream, cudaStreamNonBlocking), "cudaStreamCreate");
   c.check(cudaStreamCreateWithFlags(&c.d2h_stream, cudaStreamNonBlocking), "cudaStreamCreate");
+  {
+    int lo = 0, hi = 0;
+    c.check(cudaDeviceGetStreamPriorityRange(&lo, &hi), "cudaDeviceGetStreamPriorityRange");
+    c.check(cudaStreamCreateWithPriority(&c.aux_stream, cudaStreamNonBlocking, hi), "cudaStreamCreateWithPriority");
+    c.check(cudaEventCreateWithFlags(&c.aux_fork, cudaEventDisableTiming), "cudaEventCreate");
+    c.check(cudaEventCreateWithFlags(&c.aux_join, cudaEventDisableTiming), "cudaEventCreate");
+  }
   // keep freed blocks in the stream-ordered pool instead of returning them to the driver
   cudaMemPool_t pool;
   c.check(cudaDeviceGetDefaultMemPool(&pool, device), "cudaDeviceGetDefaultMemPool");
@@ -109,6 +116,7 @@ void b200_ctx_destroy(b200_ctx* ctx) {
   cudaSetDevice(c.device);
   cudaStreamSynchronize(c.stream);
   cudaStreamSynchronize(c.d2h_stream);
+  if (c.aux_stream) cudaStreamSynchronize(c.aux_stream);
   {
     std::lock_guard<std::mutex> g(c.mu);
     c.arrays.clear();
@@ -123,6 +131,9 @@ void b200_ctx_destroy(b200_ctx* ctx) {
   cudaStreamSynchronize(c.stream);
   cudaFree(c.d_words);
   cudaStreamDestroy(c.d2h_stream);
+  if (c.aux_fork) cudaEventDestroy(c.aux_fork);
+  if (c.aux_join) cudaEventDestroy(c.aux_join);
+  if (c.aux_stream) cudaStreamDestroy(c.aux_stream);
   cudaStreamDestroy(c.stream);
   delete ctx;
 }

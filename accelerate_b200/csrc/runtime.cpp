@@ -296,6 +296,14 @@ std::map<std::string, std::string> stencil2d_bulk_variant(const Stencil2dBulkSha
   return {{"ST2_BULK", "1"}, {"ACC_OPT_PARAMS", "1"}, {"ST2_DEPTH", "0"}, {"SCAN_TILE", "128"}, {"ST2_WARPS", std::to_string(bs.warps)},
           {"ST2_MIN_BLOCKS", std::to_string(bs.minb)}, {"ST2B_SLOTS", std::to_string(bs.slots)}, {"ST2B_ROWS", std::to_string(bs.rows)}};
 }
+std::map<std::string, std::string> stencil2d_variant();
+std::map<std::string, std::string> stencil2d_frame_variant() {
+  std::map<std::string, std::string> v = stencil2d_variant();
+  v["ST2_FRAME"] = "1";
+  v["ACC_OPT_PARAMS"] = "1";
+  v["ST2_ROWS"] = "8";
+  return v;
+}
 std::map<std::string, std::string> stencil2d_variant() {
   Stencil2dShape s = stencil2d_shape();
   return {{"ST2_WARPS", std::to_string(s.warps)}, {"ST2_ROWS", std::to_string(s.rows)}, {"ST2_MIN_BLOCKS", std::to_string(s.minb)},
@@ -348,10 +356,7 @@ std::vector<std::pair<std::string, std::map<std::string, std::string>>> default_
         v.push_back({"stencil2d", stencil2d_variant()});
         if (g.defines.count("ST2_BULK_OK") && g.defines.at("ST2_BULK_OK") == "1") {
           v.push_back({"stencil2d", stencil2d_bulk_variant(stencil2d_bulk_shape())});
-          auto fv = stencil2d_variant();
-          fv["ST2_FRAME"] = "1";
-          fv["ACC_OPT_PARAMS"] = "1";
-          v.push_back({"stencil2d", fv});
+          v.push_back({"stencil2d", stencil2d_frame_variant()});
         }
       }
       break;
@@ -626,12 +631,12 @@ struct Launcher {
     if (pb.size() * 8 > 4000) throw Error(B200_ERR_UNSUPPORTED, "kernel parameter block exceeds 4 KB");
     return pb;
   }
-  void launch(CompiledKernel& k, int64_t grid, int threads, size_t smem) {
+  void launch(CompiledKernel& k, int64_t grid, int threads, size_t smem, cudaStream_t on = nullptr) {
     if (grid <= 0) return;
     if (grid > 2147483647LL) throw Error(B200_ERR_UNSUPPORTED, "grid too large");
     std::vector<uint64_t> pb = block();
     void* args[1] = {pb.data()};
-    ctx->check(ctx->drv.LaunchKernel(k.fn, (unsigned)grid, 1, 1, (unsigned)threads, 1, 1, (unsigned)smem, (CUstream)ctx->stream, args, nullptr),
+    ctx->check(ctx->drv.LaunchKernel(k.fn, (unsigned)grid, 1, 1, (unsigned)threads, 1, 1, (unsigned)smem, (CUstream)(on ? on : ctx->stream), args, nullptr),
                "cuLaunchKernel");
     ctx->launches++;
   }
@@ -1165,16 +1170,12 @@ void Program::exec_kernel_node(const Node& n, Env& env_ref) {
             const std::map<std::string, std::string> bvar = stencil2d_bulk_variant(bs);
             const size_t smem = (size_t)bs.warps * bs.slots * 128 * point_bytes;
             CompiledKernel& kb = c.kernel(assemble_source(st.glue, "stencil2d", bvar), "acc_stencil2d_bulk", bs.warps * 32, smem);
-            const int64_t mid_blocks = (mid_r1 - mid_r0 + bs.rows - 1) / bs.rows;
-            L.named["row0"] = mid_r0;
-            L.named["row1"] = mid_r1;
-            L.named["strip0"] = 1;
-            L.named["tiles1"] = mid_blocks;
-            L.named["tiles2"] = mid_strips;
-            L.launch(kb, (mid_strips * mid_blocks + bs.warps - 1) / bs.warps, bs.warps * 32, smem);
-            // the frame: strip 0 and the strips after the middle ones over all rows, the rows above and below
-            // the middle of the middle strips
-            const int64_t ra = (o[1] + rows - 1) / rows, rc = (mid_r0 + rows - 1) / rows, rd = (o[1] - mid_r1 + rows - 1) / rows;
+            // The frame first, on the auxiliary stream: strip 0 and the strips after the middle ones over all rows,
+            // the rows above and below the middle of the middle strips.  Its few warps march down their tasks at
+            // the pace of dependent loads, so it runs beside the staged kernel instead of after it, in tasks of
+            // 8 rows.
+            const int frows = 8;
+            const int64_t ra = (o[1] + frows - 1) / frows, rc = (mid_r0 + frows - 1) / frows, rd = (o[1] - mid_r1 + frows - 1) / frows;
             const int64_t frame_tasks = (strips - mid_strips) * ra + mid_strips * (rc + rd);
             L.named["row0"] = 0;
             L.named["row1"] = o[1];
@@ -1183,11 +1184,20 @@ void Program::exec_kernel_node(const Node& n, Env& env_ref) {
             L.named["fr_strips"] = mid_strips;
             L.named["fr_r0"] = mid_r0;
             L.named["fr_r1"] = mid_r1;
-            std::map<std::string, std::string> fvar = var;
-            fvar["ST2_FRAME"] = "1";
-            fvar["ACC_OPT_PARAMS"] = "1";
+            std::map<std::string, std::string> fvar = stencil2d_frame_variant();
             CompiledKernel& kf = c.kernel(assemble_source(st.glue, "stencil2d", fvar), "acc_stencil2d", warps * 32, 0);
-            L.launch(kf, (frame_tasks + warps - 1) / warps, warps * 32, 0);
+            c.check(cudaEventRecord(c.aux_fork, c.stream), "cudaEventRecord");
+            c.check(cudaStreamWaitEvent(c.aux_stream, c.aux_fork, 0), "cudaStreamWaitEvent");
+            L.launch(kf, (frame_tasks + warps - 1) / warps, warps * 32, 0, c.aux_stream);
+            c.check(cudaEventRecord(c.aux_join, c.aux_stream), "cudaEventRecord");
+            const int64_t mid_blocks = (mid_r1 - mid_r0 + bs.rows - 1) / bs.rows;
+            L.named["row0"] = mid_r0;
+            L.named["row1"] = mid_r1;
+            L.named["strip0"] = 1;
+            L.named["tiles1"] = mid_blocks;
+            L.named["tiles2"] = mid_strips;
+            L.launch(kb, (mid_strips * mid_blocks + bs.warps - 1) / bs.warps, bs.warps * 32, smem);
+            c.check(cudaStreamWaitEvent(c.stream, c.aux_join, 0), "cudaStreamWaitEvent");
             break;
           }
           const int64_t ctas = (strips * rowblocks + warps - 1) / warps;

@@ -74,6 +74,10 @@ struct Ctx {
   int sm_count = 148;
   cudaStream_t stream = nullptr;
   cudaStream_t d2h_stream = nullptr;   // asynchronous downloads run here, beside kernels and uploads
+  // A small kernel that may run beside a large one of the same node (the frame of a staged stencil) goes
+  // to this higher-priority stream, forked from and joined to `stream` with the two events.
+  cudaStream_t aux_stream = nullptr;
+  cudaEvent_t aux_fork = nullptr, aux_join = nullptr;
   // buffers released while a download was still reading them: freed once that copy has completed,
   // without making the main stream wait for it
   struct Deferred { void* ptr; size_t bytes, capacity; cudaEvent_t done; };

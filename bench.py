@@ -648,7 +648,7 @@ def main():
         jac_full = wd.name.startswith("jacobi") and args.scale == 0
         roofline = {"bound": "hbm", "kernel": wd.kernel, "workload": wd.name, "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s",
                     "frac": round(achieved / peak, 4), "peak_kind": f"of {peak_kind}", "frac_of_nominal_8tbs": round(achieved / NOMINAL_HBM_GBS, 4),
-                    "traffic": 493.4e6 * 4 if jac_full else None, "traffic_from": "ncu capture of the 8192^2 case x4 (scaled, not measured at this size)" if jac_full else None,
+                    "traffic": 492.4e6 * 4 if jac_full else None, "traffic_from": "ncu capture of the 8192^2 case x4 (scaled, not measured at this size)" if jac_full else None,
                     "launch_ms": round(launch_ms, 4)}
 
     # parity of what was just timed: one more run of every workload, checked against NumPy on every rank
