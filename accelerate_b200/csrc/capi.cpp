@@ -37,7 +37,7 @@ Type parse_type_text(const char* s) {
 // every node that launches kernels, the bodies of control nodes included, in program order
 void kernel_nodes(const std::vector<Node>& ns, std::vector<const Node*>& out) {
   for (auto& n : ns) {
-    if (n.kind == N_USE || n.kind == N_ACOND || n.kind == N_AWHILE || n.kind == N_APPLY) {
+    if (n.kind == N_USE || n.kind == N_ACOND || n.kind == N_AWHILE || n.kind == N_APPLY || n.kind == N_ATRACE) {
       for (auto& b : n.body) kernel_nodes(b.nodes, out);
     } else if (n.kind != N_RESHAPE) {
       out.push_back(&n);
@@ -126,7 +126,9 @@ void b200_ctx_destroy(b200_ctx* ctx) {
     for (auto& k : c.kernels)
       if (k.second.module) c.drv.ModuleUnload(k.second.module);
     c.kernels.clear();
-    if (c.scan_scratch) cudaFreeAsync(c.scan_scratch, c.stream);
+    for (auto& r : c.scan_regions)
+      if (r.second.ptr) cudaFreeAsync(r.second.ptr, c.stream);
+    c.scan_regions.clear();
   }
   cudaStreamSynchronize(c.stream);
   cudaFree(c.d_words);

@@ -524,7 +524,7 @@ void parse_node(ProgramIR& p, std::vector<Node>& into, const Sx& bind, TEnv& env
   n.id = p.n_nodes++;
   const std::string k = x.head();
   // (control nodes are not hashed into any kernel: their text, which may embed whole arrays, is not kept)
-  if (k != "use" && k != "acond" && k != "awhile" && k != "apply") n.text = sx_text(x);
+  if (k != "use" && k != "acond" && k != "awhile" && k != "apply" && k != "atrace") n.text = sx_text(x);
   auto is_operand = [](const Sx& s) { return s.head() == "manifest" || s.head() == "delayed"; };
   std::vector<ArrayInfo> outs;
   if (k == "generate") {
@@ -673,6 +673,23 @@ void parse_node(ProgramIR& p, std::vector<Node>& into, const Sx& bind, TEnv& env
     }
     if (!same_arrays(given, n.body[0].param_info)) throw Error(B200_ERR_TYPE, "apply: arguments do not match the function's parameters");
     outs = body_result(p, n.body[0]);
+  } else if (k == "atrace") {
+    // (atrace (hex MESSAGE) (show a..) (args b..)): Atrace, Interpreter.hs:215 -- print the message and the
+    // arrays a.., hand the arrays b.. on unchanged
+    n.kind = N_ATRACE;
+    const Sx& h = x.at(1);
+    if (h.head() != "hex" || x.at(2).head() != "show" || x.at(3).head() != "args") throw Error(B200_ERR_PARSE, "expected (atrace (hex ..) (show ..) (args ..))");
+    const std::string digits = h.size() > 1 ? h.at(1).s : std::string();
+    if (digits.size() % 2) throw Error(B200_ERR_PARSE, "atrace: odd number of hex digits");
+    for (size_t i = 0; i + 1 < digits.size(); i += 2) n.message.push_back((char)(hex_digit(digits[i]) * 16 + hex_digit(digits[i + 1])));
+    for (size_t j = 1; j < x.at(2).size(); ++j) {
+      n.shown.push_back(x.at(2).k[j].s);
+      env.array(n.shown.back());
+    }
+    for (size_t j = 1; j < x.at(3).size(); ++j) {
+      n.args.push_back(x.at(3).k[j].s);
+      outs.push_back(env.array(n.args.back()));
+    }
   } else if (k == "reshape") {
     n.kind = N_RESHAPE;
     n.extent = parse_expr(x.at(1), env);
@@ -724,6 +741,7 @@ void node_arrays(const Node& n, std::vector<std::string>& used) {
   }
   if (!n.arr.empty()) used.push_back(n.arr);
   for (auto& a : n.args) used.push_back(a);
+  for (auto& a : n.shown) used.push_back(a);
   for (auto& b : n.body) {
     for (auto& m : b.nodes) node_arrays(m, used);
     for (auto& o : b.outs) used.push_back(o);

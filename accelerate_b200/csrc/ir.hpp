@@ -127,7 +127,7 @@ struct BoundarySpec {
 // Use (a constant array embedded in the program), Acond, Awhile and Apply, whose operands are
 // array-level functions (`Body`).
 enum NodeKind { N_GENERATE, N_FOLD, N_FOLDSEG, N_SCAN, N_SCAN2, N_PERMUTE, N_STENCIL, N_STENCIL2, N_RESHAPE,
-                N_USE, N_ACOND, N_AWHILE, N_APPLY };
+                N_USE, N_ACOND, N_AWHILE, N_APPLY, N_ATRACE };
 struct Node;
 // An array-level function or a branch: parameters (none for branches), nodes, results.
 struct Body {
@@ -140,7 +140,9 @@ struct Node {
   NodeKind kind = N_GENERATE;
   int id = -1;                            // position in Program::nodes (unique over all bodies)
   std::vector<Body> body;                 // acond: then, else; awhile: condition, step; apply: the function
-  std::vector<std::string> args;          // awhile: initial state; apply: arguments
+  std::vector<std::string> args;          // awhile: initial state; apply: arguments; atrace: the arrays handed on
+  std::vector<std::string> shown;         // atrace: the arrays to print
+  std::string message;                    // atrace
   std::unique_ptr<Expr> pred;             // acond
   std::vector<int64_t> use_shape;         // use
   std::vector<std::string> use_data;      // use: raw bytes of every scalar leaf

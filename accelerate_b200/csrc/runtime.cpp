@@ -187,24 +187,30 @@ CompiledKernel& Ctx::kernel(const std::string& source, const std::string& entry,
 }
 
 void* Ctx::scan_descriptors(size_t bytes, const std::string& layout) {
-  // status words of a fresh (zeroed) buffer never match an epoch >= 1
-  if (bytes > scan_scratch_bytes || scan_epoch >= (1u << 29)) {
-    if (scan_scratch) check(cudaFreeAsync(scan_scratch, stream), "cudaFreeAsync");
-    size_t want = std::max(bytes, (size_t)1 << 20);
-    check(cudaMallocAsync(&scan_scratch, want, stream), "cudaMallocAsync");
-    check(cudaMemsetAsync(scan_scratch, 0, want, stream), "cudaMemsetAsync");
-    scan_scratch_bytes = want;
-    scan_epoch = 0;
-    scan_layout = layout;
-  } else if (layout != scan_layout) {
-    // Epoch tags tell one launch from the next only while status words stay where they are.  Under
-    // another layout (descriptor width or spacing, region offsets) the words this launch polls may
-    // hold an earlier launch's VALUE bits, which can look like a current status: clear them.
-    check(cudaMemsetAsync(scan_scratch, 0, bytes, stream), "cudaMemsetAsync");
-    scan_layout = layout;
+  ScanRegion& r = scan_regions[layout];
+  // status words of a fresh (zeroed) region never match an epoch >= 1
+  if (bytes > r.bytes || r.epoch >= (1u << 29)) {
+    if (r.ptr) check(cudaFreeAsync(r.ptr, stream), "cudaFreeAsync");
+    r.ptr = nullptr;
+    r.bytes = 0;
+    if (scan_regions.size() > kScanRegions) {
+      auto victim = scan_regions.end();
+      for (auto it = scan_regions.begin(); it != scan_regions.end(); ++it)
+        if (&it->second != &r && (victim == scan_regions.end() || it->second.last_use < victim->second.last_use)) victim = it;
+      if (victim != scan_regions.end()) {
+        if (victim->second.ptr) check(cudaFreeAsync(victim->second.ptr, stream), "cudaFreeAsync");
+        scan_regions.erase(victim);
+      }
+    }
+    const size_t want = std::max(bytes, (size_t)1 << 16);
+    check(cudaMallocAsync(&r.ptr, want, stream), "cudaMallocAsync");
+    check(cudaMemsetAsync(r.ptr, 0, want, stream), "cudaMemsetAsync");
+    r.bytes = want;
+    r.epoch = 0;
   }
-  ++scan_epoch;
-  return scan_scratch;
+  r.last_use = ++scan_clock;
+  scan_epoch = ++r.epoch;
+  return r.ptr;
 }
 
 // The ring scan kernel fetches whole tiles with cp.async.bulk, which needs 16-byte aligned global
@@ -782,6 +788,46 @@ std::vector<DevArrayP> Program::call(const Body& b, const std::vector<DevArrayP>
   return r;
 }
 
+// "Vector (Z :. 3) [1,2,3]": constructor by rank, shape, elements in row-major order (tuples in parentheses).
+static std::string trace_render(Ctx& c, const DevArray& a) {
+  const int64_t n = a.size();
+  std::vector<std::string> host(a.leaf.size());
+  for (size_t l = 0; l < a.leaf.size(); ++l) {
+    host[l].resize((size_t)n * ty_bytes[a.leaf_ty[l]]);
+    if (n) c.check(cudaMemcpyAsync(&host[l][0], a.leaf[l]->ptr, host[l].size(), cudaMemcpyDeviceToHost, c.stream), "cudaMemcpyAsync");
+  }
+  c.check(cudaStreamSynchronize(c.stream), "cudaStreamSynchronize");
+  const size_t rank = a.shape.size();
+  std::string out = rank == 0 ? "Scalar" : rank == 1 ? "Vector" : rank == 2 ? "Matrix" : "Array";
+  out += rank ? " (Z" : " Z";
+  for (int64_t d : a.shape) out += " :. " + std::to_string(d);
+  out += rank ? ") [" : " [";
+  char buf[64];
+  for (int64_t i = 0; i < n; ++i) {
+    if (i) out += ",";
+    if (a.leaf.size() > 1) out += "(";
+    for (size_t l = 0; l < a.leaf.size(); ++l) {
+      if (l) out += ",";
+      const char* q = host[l].data() + (size_t)i * ty_bytes[a.leaf_ty[l]];
+      switch (a.leaf_ty[l]) {
+        case I8: snprintf(buf, sizeof buf, "%d", (int)*(const int8_t*)q); break;
+        case I16: { int16_t v; memcpy(&v, q, 2); snprintf(buf, sizeof buf, "%d", (int)v); break; }
+        case I32: { int32_t v; memcpy(&v, q, 4); snprintf(buf, sizeof buf, "%d", v); break; }
+        case I64: { int64_t v; memcpy(&v, q, 8); snprintf(buf, sizeof buf, "%lld", (long long)v); break; }
+        case U8: snprintf(buf, sizeof buf, "%u", (unsigned)*(const uint8_t*)q); break;
+        case U16: { uint16_t v; memcpy(&v, q, 2); snprintf(buf, sizeof buf, "%u", (unsigned)v); break; }
+        case U32: { uint32_t v; memcpy(&v, q, 4); snprintf(buf, sizeof buf, "%u", v); break; }
+        case U64: { uint64_t v; memcpy(&v, q, 8); snprintf(buf, sizeof buf, "%llu", (unsigned long long)v); break; }
+        case F32: { float v; memcpy(&v, q, 4); snprintf(buf, sizeof buf, "%.9g", (double)v); break; }
+        default: { double v; memcpy(&v, q, 8); snprintf(buf, sizeof buf, "%.17g", v); break; }
+      }
+      out += buf;
+    }
+    if (a.leaf.size() > 1) out += ")";
+  }
+  return out + "]";
+}
+
 void Program::exec(const std::vector<Node>& ns, Env& env) {
   Ctx& c = *ctx;
   for (const Node& n : ns) {
@@ -825,9 +871,44 @@ void Program::exec(const std::vector<Node>& ns, Env& env) {
         for (size_t k = 0; k < n.outs.size(); ++k) env[n.outs[k]] = r[k];
         break;
       }
+      case N_ATRACE: {
+        // Interpreter.hs:215, atraceOp (:873-880): the message, then ": " and the arrays if there are any, on
+        // standard error.  The arrays are rendered by this library (trace_render), not by the `show` of the
+        // host program's Message, which cannot cross the boundary.
+        std::string line = n.message;
+        for (size_t k = 0; k < n.shown.size(); ++k) line += (k ? ", " : ": ") + trace_render(c, *env.at(n.shown[k]));
+        fprintf(stderr, "%s\n", line.c_str());
+        fflush(stderr);
+        for (size_t k = 0; k < n.outs.size(); ++k) env[n.outs[k]] = env.at(n.args[k]);
+        break;
+      }
       default: exec_kernel_node(n, env);
     }
   }
+}
+
+// The kernel of one node for one variant.  Assembling the source text and hashing it (what Ctx::kernel
+// keys on) costs tens of microseconds, too much for every launch of a program that runs many small
+// kernels, so a node remembers the kernels it has asked for by skeleton, entry point and variant.
+static CompiledKernel& node_kernel(Ctx& c, NodeState& st, const char* skeleton, const std::map<std::string, std::string>& variant, const char* entry,
+                                   int threads, size_t smem) {
+  std::string key = skeleton;
+  key += '|';
+  key += entry;
+  for (auto& kv : variant) {
+    key += '|';
+    key += kv.first;
+    key += '=';
+    key += kv.second;
+  }
+  auto it = st.kernel_memo.find(key);
+  if (it != st.kernel_memo.end()) {
+    c.mem_hits++;
+    return *it->second;
+  }
+  CompiledKernel& k = c.kernel(assemble_source(st.glue, skeleton, variant), entry, threads, smem);
+  st.kernel_memo[key] = &k;
+  return k;
 }
 
 void Program::exec_kernel_node(const Node& n, Env& env_ref) {
@@ -861,7 +942,7 @@ void Program::exec_kernel_node(const Node& n, Env& env_ref) {
         const int64_t inner = sh.empty() ? 1 : sh.back();
         L.named["n"] = total;
         L.named["vec"] = (L.fast("D0") && (sh.size() <= 1 || inner % 4 == 0)) ? 1 : 0;
-        CompiledKernel& k = c.kernel(assemble_source(st.glue, "elementwise", {}), "acc_generate", 256, 0);
+        CompiledKernel& k = node_kernel(c, st, "elementwise", {}, "acc_generate", 256, 0);
         int64_t work = L.named["vec"] ? (total + 3) / 4 : total;
         int64_t grid = std::min<int64_t>((work + 255) / 256, (int64_t)c.sm_count * k.max_blocks_per_sm * 4);
         L.launch(k, std::max<int64_t>(grid, 1), 256, 0);
@@ -883,7 +964,7 @@ void Program::exec_kernel_node(const Node& n, Env& env_ref) {
         L.named["vec"] = (L.fast("D0") && (rows == 1 || m % 4 == 0)) ? 1 : 0;
         if (rows <= 8 && (rows == 1 || m >= (1 << 16))) {
           std::map<std::string, std::string> var = {{"FOLD_G", "32"}};
-          CompiledKernel& k = c.kernel(assemble_source(st.glue, "fold", var), "acc_fold_all", 256, 0);
+          CompiledKernel& k = node_kernel(c, st, "fold", var, "acc_fold_all", 256, 0);
           const int64_t ntiles = (m + 1023) / 1024;
           int64_t grid = std::max<int64_t>(1, std::min<int64_t>(ntiles, (int64_t)c.sm_count * k.max_blocks_per_sm));
           const size_t sb = struct_bytes(n.elt);
@@ -899,7 +980,7 @@ void Program::exec_kernel_node(const Node& n, Env& env_ref) {
         } else {
           const int g = pow2_at_least((m + 7) / 8);
           std::map<std::string, std::string> var = {{"FOLD_G", std::to_string(g)}};
-          CompiledKernel& k = c.kernel(assemble_source(st.glue, "fold", var), "acc_fold_rows", 256, 0);
+          CompiledKernel& k = node_kernel(c, st, "fold", var, "acc_fold_rows", 256, 0);
           const int64_t warps = (rows + (32 / g) - 1) / (32 / g);
           int64_t grid = std::min<int64_t>((warps + 7) / 8, (int64_t)c.sm_count * k.max_blocks_per_sm);
           L.launch(k, std::max<int64_t>(grid, 1), 256, 0);
@@ -926,7 +1007,7 @@ void Program::exec_kernel_node(const Node& n, Env& env_ref) {
         L.named["vec"] = (L.fast("D0") && (rows == 1 || m % 4 == 0)) ? 1 : 0;
         const int g = pow2_at_least((m / std::max<int64_t>(segs, 1) + 7) / 8);
         std::map<std::string, std::string> var = {{"FOLDSEG_G", std::to_string(g)}};
-        CompiledKernel& k = c.kernel(assemble_source(st.glue, "foldseg", var), "acc_foldseg", 256, 0);
+        CompiledKernel& k = node_kernel(c, st, "foldseg", var, "acc_foldseg", 256, 0);
         const int64_t warps = (rows * segs + (32 / g) - 1) / (32 / g);
         int64_t grid = std::min<int64_t>((warps + 7) / 8, (int64_t)c.sm_count * k.max_blocks_per_sm);
         L.launch(k, std::max<int64_t>(grid, 1), 256, 0);
@@ -997,7 +1078,7 @@ void Program::exec_kernel_node(const Node& n, Env& env_ref) {
             L.named["status"] = (int64_t)(uintptr_t)rbase;
             L.named["epoch"] = c.scan_epoch;
             const int threads = 256 + 32 * rs.redw + 32 * rs.lbw;     // 8 finisher warps, the reducer warps, the look-back warps
-            CompiledKernel& k = c.kernel(assemble_source(st.glue, "scan", var), "acc_scan_ring", threads, smem);
+            CompiledKernel& k = node_kernel(c, st, "scan", var, "acc_scan_ring", threads, smem);
             const int64_t grid = std::min<int64_t>(total_batches, (int64_t)c.sm_count * k.max_blocks_per_sm);
             L.launch(k, grid, threads, smem);
             break;
@@ -1021,7 +1102,7 @@ void Program::exec_kernel_node(const Node& n, Env& env_ref) {
         }
         auto svar = scan_variant(n.elt, small);
         scan_poll_variant(svar, total_tiles);
-        CompiledKernel& k = c.kernel(assemble_source(st.glue, "scan", svar), "acc_scan", 256, 0);
+        CompiledKernel& k = node_kernel(c, st, "scan", svar, "acc_scan", 256, 0);
         L.launch(k, total_tiles, 256, 0);
         break;
       }
@@ -1079,12 +1160,12 @@ void Program::exec_kernel_node(const Node& n, Env& env_ref) {
           L.named["choice"] = (int64_t)(uintptr_t)choice;
           L.named["priv"] = std::min<int64_t>(out_n, cap / bytes);
           L.named["priv16"] = 0;
-          CompiledKernel& ks = c.kernel(assemble_source(st.glue, "permute", {{"PERMUTE_SAMPLE", "1"}}), "acc_permute_sample", 1024, 0);
+          CompiledKernel& ks = node_kernel(c, st, "permute", {{"PERMUTE_SAMPLE", "1"}}, "acc_permute_sample", 1024, 0);
           L.launch(ks, 1, 1024, 0);
           const int64_t words16 = (out_n + 1) / 2;
           const size_t smem = (size_t)words16 * 4;
           std::map<std::string, std::string> var = {{"PERMUTE_SMEM16", "1"}, {"PERMUTE_THREADS", "1024"}, {"PERMUTE_CHOICE_ID", "1"}};
-          CompiledKernel& k = c.kernel(assemble_source(st.glue, "permute", var), "acc_permute", 1024, smem);
+          CompiledKernel& k = node_kernel(c, st, "permute", var, "acc_permute", 1024, smem);
           if (smem > 48 * 1024) c.check(c.drv.FuncSetAttribute(k.fn, CU_FUNC_ATTRIBUTE_MAX_DYNAMIC_SHARED_SIZE_BYTES, (int)smem), "cuFuncSetAttribute");
           L.named["priv16"] = words16;
           const int64_t work = (total + 3) / 4;
@@ -1097,7 +1178,7 @@ void Program::exec_kernel_node(const Node& n, Env& env_ref) {
           const int64_t priv = std::min<int64_t>(out_n, cap / bytes);
           const size_t smem = (size_t)priv * bytes;
           std::map<std::string, std::string> var = {{"PERMUTE_SMEM", "1"}, {"PERMUTE_THREADS", "1024"}};
-          CompiledKernel& k = c.kernel(assemble_source(st.glue, "permute", var), "acc_permute", 1024, smem);
+          CompiledKernel& k = node_kernel(c, st, "permute", var, "acc_permute", 1024, smem);
           if (smem > 48 * 1024) c.check(c.drv.FuncSetAttribute(k.fn, CU_FUNC_ATTRIBUTE_MAX_DYNAMIC_SHARED_SIZE_BYTES, (int)smem), "cuFuncSetAttribute");
           int nb = 1;
           c.check(c.drv.OccupancyMaxActiveBlocksPerMultiprocessor(&nb, k.fn, 1024, smem), "occupancy");
@@ -1107,7 +1188,7 @@ void Program::exec_kernel_node(const Node& n, Env& env_ref) {
           L.launch(k, std::max<int64_t>(grid, 1), 1024, smem);
         } else {
           L.named["priv"] = 0;
-          CompiledKernel& k = c.kernel(assemble_source(st.glue, "permute", {}), "acc_permute", 512, 0);
+          CompiledKernel& k = node_kernel(c, st, "permute", {}, "acc_permute", 512, 0);
           const int64_t work = L.named["vec"] ? (total + 3) / 4 : total;
           int64_t grid = std::min<int64_t>((work + 511) / 512, (int64_t)c.sm_count * k.max_blocks_per_sm * 2);
           L.launch(k, std::max<int64_t>(grid, 1), 512, 0);
@@ -1149,7 +1230,6 @@ void Program::exec_kernel_node(const Node& n, Env& env_ref) {
           L.named["tiles1"] = rowblocks;
           L.named["tiles2"] = strips;
           const std::map<std::string, std::string> var = stencil2d_variant();
-          CompiledKernel& k2 = c.kernel(assemble_source(st.glue, "stencil2d", var), "acc_stencil2d", warps * 32, 0);
           // Rows staged through shared memory (acc_stencil2d_bulk) for the middle of the arrays, when the
           // register windows of acc_stencil2d are wide (8 bytes or more per point over all inputs: they
           // then leave too few registers for rows requested ahead); acc_stencil2d computes the frame.
@@ -1169,7 +1249,7 @@ void Program::exec_kernel_node(const Node& n, Env& env_ref) {
           if (staged && point_bytes >= bs.min_point_bytes && mid_strips > 0 && mid_r1 - mid_r0 >= bs.rows) {
             const std::map<std::string, std::string> bvar = stencil2d_bulk_variant(bs);
             const size_t smem = (size_t)bs.warps * bs.slots * 128 * point_bytes;
-            CompiledKernel& kb = c.kernel(assemble_source(st.glue, "stencil2d", bvar), "acc_stencil2d_bulk", bs.warps * 32, smem);
+            CompiledKernel& kb = node_kernel(c, st, "stencil2d", bvar, "acc_stencil2d_bulk", bs.warps * 32, smem);
             // The frame first, on the auxiliary stream: strip 0 and the strips after the middle ones over all rows,
             // the rows above and below the middle of the middle strips.  Its few warps march down their tasks at
             // the pace of dependent loads, so it runs beside the staged kernel instead of after it, in tasks of
@@ -1185,7 +1265,7 @@ void Program::exec_kernel_node(const Node& n, Env& env_ref) {
             L.named["fr_r0"] = mid_r0;
             L.named["fr_r1"] = mid_r1;
             std::map<std::string, std::string> fvar = stencil2d_frame_variant();
-            CompiledKernel& kf = c.kernel(assemble_source(st.glue, "stencil2d", fvar), "acc_stencil2d", warps * 32, 0);
+            CompiledKernel& kf = node_kernel(c, st, "stencil2d", fvar, "acc_stencil2d", warps * 32, 0);
             c.check(cudaEventRecord(c.aux_fork, c.stream), "cudaEventRecord");
             c.check(cudaStreamWaitEvent(c.aux_stream, c.aux_fork, 0), "cudaStreamWaitEvent");
             L.launch(kf, (frame_tasks + warps - 1) / warps, warps * 32, 0, c.aux_stream);
@@ -1200,11 +1280,12 @@ void Program::exec_kernel_node(const Node& n, Env& env_ref) {
             c.check(cudaStreamWaitEvent(c.stream, c.aux_join, 0), "cudaStreamWaitEvent");
             break;
           }
+          CompiledKernel& k2 = node_kernel(c, st, "stencil2d", var, "acc_stencil2d", warps * 32, 0);
           const int64_t ctas = (strips * rowblocks + warps - 1) / warps;
           L.launch(k2, ctas, warps * 32, 0);  // one warp per task; the hardware scheduler balances the tail
           break;
         }
-        CompiledKernel& k = c.kernel(assemble_source(st.glue, "stencil", stencil_variant(rank)), "acc_stencil", t.threads, 0);
+        CompiledKernel& k = node_kernel(c, st, "stencil", stencil_variant(rank), "acc_stencil", t.threads, 0);
         L.launch(k, tiles0 * tiles1 * tiles2, t.threads, 0);
         break;
       }

@@ -107,10 +107,16 @@ struct Ctx {
   // device words: [0] error status, [1] fold ticket counter, [2] scan ticket counter, [3] scan exit counter, [4] permute kernel choice
   int* d_words = nullptr;
   // scan descriptors (persistent, epoch-tagged)
-  void* scan_scratch = nullptr;
-  size_t scan_scratch_bytes = 0;
-  uint32_t scan_epoch = 0;
-  std::string scan_layout;      // how the last scan laid its descriptors out in the scratch buffer
+  // One region per descriptor layout (width, spacing, region offsets: the layout string), at most
+  // kScanRegions of them, the least recently used one making room.  Epoch tags tell one launch from the
+  // next only while status words stay where they are; under another layout the words a launch polls
+  // could hold an earlier launch's VALUE bits, so layouts never share memory (clearing a shared buffer
+  // at every change of layout cost a memset of up to 17 MB in front of every scan of a mixed program).
+  struct ScanRegion { void* ptr = nullptr; size_t bytes = 0; uint32_t epoch = 0; uint64_t last_use = 0; };
+  std::map<std::string, ScanRegion> scan_regions;
+  static constexpr size_t kScanRegions = 8;
+  uint64_t scan_clock = 0;
+  uint32_t scan_epoch = 0;      // epoch of the launch that scan_descriptors was last called for
   std::map<std::string, CompiledKernel> kernels;  // by content hash of the source
   CompileStats cstats;
   std::atomic<long long> launches{0}, h2d{0}, d2h{0}, mem_hits{0}, allocated{0}, runs{0}, inplace_permutes{0};
@@ -128,6 +134,7 @@ struct Ctx {
 struct NodeState {
   Glue glue;
   bool has_glue = false;
+  std::map<std::string, CompiledKernel*> kernel_memo;   // by skeleton, entry point and variant (entries of Ctx::kernels, which only grows)
 };
 struct Program {
   Ctx* ctx = nullptr;

@@ -961,6 +961,28 @@ def apply(f, *args):
     return out[0] if single else tuple(out)
 
 
+def aforeign(name, fallback, *args):
+    """``Aforeign`` (AST.hs; Interpreter.hs:217): a backend that has no foreign implementation under ``name``
+    runs the pure Accelerate function given as the fallback, which is what the interpreter always does and
+    what this backend does."""
+    del name
+    return apply(fallback, *args)
+
+
+def atrace(message, shown, result):
+    """``Atrace`` (Language.hs ``atrace``/``atraceArray``; Interpreter.hs:215, atraceOp :873-880): when the term is
+    evaluated, the message and the arrays ``shown`` (one, several or none) go to standard error; the value is
+    ``result`` (an array or a tuple of arrays), unchanged."""
+    single = not isinstance(result, (list, tuple))
+    sh = [compute(use(x)) for x in _as_list(shown)] if shown is not None else []
+    rs = [compute(use(x)) for x in _as_list(result)]
+    sx = "(atrace (hex %s) (show %s) (args %s))" % (message.encode().hex(), " ".join(a.name for a in sh), " ".join(a.name for a in rs))
+    node = _mk("atrace", rs[0].rank, rs[0].elt, sx, [a.node for a in sh + rs], nouts=len(rs),
+               ranks=[a.rank for a in rs], elts=[a.elt for a in rs])
+    out = [Acc(a.rank, a.elt, node=node, out=k) for k, a in enumerate(rs)]
+    return out[0] if single else tuple(out)
+
+
 def pipe(f, g):
     """``f >-> g`` (Language.hs:365-372): two computations kept apart, the second applied to the first's result."""
     return lambda *xs: apply(g, *_as_list(apply(f, *xs)))

@@ -68,6 +68,9 @@ import Foreign.Marshal.Array
 import Foreign.Ptr
 import Foreign.Storable
 import Numeric                                                      ( showHFloat, showHex )
+import qualified Data.ByteString                                    as B
+import qualified Data.Text                                          as T
+import qualified Data.Text.Encoding                                 as T
 import System.IO.Unsafe                                             ( unsafePerformIO )
 
 
@@ -389,8 +392,16 @@ nodeText pacc ns s = case pacc of
   Apply _ f a                  -> let (xs, s1) = manifestArrays a ns s
                                       (fb, s2) = afunText f ns s1
                                   in  (sx ["apply", fb, sx ("args" : xs)], s2)
-  Aforeign{}                   -> unsupported "foreign functions"
-  Atrace{}                     -> unsupported "atrace"
+  -- no foreign implementation is registered for this backend: the pure fallback runs, as in the
+  -- interpreter (Interpreter.hs:217)
+  Aforeign _ _ f a             -> let (xs, s1) = manifestArrays a ns s
+                                      (fb, s2) = afunText f ns s1
+                                  in  (sx ["apply", fb, sx ("args" : xs)], s2)
+  -- Interpreter.hs:215: the library prints the message and its own rendering of the arrays (the
+  -- Message's `show` is a Haskell closure and stays on this side of the boundary)
+  Atrace (Message _ _ msg) a b -> let (xs, s1) = manifestArrays a ns s
+                                      (ys, s2) = manifestArrays b ns s1
+                                  in  (sx ["atrace", sx ["hex", hexText msg], sx ("show" : xs), sx ("args" : ys)], s2)
   _                            -> internalError "node should have been fused away (Fusion.hs:198-200)"
   where
     seed Nothing  = []
@@ -421,6 +432,11 @@ bindParams (LeftHandSideSingle (ArrayR shr tp)) ns s =
   in  (push ns nm, ["(" ++ nm ++ " (array " ++ show (rank shr) ++ " " ++ typeText tp ++ "))"], s { fresh = fresh s + 1 })
 
 -- Payload of an embedded array: the bytes of every scalar leaf as hexadecimal text.
+-- UTF-8 bytes of a message as hex digits
+hexText :: T.Text -> String
+hexText = concatMap byte . B.unpack . T.encodeUtf8
+  where byte w = let h = showHex w "" in if length h == 1 then '0' : h else h
+
 hexLeaves :: TypeR e -> ArrayData e -> Int -> [String]
 hexLeaves tp ad n = unsafePerformIO $ do
   ref <- newIORef []

@@ -177,6 +177,39 @@ int64_t shape_size(const std::vector<int64_t>& sh) {
   return n;
 }
 
+// how `atrace` prints an array, e.g. "Vector (Z :. 3) [1,2,3]" (tuples in parentheses)
+std::string trace_render(const Array& a) {
+  const size_t rank = a.sh.size();
+  std::string out = rank == 0 ? "Scalar" : rank == 1 ? "Vector" : rank == 2 ? "Matrix" : "Array";
+  out += rank ? " (Z" : " Z";
+  for (int64_t d : a.sh) out += " :. " + std::to_string(d);
+  out += rank ? ") [" : " [";
+  char buf[64];
+  for (int64_t i = 0; i < a.n; ++i) {
+    if (i) out += ",";
+    if (a.leaf.size() > 1) out += "(";
+    for (size_t l = 0; l < a.leaf.size(); ++l) {
+      if (l) out += ",";
+      const uint8_t* q = a.leaf[l].data() + (size_t)i * ty_bytes[a.leaf_ty[l]];
+      switch (a.leaf_ty[l]) {
+        case I8: snprintf(buf, sizeof buf, "%d", (int)*(const int8_t*)q); break;
+        case I16: { int16_t v; memcpy(&v, q, 2); snprintf(buf, sizeof buf, "%d", (int)v); break; }
+        case I32: { int32_t v; memcpy(&v, q, 4); snprintf(buf, sizeof buf, "%d", v); break; }
+        case I64: { int64_t v; memcpy(&v, q, 8); snprintf(buf, sizeof buf, "%lld", (long long)v); break; }
+        case U8: snprintf(buf, sizeof buf, "%u", (unsigned)*q); break;
+        case U16: { uint16_t v; memcpy(&v, q, 2); snprintf(buf, sizeof buf, "%u", (unsigned)v); break; }
+        case U32: { uint32_t v; memcpy(&v, q, 4); snprintf(buf, sizeof buf, "%u", v); break; }
+        case U64: { uint64_t v; memcpy(&v, q, 8); snprintf(buf, sizeof buf, "%llu", (unsigned long long)v); break; }
+        case F32: { float v; memcpy(&v, q, 4); snprintf(buf, sizeof buf, "%.9g", (double)v); break; }
+        default: { double v; memcpy(&v, q, 8); snprintf(buf, sizeof buf, "%.17g", v); break; }
+      }
+      out += buf;
+    }
+    if (a.leaf.size() > 1) out += ")";
+  }
+  return out + "]";
+}
+
 ArrayP new_array(const EltTy& elt, const std::vector<int64_t>& sh) {
   auto a = std::make_shared<Array>();
   a->elt = elt;
@@ -848,7 +881,9 @@ struct Node {
   std::string kind;
   std::vector<int> outs;  // array slots defined
   std::vector<Body> body;              // acond: then, else; awhile: condition, step; apply: function
-  std::vector<int> args;               // awhile: initial state; apply: arguments
+  std::vector<int> args;               // awhile: initial state; apply: arguments; atrace: the arrays handed on
+  std::vector<int> shown;              // atrace: the arrays to print
+  std::string message;                 // atrace
   ArrayP use_val;                      // use: the embedded array
   std::vector<std::unique_ptr<Fun>> f;
   std::vector<std::unique_ptr<Exp>> x;
@@ -1036,6 +1071,13 @@ void parse_node(Program& p, std::vector<Node>& into, const Sx& bind, Scope& sc) 
   } else if (k == "apply") {
     n.body.push_back(parse_body(p, x[1], sc, true));
     for (size_t j = 1; j < x[2].size(); ++j) n.args.push_back(sc.array(x[2].k[j].s));
+  } else if (k == "atrace") {
+    // (atrace (hex MESSAGE) (show a..) (args b..))
+    const std::string digits = x[1].size() > 1 ? x[1].k[1].s : std::string();
+    auto hv = [](char ch) { return ch <= '9' ? ch - '0' : (ch | 32) - 'a' + 10; };
+    for (size_t i = 0; i + 1 < digits.size(); i += 2) n.message.push_back((char)(hv(digits[i]) * 16 + hv(digits[i + 1])));
+    for (size_t j = 1; j < x[2].size(); ++j) n.shown.push_back(sc.array(x[2].k[j].s));
+    for (size_t j = 1; j < x[3].size(); ++j) n.args.push_back(sc.array(x[3].k[j].s));
   } else {
     throw std::runtime_error("unknown array node '" + k + "'");
   }
@@ -1170,6 +1212,14 @@ void run_node(Program& p, const Node& n, Env& env) {
     for (int a : n.args) as.push_back(vals[a]);
     std::vector<ArrayP> r = call_body(p, n.body[0], as, env);
     for (size_t i = 0; i < n.outs.size(); ++i) vals[n.outs[i]] = r[i];
+  } else if (k == "atrace") {
+    // Interp:215 and atraceOp (Interp:873-880): the message, ": " and the arrays when there are any, on standard
+    // error; the arrays behind it are handed on.  (Rendering: constructor by rank, shape, elements in row-major order.)
+    std::string line = n.message;
+    for (size_t j = 0; j < n.shown.size(); ++j) line += (j ? ", " : ": ") + trace_render(*vals[n.shown[j]]);
+    fprintf(stderr, "%s\n", line.c_str());
+    fflush(stderr);
+    for (size_t i = 0; i < n.outs.size(); ++i) vals[n.outs[i]] = vals[n.args[i]];
   } else if (k == "generate") {
     // generateOp Interp:269-275 via fromFunctionM (Representation/Array.hs:109-122)
     auto sh = value_shape(eval(*n.x[0], env));

@@ -67,3 +67,36 @@ def test_control_flow_type_errors(lib_built):
     with pytest.raises(backend.B200Error) as e:
         backend.compile_check(twice)
     assert e.value.code == 1
+
+
+def test_atrace_prints_message_and_arrays_and_hands_the_result_on(capfd):
+    # Atrace (Interpreter.hs:215, atraceOp :873-880): message, ": " and the arrays when there are any, on stderr
+    x = np.arange(6, dtype=np.int32).reshape(2, 3)
+    y = np.array([1.5, 2.25], dtype=np.float32)
+    t = A.atrace("after map", [A.map(lambda v: v + 1, x), A.zip(y, y)], A.map(lambda v: v * 2, x))
+    capfd.readouterr()
+    got = oracle.run(t)
+    err = capfd.readouterr().err
+    assert np.array_equal(got, x * 2)
+    assert err == "after map: Matrix (Z :. 2 :. 3) [1,2,3,4,5,6], Vector (Z :. 2) [(1.5,1.5),(2.25,2.25)]\n"
+    got = oracle.run(A.map(lambda v: v + 1, A.atrace("no arrays", None, x)))
+    assert np.array_equal(got, x + 1) and capfd.readouterr().err == "no arrays\n"
+    s = A.atrace("scalar", A.fold(lambda a, b: a + b, 0, A.use(np.arange(5, dtype=np.int64))), (x, y))
+    a, b = oracle.run(list(s))
+    assert np.array_equal(a, x) and np.array_equal(b, y) and capfd.readouterr().err == "scalar: Scalar Z [10]\n"
+
+
+def test_aforeign_runs_the_pure_fallback():
+    # Aforeign (Interpreter.hs:217): without a foreign implementation the fallback function is applied
+    x = np.arange(7, dtype=np.float32)
+    t = A.aforeign("vendor.scale", lambda a: A.map(lambda v: v * 3.0, a), x)
+    assert np.array_equal(oracle.run(t), x * 3)
+
+
+def test_atrace_and_aforeign_programs_compile(lib_built):
+    from accelerate_b200 import backend
+    x = np.arange(6, dtype=np.int32).reshape(2, 3)
+    for t in (A.atrace("m", [A.map(lambda v: v + 1, x)], A.map(lambda v: v * 2, x)), A.aforeign("f", lambda a: A.map(lambda v: v * 3, a), x)):
+        assert "ok" in backend.compile_check(A.build_program(t).text)
+    with pytest.raises(backend.B200Error):
+        backend.compile_check("(program (in a0 (array 1 i32)) (let a1 (atrace (hex 6d) (show a9) (args a0))) (out a1))")

@@ -156,3 +156,19 @@ def test_gpu_permute_updates_unshared_defaults_in_place(gpu_ctx):
     np.add.at(w, c % 64, 3 * c)
     assert np.array_equal(got, w)
     assert gpu_ctx.memory_stats()["inplace_permutes"] == m0 + 1
+
+
+def test_gpu_atrace_and_aforeign(gpu_ctx, capfd):
+    # the same lines on standard error as the oracle writes; the traced term's value is handed on
+    x = np.arange(6, dtype=np.int32).reshape(2, 3)
+    y = np.array([1.5, 2.25], dtype=np.float32)
+    t = A.atrace("after map", [A.map(lambda v: v + 1, x), A.zip(y, y)], A.map(lambda v: v * 2, x))
+    capfd.readouterr()
+    got = backend.run(t, gpu_ctx)
+    err = capfd.readouterr().err
+    assert np.array_equal(got, x * 2)
+    assert err == "after map: Matrix (Z :. 2 :. 3) [1,2,3,4,5,6], Vector (Z :. 2) [(1.5,1.5),(2.25,2.25)]\n"
+    got = backend.run(A.map(lambda v: v + 1, A.atrace("no arrays", None, x)), gpu_ctx)
+    assert np.array_equal(got, x + 1) and capfd.readouterr().err == "no arrays\n"
+    t = A.aforeign("vendor.scale", lambda a: A.map(lambda v: v * 3.0, a), y)
+    assert np.array_equal(backend.run(t, gpu_ctx), y * 3)
