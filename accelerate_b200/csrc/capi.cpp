@@ -30,6 +30,12 @@ DevArrayP lookup(Ctx& c, uint64_t id) {
   if (it == c.arrays.end()) throw Error(B200_ERR_ARG, "unknown array id " + std::to_string(id));
   return it->second;
 }
+// the same for an array that is about to be used on the main stream (or handed out as a raw pointer)
+DevArrayP lookup_used(Ctx& c, uint64_t id) {
+  DevArrayP a = lookup(c, id);
+  for (auto& b : a->leaf) b->fresh = false;
+  return a;
+}
 Type parse_type_text(const char* s) {
   Sx x = parse_sexp(s, strlen(s));
   return parse_type(x);
@@ -86,6 +92,8 @@ int b200_ctx_create(int device, uint32_t flags, b200_ctx** out) {
   c.sm_count = prop.multiProcessorCount;
   c.check(cudaStreamCreateWithFlags(&c.stream, cudaStreamNonBlocking), "cudaStreamCreate");
   c.check(cudaStreamCreateWithFlags(&c.d2h_stream, cudaStreamNonBlocking), "cudaStreamCreate");
+  c.check(cudaStreamCreateWithFlags(&c.h2d_stream, cudaStreamNonBlocking), "cudaStreamCreate");
+  c.check(cudaEventCreateWithFlags(&c.h2d_fence, cudaEventDisableTiming), "cudaEventCreate");
   {
     int lo = 0, hi = 0;
     c.check(cudaDeviceGetStreamPriorityRange(&lo, &hi), "cudaDeviceGetStreamPriorityRange");
@@ -133,6 +141,8 @@ void b200_ctx_destroy(b200_ctx* ctx) {
   cudaStreamSynchronize(c.stream);
   cudaFree(c.d_words);
   cudaStreamDestroy(c.d2h_stream);
+  if (c.h2d_fence) cudaEventDestroy(c.h2d_fence);
+  if (c.h2d_stream) cudaStreamDestroy(c.h2d_stream);
   if (c.aux_fork) cudaEventDestroy(c.aux_fork);
   if (c.aux_join) cudaEventDestroy(c.aux_join);
   if (c.aux_stream) cudaStreamDestroy(c.aux_stream);
@@ -146,7 +156,7 @@ int b200_array_new(b200_ctx* ctx, const char* elt_type, int rank, const int64_t*
   Ctx& c = ctx->c;
   std::lock_guard<std::mutex> g(c.mu);
   c.check(cudaSetDevice(c.device), "cudaSetDevice");
-  DevArrayP a = c.new_array(parse_type_text(elt_type), std::vector<int64_t>(shape, shape + rank));
+  DevArrayP a = c.new_array(parse_type_text(elt_type), std::vector<int64_t>(shape, shape + rank), true);
   *id = c.next_id++;
   c.arrays[*id] = a;
   B200_END
@@ -187,27 +197,20 @@ int b200_array_upload(b200_ctx* ctx, uint64_t id, int leaf, const void* host, si
   if ((size_t)leaf < a->pending.size()) a->pending[leaf] = nullptr;      // an explicit upload replaces an adopted payload
   if (bytes) {
     if (!host) throw Error(B200_ERR_ARG, "null host pointer");
-    c.check(cudaMemcpyAsync(a->leaf[leaf]->ptr, host, bytes, cudaMemcpyHostToDevice, c.stream), "cudaMemcpyAsync(H2D)");
-    // the caller's buffer may be reused or collected as soon as we return
-    c.check(cudaStreamSynchronize(c.stream), "cudaStreamSynchronize");
-    c.h2d += (long long)bytes;
+    c.upload(*a->leaf[leaf], host, bytes);
   }
   B200_END
 }
 
 // Copy adopted host payloads now: the array is about to be used on the device (caller holds c.mu).
 static void materialise(Ctx& c, DevArray& a) {
-  bool any = false;
   for (size_t k = 0; k < a.pending.size(); ++k) {
     if (!a.pending[k]) continue;
-    const size_t bytes = a.leaf[k]->bytes;
-    c.check(cudaMemcpyAsync(a.leaf[k]->ptr, a.pending[k], bytes, cudaMemcpyHostToDevice, c.stream), "cudaMemcpyAsync(H2D)");
-    c.h2d += (long long)bytes;
+    // (the owner of the host buffers may let go of them as soon as the call that triggered the copy returns:
+    // Ctx::upload waits for the copy)
+    c.upload(*a.leaf[k], a.pending[k], a.leaf[k]->bytes);
     a.pending[k] = nullptr;
-    any = true;
   }
-  // the owner of the host buffers may let go of them as soon as the call that triggered the copy returns
-  if (any) c.check(cudaStreamSynchronize(c.stream), "cudaStreamSynchronize");
 }
 
 int b200_array_adopt_host(b200_ctx* ctx, uint64_t id, int leaf, const void* host, size_t bytes) {
@@ -244,7 +247,7 @@ int b200_array_download(b200_ctx* ctx, uint64_t id, int leaf, void* host, size_t
   Ctx& c = ctx->c;
   std::lock_guard<std::mutex> g(c.mu);
   c.check(cudaSetDevice(c.device), "cudaSetDevice");
-  DevArrayP a = lookup(c, id);
+  DevArrayP a = lookup_used(c, id);
   if (leaf < 0 || (size_t)leaf >= a->leaf.size()) throw Error(B200_ERR_ARG, "leaf index out of range");
   if (bytes != a->leaf[leaf]->bytes) throw Error(B200_ERR_ARG, "download size does not match the array");
   materialise(c, *a);
@@ -263,7 +266,7 @@ int b200_array_download_async(b200_ctx* ctx, uint64_t id, int leaf, void* host, 
   Ctx& c = ctx->c;
   std::lock_guard<std::mutex> g(c.mu);
   c.check(cudaSetDevice(c.device), "cudaSetDevice");
-  DevArrayP a = lookup(c, id);
+  DevArrayP a = lookup_used(c, id);
   if (leaf < 0 || (size_t)leaf >= a->leaf.size()) throw Error(B200_ERR_ARG, "leaf index out of range");
   if (bytes != a->leaf[leaf]->bytes) throw Error(B200_ERR_ARG, "download size does not match the array");
   materialise(c, *a);
@@ -299,7 +302,7 @@ int b200_array_intern(b200_ctx* ctx, uint64_t key, const char* elt_type, int ran
     if (a->elt != elt || a->shape != sh) throw Error(B200_ERR_ARG, "array key " + std::to_string(key) + " was registered with another type or shape");
   } else {
     c.check(cudaSetDevice(c.device), "cudaSetDevice");
-    a = c.new_array(elt, sh);
+    a = c.new_array(elt, sh, true);
     if (a->size() > 0) {
       if (!host_leaves) throw Error(B200_ERR_ARG, "null host pointer");
       a->pending.assign(a->leaf.size(), nullptr);
@@ -363,7 +366,7 @@ int b200_array_leaf_type(b200_ctx* ctx, uint64_t id, int leaf, const char** name
 int b200_array_devptr(b200_ctx* ctx, uint64_t id, int leaf, void** ptr) {
   B200_TRY
   std::lock_guard<std::mutex> g(ctx->c.mu);
-  DevArrayP a = lookup(ctx->c, id);
+  DevArrayP a = lookup_used(ctx->c, id);
   if (leaf < 0 || (size_t)leaf >= a->leaf.size()) throw Error(B200_ERR_ARG, "leaf index out of range");
   ctx->c.check(cudaSetDevice(ctx->c.device), "cudaSetDevice");
   materialise(ctx->c, *a);
@@ -407,7 +410,7 @@ int b200_program_run(b200_program* prog, const uint64_t* in_ids, int n_in, uint6
   std::lock_guard<std::mutex> g(c.mu);
   c.check(cudaSetDevice(c.device), "cudaSetDevice");
   std::vector<DevArrayP> ins, outs;
-  for (int k = 0; k < n_in; ++k) ins.push_back(lookup(c, in_ids[k]));
+  for (int k = 0; k < n_in; ++k) ins.push_back(lookup_used(c, in_ids[k]));
   for (auto& a : ins) materialise(c, *a);
   prog->p.run(ins, outs);
   if ((int)outs.size() != n_out) throw Error(B200_ERR_ARG, "program yields " + std::to_string(outs.size()) + " arrays");
@@ -425,9 +428,9 @@ int b200_program_run_rows(b200_program* prog, const uint64_t* in_ids, int n_in, 
   std::lock_guard<std::mutex> g(c.mu);
   c.check(cudaSetDevice(c.device), "cudaSetDevice");
   std::vector<DevArrayP> ins;
-  for (int k = 0; k < n_in; ++k) ins.push_back(lookup(c, in_ids[k]));
+  for (int k = 0; k < n_in; ++k) ins.push_back(lookup_used(c, in_ids[k]));
   for (auto& a : ins) materialise(c, *a);
-  prog->p.run_rows(ins, lookup(c, out_id), row_lo, row_hi);
+  prog->p.run_rows(ins, lookup_used(c, out_id), row_lo, row_hi);
   B200_END
 }
 

@@ -137,6 +137,7 @@ bool nccl_type(Ty t, ncclDataType_t* out) {
 DevArrayP lookup(Ctx& c, uint64_t id) {
   auto it = c.arrays.find(id);
   if (it == c.arrays.end()) throw Error(B200_ERR_ARG, "unknown array id " + std::to_string(id));
+  for (auto& b : it->second->leaf) b->fresh = false;      // about to be used on the context's streams
   return it->second;
 }
 

@@ -62,7 +62,9 @@ void Ctx::release(void* ptr, size_t capacity) {
   {
     std::lock_guard<std::mutex> g(nursery.mu);
     if (capacity && nursery.bytes + capacity <= nursery.limit) {
-      nursery.blocks.emplace(capacity, ptr);
+      cudaEvent_t ev = nullptr;
+      if (cudaEventCreateWithFlags(&ev, cudaEventDisableTiming) == cudaSuccess) cudaEventRecord(ev, stream);
+      nursery.blocks.emplace(capacity, Nursery::Block{ptr, ev});
       nursery.bytes += capacity;
       return;
     }
@@ -72,9 +74,27 @@ void Ctx::release(void* ptr, size_t capacity) {
 
 void Ctx::purge() {
   std::lock_guard<std::mutex> g(nursery.mu);
-  for (auto& b : nursery.blocks) cudaFreeAsync(b.second, stream);
+  for (auto& b : nursery.blocks) {
+    if (b.second.released) cudaEventDestroy(b.second.released);
+    cudaFreeAsync(b.second.ptr, stream);
+  }
   nursery.blocks.clear();
   nursery.bytes = 0;
+}
+
+void Ctx::upload(Buffer& b, const void* host, size_t bytes) {
+  if (!bytes) return;
+  if (b.busy && cudaEventQuery(b.busy) != cudaSuccess) check(cudaStreamWaitEvent(h2d_stream, b.busy, 0), "cudaStreamWaitEvent");
+  if (!b.fresh) {
+    // the block may still be read or written by work queued on the main stream: the copy goes behind it
+    check(cudaEventRecord(h2d_fence, stream), "cudaEventRecord");
+    check(cudaStreamWaitEvent(h2d_stream, h2d_fence, 0), "cudaStreamWaitEvent");
+  }
+  check(cudaMemcpyAsync(b.ptr, host, bytes, cudaMemcpyHostToDevice, h2d_stream), "cudaMemcpyAsync(H2D)");
+  // the caller's buffer may be reused or collected as soon as we return; and whatever is launched on the
+  // main stream from now on finds the data in place
+  check(cudaStreamSynchronize(h2d_stream), "cudaStreamSynchronize");
+  h2d += (long long)bytes;
 }
 
 void Ctx::reap(bool wait) {
@@ -92,7 +112,7 @@ void Ctx::reap(bool wait) {
   deferred.resize(kept);
 }
 
-std::shared_ptr<Buffer> Ctx::alloc(size_t bytes) {
+std::shared_ptr<Buffer> Ctx::alloc(size_t bytes, bool for_caller) {
   auto b = std::make_shared<Buffer>();
   b->ctx = this;
   b->bytes = bytes;
@@ -104,7 +124,11 @@ std::shared_ptr<Buffer> Ctx::alloc(size_t bytes) {
       std::lock_guard<std::mutex> g(nursery.mu);
       auto it = nursery.blocks.find(cap);
       if (it != nursery.blocks.end()) {
-        b->ptr = it->second;
+        b->ptr = it->second.ptr;
+        if (it->second.released) {
+          b->fresh = for_caller && cudaEventQuery(it->second.released) == cudaSuccess;
+          cudaEventDestroy(it->second.released);
+        }
         nursery.blocks.erase(it);
         nursery.bytes -= cap;
         nursery.hits++;
@@ -140,13 +164,13 @@ bool DevArray::aligned16() const {
   return true;
 }
 
-DevArrayP Ctx::new_array(const Type& elt, const std::vector<int64_t>& shape) {
+DevArrayP Ctx::new_array(const Type& elt, const std::vector<int64_t>& shape, bool for_caller) {
   auto a = std::make_shared<DevArray>();
   a->elt = elt;
   a->leaf_ty = elt.leaves();
   a->shape = shape;
   const int64_t n = a->size();
-  for (Ty t : a->leaf_ty) a->leaf.push_back(alloc((size_t)n * ty_bytes[t]));
+  for (Ty t : a->leaf_ty) a->leaf.push_back(alloc((size_t)n * ty_bytes[t], for_caller));
   return a;
 }
 

@@ -54,6 +54,10 @@ struct Buffer {
   size_t bytes = 0;
   size_t capacity = 0;          // what was asked of the allocator (bytes rounded up to the nursery's chunk)
   bool owned = true;
+  // No work that touches this block is queued on the context's main stream: it was created for the caller
+  // from a nursery block whose previous owner's work had finished, and has not been handed to a program, a
+  // download or an exchange since.  An upload into such a buffer need not wait for the kernels in flight.
+  bool fresh = false;
   cudaEvent_t busy = nullptr;   // last asynchronous download of this buffer (on the copy-out stream)
   ~Buffer();
 };
@@ -74,6 +78,8 @@ struct Ctx {
   int sm_count = 148;
   cudaStream_t stream = nullptr;
   cudaStream_t d2h_stream = nullptr;   // asynchronous downloads run here, beside kernels and uploads
+  cudaStream_t h2d_stream = nullptr;   // uploads run here: they wait for the copy, not for the kernels in flight
+  cudaEvent_t h2d_fence = nullptr;
   // A small kernel that may run beside a large one of the same node (the frame of a staged stencil) goes
   // to this higher-priority stream, forked from and joined to `stream` with the two events.
   cudaStream_t aux_stream = nullptr;
@@ -92,7 +98,8 @@ struct Ctx {
   // reuse needs no further ordering.
   struct Nursery {
     std::mutex mu;
-    std::multimap<size_t, void*> blocks;
+    struct Block { void* ptr; cudaEvent_t released; };   // `released`: recorded on the main stream when the block came here
+    std::multimap<size_t, Block> blocks;
     size_t bytes = 0, limit = 0;
     long long hits = 0;
   } nursery;
@@ -122,8 +129,11 @@ struct Ctx {
   std::atomic<long long> launches{0}, h2d{0}, d2h{0}, mem_hits{0}, allocated{0}, runs{0}, inplace_permutes{0};
   long long spin_limit = 1 << 22;
 
-  DevArrayP new_array(const Type& elt, const std::vector<int64_t>& shape);
-  std::shared_ptr<Buffer> alloc(size_t bytes);
+  DevArrayP new_array(const Type& elt, const std::vector<int64_t>& shape, bool for_caller = false);
+  // Host -> device copy of one leaf on the upload stream; returns when the host buffer may be reused.
+  void upload(Buffer& b, const void* host, size_t bytes);
+  // `for_caller`: the buffer is created through the C ABI for host data (it may turn out `fresh`)
+  std::shared_ptr<Buffer> alloc(size_t bytes, bool for_caller = false);
   void check(cudaError_t e, const char* what);
   void check(CUresult e, const char* what);
   CompiledKernel& kernel(const std::string& source, const std::string& entry, int threads, size_t dyn_smem);
