@@ -737,11 +737,16 @@ Glue build_glue(const Node& n, const std::map<std::string, ArrayInfo>& arrays) {
           CVal r;
           r.ty = pelemT;
           r.leaf.push_back(m.leaf[0]);
-          // linear target, or -1 when any component lies outside its dimension
+          // linear target, or -1 when any component lies outside its dimension.  (A rank-1 target is its own
+          // linear index and the kernel compares every linear index with the target's size: nothing to add.)
           std::vector<std::string> tix(m.leaf.begin() + 1, m.leaf.end());
-          std::string inside = "true";
-          for (size_t d = 0; d < tix.size(); ++d) inside += " && (u64)(" + tix[d] + ") < (u64)(" + outsh[d] + ")";
-          r.leaf.push_back(g.def(I64, "(" + inside + ") ? " + g.to_index(outsh, tix) + " : (i64)-1"));
+          if (tix.size() == 1) {
+            r.leaf.push_back(tix[0]);
+          } else {
+            std::string inside = "true";
+            for (size_t d = 0; d < tix.size(); ++d) inside += " && (u64)(" + tix[d] + ") < (u64)(" + outsh[d] + ")";
+            r.leaf.push_back(g.def(I64, "(" + inside + ") ? " + g.to_index(outsh, tix) + " : (i64)-1"));
+          }
           r.leaf.insert(r.leaf.end(), v.leaf.begin(), v.leaf.end());
           return r;
         });

@@ -1185,7 +1185,7 @@ void Program::exec_kernel_node(const Node& n, Env& env_ref) {
           L.named["priv"] = std::min<int64_t>(out_n, cap / bytes);
           L.named["priv16"] = 0;
           CompiledKernel& ks = node_kernel(c, st, "permute", {{"PERMUTE_SAMPLE", "1"}}, "acc_permute_sample", 1024, 0);
-          L.launch(ks, 1, 1024, 0);
+          L.launch(ks, (std::min<int64_t>(total, 65536) + 1023) / 1024, 1024, 0);
           const int64_t words16 = (out_n + 1) / 2;
           const size_t smem = (size_t)words16 * 4;
           std::map<std::string, std::string> var = {{"PERMUTE_SMEM16", "1"}, {"PERMUTE_THREADS", "1024"}, {"PERMUTE_CHOICE_ID", "1"}};

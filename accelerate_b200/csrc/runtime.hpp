@@ -111,7 +111,7 @@ struct Ctx {
   std::map<uint64_t, DevArrayP> arrays;
   uint64_t next_id = 1;
   std::map<uint64_t, DevArrayP> table;   // device copies of host arrays by the host array's unique id
-  // device words: [0] error status, [1] fold ticket counter, [2] scan ticket counter, [3] scan exit counter, [4] permute kernel choice
+  // device words: [0] error status, [1] fold ticket counter, [2] scan ticket counter, [3] scan exit counter, [4..6] permute kernel choice (verdict, count, ticket)
   int* d_words = nullptr;
   // scan descriptors (persistent, epoch-tagged)
   // One region per descriptor layout (width, spacing, region offsets: the layout string), at most

@@ -191,12 +191,13 @@ __device__ __forceinline__ void permute_update(const Params& p, i64 dst, const e
 #endif
 }
 
-__device__ __forceinline__ void permute_elem(const Params& p, const pelem_t& e) {
+__device__ __forceinline__ void permute_elem(const Params& p, const pelem_t& e, bool& outside) {
   // the reference checks every component of the target index (indexCheck in toIndex,
-  // Shape.hs:102-106); the generated index function yields -1 for a target outside the array
+  // Shape.hs:102-106); the generated index function yields -1 for a target outside the array.
+  // The thread only notes the fact here and reports it once, after its loop.
   if (e.l0 != 0) {
     if ((u64)e.l1 < (u64)p.out_n) permute_update(p, e.l1, P_value(e));
-    else acc_fail(p.err, 1003 /* index out of bounds */);
+    else outside = true;
   }
 }
 
@@ -208,6 +209,9 @@ __device__ __forceinline__ void permute_elem(const Params& p, const pelem_t& e) 
 // *choice if more than 1 in 64 of their targets lie outside the first `priv` elements, else 0; both
 // kernels are launched behind it and the one that is not chosen returns at once (no host round trip).
 #if defined(PERMUTE_SAMPLE) && PERMUTE_SAMPLE
+// One sample per thread, ceil(samples / 1024) CTAs (a single CTA walking all 65 536 samples took 90 us:
+// every sample is a separate sector).  `choice` points at three words: the verdict, the count so far and a
+// ticket; the CTA that draws the last ticket writes the verdict and clears the other two for the next launch.
 extern "C" __global__ void __launch_bounds__(1024) acc_permute_sample(const Params p) {
   __shared__ u32 outside;
   const i64 n = p.n, inner = P_INNER;
@@ -215,17 +219,29 @@ extern "C" __global__ void __launch_bounds__(1024) acc_permute_sample(const Para
   __syncthreads();
   const i64 samples = n < 65536 ? n : 65536;
   const i64 step = n / samples;
-  u32 mine = 0;
-  for (i64 k = threadIdx.x; k < samples; k += 1024) {
+  const i64 k = (i64)blockIdx.x * 1024 + threadIdx.x;
+  bool out = false;
+  if (k < samples) {
     const i64 i = k * step;
     i64 row = 0, j = i;
     if (inner != n) { row = i / inner; j = i - row * inner; }
     const pelem_t e = P_get(p, row, j);
-    if (e.l0 != 0 && e.l1 >= p.priv) ++mine;
+    out = e.l0 != 0 && e.l1 >= p.priv;
   }
-  atomicAdd(&outside, mine);
+  const unsigned m = __ballot_sync(ACC_FULL_MASK, out);
+  if ((threadIdx.x & 31) == 0 && m) atomicAdd(&outside, (u32)__popc(m));
   __syncthreads();
-  if (threadIdx.x == 0) *reinterpret_cast<int*>(p.choice) = (i64)outside * 64 > samples ? 1 : 0;
+  if (threadIdx.x == 0) {
+    int* w = reinterpret_cast<int*>(p.choice);
+    if (outside) atomicAdd(&w[1], (int)outside);
+    __threadfence();
+    if (atomicAdd(&w[2], 1) == (int)gridDim.x - 1) {
+      __threadfence();
+      const i64 total = atomicExch(&w[1], 0);
+      w[0] = total * 64 > samples ? 1 : 0;
+      w[2] = 0;
+    }
+  }
 }
 #endif
 #ifndef PERMUTE_CHOICE_ID
@@ -252,6 +268,7 @@ extern "C" __global__ void __launch_bounds__(PERMUTE_THREADS) acc_permute(const 
   __syncthreads();
 #endif
   i64 done = 0;
+  bool outside = false;             // some target index of this thread lay outside the array
   if (p.vec) {
     const i64 nv = n >> 2;
     i64 v = tid;
@@ -281,7 +298,7 @@ extern "C" __global__ void __launch_bounds__(PERMUTE_THREADS) acc_permute(const 
         for (int k = 0; k < 4; ++k) {
           const pelem_t& e = x[u][k];
           if (e.l0 != 0) {
-            if ((u64)e.l1 >= (u64)p.out_n) acc_fail(p.err, 1003 /* index out of bounds */);
+            if ((u64)e.l1 >= (u64)p.out_n) outside = true;
             else permute_settle16(p, e.l1, permute_bits(P_value(e).l0), found[u][k]);
           }
         }
@@ -290,7 +307,7 @@ extern "C" __global__ void __launch_bounds__(PERMUTE_THREADS) acc_permute(const 
 #pragma unroll
       for (int u = 0; u < PERMUTE_UNROLL; ++u) {
 #pragma unroll
-        for (int k = 0; k < 4; ++k) permute_elem(p, x[u][k]);
+        for (int k = 0; k < 4; ++k) permute_elem(p, x[u][k], outside);
       }
 #endif
     }
@@ -301,15 +318,16 @@ extern "C" __global__ void __launch_bounds__(PERMUTE_THREADS) acc_permute(const 
       pelem_t x[4];
       P_get4(p, row, j, x);
 #pragma unroll
-      for (int k = 0; k < 4; ++k) permute_elem(p, x[k]);
+      for (int k = 0; k < 4; ++k) permute_elem(p, x[k], outside);
     }
     done = nv << 2;
   }
   for (i64 i = done + tid; i < n; i += nthreads) {
     i64 row = 0, j = i;
     if (inner != n) { row = i / inner; j = i - row * inner; }
-    permute_elem(p, P_get(p, row, j));
+    permute_elem(p, P_get(p, row, j), outside);
   }
+  if (outside) acc_fail(p.err, 1003 /* index out of bounds */);
 #if PERMUTE_SMEM
   __syncthreads();
   for (i64 b = threadIdx.x; b < p.priv; b += PERMUTE_THREADS) {
