@@ -196,3 +196,22 @@ def test_kernel_cache_disk_hit_force_recompile_and_damaged_files(lib_built, tmp_
     # another scalar body is another kernel; another array SIZE is not (shapes are kernel parameters)
     assert "compiled" in _check(A.build_program(A.map(lambda v: v * 7 + 4, np.zeros(8, np.int32))).text)
     assert "from the disk cache" in _check(A.build_program(A.map(lambda v: v * 7 + 3, np.zeros(100000, np.int32))).text)
+
+
+def test_bench_strong_scaling_parts_are_consistent():
+    # bench.py splits the config size over the ranks for its strong-scaling figures: the first 1/N of every input,
+    # and for fold1Seg whole segments whose lengths add up to the values that are kept
+    import importlib.util
+    spec = importlib.util.spec_from_file_location("bench_mod", os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "bench.py"))
+    bench = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(bench)
+    ws = {w.name: w for w in bench.suite(scale=14)}
+    for world in (2, 3, 8):
+        w = ws["fold1seg_add_i32"]
+        vals, lens = [f() for f in w.inputs]
+        v2, l2 = bench.strong_part(w, [vals, lens], world)
+        assert int(l2.sum()) == v2.size and 0 < v2.size <= vals.size // world + 2048 and np.array_equal(v2, vals[:v2.size])
+        w = ws["fold_max_rows_f32"]
+        m, = [f() for f in w.inputs]
+        p, = bench.strong_part(w, [m], world)
+        assert p.shape == (max(1, m.shape[0] // world), m.shape[1])
