@@ -63,6 +63,7 @@ def lib():
         l.b200_program_num_outputs.argtypes = [vp, ctypes.POINTER(ctypes.c_int)]
         l.b200_program_run.argtypes = [vp, u64p, ctypes.c_int, u64p, ctypes.c_int]
         l.b200_program_run_rows.argtypes = [vp, u64p, ctypes.c_int, ctypes.c_uint64, ctypes.c_int64, ctypes.c_int64]
+        l.b200_program_run_rows2.argtypes = [vp, u64p, ctypes.c_int, ctypes.c_uint64, ctypes.c_int64, ctypes.c_int64, ctypes.c_int64, ctypes.c_int64]
         l.b200_group_unique_id.argtypes = [ctypes.c_char_p]
         l.b200_group_create.argtypes = [vp, ctypes.c_char_p, ctypes.c_int, ctypes.c_int, ctypes.c_double, ctypes.POINTER(vp)]
         l.b200_group_destroy.argtypes = [vp]
@@ -272,6 +273,12 @@ class Context:
         p = self.load(text)
         ins = (ctypes.c_uint64 * max(1, len(inputs)))(*[a.id for a in inputs])
         _check(lib().b200_program_run_rows(p, ins, len(inputs), out.id, row_lo, row_hi))
+
+    def run_rows2(self, text, inputs, out, row_lo, row_hi, row_lo2, row_hi2):
+        """The same for two ranges of rows (the second above the first) in one launch."""
+        p = self.load(text)
+        ins = (ctypes.c_uint64 * max(1, len(inputs)))(*[a.id for a in inputs])
+        _check(lib().b200_program_run_rows2(p, ins, len(inputs), out.id, row_lo, row_hi, row_lo2, row_hi2))
 
     def sync(self):
         try:

@@ -434,6 +434,20 @@ int b200_program_run_rows(b200_program* prog, const uint64_t* in_ids, int n_in, 
   B200_END
 }
 
+int b200_program_run_rows2(b200_program* prog, const uint64_t* in_ids, int n_in, uint64_t out_id, int64_t row_lo, int64_t row_hi,
+                           int64_t row_lo2, int64_t row_hi2) {
+  B200_TRY
+  if (!prog) throw Error(B200_ERR_ARG, "null program");
+  Ctx& c = *prog->p.ctx;
+  std::lock_guard<std::mutex> g(c.mu);
+  c.check(cudaSetDevice(c.device), "cudaSetDevice");
+  std::vector<DevArrayP> ins;
+  for (int k = 0; k < n_in; ++k) ins.push_back(lookup_used(c, in_ids[k]));
+  for (auto& a : ins) materialise(c, *a);
+  prog->p.run_rows(ins, lookup_used(c, out_id), row_lo, row_hi, row_lo2, row_hi2);
+  B200_END
+}
+
 int b200_sync(b200_ctx* ctx) {
   B200_TRY
   if (!ctx) throw Error(B200_ERR_ARG, "null context");

@@ -1007,7 +1007,7 @@ Glue build_glue(const Node& n, const std::map<std::string, ArrayInfo>& arrays) {
       named = {"n", "rows", "tiles_per_row", "total_tiles", "batches_per_row", "total_batches", "in_vec", "out_vec", "status", "agg", "incl", "gstatus", "groups_per_row", "counter", "epoch", "err", "spin_limit"};
       break;
     case N_PERMUTE: named = {"n", "vec", "out_n", "priv", "priv16", "choice", "locks", "err", "spin_limit"}; break;
-    case N_STENCIL: case N_STENCIL2: named = {"o0", "o1", "o2", "row0", "row1", "tiles1", "tiles2", "vec", "?fr_strips", "?fr_r0", "?fr_r1", "?strip0", "?err", "?spin_limit"}; break;
+    case N_STENCIL: case N_STENCIL2: named = {"o0", "o1", "o2", "row0", "row1", "tiles1", "tiles2", "vec", "?fr_strips", "?fr_r0", "?fr_r1", "?strip0", "?err", "?spin_limit", "?row2", "?row3"}; break;
     default: break;
   }
   for (auto& nm : named) b.ps.use_named(nm);

@@ -388,6 +388,12 @@ std::vector<std::pair<std::string, std::map<std::string, std::string>>> default_
           v.push_back({"stencil2d", stencil2d_bulk_variant(stencil2d_bulk_shape())});
           v.push_back({"stencil2d", stencil2d_frame_variant()});
         }
+        {
+          auto tv = stencil2d_variant();
+          tv["ST2_TWOWIN"] = "1";
+          tv["ACC_OPT_PARAMS"] = "1";
+          v.push_back({"stencil2d", tv});
+        }
       }
       break;
     case N_RESHAPE: break;
@@ -786,12 +792,13 @@ void Program::run(const std::vector<DevArrayP>& inputs, std::vector<DevArrayP>& 
   for (auto& o : ir->outputs) outputs.push_back(env.at(o));
 }
 
-void Program::run_rows(const std::vector<DevArrayP>& inputs, const DevArrayP& out, int64_t row_lo, int64_t row_hi) {
+void Program::run_rows(const std::vector<DevArrayP>& inputs, const DevArrayP& out, int64_t row_lo, int64_t row_hi, int64_t row_lo2, int64_t row_hi2) {
   if (ir->nodes.size() != 1 || (ir->nodes[0].kind != N_STENCIL && ir->nodes[0].kind != N_STENCIL2) || ir->outputs.size() != 1 ||
       ir->outputs[0] != ir->nodes[0].outs[0])
     throw Error(B200_ERR_ARG, "a row window needs a program that is exactly one stencil node");
   if (!out) throw Error(B200_ERR_ARG, "null output array");
-  Window w{out, row_lo, row_hi};
+  if (row_lo2 < row_hi2 && (row_lo2 < row_hi || row_lo >= row_hi)) throw Error(B200_ERR_ARG, "row windows: the second range must lie above a non-empty first one");
+  Window w{out, row_lo, row_hi, row_lo2, std::max(row_lo2, row_hi2)};
   struct Guard { const Window*& slot; ~Guard() { slot = nullptr; } } guard{window};
   window = &w;
   std::vector<DevArrayP> outs;
@@ -1226,7 +1233,8 @@ void Program::exec_kernel_node(const Node& n, Env& env_ref) {
         std::vector<int64_t> osh = ext[0];
         for (size_t a = 1; a < ext.size(); ++a)
           for (int d = 0; d < rank; ++d) osh[d] = std::min(osh[d], ext[a][d]);  // Shape.hs:81-91
-        if (window && (rank != 2 || window->out->shape != osh || window->out->elt != n.elt || window->lo < 0 || window->hi > osh[0] || window->lo > window->hi))
+        if (window && (rank != 2 || window->out->shape != osh || window->out->elt != n.elt || window->lo < 0 || window->hi > osh[0] || window->lo > window->hi ||
+                       window->hi2 > osh[0]))
           throw Error(B200_ERR_ARG, "row window: the output array does not have the shape and type of the stencil's result, or the rows lie outside it");
         DevArrayP out = window ? window->out : c.new_array(n.elt, osh);
         L.outs = {out};
@@ -1305,6 +1313,19 @@ void Program::exec_kernel_node(const Node& n, Env& env_ref) {
             break;
           }
           CompiledKernel& k2 = node_kernel(c, st, "stencil2d", var, "acc_stencil2d", warps * 32, 0);
+          if (window && window->hi2 > window->lo2) {
+            // two row ranges in one launch (the rows at either edge of a slab)
+            std::map<std::string, std::string> tvar = var;
+            tvar["ST2_TWOWIN"] = "1";
+            tvar["ACC_OPT_PARAMS"] = "1";
+            const int64_t both = rowblocks + (window->hi2 - window->lo2 + rows - 1) / rows;
+            L.named["tiles1"] = both;
+            L.named["row2"] = window->lo2;
+            L.named["row3"] = window->hi2;
+            CompiledKernel& kt = node_kernel(c, st, "stencil2d", tvar, "acc_stencil2d", warps * 32, 0);
+            L.launch(kt, (strips * both + warps - 1) / warps, warps * 32, 0);
+            break;
+          }
           const int64_t ctas = (strips * rowblocks + warps - 1) / warps;
           L.launch(k2, ctas, warps * 32, 0);  // one warp per task; the hardware scheduler balances the tail
           break;

@@ -157,10 +157,11 @@ struct Program {
   void run(const std::vector<DevArrayP>& inputs, std::vector<DevArrayP>& outputs);
   // A program that is one rank-2 stencil (or stencil2) node: produce rows [row_lo, row_hi) of its
   // result in the existing array `out` (same shape and element type as the result).
-  void run_rows(const std::vector<DevArrayP>& inputs, const DevArrayP& out, int64_t row_lo, int64_t row_hi);
+  // (`row_lo2 < row_hi2`: a second range of rows, above the first, computed by the same launch)
+  void run_rows(const std::vector<DevArrayP>& inputs, const DevArrayP& out, int64_t row_lo, int64_t row_hi, int64_t row_lo2 = 0, int64_t row_hi2 = 0);
 
  private:
-  struct Window { DevArrayP out; int64_t lo, hi; };
+  struct Window { DevArrayP out; int64_t lo, hi, lo2, hi2; };
   const Window* window = nullptr;
   typedef std::map<std::string, DevArrayP> Env;
   void liveness_of(const std::vector<Node>& nodes, const std::vector<std::string>& keep);

@@ -28,6 +28,9 @@
 #ifndef ST2_FRAME
 #define ST2_FRAME 0      // 1: the kernel computes the frame around acc_stencil2d_bulk's part (see the kernel)
 #endif
+#ifndef ST2_TWOWIN
+#define ST2_TWOWIN 0     // 1: two row ranges (named parameters row2, row3 besides row0, row1)
+#endif
 #ifndef ST2_WARPS
 #define ST2_WARPS 4
 #endif
@@ -85,7 +88,18 @@
 
 extern "C" __global__ void __launch_bounds__(ST2_THREADS, ST2_MIN_BLOCKS) acc_stencil2d(const Params p) {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-#if !ST2_FRAME
+#if ST2_TWOWIN
+  // two row ranges in one launch: rows row0 .. row1-1, then rows row2 .. row3-1 (tiles1 counts the row blocks of both)
+  const i64 task = (i64)blockIdx.x * ST2_WARPS + warp;
+  if (task >= p.tiles1 * p.tiles2) return;
+  const int o1 = (int)p.o1, o2 = (int)p.o2;
+  const int rb = (int)(task / p.tiles2);
+  const int strip = (int)(task - (i64)rb * p.tiles2);
+  const int gx0 = strip * ST2_STRIP - 4 + lane * 4;
+  const int rb1 = (int)((p.row1 - p.row0 + ST2_ROWS - 1) / ST2_ROWS);
+  const int y0 = rb < rb1 ? (int)p.row0 + rb * ST2_ROWS : (int)p.row2 + (rb - rb1) * ST2_ROWS;
+  const int y1 = min(y0 + ST2_ROWS, rb < rb1 ? (int)p.row1 : (int)p.row3);
+#elif !ST2_FRAME
   const i64 ntasks = p.tiles1 * p.tiles2;
   const i64 task = (i64)blockIdx.x * ST2_WARPS + warp;
   if (task >= ntasks) return;

@@ -109,6 +109,9 @@ class GpuExecutor:
     def run_rows(self, text, inputs, out, row_lo, row_hi):
         self.ctx.run_rows(text, inputs, out, row_lo, row_hi)
 
+    def run_rows2(self, text, inputs, out, row_lo, row_hi, row_lo2, row_hi2):
+        self.ctx.run_rows2(text, inputs, out, row_lo, row_hi, row_lo2, row_hi2)
+
     def run(self, key, build, inputs):
         """``build(*params)`` -> term(s).  The built program is cached under the input signature
         and the builder's own identity (its code and everything it captures: ``closure_key``);
@@ -369,9 +372,11 @@ class Sharded:
                 dst = spare[k % 2]
                 self.ex.run_rows(text, [src], dst, ilo, ihi)
                 g.halo_wait()
-                if ilo > lo:
+                if ilo > lo and ihi < hi:
+                    self.ex.run_rows2(text, [src], dst, lo, ilo, ihi, hi)      # both edges in one launch
+                elif ilo > lo:
                     self.ex.run_rows(text, [src], dst, lo, ilo)
-                if ihi < hi:
+                elif ihi < hi:
                     self.ex.run_rows(text, [src], dst, ihi, hi)
                 if k + 1 < iterations:
                     g.halo_exchange(dst, h.top, h.rows, h.bot, radius, up, down, overlap=True)

@@ -122,6 +122,10 @@ int b200_program_run(b200_program* prog, const uint64_t* in_ids, int n_in, uint6
  * Interpreter.hs:637-649, restricted to a range of its index space). */
 int b200_program_run_rows(b200_program* prog, const uint64_t* in_ids, int n_in, uint64_t out_id, int64_t row_lo,
                           int64_t row_hi);
+/* The same for two ranges of rows in one launch, [row_lo, row_hi) and, above it, [row_lo2, row_hi2): the rows at
+ * either edge of a slab once the neighbours' halo rows have arrived. */
+int b200_program_run_rows2(b200_program* prog, const uint64_t* in_ids, int n_in, uint64_t out_id, int64_t row_lo,
+                           int64_t row_hi, int64_t row_lo2, int64_t row_hi2);
 
 /* Wait for all work of the context (asynchronous downloads included) and report device-side failures. */
 int b200_sync(b200_ctx* ctx);

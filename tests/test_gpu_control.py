@@ -172,3 +172,32 @@ def test_gpu_atrace_and_aforeign(gpu_ctx, capfd):
     assert np.array_equal(got, x + 1) and capfd.readouterr().err == "no arrays\n"
     t = A.aforeign("vendor.scale", lambda a: A.map(lambda v: v * 3.0, a), y)
     assert np.array_equal(backend.run(t, gpu_ctx), y * 3)
+
+
+def test_gpu_stencil_row_windows_one_and_two_ranges(gpu_ctx):
+    # b200_program_run_rows / _rows2: rows of a one-stencil program's result written into an existing array
+    # (what the multi-GPU stencil uses for the rows that do and do not need fresh halo rows)
+    from accelerate_b200 import language as L
+    g = np.random.default_rng(3)
+    m = g.uniform(0, 1, (70, 300)).astype(np.float32)
+    jac = lambda s: 0.25 * (s[0][1] + s[2][1] + s[1][0] + s[1][2])  # noqa: E731
+    L.reset_names()
+    text = A.build_program(A.stencil(jac, A.clamp, L.param(2, "f32"))).text
+    a = gpu_ctx.from_host(m)
+    full, = gpu_ctx.execute(text, [a], 1)
+    want = full.download()
+    out = gpu_ctx.from_host(np.zeros_like(m))
+    gpu_ctx.run_rows(text, [a], out, 10, 40)
+    got = out.download()
+    assert np.array_equal(got[10:40], want[10:40]) and not got[:10].any() and not got[40:].any()
+    out2 = gpu_ctx.from_host(np.zeros_like(m))
+    gpu_ctx.run_rows2(text, [a], out2, 0, 3, 37, 70)
+    got = out2.download()
+    assert np.array_equal(got[:3], want[:3]) and np.array_equal(got[37:], want[37:]) and not got[3:37].any()
+    gpu_ctx.run_rows2(text, [a], out2, 3, 36, 36, 37)                  # the rest, in two ranges of very different size
+    assert np.array_equal(out2.download(), want)
+    with pytest.raises(backend.B200Error) as e:
+        gpu_ctx.run_rows2(text, [a], out2, 10, 20, 15, 30)             # overlapping ranges
+    assert e.value.code == 7
+    with pytest.raises(backend.B200Error):
+        gpu_ctx.run_rows2(text, [a], out2, 0, 3, 60, 71)               # outside the array
