@@ -702,6 +702,27 @@ Glue build_glue(const Node& n, const std::map<std::string, ArrayInfo>& arrays) {
       if (n.seed) b.nullary_fun("F_seed", *n.seed);
       def["ACC_SEEDED"] = n.seed ? "1" : "0";
       def["ACC_COMMUTATIVE"] = is_simple_prim(*n.f, &op, &opty) ? "1" : "0";
+      if (n.kind == N_FOLD && is_simple_prim(*n.f, &op, &opty) && (opty == I32 || opty == U32) && !n.elt.tuple) {
+        // a whole warp's 32-bit integers combine in one redux.sync (add, min, max, and, or, xor)
+        const char* r = nullptr;
+        switch (op) {
+          case P_ADD: r = "add"; break;
+          case P_MIN: r = "min"; break;
+          case P_MAX: r = "max"; break;
+          case P_BAND: r = "and"; break;
+          case P_BOR: r = "or"; break;
+          case P_BXOR: r = "xor"; break;
+          default: break;
+        }
+        if (r) {
+          const bool bits = op == P_BAND || op == P_BOR || op == P_BXOR;
+          def["FOLD_REDUX"] = std::string("\"redux.sync.") + r + (bits ? ".b32" : (opty == I32 ? ".s32" : ".u32")) + " %0, %1, 0xffffffff;\"";
+          def["FOLD_REDUX_IDENTITY"] = op == P_ADD || op == P_BOR || op == P_BXOR ? "0u"
+                                       : op == P_BAND ? "0xffffffffu"
+                                       : op == P_MIN ? (opty == I32 ? "0x7fffffffu" : "0xffffffffu")
+                                                     : (opty == I32 ? "0x80000000u" : "0u");
+        }
+      }
       b.output(0, n.elt);
       if (n.kind == N_SCAN2) b.output(1, n.elt);
       if (n.kind == N_FOLDSEG) def["seg_t"] = b.ps.need_struct(n.d[1].elt);

@@ -53,7 +53,20 @@ template <class T> __device__ __forceinline__ T fold_ld_shared_result(const T* s
 // is valid in thread 0.
 __device__ __forceinline__ void fold_block_reduce(const Params& p, elt_t& v, bool& have, elt_t* sm_v, int* sm_h) {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+#if defined(FOLD_REDUX)
+  {
+    // 32-bit integer (+), min, max, and, or, xor: the warp's values combine in one redux.sync; lanes that hold
+    // nothing contribute the operation's identity
+    const unsigned holders = __ballot_sync(ACC_FULL_MASK, have);
+    u32 x = FOLD_REDUX_IDENTITY, r;
+    if (have) memcpy(&x, &v.l0, 4);
+    asm volatile(FOLD_REDUX : "=r"(r) : "r"(x));
+    memcpy(&v.l0, &r, 4);
+    have = holders != 0;
+  }
+#else
   fold_group_reduce<32>(p, v, have, lane);
+#endif
   if (lane == 0) { sm_v[warp] = v; sm_h[warp] = have; }
   __syncthreads();
   if (threadIdx.x == 0) {
