@@ -277,6 +277,7 @@ unsupported what = error ("accelerate-b200: " ++ what ++ " are not supported by 
 --            | (use (array RANK ELT) (shape d..) (hex BYTES)+)        -- Use: one (hex ..) per scalar leaf
 --            | (acond exp (branch BODY) (branch BODY))                 -- Acond
 --            | (awhile AFUN AFUN (args NAME*)) | (apply AFUN (args NAME*))
+--            | (atrace (hex MESSAGE) (show NAME*) (args NAME*))        -- Atrace: print, then hand the args on
 --   AFUN    := (afun ((NAME (array RANK ELT))*) BODY)
 --   BODY    := (let LHS NODE)* (out NAME+)
 --   D       := (manifest NAME) | (delayed extent fun)
