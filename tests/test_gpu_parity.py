@@ -602,3 +602,16 @@ def test_bounded_wait_expiry_is_reported_and_the_context_stays_usable(monkeypatc
         assert np.array_equal(out.download(), np.cumsum(y, dtype=np.int32))
     finally:
         ctx.close()
+
+
+def test_sixteen_component_tuples():
+    # the widest tuples the reference's Elt instances cover (Sugar/Elt.hs: tuples up to 16): one buffer per component
+    a = ints(3000, np.int32, -50, 50)
+    wide = A.map(lambda v: A.tup(*[v + k for k in range(16)]), a)
+    plus = lambda p, q: A.tup(*[p[k] + q[k] for k in range(16)])  # noqa: E731
+    zero = A.tup(*[A.constant(np.int32(0)) for _ in range(16)])
+    check(wide)
+    check(A.fold(plus, zero, wide))
+    check(A.scanl1(plus, wide))
+    au = A.use(a)
+    check(A.permute(plus, A.fill(7, zero), lambda ix: A.Just_(A.index(A.from_integral(au[ix] % 7, "i64"))), wide))
