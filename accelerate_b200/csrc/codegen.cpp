@@ -1016,8 +1016,8 @@ Glue build_glue(const Node& n, const std::map<std::string, ArrayInfo>& arrays) {
       b.output(0, n.elt);
       break;
     }
-    case N_RESHAPE:
-      throw Error(B200_ERR_UNSUPPORTED, "reshape has no kernel");
+    default:
+      throw Error(B200_ERR_UNSUPPORTED, "this node has no kernel");      // reshape and the host-evaluated nodes
   }
   def["elt_t"] = E;
   switch (n.kind) {

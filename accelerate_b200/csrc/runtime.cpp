@@ -396,7 +396,7 @@ std::vector<std::pair<std::string, std::map<std::string, std::string>>> default_
         }
       }
       break;
-    case N_RESHAPE: break;
+    default: break;   // reshape and the host-evaluated nodes launch nothing
   }
   return v;
 }
