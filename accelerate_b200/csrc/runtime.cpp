@@ -46,29 +46,32 @@ Buffer::~Buffer() {
   if (busy) {
     cudaSetDevice(ctx->device);
     if (owned && ptr && cudaEventQuery(busy) != cudaSuccess) {
-      ctx->deferred.push_back({ptr, bytes, capacity, busy});     // a download is still reading the buffer
+      ctx->deferred.push_back({ptr, bytes, capacity, busy, reuse});     // a download is still reading the buffer
       return;
     }
     cudaEventDestroy(busy);
   }
   if (owned && ptr) {
     cudaSetDevice(ctx->device);
-    ctx->release(ptr, capacity);
+    ctx->release(ptr, capacity, reuse);
     ctx->allocated -= (long long)bytes;
+  } else if (reuse) {
+    cudaEventDestroy(reuse);
   }
 }
 
-void Ctx::release(void* ptr, size_t capacity) {
+void Ctx::release(void* ptr, size_t capacity, cudaEvent_t ev) {
   {
     std::lock_guard<std::mutex> g(nursery.mu);
     if (capacity && nursery.bytes + capacity <= nursery.limit) {
-      cudaEvent_t ev = nullptr;
-      if (cudaEventCreateWithFlags(&ev, cudaEventDisableTiming) == cudaSuccess) cudaEventRecord(ev, stream);
+      if (!ev && cudaEventCreateWithFlags(&ev, cudaEventDisableTiming) != cudaSuccess) ev = nullptr;
+      if (ev) cudaEventRecord(ev, stream);
       nursery.blocks.emplace(capacity, Nursery::Block{ptr, ev});
       nursery.bytes += capacity;
       return;
     }
   }
+  if (ev) cudaEventDestroy(ev);
   cudaFreeAsync(ptr, stream);
 }
 
@@ -103,7 +106,7 @@ void Ctx::reap(bool wait) {
     if (wait) cudaEventSynchronize(d.done);
     if (cudaEventQuery(d.done) == cudaSuccess) {
       cudaEventDestroy(d.done);
-      release(d.ptr, d.capacity);
+      release(d.ptr, d.capacity, d.reuse);
       allocated -= (long long)d.bytes;
     } else {
       deferred[kept++] = d;
@@ -127,7 +130,7 @@ std::shared_ptr<Buffer> Ctx::alloc(size_t bytes, bool for_caller) {
         b->ptr = it->second.ptr;
         if (it->second.released) {
           b->fresh = for_caller && cudaEventQuery(it->second.released) == cudaSuccess;
-          cudaEventDestroy(it->second.released);
+          b->reuse = it->second.released;          // travels with the block
         }
         nursery.blocks.erase(it);
         nursery.bytes -= cap;

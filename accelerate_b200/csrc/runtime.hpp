@@ -59,6 +59,7 @@ struct Buffer {
   // download or an exchange since.  An upload into such a buffer need not wait for the kernels in flight.
   bool fresh = false;
   cudaEvent_t busy = nullptr;   // last asynchronous download of this buffer (on the copy-out stream)
+  cudaEvent_t reuse = nullptr;  // the event that came with the block from the nursery: goes back there with it
   ~Buffer();
 };
 struct DevArray {
@@ -86,7 +87,7 @@ struct Ctx {
   cudaEvent_t aux_fork = nullptr, aux_join = nullptr;
   // buffers released while a download was still reading them: freed once that copy has completed,
   // without making the main stream wait for it
-  struct Deferred { void* ptr; size_t bytes, capacity; cudaEvent_t done; };
+  struct Deferred { void* ptr; size_t bytes, capacity; cudaEvent_t done, reuse; };
   std::vector<Deferred> deferred;
   void reap(bool wait);
   // Freed buffers wait here, by size, for the next allocation of the same size (the reference's
@@ -104,7 +105,9 @@ struct Ctx {
     long long hits = 0;
   } nursery;
   static constexpr size_t kChunk = 512;
-  void release(void* ptr, size_t capacity);   // into the nursery, or back to the driver when it is full
+  // into the nursery, or back to the driver when it is full; `ev` is an event to record the release with
+  // (one is created when none is given)
+  void release(void* ptr, size_t capacity, cudaEvent_t ev = nullptr);
   void purge();                               // everything in the nursery back to the driver
   Driver drv;
   std::mutex mu;
