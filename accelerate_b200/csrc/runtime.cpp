@@ -1002,10 +1002,11 @@ void Program::exec_kernel_node(const Node& n, Env& env_ref) {
           const int64_t ntiles = (m + 1023) / 1024;
           int64_t grid = std::max<int64_t>(1, std::min<int64_t>(ntiles, (int64_t)c.sm_count * k.max_blocks_per_sm));
           const size_t sb = struct_bytes(n.elt);
-          auto scratch = c.alloc((size_t)grid * sb + 16);
-          auto flags = c.alloc((size_t)grid * 4);
+          // per-CTA partial results, then the per-CTA flags, in one buffer
+          const size_t part_bytes = ((size_t)grid * sb + 16 + 255) / 256 * 256;
+          auto scratch = c.alloc(part_bytes + (size_t)grid * 4);
           L.named["scratch"] = (int64_t)(uintptr_t)scratch->ptr;
-          L.named["flags"] = (int64_t)(uintptr_t)flags->ptr;
+          L.named["flags"] = (int64_t)(uintptr_t)((char*)scratch->ptr + part_bytes);
           L.named["counter"] = (int64_t)(uintptr_t)(c.d_words + 1);
           for (int64_t r = 0; r < rows; ++r) {
             L.named["row"] = r;
