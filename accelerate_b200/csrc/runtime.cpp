@@ -253,9 +253,10 @@ bool scan_ring_aligned(int elt_bytes, int64_t m, int64_t rows, bool right) {
 // ---- source assembly -------------------------------------------------------------------------
 std::string assemble_source(const Glue& g, const std::string& skeleton, const std::map<std::string, std::string>& variant) {
   std::ostringstream o;
-  o << prelude_source() << "\n";
+  // (the defines come first: they are only text, and the prelude tests some of them)
   for (auto& d : g.defines) o << "#define " << d.first << " " << d.second << "\n";
   for (auto& d : variant) o << "#define " << d.first << " " << d.second << "\n";
+  o << prelude_source() << "\n";
   if (skeleton == "stencil") o << skeleton_source("stencil_pre") << "\n";
   if (skeleton == "stencil2d") o << skeleton_source("stencil2d_pre") << "\n";
   o << g.code << "\n" << skeleton_source(skeleton) << "\n";
@@ -355,10 +356,10 @@ std::vector<std::pair<std::string, std::map<std::string, std::string>>> default_
   switch (n.kind) {
     case N_GENERATE: v.push_back({"elementwise", {}}); break;
     case N_FOLD:
-      v.push_back({"fold", {{"FOLD_G", "32"}}});
-      v.push_back({"fold", {{"FOLD_G", "4"}}});
+      v.push_back({"fold", {{"FOLD_G", "32"}, {"ACC_STREAM_LOADS", "1"}}});
+      v.push_back({"fold", {{"FOLD_G", "4"}, {"ACC_STREAM_LOADS", "1"}}});
       break;
-    case N_FOLDSEG: v.push_back({"foldseg", {{"FOLDSEG_G", "32"}}}); break;
+    case N_FOLDSEG: v.push_back({"foldseg", {{"FOLDSEG_G", "32"}, {"ACC_STREAM_LOADS", "1"}}}); break;
     case N_SCAN: case N_SCAN2: {
       for (bool small : {false, true}) {
         auto sv = scan_variant(n.elt, small);
@@ -997,7 +998,7 @@ void Program::exec_kernel_node(const Node& n, Env& env_ref) {
         L.named["rows"] = rows;
         L.named["vec"] = (L.fast("D0") && (rows == 1 || m % 4 == 0)) ? 1 : 0;
         if (rows <= 8 && (rows == 1 || m >= (1 << 16))) {
-          std::map<std::string, std::string> var = {{"FOLD_G", "32"}};
+          std::map<std::string, std::string> var = {{"FOLD_G", "32"}, {"ACC_STREAM_LOADS", "1"}};
           CompiledKernel& k = node_kernel(c, st, "fold", var, "acc_fold_all", 256, 0);
           const int64_t ntiles = (m + 1023) / 1024;
           int64_t grid = std::max<int64_t>(1, std::min<int64_t>(ntiles, (int64_t)c.sm_count * k.max_blocks_per_sm));
@@ -1014,7 +1015,7 @@ void Program::exec_kernel_node(const Node& n, Env& env_ref) {
           }
         } else {
           const int g = pow2_at_least((m + 7) / 8);
-          std::map<std::string, std::string> var = {{"FOLD_G", std::to_string(g)}};
+          std::map<std::string, std::string> var = {{"FOLD_G", std::to_string(g)}, {"ACC_STREAM_LOADS", "1"}};
           CompiledKernel& k = node_kernel(c, st, "fold", var, "acc_fold_rows", 256, 0);
           const int64_t warps = (rows + (32 / g) - 1) / (32 / g);
           int64_t grid = std::min<int64_t>((warps + 7) / 8, (int64_t)c.sm_count * k.max_blocks_per_sm);
@@ -1041,7 +1042,7 @@ void Program::exec_kernel_node(const Node& n, Env& env_ref) {
         L.named["rows"] = rows;
         L.named["vec"] = (L.fast("D0") && (rows == 1 || m % 4 == 0)) ? 1 : 0;
         const int g = pow2_at_least((m / std::max<int64_t>(segs, 1) + 7) / 8);
-        std::map<std::string, std::string> var = {{"FOLDSEG_G", std::to_string(g)}};
+        std::map<std::string, std::string> var = {{"FOLDSEG_G", std::to_string(g)}, {"ACC_STREAM_LOADS", "1"}};
         CompiledKernel& k = node_kernel(c, st, "foldseg", var, "acc_foldseg", 256, 0);
         const int64_t warps = (rows * segs + (32 / g) - 1) / (32 / g);
         int64_t grid = std::min<int64_t>((warps + 7) / 8, (int64_t)c.sm_count * k.max_blocks_per_sm);

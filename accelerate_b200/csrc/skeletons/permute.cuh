@@ -222,7 +222,9 @@ extern "C" __global__ void __launch_bounds__(1024) acc_permute_sample(const Para
   const i64 k = (i64)blockIdx.x * 1024 + threadIdx.x;
   bool out = false;
   if (k < samples) {
-    const i64 i = k * step;
+    // one element from every stretch of `step`, at a position that depends on k: a regular stride can fall
+    // into step with a period of the data and then sees the same few elements over and over
+    const i64 i = k * step + (i64)((((u64)k * 0x9E3779B97F4A7C15ull) >> 33) % (u64)step);
     i64 row = 0, j = i;
     if (inner != n) { row = i / inner; j = i - row * inner; }
     const pelem_t e = P_get(p, row, j);
