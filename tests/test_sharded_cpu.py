@@ -1,4 +1,4 @@
-"""World-size-2 and -3 runs of the sharded skeletons on CPU (gloo), with the
+"""World-size-2, -3 and -8 runs of the sharded skeletons on CPU (gloo), with the
 oracle as each rank's local executor; results must equal the undivided run."""
 import os
 import socket
@@ -18,7 +18,7 @@ def _free_port():
     return p
 
 
-@pytest.mark.parametrize("world", [2, 3])
+@pytest.mark.parametrize("world", [2, 3, 8])
 def test_sharded_skeletons_match_the_undivided_run(world):
     port = _free_port()
     procs = [subprocess.Popen([sys.executable, os.path.join(HERE, "sharded_worker.py"), str(r), str(world), str(port)],
