@@ -31,6 +31,9 @@ std::string struct_name(const Type& t) {
   return s;
 }
 
+// (a Half travels through the kernels as its 16 bits; only the primitives look inside)
+std::string cty(Ty t) { return t == F16 ? "u16" : ty_name[t]; }
+
 struct ParamSet {
   std::vector<std::string> arrays;             // arrays referenced, first-use order
   std::vector<std::string> named;              // named fields, first-use order
@@ -53,7 +56,7 @@ struct ParamSet {
       std::vector<Ty> l = t.leaves();
       std::ostringstream o;
       o << "struct " << nm << " {";
-      for (size_t i = 0; i < l.size(); ++i) o << " " << ty_name[l[i]] << " l" << i << ";";
+      for (size_t i = 0; i < l.size(); ++i) o << " " << cty(l[i]) << " l" << i << ";";
       o << " };\n";
       const char* sh[3] = {"down", "up", "idx"};
       for (int k = 0; k < 3; ++k) {
@@ -67,7 +70,6 @@ struct ParamSet {
   }
 };
 
-std::string cty(Ty t) { return ty_name[t]; }
 std::string uty(Ty t) {
   switch (ty_bytes[t]) { case 1: return "u8"; case 2: return "u16"; case 4: return "u32"; default: return "u64"; }
 }
@@ -79,7 +81,9 @@ std::string float_literal(Ty t, const std::string& lit) {
   else if (lit == "nan") d = NAN;
   else d = strtod(lit.c_str(), nullptr);
   char buf[96];
-  if (t == F32) {
+  if (t == F16) {
+    snprintf(buf, sizeof buf, "((u16)0x%04xu)", (unsigned)half_from_float((float)d));
+  } else if (t == F32) {
     float f = (float)d;
     uint32_t b;
     memcpy(&b, &f, 4);
@@ -345,7 +349,11 @@ class Gen {
       CVal v = gen(*c);
       x.insert(x.end(), v.leaf.begin(), v.leaf.end());
     }
-    const Ty t = e.t1;
+    // Half: the Float primitive on the converted operands, rounded back (Numeric.Half's instances)
+    const bool half = e.t1 == F16;
+    const Ty t = half ? F32 : e.t1;
+    if (half)
+      for (auto& s : x) s = "acc_h2f(" + s + ")";
     const std::string T = cty(t), U = uty(t);
     const bool fl = ty_is_float(t), sg = ty_is_signed(t);
     const int bits = ty_bits(t);
@@ -353,7 +361,8 @@ class Gen {
     CVal r;
     r.ty = e.ty;
     auto one = [&](Ty rt, const std::string& s) {
-      r.leaf.push_back(def(rt, s));
+      if (half && rt == F32) r.leaf.push_back(def(F16, "acc_f2h(" + s + ")"));
+      else r.leaf.push_back(def(rt, s));
       return r;
     };
     auto wrap2 = [&](const char* op) {  // integer arithmetic in the unsigned type, then narrowed
@@ -421,7 +430,10 @@ class Gen {
       case P_ROUND: return one(e.t2, "(" + cty(e.t2) + ")acc_f2i<" + T + ">(rint" + sfx + "(" + x[0] + "))");
       case P_FLOOR: return one(e.t2, "(" + cty(e.t2) + ")acc_f2i<" + T + ">(floor" + sfx + "(" + x[0] + "))");
       case P_CEILING: return one(e.t2, "(" + cty(e.t2) + ")acc_f2i<" + T + ">(ceil" + sfx + "(" + x[0] + "))");
-      case P_FROMINTEGRAL: case P_TOFLOATING: return one(e.t2, "(" + cty(e.t2) + ")" + x[0]);
+      case P_FROMINTEGRAL: case P_TOFLOATING:
+        if (e.t2 == F16) { r.leaf.push_back(def(F16, "acc_f2h((f32)" + x[0] + ")")); return r; }
+        if (half) { r.leaf.push_back(def(e.t2, "(" + cty(e.t2) + ")" + x[0])); return r; }
+        return one(e.t2, "(" + cty(e.t2) + ")" + x[0]);
       case P_ISNAN: return one(U8, "(u8)(" + x[0] + " != " + x[0] + ")");
       case P_ISINF: return one(U8, "(u8)(isinf(" + x[0] + ") != 0)");
       case P_LT: return one(U8, "(u8)(" + x[0] + " < " + x[1] + ")");
@@ -657,6 +669,12 @@ struct GlueBuilder {
     pb << "};\n";
     // element structs do not depend on Params; functions do
     glue.code = ps.struct_code + pb.str() + fns.str();
+    // conversions of Half, only in programs that compute with it (cvt.rn: round to nearest even)
+    if (glue.code.find("acc_h2f(") != std::string::npos || glue.code.find("acc_f2h(") != std::string::npos)
+      glue.code =
+          "__device__ __forceinline__ f32 acc_h2f(u16 h) { f32 f; asm(\"{ .reg .b16 t; mov.b16 t, %1; cvt.f32.f16 %0, t; }\" : \"=f\"(f) : \"h\"(h)); return f; }\n"
+          "__device__ __forceinline__ u16 acc_f2h(f32 f) { u16 h; asm(\"{ .reg .b16 t; cvt.rn.f16.f32 t, %1; mov.b16 %0, t; }\" : \"=h\"(h) : \"f\"(f)); return h; }\n" +
+          glue.code;
     return glue;
   }
 };

@@ -6,8 +6,8 @@
 
 namespace accb200 {
 
-const char* const ty_name[NTY] = {"i8", "i16", "i32", "i64", "u8", "u16", "u32", "u64", "f32", "f64"};
-const int ty_bytes[NTY] = {1, 2, 4, 8, 1, 2, 4, 8, 4, 8};
+const char* const ty_name[NTY] = {"i8", "i16", "i32", "i64", "u8", "u16", "u32", "u64", "f32", "f64", "f16"};
+const int ty_bytes[NTY] = {1, 2, 4, 8, 1, 2, 4, 8, 4, 8, 2};
 const char* const prim_name[P_NPRIMS] = {
     "add", "sub", "mul", "neg", "abs", "sig", "quot", "rem", "quotrem", "idiv", "mod", "divmod",
     "band", "bor", "bxor", "bnot", "shl", "shr", "rotl", "rotr", "popcount", "clz", "ctz",
@@ -184,7 +184,7 @@ std::unique_ptr<Expr> parse_expr(const Sx& x, TEnv& env) {
     e->ty = Type::scalar(t);
     if (h == "pi") {
       if (!ty_is_float(t)) throw Error(B200_ERR_TYPE, "pi needs a floating type");
-      e->lit = t == F32 ? "0x1.921fb6p+1" : "0x1.921fb54442d18p+1";
+      e->lit = t == F16 ? "0x1.92p+1" : (t == F32 ? "0x1.921fb6p+1" : "0x1.921fb54442d18p+1");
     } else {
       if (!ty_is_int(t)) throw Error(B200_ERR_TYPE, h + " needs an integral type");
       int b = ty_bits(t);

@@ -7,6 +7,7 @@
 #pragma once
 
 #include <cstdint>
+#include <cstring>
 #include <map>
 #include <memory>
 #include <stdexcept>
@@ -37,14 +38,51 @@ struct Sx {
 Sx parse_sexp(const char* text, size_t len);
 
 // ---- scalar and element types (Type.hs:112-152; Int = 64 bit, Bool = Word8) --
-enum Ty : uint8_t { I8, I16, I32, I64, U8, U16, U32, U64, F32, F64, NTY };
+enum Ty : uint8_t { I8, I16, I32, I64, U8, U16, U32, U64, F32, F64, F16, NTY };
 extern const char* const ty_name[NTY];
 extern const int ty_bytes[NTY];
 inline bool ty_is_int(Ty t) { return t <= U64; }
 inline bool ty_is_signed(Ty t) { return t <= I64; }
-inline bool ty_is_float(Ty t) { return t == F32 || t == F64; }
+inline bool ty_is_float(Ty t) { return t == F32 || t == F64 || t == F16; }
 inline int ty_bits(Ty t) { return ty_bytes[t] * 8; }
 Ty parse_ty(const std::string& s);
+
+// Half (Type.hs:127, Numeric.Half): IEEE-754 binary16 kept as its 16 bits.  Every operation on it is the
+// Float operation on the converted operands, rounded back to nearest-even, as the Num/Fractional/Floating
+// instances of Numeric.Half define it (toHalf (fromHalf a + fromHalf b), ...).
+inline uint16_t half_from_float(float f) {
+  uint32_t x;
+  memcpy(&x, &f, 4);
+  const uint32_t sign = (x >> 16) & 0x8000u, ax = x & 0x7fffffffu;
+  if (ax > 0x7f800000u) return (uint16_t)(sign | 0x7e00u);  // NaN
+  if (ax >= 0x38800000u) {                                   // at least 2^-14: a normal half, or infinity
+    uint32_t h = (((ax >> 23) - 112) << 10) | ((ax & 0x7fffffu) >> 13);
+    const uint32_t rem = ax & 0x1fffu;
+    if (ax >= 0x47800000u) h = 0x7c00u;
+    else if (rem > 0x1000u || (rem == 0x1000u && (h & 1))) ++h;  // a carry runs into the exponent, up to infinity
+    return (uint16_t)(sign | h);
+  }
+  if (ax <= 0x33000000u) return (uint16_t)sign;              // at most 2^-25: rounds to zero
+  const int shift = 126 - (int)(ax >> 23);                    // 14..24: units of 2^-24
+  const uint32_t m = (ax & 0x7fffffu) | 0x800000u, rem = m & ((1u << shift) - 1), mid = 1u << (shift - 1);
+  uint32_t h = m >> shift;
+  if (rem > mid || (rem == mid && (h & 1))) ++h;
+  return (uint16_t)(sign | h);
+}
+inline float half_to_float(uint16_t h) {
+  const uint32_t sign = (uint32_t)(h & 0x8000u) << 16, e = (h >> 10) & 31u, m = h & 0x3ffu;
+  uint32_t x;
+  if (e == 31) x = sign | 0x7f800000u | (m << 13);
+  else if (e != 0) x = sign | ((e + 112) << 23) | (m << 13);
+  else {
+    float v = (float)m * 5.9604644775390625e-08f;  // m * 2^-24, exact
+    memcpy(&x, &v, 4);
+    x |= sign;
+  }
+  float f;
+  memcpy(&f, &x, 4);
+  return f;
+}
 
 struct Type {
   bool tuple = false;

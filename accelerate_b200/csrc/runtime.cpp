@@ -432,7 +432,11 @@ struct HostEval {
     }
   }
   HVal scalar_i(Ty t, int64_t v) { HVal r; r.ty = Type::scalar(t); r.i = {v}; r.f = {0}; return r; }
-  HVal scalar_f(Ty t, double v) { HVal r; r.ty = Type::scalar(t); r.i = {0}; r.f = {v}; return r; }
+  HVal scalar_f(Ty t, double v) {
+    if (t == F32) v = (double)(float)v;
+    if (t == F16) v = (double)half_to_float(half_from_float((float)v));  // through Float, as Numeric.Half does
+    HVal r; r.ty = Type::scalar(t); r.i = {0}; r.f = {v}; return r;
+  }
   HVal read(const DevArray& a, int64_t lin) {
     if (lin < 0 || lin >= a.size()) throw Error(B200_ERR_BOUNDS, "index out of bounds");
     HVal r;
@@ -445,6 +449,7 @@ struct HostEval {
       ctx->d2h += ty_bytes[t];
       if (t == F32) { float v; memcpy(&v, buf, 4); r.i.push_back(0); r.f.push_back(v); }
       else if (t == F64) { double v; memcpy(&v, buf, 8); r.i.push_back(0); r.f.push_back(v); }
+      else if (t == F16) { uint16_t v; memcpy(&v, buf, 2); r.i.push_back(0); r.f.push_back((double)half_to_float(v)); }
       else { uint64_t v = 0; memcpy(&v, buf, ty_bytes[t]); r.i.push_back(wrap(t, v)); r.f.push_back(0); }
     }
     return r;
@@ -854,6 +859,7 @@ static std::string trace_render(Ctx& c, const DevArray& a) {
         case U32: { uint32_t v; memcpy(&v, q, 4); snprintf(buf, sizeof buf, "%u", v); break; }
         case U64: { uint64_t v; memcpy(&v, q, 8); snprintf(buf, sizeof buf, "%llu", (unsigned long long)v); break; }
         case F32: { float v; memcpy(&v, q, 4); snprintf(buf, sizeof buf, "%.9g", (double)v); break; }
+        case F16: { uint16_t v; memcpy(&v, q, 2); snprintf(buf, sizeof buf, "%.5g", (double)half_to_float(v)); break; }
         default: { double v; memcpy(&v, q, 8); snprintf(buf, sizeof buf, "%.17g", v); break; }
       }
       out += buf;

@@ -26,11 +26,11 @@ import numpy as np
 # Types.  Scalars are strings; tuples are Python tuples of types.
 # ``Int`` is 64-bit (Array/Data.hs:380-384); ``Bool`` is a Word8 tag.
 # ----------------------------------------------------------------------------
-SCALARS = ("i8", "i16", "i32", "i64", "u8", "u16", "u32", "u64", "f32", "f64")
+SCALARS = ("i8", "i16", "i32", "i64", "u8", "u16", "u32", "u64", "f32", "f64", "f16")
 NP_OF = {
     "i8": np.int8, "i16": np.int16, "i32": np.int32, "i64": np.int64,
     "u8": np.uint8, "u16": np.uint16, "u32": np.uint32, "u64": np.uint64,
-    "f32": np.float32, "f64": np.float64,
+    "f32": np.float32, "f64": np.float64, "f16": np.float16,   # Half (Type.hs:127)
 }
 TY_OF_NP = {np.dtype(v): k for k, v in NP_OF.items()}
 TY_OF_NP[np.dtype(np.bool_)] = "u8"
@@ -38,7 +38,7 @@ INT, BOOL = "i64", "u8"
 
 
 def is_float(t):
-    return t in ("f32", "f64")
+    return t in ("f32", "f64", "f16")
 
 
 def is_scalar(t):
@@ -82,7 +82,7 @@ def reset_names():
 # ----------------------------------------------------------------------------
 def _lit(t, v):
     if is_float(t):
-        f = float(np.float32(v)) if t == "f32" else float(v)
+        f = float(np.float32(v)) if t == "f32" else (float(np.float16(v)) if t == "f16" else float(v))
         if f != f:
             s = "nan"
         elif f in (float("inf"), float("-inf")):

@@ -246,7 +246,7 @@ scalarPayload (SingleScalarType (NumSingleType nt)) ad = case nt of
     TypeWord32 -> (4, castPtr (unsafeUniqueArrayPtr ad)); TypeWord64 -> (8, castPtr (unsafeUniqueArrayPtr ad))
   FloatingNumType ft -> case ft of
     TypeFloat  -> (4, castPtr (unsafeUniqueArrayPtr ad)); TypeDouble -> (8, castPtr (unsafeUniqueArrayPtr ad))
-    TypeHalf   -> unsupported "Half arrays"
+    TypeHalf   -> (2, castPtr (unsafeUniqueArrayPtr ad))   -- the 16 bits of Numeric.Half, as the library keeps them
 scalarPayload VectorScalarType{} _ = unsupported "SIMD vector element types"
 
 -- 'getUniqueId' of the leaf's 'UniqueArray' (Array/Unique.hs:48-51, 66-69).
@@ -258,7 +258,7 @@ scalarUniqueId (SingleScalarType (NumSingleType nt)) ad = case nt of
     TypeWord32 -> getUniqueId ad; TypeWord64 -> getUniqueId ad
   FloatingNumType ft -> case ft of
     TypeFloat  -> getUniqueId ad; TypeDouble -> getUniqueId ad
-    TypeHalf   -> unsupported "Half arrays"
+    TypeHalf   -> getUniqueId ad
 scalarUniqueId VectorScalarType{} _ = unsupported "SIMD vector element types"
 
 unsupported :: String -> a
@@ -599,7 +599,7 @@ scalarText (SingleScalarType (NumSingleType nt)) = case nt of
     TypeInt -> "i64"; TypeInt8 -> "i8"; TypeInt16 -> "i16"; TypeInt32 -> "i32"; TypeInt64 -> "i64"
     TypeWord -> "u64"; TypeWord8 -> "u8"; TypeWord16 -> "u16"; TypeWord32 -> "u32"; TypeWord64 -> "u64"
   FloatingNumType ft -> case ft of
-    TypeFloat -> "f32"; TypeDouble -> "f64"; TypeHalf -> unsupported "Half values"
+    TypeFloat -> "f32"; TypeDouble -> "f64"; TypeHalf -> "f16"
 scalarText VectorScalarType{} = unsupported "SIMD vector types"
 
 constText :: TypeR t -> t -> String
@@ -614,7 +614,7 @@ literal (SingleScalarType (NumSingleType nt)) v = case nt of
   FloatingNumType ft -> case ft of
     TypeFloat  -> hex (realToFrac v :: Double)
     TypeDouble -> hex v
-    TypeHalf   -> unsupported "Half values"
+    TypeHalf   -> hex (realToFrac v :: Double)   -- exact: every Half is a Double
   where hex d | isNaN d = "nan" | isInfinite d = if d > 0 then "inf" else "-inf" | otherwise = showHFloat d ""
 literal VectorScalarType{} _ = unsupported "SIMD vector constants"
 

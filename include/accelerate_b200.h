@@ -55,8 +55,8 @@ void b200_ctx_destroy(b200_ctx* ctx);
 /* Device arrays in struct-of-arrays layout, one buffer per scalar leaf of the
  * element type, row-major, innermost dimension last (Representation/Array.hs:43-46,
  * Array/Data.hs:95-98; device side of Array/Remote/Class.hs:47-73 mallocRemote).
- * `elt_type` is the element type as text: i8..i64, u8..u64, f32, f64 or
- * "(tup t1 t2 ...)". */
+ * `elt_type` is the element type as text: i8..i64, u8..u64, f32, f64, f16 (Half, Type.hs:127: two bytes
+ * per element) or "(tup t1 t2 ...)". */
 int b200_array_new(b200_ctx* ctx, const char* elt_type, int rank, const int64_t* shape, uint64_t* id);
 /* Adopt device memory owned by the caller (one pointer per leaf); never freed. */
 int b200_array_wrap(b200_ctx* ctx, const char* elt_type, int rank, const int64_t* shape, void* const* leaf_ptrs,

@@ -84,9 +84,9 @@ struct SxParser {
 // ----------------------------------------------------------------------------
 // Scalar types and values
 // ----------------------------------------------------------------------------
-enum Ty : uint8_t { I8, I16, I32, I64, U8, U16, U32, U64, F32, F64, NTY };
-const char* ty_name[] = {"i8", "i16", "i32", "i64", "u8", "u16", "u32", "u64", "f32", "f64"};
-const int ty_bytes[] = {1, 2, 4, 8, 1, 2, 4, 8, 4, 8};
+enum Ty : uint8_t { I8, I16, I32, I64, U8, U16, U32, U64, F32, F64, F16, NTY };
+const char* ty_name[] = {"i8", "i16", "i32", "i64", "u8", "u16", "u32", "u64", "f32", "f64", "f16"};
+const int ty_bytes[] = {1, 2, 4, 8, 1, 2, 4, 8, 4, 8, 2};
 inline bool ty_signed(Ty t) { return t <= I64; }
 inline bool ty_int(Ty t) { return t <= U64; }
 inline int ty_bits(Ty t) { return ty_bytes[t] * 8; }
@@ -126,6 +126,27 @@ inline int64_t wrap_int(Ty t, uint64_t v) {
 inline Scalar mk_int(Ty t, uint64_t v) { Scalar s; s.ty = t; s.i = wrap_int(t, v); return s; }
 inline Scalar mk_f32(float v) { Scalar s; s.ty = F32; s.i = 0; s.f = v; return s; }
 inline Scalar mk_f64(double v) { Scalar s; s.ty = F64; s.d = v; return s; }
+// Half (Type.hs:127): the value is kept in .f, always one a binary16 can hold.  The package behind it
+// (half >= 0.3, accelerate.cabal:335; not in the tree) computes every operation in Float and converts
+// back, rounding to nearest even; the compiler's _Float16 conversion does that rounding here.
+inline Scalar mk_f16(float v) { Scalar s; s.ty = F16; s.i = 0; s.f = (float)(_Float16)v; return s; }
+// (NaNs keep their payload and their signalling bit on the way in and out, as a bit pattern stored in an
+// array does in the reference: a conversion instruction would quieten them)
+inline uint16_t f16_bits(float v) {
+  if (v != v) {
+    uint32_t x; memcpy(&x, &v, 4);
+    uint16_t m = (uint16_t)((x >> 13) & 0x3ffu);
+    return (uint16_t)(((x >> 16) & 0x8000u) | 0x7c00u | (m ? m : 0x200u));
+  }
+  _Float16 h = (_Float16)v; uint16_t b; memcpy(&b, &h, 2); return b;
+}
+inline float f16_value(uint16_t b) {
+  if ((b & 0x7c00u) == 0x7c00u && (b & 0x3ffu)) {
+    uint32_t x = ((uint32_t)(b & 0x8000u) << 16) | 0x7f800000u | ((uint32_t)(b & 0x3ffu) << 13);
+    float f; memcpy(&f, &x, 4); return f;
+  }
+  _Float16 h; memcpy(&h, &b, 2); return (float)h;
+}
 inline Scalar mk_bool(bool b) { return mk_int(U8, b ? 1 : 0); }
 
 // Values are tuple trees of scalars (the reference's nested-pair EltR, flattened
@@ -201,6 +222,7 @@ std::string trace_render(const Array& a) {
         case U32: { uint32_t v; memcpy(&v, q, 4); snprintf(buf, sizeof buf, "%u", v); break; }
         case U64: { uint64_t v; memcpy(&v, q, 8); snprintf(buf, sizeof buf, "%llu", (unsigned long long)v); break; }
         case F32: { float v; memcpy(&v, q, 4); snprintf(buf, sizeof buf, "%.9g", (double)v); break; }
+        case F16: { uint16_t v; memcpy(&v, q, 2); snprintf(buf, sizeof buf, "%.5g", (double)f16_value(v)); break; }
         default: { double v; memcpy(&v, q, 8); snprintf(buf, sizeof buf, "%.17g", v); break; }
       }
       out += buf;
@@ -237,6 +259,7 @@ inline Scalar read_leaf(const Array& a, size_t l, int64_t i) {
     case U64: { uint64_t v; memcpy(&v, p, 8); s.i = (int64_t)v; break; }
     case F32: memcpy(&s.f, p, 4); break;
     case F64: memcpy(&s.d, p, 8); break;
+    case F16: { uint16_t v; memcpy(&v, p, 2); s.f = f16_value(v); break; }
     default: break;
   }
   return s;
@@ -247,6 +270,7 @@ inline void write_leaf(Array& a, size_t l, int64_t i, const Scalar& s) {
   switch (t) {
     case F32: memcpy(p, &s.f, 4); break;
     case F64: memcpy(p, &s.d, 8); break;
+    case F16: { uint16_t v = f16_bits(s.f); memcpy(p, &v, 2); break; }
     default: memcpy(p, &s.i, ty_bytes[t]); break;  // little endian: low bytes
   }
 }
@@ -385,12 +409,13 @@ struct Scope {
 };
 
 Scalar parse_const(Ty t, const std::string& lit) {
-  if (t == F32 || t == F64) {
+  if (t == F32 || t == F64 || t == F16) {
     double d;
     if (lit == "inf") d = INFINITY;
     else if (lit == "-inf") d = -INFINITY;
     else if (lit == "nan") d = NAN;
     else d = strtod(lit.c_str(), nullptr);  // accepts C99 hex floats
+    if (t == F16) return mk_f16((float)d);
     return t == F32 ? mk_f32((float)d) : mk_f64(d);
   }
   if (ty_signed(t)) return mk_int(t, (uint64_t)strtoll(lit.c_str(), nullptr, 10));
@@ -432,7 +457,7 @@ std::unique_ptr<Exp> parse_exp(const Sx& x, Scope& sc) {
   } else if (h == "pi") {
     e->kind = E_CONST;
     Ty t = parse_ty(x[1].s);
-    e->c = (t == F32) ? mk_f32((float)M_PI) : mk_f64(M_PI);
+    e->c = t == F16 ? mk_f16((float)M_PI) : ((t == F32) ? mk_f32((float)M_PI) : mk_f64(M_PI));
   } else if (h == "var") {
     e->kind = E_VAR;
     e->slot = sc.lookup(x[1].s);
@@ -535,7 +560,7 @@ std::unique_ptr<Exp> parse_exp(const Sx& x, Scope& sc) {
 // Primitive functions (Interp:1086-1416; arithmetic itself is GHC base:
 // two's-complement wrap, IEEE-754 round-to-nearest-even, floor div/mod)
 // ----------------------------------------------------------------------------
-inline double as_double(const Scalar& s) { return s.ty == F32 ? (double)s.f : s.d; }
+inline double as_double(const Scalar& s) { return s.ty == F32 || s.ty == F16 ? (double)s.f : s.d; }
 
 #define FUN1(NAME)                                                        \
   do {                                                                    \
@@ -556,7 +581,7 @@ int64_t floor_mod(int64_t a, int64_t b) {
 
 template <class F>
 bool cmp_scalar(Ty t, const Scalar& a, const Scalar& b, F f) {
-  if (t == F32) return f(a.f, b.f);
+  if (t == F32 || t == F16) return f(a.f, b.f);
   if (t == F64) return f(a.d, b.d);
   if (ty_signed(t)) return f(a.i, b.i);
   return f((uint64_t)a.i, (uint64_t)b.i);
@@ -586,12 +611,12 @@ Scalar convert_to(Ty from, Ty to, const Scalar& x, Op how) {
   return mk_int(to, (uint64_t)(int64_t)r);
 }
 
-Value eval_prim(const Exp& e, const std::vector<Value>& arg) {
-  Ty t = e.t1;
+Value eval_prim_at(Op op, Ty t1, Ty t2, const std::vector<Value>& arg) {
+  Ty t = t1;
   const Scalar& x = arg[0].s;
   const Scalar* yp = arg.size() > 1 ? &arg[1].s : nullptr;
   auto ibin = [&](uint64_t v) { return Value::scalar(mk_int(t, v)); };
-  switch (e.op) {
+  switch (op) {
     case O_ADD:
       if (t == F32) return Value::scalar(mk_f32(x.f + yp->f));
       if (t == F64) return Value::scalar(mk_f64(x.d + yp->d));
@@ -625,14 +650,14 @@ Value eval_prim(const Exp& e, const std::vector<Value>& arg) {
       if (ty_signed(t)) {
         int64_t a = x.i, b = yp->i;
         if (b == -1) { q = (uint64_t)0 - (uint64_t)a; r = 0; }  // avoids the INT64_MIN trap; wraps
-        else if (e.op == O_QUOT || e.op == O_REM || e.op == O_QUOTREM) { q = (uint64_t)(a / b); r = (uint64_t)(a % b); }
+        else if (op == O_QUOT || op == O_REM || op == O_QUOTREM) { q = (uint64_t)(a / b); r = (uint64_t)(a % b); }
         else { q = (uint64_t)floor_div(a, b); r = (uint64_t)floor_mod(a, b); }
       } else {
         uint64_t a = (uint64_t)x.i, b = (uint64_t)yp->i;
         q = a / b; r = a % b;
       }
-      if (e.op == O_QUOT || e.op == O_IDIV) return ibin(q);
-      if (e.op == O_REM || e.op == O_MOD) return ibin(r);
+      if (op == O_QUOT || op == O_IDIV) return ibin(q);
+      if (op == O_REM || op == O_MOD) return ibin(r);
       return Value::tup({Value::scalar(mk_int(t, q)), Value::scalar(mk_int(t, r))});
     }
     case O_BAND: return ibin((uint64_t)x.i & (uint64_t)yp->i);
@@ -653,7 +678,7 @@ Value eval_prim(const Exp& e, const std::vector<Value>& arg) {
     case O_ROTL: case O_ROTR: {
       int b = ty_bits(t);
       int64_t n = yp->i;
-      if (e.op == O_ROTR) n = -n;
+      if (op == O_ROTR) n = -n;
       int r = (int)(((n % b) + b) % b);
       uint64_t mask = b == 64 ? ~(uint64_t)0 : (((uint64_t)1 << b) - 1);
       uint64_t v = (uint64_t)x.i & mask;
@@ -665,8 +690,8 @@ Value eval_prim(const Exp& e, const std::vector<Value>& arg) {
       uint64_t mask = b == 64 ? ~(uint64_t)0 : (((uint64_t)1 << b) - 1);
       uint64_t v = (uint64_t)x.i & mask;
       int64_t r;
-      if (e.op == O_POPCNT) r = __builtin_popcountll(v);
-      else if (e.op == O_CLZ) r = v == 0 ? b : (__builtin_clzll(v) - (64 - b));
+      if (op == O_POPCNT) r = __builtin_popcountll(v);
+      else if (op == O_CLZ) r = v == 0 ? b : (__builtin_clzll(v) - (64 - b));
       else r = v == 0 ? b : __builtin_ctzll(v);
       return Value::scalar(mk_int(I64, (uint64_t)r));
     }
@@ -702,7 +727,7 @@ Value eval_prim(const Exp& e, const std::vector<Value>& arg) {
       return Value::scalar(mk_f64(atan2(x.d, yp->d)));
     case O_TRUNCATE: case O_ROUND: case O_FLOOR: case O_CEILING:
     case O_FROMINTEGRAL: case O_TOFLOATING:
-      return Value::scalar(convert_to(e.t1, e.t2, x, e.op));
+      return Value::scalar(convert_to(t1, t2, x, op));
     case O_ISNAN: return Value::scalar(mk_bool(t == F32 ? std::isnan(x.f) : std::isnan(x.d)));
     case O_ISINF: return Value::scalar(mk_bool(t == F32 ? std::isinf(x.f) : std::isinf(x.d)));
     case O_LT: return Value::scalar(mk_bool(cmp_scalar(t, x, *yp, [](auto a, auto b) { return a < b; })));
@@ -720,6 +745,20 @@ Value eval_prim(const Exp& e, const std::vector<Value>& arg) {
     default: break;
   }
   throw std::runtime_error("unhandled primitive");
+}
+
+Value eval_prim(const Exp& e, const std::vector<Value>& arg) {
+  if (e.t1 != F16 && e.t2 != F16) return eval_prim_at(e.op, e.t1, e.t2, arg);
+  // Numeric.Half: a + b = toHalf (fromHalf a + fromHalf b), and so on for every class method; the
+  // comparisons compare the converted values.  (.f of a Half scalar already is that Float.)
+  std::vector<Value> a = arg;
+  if (e.t1 == F16)
+    for (auto& v : a)
+      if (!v.tuple && v.s.ty == F16) v.s.ty = F32;
+  Value r = eval_prim_at(e.op, e.t1 == F16 ? F32 : e.t1, e.t2 == F16 ? F32 : e.t2, a);
+  const bool to_float = (e.op == O_TOFLOATING || e.op == O_FROMINTEGRAL) && e.t2 == F32;
+  if (!r.tuple && r.s.ty == F32 && !to_float) r.s = mk_f16(r.s.f);
+  return r;
 }
 
 Value undef_value(const EltTy& t) {
@@ -832,9 +871,11 @@ Value eval(const Exp& e, Env& env) {
       // bit reinterpretation between equal-sized scalar types (Interp:1010-1012)
       Value v = eval(*e.a[0], env);
       uint64_t bits = 0;
-      if (e.t1 == F32) memcpy(&bits, &v.s.f, 4);
+      if (e.t1 == F16) bits = f16_bits(v.s.f);
+      else if (e.t1 == F32) memcpy(&bits, &v.s.f, 4);
       else if (e.t1 == F64) memcpy(&bits, &v.s.d, 8);
       else bits = (uint64_t)v.s.i;
+      if (e.t2 == F16) { Scalar h; h.ty = F16; h.i = 0; h.f = f16_value((uint16_t)bits); return Value::scalar(h); }
       if (e.t2 == F32) { float f; uint32_t b = (uint32_t)bits; memcpy(&f, &b, 4); return Value::scalar(mk_f32(f)); }
       if (e.t2 == F64) { double d; memcpy(&d, &bits, 8); return Value::scalar(mk_f64(d)); }
       return Value::scalar(mk_int(e.t2, bits));

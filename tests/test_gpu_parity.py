@@ -615,3 +615,75 @@ def test_sixteen_component_tuples():
     check(A.scanl1(plus, wide))
     au = A.use(a)
     check(A.permute(plus, A.fill(7, zero), lambda ix: A.Just_(A.index(A.from_integral(au[ix] % 7, "i64"))), wide))
+
+
+# ---- Half (Type.hs:127): binary16 whose every operation is the Float operation rounded back ---------------
+def halves(n):
+    x = rng.integers(0, 65536, size=n).astype(np.uint16).view(np.float16)
+    x[:8] = np.array([0.0, -0.0, np.inf, -np.inf, 65504, 6e-8, 1.0, 2049], np.float16)
+    return x
+
+
+def test_half_primitives_exact():
+    x, y = halves(4096), halves(4096)[::-1].copy()
+    xs, ys = A.use(x), A.use(y)
+    got = check(A.generate(A.index(4096), lambda ix: A.tup(
+        xs[ix] + ys[ix], xs[ix] - ys[ix], xs[ix] * ys[ix], xs[ix] / ys[ix], -xs[ix], abs(xs[ix]), A.signum(xs[ix]),
+        A.sqrt(abs(xs[ix])), A.recip(ys[ix]), A.max_(xs[ix], ys[ix]), A.min_(xs[ix], ys[ix]),
+        xs[ix] < ys[ix], xs[ix].eq(ys[ix]), A.is_nan(xs[ix]), A.is_infinite(xs[ix]),
+        A.bitcast(xs[ix], "u16"), A.pi("f16") * xs[ix], xs[ix] + 0.1)))
+    with np.errstate(all="ignore"):
+        want = x * y                                   # NumPy's float16 is the same definition: a third opinion
+    ok = ~np.isnan(want)
+    assert np.array_equal(got[2].view(np.uint16)[ok], want.view(np.uint16)[ok])
+
+
+def test_half_conversions_exact():
+    i = ints(2000, np.int32, -70000, 70000)
+    f = (rng.normal(size=2000) * rng.choice([1e-6, 1.0, 300.0, 1e5], size=2000)).astype(np.float32)
+    d = f.astype(np.float64) * 1.0000001
+    h = rng.uniform(-3000, 3000, size=2000).astype(np.float16)
+    h[:6] = np.array([0.5, 1.5, 2.5, -0.5, -1.5, -2.5], np.float16)
+    is_, fs, ds, hs = A.use(i), A.use(f), A.use(d), A.use(h)
+    check(A.generate(A.index(2000), lambda ix: A.tup(
+        A.from_integral(is_[ix], "f16"), A.to_floating(fs[ix], "f16"), A.to_floating(ds[ix], "f16"),
+        A.to_floating(hs[ix], "f32"), A.to_floating(hs[ix], "f64"), A.truncate(hs[ix]), A.round_(hs[ix], "i32"),
+        A.floor(hs[ix]), A.ceiling(hs[ix]), A.bitcast(A.bitcast(hs[ix], "i16"), "f16"))))
+
+
+def test_half_transcendentals():
+    x = rng.uniform(0.1, 3.0, size=500).astype(np.float16)
+    xs = A.use(x)
+    # one unit in the last place of a Half at most (the Float results differ in their last place): far
+    # inside the reference suite's tolerance for Half, absolute 0.05 / relative 0.5 (Test/Similar.hs:89)
+    check(A.generate(A.index(500), lambda ix: A.tup(A.sin(xs[ix]), A.cos(xs[ix]), A.exp(xs[ix]), A.log(xs[ix]),
+                                                     A.tanh(xs[ix]), xs[ix] ** 1.5, A.atan2(xs[ix], 2.0))), rtol=2e-3, atol=1e-3)
+
+
+@pytest.mark.parametrize("n", [0, 1, 300, 5000, 100004])
+def test_half_collectives_order_independent(n, monkeypatch):
+    # zeros and ones whose sums stay below 2048: every partial sum is a Half whatever the association, so the
+    # kernels' tree order must give the sequential result exactly (4096-element rows keep to that too)
+    x = (rng.random(n) < 1500.0 / max(n, 1500)).astype(np.float16)
+    check(A.fold(add, np.float16(0), x))
+    check(A.scanl1(add, x))
+    check(list(A.scanr_prime(add, np.float16(0), x)))
+    if n:
+        check(A.fold1(A.max_, rng.normal(size=n).astype(np.float16)))     # (no NaN: max is a monoid without it)
+        k = A.use(ints(n, np.int32, 0, 37))
+        check(A.permute(add, A.fill(37, A.constant(np.float16(0))), lambda ix: A.Just_(A.index(A.from_integral(k[ix], "i64"))), x))
+        lens = np.full(n // 50, 50, np.int32)
+        check(A.foldSeg(add, np.float16(0), x[:lens.sum()], lens))
+    monkeypatch.setenv("ACCELERATE_B200_SCAN_NO_SMALL", "1")
+    check(A.scanl(add, np.float16(1), x))
+
+
+def test_half_stencil_and_tuples():
+    m = rng.uniform(0, 1, size=(70, 132)).astype(np.float16)
+    check(A.stencil(lambda s: (s[0][1] + s[2][1] + s[1][0] + s[1][2]) * 0.25, A.mirror, m))
+    v = rng.uniform(-4, 4, size=3001).astype(np.float16)
+    check(A.stencil(lambda s: s[0] * 0.25 + s[1] * 0.5 + s[2] * 0.25, A.function(lambda ix: A.constant(np.float16(7))), v, extent=(3,)))
+    w = ints(3001, np.int32, -9, 9)
+    pairs = A.zip(v, w)
+    check(A.map(lambda p: A.tup(p[0] * A.from_integral(p[1], "f16"), p[1]), pairs), embed=True)
+    check(A.scanl1(lambda a, b: A.tup(A.max_(a[0], b[0]), a[1] + b[1]), pairs))
