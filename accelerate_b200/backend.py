@@ -80,6 +80,7 @@ def lib():
         l.b200_ctx_stream.argtypes = [vp, ctypes.POINTER(vp)]
         l.b200_compile_check.argtypes = [cp, ctypes.c_size_t, ctypes.c_char_p, ctypes.c_size_t]
         l.b200_kernel_source.argtypes = [cp, ctypes.c_size_t, ctypes.c_int, ctypes.c_char_p, ctypes.c_size_t]
+        l.b200_program_lowered.argtypes = [cp, ctypes.c_size_t, ctypes.c_char_p, ctypes.c_size_t]
         _lib = l
     return _lib
 
@@ -97,6 +98,14 @@ def compile_check(text):
     if rc != 0:
         raise B200Error(rc, log.value.decode(errors="replace"))
     return log.value.decode()
+
+
+def program_lowered(text):
+    """The program text after the library's own rewriting (arrays of SIMD vectors regrouped at the boundary)."""
+    buf = ctypes.create_string_buffer(len(text) * 4 + (1 << 16))
+    b = text.encode()
+    _check(lib().b200_program_lowered(b, len(b), buf, len(buf)))
+    return buf.value.decode()
 
 
 def kernel_source(text, node=0):

@@ -557,4 +557,13 @@ int b200_kernel_source(const char* text, size_t len, int node, char* out, size_t
   B200_END
 }
 
+int b200_program_lowered(const char* text, size_t len, char* out, size_t out_len) {
+  B200_TRY
+  if (!text || !out || !out_len) throw Error(B200_ERR_ARG, "bad argument");
+  const std::string src = program_text_lowered(text, len);
+  if (src.size() + 1 > out_len) throw Error(B200_ERR_ARG, "buffer too small for the program text");
+  memcpy(out, src.data(), src.size() + 1);
+  B200_END
+}
+
 }  // extern "C"

@@ -2,6 +2,7 @@
 #include "ir.hpp"
 
 #include <cstdlib>
+#include <functional>
 #include <cstring>
 
 namespace accb200 {
@@ -83,6 +84,7 @@ void Type::flatten(std::vector<Ty>& out) const {
 }
 std::string Type::str() const {
   if (!tuple) return ty_name[s];
+  if (vec && !e.empty()) return "(vec " + std::to_string(e.size()) + " " + e[0].str() + ")";
   std::string r = "(tup";
   for (auto& c : e) r += " " + c.str();
   return r + ")";
@@ -95,6 +97,14 @@ bool Type::is_shape() const {
 }
 Type parse_type(const Sx& x) {
   if (x.atom) return Type::scalar(parse_ty(x.s));
+  if (x.head() == "vec") {
+    // (vec N T), N in 2, 3, 4, 8, 16 (Type.hs:140-152; VecElt instances, Sugar/Vec.hs)
+    const int n = atoi(x.at(1).s.c_str());
+    if (!x.at(2).atom || !(n == 2 || n == 3 || n == 4 || n == 8 || n == 16)) throw Error(B200_ERR_TYPE, "expected (vec 2|3|4|8|16 scalar)");
+    Type r = Type::tup(std::vector<Type>((size_t)n, Type::scalar(parse_ty(x.at(2).s))));
+    r.vec = true;
+    return r;
+  }
   std::vector<Type> xs;
   size_t b = x.head() == "tup" ? 1 : 0;
   for (size_t i = b; i < x.size(); ++i) xs.push_back(parse_type(x.k[i]));
@@ -173,6 +183,21 @@ std::unique_ptr<Expr> parse_expr(const Sx& x, TEnv& env) {
     e->a.push_back(parse_expr(x.at(i), env));
     return *e->a.back();
   };
+  if (h == "vecpack" || h == "vecunpack") {
+    // VecPack / VecUnpack (AST.hs:566-573; Interpreter.hs:951-952): (vecpack N T e) takes the tuple of N
+    // components to the vector, (vecunpack N T e) back.  Both are the identity on what the kernels hold.
+    Sx vt;
+    vt.k.resize(3);
+    vt.k[0].atom = true;
+    vt.k[0].s = "vec";
+    vt.k[1] = x.at(1);
+    vt.k[2] = x.at(2);
+    const Type v = parse_type(vt);
+    e = parse_expr(x.at(3), env);
+    if (e->ty != v) throw Error(B200_ERR_TYPE, h + ": operand is " + e->ty.str() + ", expected the components of " + v.str());
+    e->ty.vec = h == "vecpack";
+    return e;
+  }
   if (h == "const") {
     e->kind = X_CONST;
     e->ty = Type::scalar(parse_ty(x.at(1).s));
@@ -748,8 +773,123 @@ void node_arrays(const Node& n, std::vector<std::string>& used) {
   }
 }
 
+// ---- arrays of SIMD vectors at the program's boundary ------------------------------------------------
+// The reference stores an `Array sh (Vec n t)` as n components side by side per element
+// (Array/Data.hs:108-119), which is byte for byte an `Array (sh :. n) t`.  A program's inputs, embedded
+// arrays and results of that type are therefore declared to the outside as rank+1 arrays of t, and the
+// program gains one `generate` per such array that regroups it: components into a tuple on the way in,
+// the tuple's components along the new innermost dimension on the way out.
+namespace {
+
+Sx atom(const std::string& s) { Sx x; x.atom = true; x.s = s; return x; }
+Sx list(std::vector<Sx> k) { Sx x; x.k = std::move(k); return x; }
+Sx i64c(int64_t v) { return list({atom("const"), atom("i64"), atom(std::to_string(v))}); }
+Sx prj(int k, Sx v) { return list({atom("prj"), atom(std::to_string(k)), std::move(v)}); }
+Sx shape_ty(int rank) {
+  std::vector<Sx> k{atom("tup")};
+  for (int d = 0; d < rank; ++d) k.push_back(atom("i64"));
+  return list(std::move(k));
+}
+bool vec_array_type(const Sx& at, int* rank, int* n, std::string* t) {
+  if (at.head() != "array" || at.size() != 3 || at.k[2].head() != "vec" || at.k[2].size() != 3) return false;
+  *rank = atoi(at.k[1].s.c_str());
+  *n = atoi(at.k[2].k[1].s.c_str());
+  *t = at.k[2].k[2].s;
+  return true;
+}
+// (let NAME (generate (vec n t) (init (shape RAW)) (lam ((v ix)) (tup (index RAW (ix.., 0)) ..))))
+Sx regroup_in(const std::string& name, const std::string& raw, int rank, int n, const std::string& t) {
+  std::vector<Sx> comps{atom("tup")};
+  for (int k = 0; k < n; ++k) {
+    std::vector<Sx> ix{atom("tup")};
+    for (int d = 0; d < rank; ++d) ix.push_back(prj(d, list({atom("var"), atom("vx")})));
+    ix.push_back(i64c(k));
+    comps.push_back(list({atom("index"), atom(raw), list(std::move(ix))}));
+  }
+  Sx lam = list({atom("lam"), list({list({atom("vx"), shape_ty(rank)})}), list(std::move(comps))});
+  Sx gen = list({atom("generate"), list({atom("vec"), atom(std::to_string(n)), atom(t)}),
+                 list({atom("init"), list({atom("shape"), atom(raw)})}), std::move(lam)});
+  return list({atom("let"), atom(name), std::move(gen)});
+}
+// (let AOS (generate t (snoc (shape NAME) n) (lam ((v ix')) (let e (index NAME (init ix')) (cond (k == 0) e.0 ..)))))
+Sx regroup_out(const std::string& aos, const std::string& name, int rank, int n, const std::string& t) {
+  Sx sel = prj(n - 1, list({atom("var"), atom("ve")}));
+  for (int k = n - 2; k >= 0; --k)
+    sel = list({atom("cond"), list({atom("prim"), atom("eq"), atom("i64"), prj(rank, list({atom("var"), atom("vx")})), i64c(k)}),
+                prj(k, list({atom("var"), atom("ve")})), std::move(sel)});
+  Sx body = list({atom("let"), atom("ve"), list({atom("index"), atom(name), list({atom("init"), list({atom("var"), atom("vx")})})}), std::move(sel)});
+  Sx lam = list({atom("lam"), list({list({atom("vx"), shape_ty(rank + 1)})}), std::move(body)});
+  Sx gen = list({atom("generate"), atom(t), list({atom("snoc"), list({atom("shape"), atom(name)}), i64c(n)}), std::move(lam)});
+  return list({atom("let"), atom(aos), std::move(gen)});
+}
+// inputs and embedded arrays, wherever they are bound
+void lower_vectors_in(Sx& x) {
+  if (x.atom) return;
+  std::vector<Sx> out;
+  for (Sx& c : x.k) {
+    int rank, n;
+    std::string t;
+    if (c.head() == "in" && c.size() == 3 && vec_array_type(c.k[2], &rank, &n, &t)) {
+      const std::string name = c.k[1].s, raw = name + "_aos";
+      out.push_back(list({atom("in"), atom(raw), list({atom("array"), atom(std::to_string(rank + 1)), atom(t)})}));
+      out.push_back(regroup_in(name, raw, rank, n, t));
+    } else if (c.head() == "let" && c.size() == 3 && c.k[2].head() == "use" && c.k[2].size() >= 3 && vec_array_type(c.k[2].k[1], &rank, &n, &t)) {
+      const std::string name = c.k[1].s, raw = name + "_aos";
+      Sx use = c.k[2];
+      use.k[1] = list({atom("array"), atom(std::to_string(rank + 1)), atom(t)});
+      use.k[2].k.push_back(atom(std::to_string(n)));      // (shape d.. n)
+      out.push_back(list({atom("let"), atom(raw), std::move(use)}));
+      out.push_back(regroup_in(name, raw, rank, n, t));
+    } else {
+      lower_vectors_in(c);
+      out.push_back(std::move(c));
+    }
+  }
+  x.k = std::move(out);
+}
+std::unique_ptr<ProgramIR> parse_program_sx(const Sx& top);
+}  // namespace
+
+Sx lower_vectors(const Sx& program) {
+  Sx top = program;
+  if (sx_text(top).find("(vec ") == std::string::npos) return top;
+  // (inputs are declared before the nodes that read them, so the regrouping nodes land in front of those)
+  lower_vectors_in(top);
+  // results: their types are known once the program has been read
+  std::unique_ptr<ProgramIR> p = parse_program_sx(top);
+  std::vector<Sx> lets;
+  for (Sx& f : top.k) {
+    if (f.head() != "out") continue;
+    for (size_t j = 1; j < f.k.size(); ++j) {
+      const ArrayInfo& ai = p->arrays.at(f.k[j].s);
+      if (!ai.elt.vec) {
+        std::function<bool(const Type&)> nested = [&](const Type& t) { if (t.vec) return true; for (auto& c : t.e) if (nested(c)) return true; return false; };
+        if (nested(ai.elt)) throw Error(B200_ERR_UNSUPPORTED, "result '" + f.k[j].s + "': SIMD vectors inside a tuple cannot leave the program");
+        continue;
+      }
+      const std::string aos = f.k[j].s + "_aos";
+      lets.push_back(regroup_out(aos, f.k[j].s, ai.rank, (int)ai.elt.e.size(), ty_name[ai.elt.e[0].s]));
+      f.k[j] = atom(aos);
+    }
+  }
+  if (!lets.empty()) {
+    std::vector<Sx> k;
+    for (Sx& f : top.k) {
+      if (f.head() == "out") { for (Sx& l : lets) k.push_back(l); lets.clear(); }
+      k.push_back(std::move(f));
+    }
+    top.k = std::move(k);
+  }
+  return top;
+}
+
 std::unique_ptr<ProgramIR> parse_program(const char* text, size_t len) {
-  Sx top = parse_sexp(text, len);
+  return parse_program_sx(lower_vectors(parse_sexp(text, len)));
+}
+std::string program_text_lowered(const char* text, size_t len) { return sx_text(lower_vectors(parse_sexp(text, len))); }
+
+namespace {
+std::unique_ptr<ProgramIR> parse_program_sx(const Sx& top) {
   if (top.head() != "program") throw Error(B200_ERR_PARSE, "expected (program ...)");
   auto p = std::make_unique<ProgramIR>();
   TEnv env;
@@ -779,5 +919,6 @@ std::unique_ptr<ProgramIR> parse_program(const char* text, size_t len) {
   if (p->outputs.empty()) throw Error(B200_ERR_PARSE, "program has no (out ...)");
   return p;
 }
+}  // namespace
 
 }  // namespace accb200

@@ -86,6 +86,11 @@ inline float half_to_float(uint16_t h) {
 
 struct Type {
   bool tuple = false;
+  // `Vec n t` (Type.hs:140-152): inside a program a SIMD vector is the tuple of its n components (one
+  // buffer per component like any tuple); the mark only says which arrays cross the program's boundary
+  // in the reference's layout, n components side by side per element (see lower_vectors in ir.cpp).
+  // Equality ignores it.
+  bool vec = false;
   Ty s = I64;
   std::vector<Type> e;
   static Type scalar(Ty t) { Type r; r.s = t; return r; }
@@ -209,6 +214,9 @@ struct ProgramIR {
 
 // Parse and type-check; throws Error.
 std::unique_ptr<ProgramIR> parse_program(const char* text, size_t len);
+// The program with its arrays of SIMD vectors regrouped at the boundary (the identity without them).
+Sx lower_vectors(const Sx& program);
+std::string program_text_lowered(const char* text, size_t len);
 
 // Free array variables of an expression / function (names, in first-use order).
 void free_arrays(const Expr& e, std::vector<std::string>& out);

@@ -45,6 +45,23 @@ def is_scalar(t):
     return isinstance(t, str)
 
 
+def vec(n, t):
+    """``Vec n t`` (Type.hs:140-152), n in 2, 3, 4, 8, 16.  To this module it is one opaque element type:
+    an ndarray of such elements has one more, innermost, axis of length n, the reference's layout for it
+    (Array/Data.hs:108-119); ``vec_unpack`` / ``vec_pack`` convert to and from the tuple of components."""
+    if n not in (2, 3, 4, 8, 16) or t not in SCALARS:
+        raise TypeError("vec(n, t): n in 2, 3, 4, 8, 16 and t a scalar type")
+    return f"(vec {n} {t})"
+
+
+def vec_parts(t):
+    """``(n, component type)`` of a vector type, else None."""
+    if isinstance(t, str) and t.startswith("(vec "):
+        _, n, c = t[1:-1].split()
+        return int(n), c
+    return None
+
+
 def ty_sx(t):
     if is_scalar(t):
         return t
@@ -279,6 +296,21 @@ def _conv(op, x, to):
     return Exp(to, f"(prim {op} {x.ty} {to} {x.sx})", x.deps)
 
 
+def vec_unpack(x):
+    """``unpackVec{2,3,4,..}'`` / VecUnpack (AST.hs:570-573): the vector's components as a tuple."""
+    n, c = vec_parts(x.ty)
+    return Exp(tuple([c] * n), f"(vecunpack {n} {c} {x.sx})", x.deps)
+
+
+def vec_pack(*xs):
+    """VecPack (AST.hs:566-569): n equally typed scalars (or one n-tuple) as a vector."""
+    x = xs[0] if len(xs) == 1 and isinstance(xs[0], Exp) else tup(*xs)
+    n, c = len(x.ty), x.ty[0]
+    if any(t != c for t in x.ty):
+        raise TypeError("vec_pack: components differ in type")
+    return Exp(vec(n, c), f"(vecpack {n} {c} {x.sx})", x.deps)
+
+
 def from_integral(x, to): return _conv("fromintegral", x, to)
 def to_floating(x, to): return _conv("tofloating", x, to)
 def truncate(x, to=INT): return _conv("truncate", x, to)
@@ -402,6 +434,13 @@ def use(a, elt=None):
         leaves = [a.view(np.uint8) if a.dtype == np.bool_ else a]
         elt = elt or TY_OF_NP[a.dtype]
     sh = tuple(int(d) for d in leaves[0].shape)
+    if vec_parts(elt):
+        # the ndarray's last axis holds the components: it is no dimension of the array of vectors
+        n, c = vec_parts(elt)
+        if isinstance(a, (tuple, list)) or not sh or sh[-1] != n or TY_OF_NP[leaves[0].dtype] != c:
+            raise TypeError(f"use: an array of {elt} is one ndarray of {c} whose last axis has length {n}")
+        node = Node("in", len(sh) - 1, elt, data=(sh, leaves))
+        return Acc(len(sh) - 1, elt, node=node)
     node = Node("in", len(sh), elt, data=(sh, leaves))
     return Acc(len(sh), elt, node=node)
 
@@ -461,6 +500,23 @@ def map_(f, a):
 def zipWith(f, a, b):
     a, b = use(a), use(b)
     return generate(intersect(a.shape, b.shape), lambda ix: f(a[ix], b[ix]))
+
+
+def _zip_with_n(f, *xs):
+    """zipWith3, zipWith4 (Prelude.hs:316-349): the extent is the intersection of all operands'."""
+    xs = [use(x) for x in xs]
+    sh = xs[0].shape
+    for x in xs[1:]:
+        sh = intersect(sh, x.shape)
+    return generate(sh, lambda ix: f(*[x[ix] for x in xs]))
+
+
+def zipWith3(f, a, b, c):
+    return _zip_with_n(f, a, b, c)
+
+
+def zipWith4(f, a, b, c, d):
+    return _zip_with_n(f, a, b, c, d)
 
 
 def zip_(a, b):
@@ -1048,7 +1104,7 @@ class _Emitter:
     def hex_use(self, n):
         sh, leaves = n.data
         body = " ".join("(hex " + np.ascontiguousarray(x).tobytes().hex() + ")" for x in leaves)
-        return f"(use (array {n.rank} {ty_sx(n.elt)}) (shape{''.join(' ' + str(d) for d in sh)}) {body})"
+        return f"(use (array {n.rank} {ty_sx(n.elt)}) (shape{''.join(' ' + str(d) for d in sh[:n.rank])}) {body})"
 
     def level(self, roots, emitted, lines, indent):
         """Emit, into ``lines``, every node the ``roots`` need that is not in ``emitted`` yet."""

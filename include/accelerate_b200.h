@@ -187,6 +187,11 @@ int b200_group_halo_wait(b200_group* group);
 int b200_compile_check(const char* text, size_t len, char* log, size_t log_len);
 /* Generated CUDA source of node `node` (default variant), for inspection. */
 int b200_kernel_source(const char* text, size_t len, int node, char* out, size_t out_len);
+/* The program as the library runs it: arrays of SIMD vectors (`(vec n t)`, Type.hs:140-152) that enter or
+ * leave the program are declared as arrays of t with one more, innermost, dimension of extent n, which is
+ * the reference's layout for them byte for byte (Array/Data.hs:108-119), and regrouped by a `generate`
+ * each.  Text without such arrays comes back unchanged.  For inspection and for the tests. */
+int b200_program_lowered(const char* text, size_t len, char* out, size_t out_len);
 
 /* Diagnostic (no counterpart in the reference; used by the host-side tests): 1 when a scan along
  * rows of `n` elements of `elt_bytes` bytes each (`rows` rows, right-to-left if `right`) meets the

@@ -169,6 +169,12 @@ EltTy parse_elt(const Sx& x) {
   EltTy t;
   if (x.atom) { t.ty = parse_ty(x.s); return t; }
   t.tuple = true;
+  if (x.size() == 3 && x.k[0].atom && x.k[0].s == "vec") {
+    // Vec n t (Type.hs:140-152): a value is its n components; evalVecPack/evalVecUnpack
+    // (Interp:951-952) convert between the two views of the same scalars
+    for (int i = 0, n = atoi(x.k[1].s.c_str()); i < n; ++i) t.e.push_back(parse_elt(x.k[2]));
+    return t;
+  }
   size_t b = (x.size() && x.k[0].atom && x.k[0].s == "tup") ? 1 : 0;
   for (size_t i = b; i < x.size(); ++i) t.e.push_back(parse_elt(x.k[i]));
   return t;
@@ -444,6 +450,7 @@ std::unique_ptr<Exp> parse_exp(const Sx& x, Scope& sc) {
   if (x.atom) throw std::runtime_error("expression must be a list, got atom '" + x.s + "'");
   std::string h = x.head();
   auto sub = [&](size_t i) { e->a.push_back(parse_exp(x[i], sc)); };
+  if (h == "vecpack" || h == "vecunpack") return parse_exp(x[3], sc);  // (vecpack N T e): same scalars
   if (h == "const") {
     e->kind = E_CONST;
     e->c = parse_const(parse_ty(x[1].s), x[2].s);

@@ -102,6 +102,12 @@ def run(results):
     from accelerate_b200 import language as L
     single = not isinstance(results, (list, tuple))
     prog = L.build_program(results)
-    outs = run_text(prog.text, [n.data for n in prog.inputs])
+    text = prog.text
+    if "(vec " in text:
+        # Arrays of SIMD vectors cross a program's boundary as arrays of their components with one more
+        # dimension; the library rewrites the text accordingly and the oracle evaluates what it wrote.
+        from accelerate_b200 import backend
+        text = backend.program_lowered(text)
+    outs = run_text(text, [n.data for n in prog.inputs])
     res = [leaves[0] if L.is_scalar(elt) else tuple(leaves) for (_, leaves), (_, elt) in zip(outs, prog.outputs)]
     return res[0] if single else res
