@@ -371,7 +371,8 @@ def run_program(prog, host_inputs, ctx=None):
     ctx = ctx or default_context()
     ins = []
     for n, (shape, leaves) in zip(prog.inputs, host_inputs):
-        ins.append(ctx.array(n.elt, shape).upload(leaves))
+        # (an array of SIMD vectors is, to the library, an array of the component type with one more dimension)
+        ins.append(ctx.array(L.vec_parts(n.elt)[1] if L.vec_parts(n.elt) else n.elt, shape).upload(leaves))
     outs = ctx.execute(prog.text, ins, len(prog.outputs))
     res = []
     for o, (_, elt) in zip(outs, prog.outputs):

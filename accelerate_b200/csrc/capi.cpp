@@ -36,9 +36,19 @@ DevArrayP lookup_used(Ctx& c, uint64_t id) {
   for (auto& b : a->leaf) b->fresh = false;
   return a;
 }
+bool mentions_vector(const Type& t) {
+  if (t.vec) return true;
+  for (auto& c : t.e)
+    if (mentions_vector(c)) return true;
+  return false;
+}
+// element type of an array the caller creates.  SIMD vectors have no array type of their own here: an
+// `Array sh (Vec n t)` is created as an array of t of shape sh :. n, the same bytes (Array/Data.hs:108-119).
 Type parse_type_text(const char* s) {
   Sx x = parse_sexp(s, strlen(s));
-  return parse_type(x);
+  Type t = parse_type(x);
+  if (mentions_vector(t)) throw Error(B200_ERR_TYPE, "an array of (vec n t) is created as an array of t with one more, innermost, dimension of extent n");
+  return t;
 }
 // every node that launches kernels, the bodies of control nodes included, in program order
 void kernel_nodes(const std::vector<Node>& ns, std::vector<const Node*>& out) {
