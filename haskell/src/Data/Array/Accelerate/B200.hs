@@ -41,7 +41,8 @@ import Data.Array.Accelerate.AST
 import Data.Array.Accelerate.AST.Idx
 import Data.Array.Accelerate.AST.LeftHandSide
 import Data.Array.Accelerate.AST.Var
-import Data.Array.Accelerate.Array.Data                             ( ArrayData, GArrayDataR )
+import Data.Array.Accelerate.Array.Data                             ( ArrayData, GArrayDataR, ScalarArrayDict(..), scalarArrayDict )
+import Data.Array.Accelerate.Representation.Vec                     ( vecRvector )
 import Data.Array.Accelerate.Array.Unique                           ( unsafeUniqueArrayPtr, getUniqueId )
 import Data.Array.Accelerate.Error
 import Data.Array.Accelerate.Representation.Array
@@ -199,7 +200,10 @@ uploadArrays ctx (TupRsingle (ArrayR shr tp)) (Array sh adata) = do
   _ <- forLeaves tp adata 0 $ \_ _ ptr -> modifyIORef ptrs (ptr :)
   leaves <- reverse <$> readIORef ptrs
   let _ = n
-  ident <- withCString (typeText tp) $ \ty -> withArrayLen (reverse dims) $ \r pd ->
+  let (eltText, dims') = case vectorElt tp of
+        Just (w, t) -> (t, fromIntegral w : dims)       -- innermost first, like shapeToList
+        Nothing     -> (typeText tp, dims)
+  ident <- withCString eltText $ \ty -> withArrayLen (reverse dims') $ \r pd ->
            withArray leaves $ \pl -> alloca $ \pid -> do
     check =<< c_arrayIntern ctx (arrayKey tp adata) ty (fromIntegral r) pd pl pid      -- shapeToList is innermost-first
     peek pid
@@ -212,7 +216,8 @@ downloadArrays ctx (TupRsingle repr@(ArrayR shr tp)) ref = do
   ident <- atomicModifyIORef' ref (\(x:xs) -> (xs, x))
   rank  <- alloca $ \p -> c_arrayRank ctx ident p >>= check >> fromIntegral <$> peek p
   dims  <- allocaArray (max 1 rank) $ \p -> c_arrayShape ctx ident p >>= check >> peekArray rank p
-  let sh = listToShape shr (reverse (map fromIntegral (dims :: [Int64])))
+  let outer = maybe id (const init) (vectorElt tp)        -- the components' dimension is no part of the shape
+      sh    = listToShape shr (reverse (map fromIntegral (outer (dims :: [Int64]))))
   arr@(Array _ adata) <- allocateArray repr sh
   forLeaves tp adata 0 $ \leaf bytesPer ptr ->
     check =<< c_arrayDownload ctx ident (fromIntegral leaf) ptr (fromIntegral (size shr sh * bytesPer))
@@ -247,7 +252,9 @@ scalarPayload (SingleScalarType (NumSingleType nt)) ad = case nt of
   FloatingNumType ft -> case ft of
     TypeFloat  -> (4, castPtr (unsafeUniqueArrayPtr ad)); TypeDouble -> (8, castPtr (unsafeUniqueArrayPtr ad))
     TypeHalf   -> (2, castPtr (unsafeUniqueArrayPtr ad))   -- the 16 bits of Numeric.Half, as the library keeps them
-scalarPayload VectorScalarType{} _ = unsupported "SIMD vector element types"
+-- An array of @Vec n t@ is one payload of t, n per element (Array/Data.hs:108-119): n * sizeof t bytes each.
+scalarPayload t@(VectorScalarType (VectorType w s)) ad
+  | ScalarArrayDict _ _ <- scalarArrayDict t = (w * singleBytes s, castPtr (unsafeUniqueArrayPtr ad))
 
 -- 'getUniqueId' of the leaf's 'UniqueArray' (Array/Unique.hs:48-51, 66-69).
 scalarUniqueId :: ScalarType t -> ArrayData t -> IO Int
@@ -259,7 +266,23 @@ scalarUniqueId (SingleScalarType (NumSingleType nt)) ad = case nt of
   FloatingNumType ft -> case ft of
     TypeFloat  -> getUniqueId ad; TypeDouble -> getUniqueId ad
     TypeHalf   -> getUniqueId ad
-scalarUniqueId VectorScalarType{} _ = unsupported "SIMD vector element types"
+scalarUniqueId t@VectorScalarType{} ad
+  | ScalarArrayDict _ _ <- scalarArrayDict t = getUniqueId ad
+
+singleBytes :: SingleType t -> Int
+singleBytes (NumSingleType nt) = case nt of
+  IntegralNumType it -> case it of
+    TypeInt -> 8; TypeInt8 -> 1; TypeInt16 -> 2; TypeInt32 -> 4; TypeInt64 -> 8
+    TypeWord -> 8; TypeWord8 -> 1; TypeWord16 -> 2; TypeWord32 -> 4; TypeWord64 -> 8
+  FloatingNumType ft -> case ft of
+    TypeHalf -> 2; TypeFloat -> 4; TypeDouble -> 8
+
+-- | @Just (n, t)@ when the elements of an array are SIMD vectors.  Such an array goes to the library as
+-- an array of t with one more, innermost, dimension of extent n: the same bytes.  (Vectors inside a
+-- tuple element have no such reading and are refused.)
+vectorElt :: TypeR e -> Maybe (Int, String)
+vectorElt (TupRsingle (VectorScalarType (VectorType w s))) = Just (w, scalarText (SingleScalarType s))
+vectorElt _                                                = Nothing
 
 unsupported :: String -> a
 unsupported what = error ("accelerate-b200: " ++ what ++ " are not supported by this backend")
@@ -570,8 +593,10 @@ openExpText ns env = go
       FromIndex _ sh i    -> sx ["fromindex", go sh, go i]
       Coerce t1 t2 e      -> sx ["coerce", scalarText t1, scalarText t2, go e]
       Foreign{}           -> unsupported "foreign scalar functions"
-      VecPack{}           -> unsupported "SIMD vectors"
-      VecUnpack{}         -> unsupported "SIMD vectors"
+      VecPack vecR e      | VectorType w s <- vecRvector vecR
+                          -> sx ["vecpack",   show w, scalarText (SingleScalarType s), go e]
+      VecUnpack vecR e    | VectorType w s <- vecRvector vecR
+                          -> sx ["vecunpack", show w, scalarText (SingleScalarType s), go e]
       IndexSlice{}        -> unsupported "IndexSlice (use the fused Transform form)"
       IndexFull{}         -> unsupported "IndexFull (use the fused Transform form)"
     goL :: OpenExp env aenv s -> String
@@ -600,7 +625,7 @@ scalarText (SingleScalarType (NumSingleType nt)) = case nt of
     TypeWord -> "u64"; TypeWord8 -> "u8"; TypeWord16 -> "u16"; TypeWord32 -> "u32"; TypeWord64 -> "u64"
   FloatingNumType ft -> case ft of
     TypeFloat -> "f32"; TypeDouble -> "f64"; TypeHalf -> "f16"
-scalarText VectorScalarType{} = unsupported "SIMD vector types"
+scalarText (VectorScalarType (VectorType w s)) = sx ["vec", show w, scalarText (SingleScalarType s)]
 
 constText :: TypeR t -> t -> String
 constText TupRunit         ()     = "(tup)"
@@ -616,7 +641,7 @@ literal (SingleScalarType (NumSingleType nt)) v = case nt of
     TypeDouble -> hex v
     TypeHalf   -> hex (realToFrac v :: Double)   -- exact: every Half is a Double
   where hex d | isNaN d = "nan" | isInfinite d = if d > 0 then "inf" else "-inf" | otherwise = showHFloat d ""
-literal VectorScalarType{} _ = unsupported "SIMD vector constants"
+literal VectorScalarType{} _ = unsupported "SIMD vector constants (pack the components instead)"
 
 primConstText :: PrimConst t -> String
 primConstText (PrimMinBound (IntegralBoundedType t)) = sx ["minbound", scalarText (SingleScalarType (NumSingleType (IntegralNumType t)))]
