@@ -850,9 +850,15 @@ void lower_vectors_in(Sx& x) {
 std::unique_ptr<ProgramIR> parse_program_sx(const Sx& top);
 }  // namespace
 
-Sx lower_vectors(const Sx& program) {
-  Sx top = program;
-  if (sx_text(top).find("(vec ") == std::string::npos) return top;
+Sx lower_vectors(Sx top) {
+  std::function<bool(const Sx&)> mentions = [&](const Sx& x) {
+    if (x.atom) return false;
+    if (x.head() == "vec") return true;
+    for (const Sx& c : x.k)
+      if (mentions(c)) return true;
+    return false;
+  };
+  if (!mentions(top)) return top;
   // (inputs are declared before the nodes that read them, so the regrouping nodes land in front of those)
   lower_vectors_in(top);
   // results: their types are known once the program has been read
@@ -884,7 +890,7 @@ Sx lower_vectors(const Sx& program) {
 }
 
 std::unique_ptr<ProgramIR> parse_program(const char* text, size_t len) {
-  return parse_program_sx(lower_vectors(parse_sexp(text, len)));
+  return parse_program_sx(lower_vectors(parse_sexp(text, len)));   // (the tree is moved, not copied)
 }
 std::string program_text_lowered(const char* text, size_t len) { return sx_text(lower_vectors(parse_sexp(text, len))); }
 

@@ -215,7 +215,7 @@ struct ProgramIR {
 // Parse and type-check; throws Error.
 std::unique_ptr<ProgramIR> parse_program(const char* text, size_t len);
 // The program with its arrays of SIMD vectors regrouped at the boundary (the identity without them).
-Sx lower_vectors(const Sx& program);
+Sx lower_vectors(Sx program);
 std::string program_text_lowered(const char* text, size_t len);
 
 // Free array variables of an expression / function (names, in first-use order).
