@@ -145,6 +145,24 @@ def test_program_text_as_the_haskell_module_writes_it(lib_built):
     assert "acc_ld4(p.a0_l0" in backend.kernel_source(HASKELL_DIALECT, 0)
 
 
+HASKELL_DIALECT_SIMD = '''(program
+  (in a0 (array 1 (vec 2 f16)))
+  (let a1 (generate (vec 2 f16) (shape a0)
+     (lam ((p0 (tup i64))) (let x0 (vecunpack 2 f16 (index a0 (var p0)))
+        (vecpack 2 f16 (snoc (snoc (tup) (last (var x0))) (prim add f16 (snoc (snoc (tup) (last (init (var x0)))) (const f16 0x1p-1)))))))))
+  (out a1))'''
+
+
+def test_simd_and_half_as_the_haskell_module_writes_them(lib_built):
+    """Vec n t as (vec n t) with VecPack/VecUnpack over snoc-list tuples, Half as f16 with hexadecimal
+    literals: (x, y) -> (y, x + 0.5) over an array the caller hands over as its (n, 2) payload."""
+    from oracle import oracle
+    x = np.arange(10, dtype=np.float16).reshape(5, 2)
+    (shape, (res,)), = oracle.run_text(backend.program_lowered(HASKELL_DIALECT_SIMD), [((5, 2), [x])])
+    assert shape == (5, 2) and np.array_equal(res, np.stack([x[:, 1], x[:, 0] + np.float16(0.5)], axis=-1))
+    assert "ok elementwise" in backend.compile_check(HASKELL_DIALECT_SIMD)
+
+
 def test_sharded_program_cache_tells_builders_apart():
     """The executor of the sharded skeletons caches built programs.  Builders are closures: the same
     call site with another function, shape or constant must not get the first call's program."""
