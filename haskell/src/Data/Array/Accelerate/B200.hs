@@ -43,6 +43,7 @@ import Data.Array.Accelerate.AST.LeftHandSide
 import Data.Array.Accelerate.AST.Var
 import Data.Array.Accelerate.Array.Data                             ( ArrayData, GArrayDataR, ScalarArrayDict(..), scalarArrayDict )
 import Data.Array.Accelerate.Representation.Vec                     ( vecRvector )
+import Data.Primitive.Vec                                           ( listOfVec )
 import Data.Array.Accelerate.Array.Unique                           ( unsafeUniqueArrayPtr, getUniqueId )
 import Data.Array.Accelerate.Error
 import Data.Array.Accelerate.Representation.Array
@@ -630,6 +631,11 @@ scalarText (VectorScalarType (VectorType w s)) = sx ["vec", show w, scalarText (
 constText :: TypeR t -> t -> String
 constText TupRunit         ()     = "(tup)"
 constText (TupRpair ta tb) (a, b) = sx ["snoc", constText ta a, constText tb b]
+-- a constant vector is the pack of its constant components (as 'showElt' takes it apart, Representation/Elt.hs:150-154)
+constText (TupRsingle (VectorScalarType (VectorType w s))) v
+  | SingleDict <- singleDict s
+  , st         <- scalarText (SingleScalarType s)
+  = sx ["vecpack", show w, st, sx ("tup" : [ sx ["const", st, literal (SingleScalarType s) x] | x <- listOfVec v ])]
 constText (TupRsingle t)   v      = sx ["const", scalarText t, literal t v]
 
 -- Integers in decimal; floating point as C99 hexadecimal literals (exact).
@@ -641,7 +647,7 @@ literal (SingleScalarType (NumSingleType nt)) v = case nt of
     TypeDouble -> hex v
     TypeHalf   -> hex (realToFrac v :: Double)   -- exact: every Half is a Double
   where hex d | isNaN d = "nan" | isInfinite d = if d > 0 then "inf" else "-inf" | otherwise = showHFloat d ""
-literal VectorScalarType{} _ = unsupported "SIMD vector constants (pack the components instead)"
+literal VectorScalarType{} _ = unsupported "SIMD vector constants outside constText"
 
 primConstText :: PrimConst t -> String
 primConstText (PrimMinBound (IntegralBoundedType t)) = sx ["minbound", scalarText (SingleScalarType (NumSingleType (IntegralNumType t)))]
