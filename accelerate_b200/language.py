@@ -791,6 +791,219 @@ def _init1(a):
     return backpermute(index(max_(a.shape[0] - 1, 0)), lambda ix: ix, a)
 
 
+# ----------------------------------------------------------------------------
+# More of the Prelude, each built from the operations above as the reference builds it
+# (shape-polymorphic slices are written with None for `All`; lenses _1, _2, .. are the
+# numbers 1, 2, .. counted from the innermost dimension)
+# ----------------------------------------------------------------------------
+All = None
+
+
+def replicate(slix, a):
+    """``replicate`` (Language.hs:265-271): ``slix`` lists every dimension of the result, outermost
+    first: ``All`` where the argument's next dimension goes, an extent where the array is repeated."""
+    a = use(a)
+    kept = [d for d, s in enumerate(slix) if s is All]
+    if len(kept) != a.rank:
+        raise TypeError("replicate: the slice has as many Alls as the array has dimensions")
+    ash = a.shape
+    ext, k = [], 0
+    for s in slix:
+        if s is All:
+            ext.append(ash[k])
+            k += 1
+        else:
+            ext.append(lift(s, INT))
+    return backpermute(index(*ext), lambda ix: index(*[ix[d] for d in kept]), a)
+
+
+def slice(a, slix):  # noqa: A001
+    """``slice`` (Language.hs:398-403): one entry per dimension of the array, ``All`` to keep it, an
+    index to cut there."""
+    a = use(a)
+    if len(slix) != a.rank:
+        raise TypeError("slice: one entry per dimension")
+    kept = [d for d, s in enumerate(slix) if s is All]
+    ash = a.shape
+
+    def src(ix):
+        k, out = 0, []
+        for s in slix:
+            if s is All:
+                out.append(ix[k])
+                k += 1
+            else:
+                out.append(lift(s, INT))
+        return index(*out)
+    return backpermute(index(*[ash[d] for d in kept]), src, a)
+
+
+def indexed(a):
+    """``indexed`` (Prelude.hs:172-173: ``imap T2``): each element paired with its index."""
+    a = use(a)
+    return generate(a.shape, lambda ix: tup(ix, a[ix]))
+
+
+def flatten(a):
+    """``flatten`` (Prelude.hs:1430-1432)."""
+    a = use(a)
+    return reshape(index(a.size()), a)
+
+
+def foldAll(f, z, a):
+    """``foldAll`` (Prelude.hs:664-670): ``fold f e (flatten arr)``."""
+    return fold(f, z, flatten(a))
+
+
+def fold1All(f, a):
+    return fold1(f, flatten(a))
+
+
+def all_(p, a):
+    """``all`` (Prelude.hs:780-784, 807-810): ``and . map p``, ``and = fold (&&) True``."""
+    return fold(land, Exp(BOOL, "(const u8 1)"), map_(p, a))
+
+
+def any_(p, a):
+    """``any`` (Prelude.hs:799-803, 814-817): ``or . map p``."""
+    return fold(lor, Exp(BOOL, "(const u8 0)"), map_(p, a))
+
+
+def prescanl(f, e, a):
+    """``prescanl f e = afst . scanl' f e`` (Prelude.hs:899-905)."""
+    return scanl_prime(f, e, a)[0]
+
+
+def postscanl(f, e, a):
+    """``postscanl f e = map (e `f`) . scanl1 f`` (Prelude.hs:916-922)."""
+    a = use(a)
+    e = lift(e, a.elt)
+    return map_(lambda x: f(e, x), scanl1(f, a))
+
+
+def prescanr(f, e, a):
+    return scanr_prime(f, e, a)[0]
+
+
+def postscanr(f, e, a):
+    a = use(a)
+    e = lift(e, a.elt)
+    return map_(lambda x: f(x, e), scanr1(f, a))
+
+
+def enumFromStepN(sh, x, y):
+    """``enumFromStepN`` (Prelude.hs:1478-1490): x, x+y, x+y+y, .. in row-major order, computed as
+    ``fromIntegral i * y + x``."""
+    sh = _shape_exp(sh)
+    x = x if isinstance(x, Exp) else constant(x)
+    y = lift(y, x.ty)
+    return generate(sh, lambda ix: from_integral(to_index(sh, ix), x.ty) * y + x, x.ty)
+
+
+def concatOn(dim, xs, ys):
+    """``concatOn`` (Prelude.hs:1588-1610) along the ``dim``-th dimension from the inside: that extent is
+    the sum, every other one the smaller of the two."""
+    xs, ys = use(xs), use(ys)
+    r = xs.rank
+    d = r - dim
+    shx, shy = xs.shape, ys.shape
+    m = shx[d]
+    ext = [(m + shy[k]) if k == d else min_(shx[k], shy[k]) for k in range(r)]
+
+    def f(ix):
+        i = ix[d]
+        return cond(i < m, xs[ix], ys[index(*[(i - m) if k == d else ix[k] for k in range(r)])])
+    return generate(index(*ext), f, xs.elt)
+
+
+def append(xs, ys):
+    """``(++)`` (Prelude.hs:1527-1531): ``concatOn _1``."""
+    return concatOn(1, xs, ys)
+
+
+def compact(keep, a):
+    """``compact`` (Prelude.hs:1652-1690): the elements of ``a`` whose flag is set, as one vector, and how
+    many each innermost row kept.  (The reference's shortcuts for empty and all-kept vectors give the
+    same values and are left out.)"""
+    keep, a = use(keep), use(a)
+    target, ln = scanl_prime(lambda x, y: x + y, constant(0), map_(lambda k: from_integral(k, INT), keep))
+    if a.rank == 1:
+        prj = lambda ix: cond(keep[ix], Just_(index(target[ix])), Nothing_(1))  # noqa: E731
+        return permute(lambda new, old: new, fill(index(the(ln)), undef(a.elt)), prj, a), ln
+    offset, valid = scanl_prime(lambda x, y: x + y, constant(0), flatten(ln))
+    sz = ln.shape
+
+    def prj(ix):
+        row = to_index(sz, index(*[ix[k] for k in range(a.rank - 1)]))
+        return cond(keep[ix], Just_(index(offset[index(row)] + target[ix])), Nothing_(1))
+    return permute(lambda new, old: new, fill(index(the(valid)), undef(a.elt)), prj, a), ln
+
+
+def filter_(p, a):
+    """``filter p arr = compact (map p arr) arr`` (Prelude.hs:1637-1641)."""
+    a = use(a)
+    return compact(compute(map_(p, a)), a)
+
+
+def gatherIf(frm, mask, pred, defaults, xs):
+    """``gatherIf`` (Prelude.hs:1726-1740): the gathered element where the mask passes, else the default."""
+    frm, mask, defaults, xs = use(frm), use(mask), use(defaults), use(xs)
+    g = gather(frm, xs)
+    sh = intersect(intersect(frm.shape, mask.shape), defaults.shape)
+    return generate(sh, lambda ix: cond(pred(mask[ix]), g[ix], defaults[ix]), xs.elt)
+
+
+def reverseOn(dim, a):
+    """``reverseOn`` (Prelude.hs:1842-1852)."""
+    a = use(a)
+    d = a.rank - dim
+    sh = a.shape
+    return backpermute(sh, lambda ix: index(*[(sh[k] - 1 - ix[k]) if k == d else ix[k] for k in range(a.rank)]), a)
+
+
+def reverse(a):
+    return reverseOn(1, a)
+
+
+def transposeOn(d1, d2, a):
+    """``transposeOn`` (Prelude.hs:1896-1912): swap two dimensions (counted from the inside)."""
+    a = use(a)
+    i, j = a.rank - d1, a.rank - d2
+    sh = a.shape
+
+    def swap(t):
+        xs = [t[k] for k in range(a.rank)]
+        xs[i], xs[j] = xs[j], xs[i]
+        return index(*xs)
+    return backpermute(swap(sh), swap, a)
+
+
+def transpose(a):
+    return transposeOn(1, 2, a)
+
+
+def take(n, a):
+    """``take`` (Prelude.hs:1933-1937)."""
+    return _take_inner(n, a)
+
+
+def drop(n, a):
+    """``drop`` (Prelude.hs:1960-1964)."""
+    return _drop_inner(n, a)
+
+
+def init(a):
+    """``init`` (Prelude.hs:1986-1989): all but the last element of every innermost row."""
+    a = use(a)
+    outer, sz = _outer_inner(a.shape, a.rank)
+    return backpermute(index(*outer, max_(sz - 1, 0)), lambda ix: ix, a)
+
+
+def tail(a):
+    """``tail`` (Prelude.hs:2012-2015)."""
+    return _drop_inner(1, a)
+
+
 def mkHeadFlags(seg):
     """Head flags of a segment descriptor for left scans: non-zero where a segment starts; a value
     above one stands for that many segments starting there (empty ones) (Prelude.hs:1364-1375)."""

@@ -42,10 +42,25 @@ def doctest_output(lines, command, occurrence=1):
                     if s == "--" or s.startswith("-- >>>") or not s.startswith("--"):
                         break
                     out.append(s[2:])
-                text = " ".join(out)
+                text = " ".join(out).strip()
+                if text.startswith("("):
+                    # a pair of arrays, as `filter` returns: "(Vector (Z :. 5) [..],Scalar Z [5])"
+                    parts = []
+                    for m in re.finditer(r"(Vector|Matrix|Array|Scalar)\s*(\(Z[^)]*\)|Z)\s*\[([^\]]*)\]", text):
+                        sh = [int(x) for x in re.findall(r"\d+", m.group(2))]
+                        parts.append({"shape": sh, "values": [int(v) for v in NUM.findall(m.group(3))]})
+                    return i + 1, None, parts
                 shape = parse_shape(text)
                 body = text[text.index("["):]
-                return i + 1, shape, [float(v) if "." in v else int(v) for v in NUM.findall(body)]
+                if "(" in body:
+                    # tuples, shapes inside them written Z :. i :. j: keep the numbers of each tuple together
+                    flat = body.replace("Z :.", "").replace(":.", ",")
+                    tuples = re.findall(r"\(([^()]*)\)", flat)
+                    return i + 1, shape, [[float(v) if "." in v else int(v) for v in NUM.findall(t)] for t in tuples]
+                vals = [float(v) if "." in v else int(v) for v in NUM.findall(body)]
+                if not vals and ("True" in body or "False" in body):
+                    vals = [1 if w == "True" else 0 for w in re.findall(r"True|False", body)]
+                return i + 1, shape, vals
     raise KeyError(command)
 
 
@@ -74,6 +89,10 @@ def main(ref):
     out = {}
 
     def add(key, path, line, shape, values):
+        if shape is None:       # several arrays: one entry each, key_0, key_1
+            for k, part in enumerate(values):
+                out[f"{key}_{k}"] = {"source": f"{os.path.relpath(path, ref)}:{line}", "shape": part["shape"], "values": part["values"]}
+            return
         out[key] = {"source": f"{os.path.relpath(path, ref)}:{line}", "shape": shape, "values": values}
 
     doc_cases = {
@@ -93,6 +112,20 @@ def main(ref):
             ("permute_histogram", "run $ histogram (use xs)", 1),
             ("permute_identity", "run $ identity 5 :: Matrix Int", 1),
             ("backpermute_transpose", "run $ backpermute (swap (shape mat')) swap mat'", 1),
+            ("replicate_rows", "run $ replicate (constant (Z :. (4::Int) :. All)) (use vec)", 1),
+            ("replicate_cols", "run $ replicate (lift (Z :. All :. (4::Int))) (use vec)", 1),
+            ("replicate_two", "run $ replicate (constant (Z :. (2::Int) :. All :. (3::Int))) (use vec)", 1),
+            ("replicate_rep0_unit", "run $ rep0 10 x", 1),
+            ("replicate_rep0_vec", "run $ rep0 5 (use vec)", 1),
+            ("replicate_rep1_vec", "run $ rep1 5 (use vec)", 1),
+            ("generate_const", "run $ generate (I1 3) (\\_ -> 1.2) :: Vector Float", 1),
+            ("fill_3", "run $ fill (constant (Z :. 3)) 1.2 :: Vector Float", 1),
+            ("slice_row", "run $ slice (use mat) (constant (Z :. (2::Int) :. All))", 1),
+            ("slice_point", "run $ slice (use mat) (constant (Z :. 4 :. 2 :: DIM2))", 1),
+            ("slice_sl0_vec", "run $ sl0 (use vec) 4", 1),
+            ("slice_sl0_mat", "run $ sl0 (use mat) 4", 1),
+            ("slice_sl1_mat", "run $ sl1 (use mat) 4", 1),
+            ("slice_sl1_cube", "run $ sl1 (use cube) 2", 1),
         ],
         "Prelude.hs": [
             ("foldSeg_mat", "run $ foldSeg (+) 0 (use mat) (use seg)", 1),
@@ -109,6 +142,36 @@ def main(ref):
             ("scanr_primeSeg_res", "res", 2),
             ("scanr_primeSeg_sums", "sums", 2),
             ("scanr1Seg_mat", "run $ scanr1Seg (+) (use mat) (use seg)", 1),
+            ("indexed_vec", "run $ indexed (use xs)", 1),
+            ("indexed_mat", "run $ indexed (use mat)", 1),
+            ("zip_mats", "run $ zip (use m1) (use m2)", 1),
+            ("foldAll_vec", "run $ foldAll (+) 42 (use vec)", 1),
+            ("foldAll_mat", "run $ foldAll (+) 0 (use mat)", 1),
+            ("all_even", "run $ all even (use mat)", 1),
+            ("any_even", "run $ any even (use mat)", 1),
+            ("product_mat", "run $ product (use mat)", 1),
+            ("prescanl_vec", "run $ prescanl (+) 0 (use vec)", 1),
+            ("postscanl_vec", "run $ postscanl (+) 42 (use vec)", 1),
+            ("fill_10", "run $ fill (constant (Z:.10)) 0 :: Vector Float", 1),
+            ("enumFromN_mat", "run $ enumFromN (constant (Z:.5:.10)) 0 :: Matrix Int", 1),
+            ("enumFromStepN_mat", "run $ enumFromStepN (constant (Z:.5:.10)) 0 0.5 :: Matrix Float", 1),
+            ("append_mats", "run $ use m1 ++ use m2", 1),
+            ("concatOn_1", "run $ concatOn _1 (use m1) (use m2)", 1),
+            ("concatOn_2", "run $ concatOn _2 (use m1) (use m2)", 1),
+            ("filter_even_vec", "run $ filter even (use vec)", 1),
+            ("filter_odd_mat", "run $ filter odd (use mat)", 1),
+            ("gatherIf", "run $ gatherIf (use from) (use mask) (> 4) (use defaults) (use input)", 1),
+            ("scatterIf", "run $ scatterIf (use to) (use mask) (> 4) (fill (constant (Z:.10)) 0) (use input)", 1),
+            ("reverseOn_1", "run $ reverseOn _1 (use mat)", 1),
+            ("reverseOn_2", "run $ reverseOn _2 (use mat)", 1),
+            ("transposeOn_mat", "run $ transposeOn _1 _2 (use mat)", 1),
+            ("transposeOn_box_12", "run $ transposeOn _1 _2 (use box)", 1),
+            ("transposeOn_box_23", "run $ transposeOn _2 _3 (use box)", 1),
+            ("transposeOn_box_13", "run $ transposeOn _1 _3 (use box)", 1),
+            ("take_5", "run $ take 5 (use mat)", 1),
+            ("drop_7", "run $ drop 7 (use mat)", 1),
+            ("init_mat", "run $ init (use mat)", 1),
+            ("tail_mat", "run $ tail (use mat)", 1),
         ],
     }
     for fname, cases in doc_cases.items():

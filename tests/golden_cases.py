@@ -123,6 +123,69 @@ def cases():
     return c
 
 
+def prelude_cases():
+    """Further haddock examples of Language.hs and Prelude.hs: combinators the reference builds from
+    the operations of the hot path (backpermute, generate, fold, scanl', permute), restated through the
+    Python front end's own versions of them."""
+    F = np.float32
+    vec10 = np.arange(10, dtype=I)
+    mat5x10 = np.arange(50, dtype=I).reshape(5, 10)
+    cube = np.arange(60, dtype=I).reshape(3, 4, 5)
+    box = np.arange(30, dtype=I).reshape(2, 3, 5)
+    evens = np.array([1, 2, 3, 4, 5, 6, 7, 8, 9, 10, 1, 1, 1, 1, 1, 2, 2, 2, 2, 2, 2, 4, 6, 8, 10, 12, 14, 16, 18, 20,
+                      1, 3, 5, 7, 9, 11, 13, 15, 17, 19], I).reshape(4, 10)
+    even = lambda v: (v % 2).eq(0)  # noqa: E731
+    odd = lambda v: (v % 2).ne(0)  # noqa: E731
+    one10 = np.arange(1, 11, dtype=I)
+    m10x3 = np.arange(30, dtype=I).reshape(10, 3)
+    m10x5 = np.arange(50, dtype=I).reshape(10, 5)
+    fv, fc = A.filter_(even, one10)
+    mv, mc = A.filter_(odd, evens)
+    gt4 = lambda v: v > 4  # noqa: E731
+    return {
+        "replicate_rows": A.replicate((4, A.All), vec10),                                             # Language.hs:196
+        "replicate_cols": A.replicate((A.All, 4), vec10),                                             # Language.hs:205
+        "replicate_two": A.replicate((2, A.All, 3), vec10),                                           # Language.hs:221
+        "replicate_rep0_unit": A.replicate((10,), A.unit(A.constant(42))),                            # Language.hs:228-235
+        "replicate_rep0_vec": A.replicate((A.All, 5), vec10),                                         # Language.hs:237
+        "replicate_rep1_vec": A.replicate((5, A.All), vec10),                                         # Language.hs:252-257
+        "generate_const": A.generate(A.index(3), lambda ix: A.constant(F(1.2))),                      # Language.hs:278
+        "fill_3": A.fill(A.index(3), F(1.2)),                                                         # Language.hs:283
+        "slice_row": A.slice(mat5x10, (2, A.All)),                                                    # Language.hs:352
+        "slice_point": A.slice(mat5x10, (4, 2)),                                                      # Language.hs:358
+        "slice_sl0_vec": A.slice(vec10, (4,)),                                                        # Language.hs:365-372
+        "slice_sl0_mat": A.slice(mat5x10, (A.All, 4)),                                                # Language.hs:375
+        "slice_sl1_mat": A.slice(mat5x10, (4, A.All)),                                                # Language.hs:380-385
+        "slice_sl1_cube": A.slice(cube, (A.All, 2, A.All)),                                           # Language.hs:388-392
+        "indexed_vec": A.indexed(np.arange(5, dtype=F)),                                              # Prelude.hs:161-162
+        "indexed_mat": A.indexed(np.arange(12, dtype=F).reshape(3, 4)),                               # Prelude.hs:165-166
+        "zip_mats": A.zip(mat5x10, np.arange(50, dtype=F).reshape(10, 5)),                            # Prelude.hs:425-427
+        "foldAll_vec": A.foldAll(add, F(42), np.arange(10, dtype=F)),                                 # Prelude.hs:656-657
+        "foldAll_mat": A.foldAll(add, F(0), np.arange(50, dtype=F).reshape(5, 10)),                   # Prelude.hs:660-661
+        "all_even": A.all_(even, evens), "any_even": A.any_(even, evens),                             # Prelude.hs:769-797
+        "product_mat": A.product(np.arange(10, dtype=I).reshape(2, 5)),                               # Prelude.hs:834-835
+        "prescanl_vec": A.prescanl(add, 0, one10),                                                    # Prelude.hs:895-896
+        "postscanl_vec": A.postscanl(add, 42, one10),                                                 # Prelude.hs:912-913
+        "fill_10": A.fill(A.index(10), F(0)),                                                         # Prelude.hs:1443
+        "enumFromN_mat": A.enumFromN(A.index(5, 10), A.constant(0)),                                  # Prelude.hs:1452
+        "enumFromStepN_mat": A.enumFromStepN(A.index(5, 10), F(0), F(0.5)),                           # Prelude.hs:1470
+        "append_mats": A.append(mat5x10, m10x3),                                                      # Prelude.hs:1495-1518
+        "concatOn_1": A.concatOn(1, mat5x10, m10x5), "concatOn_2": A.concatOn(2, mat5x10, m10x5),     # Prelude.hs:1541-1570
+        "filter_even_vec_0": fv, "filter_even_vec_1": fc,                                             # Prelude.hs:1619-1624
+        "filter_odd_mat_0": mv, "filter_odd_mat_1": mc,                                               # Prelude.hs:1626-1635
+        "gatherIf": A.gatherIf(np.array([1, 3, 7, 2, 5, 3], I), np.array([3, 4, 9, 2, 7, 5], I), gt4, np.full(6, 6, F),
+                               np.array([1, 9, 6, 4, 4, 2, 0, 1, 2], F)),                             # Prelude.hs:1719-1724
+        "scatterIf": A.scatterIf(np.array([1, 3, 7, 2, 5, 8], I), np.array([3, 4, 9, 2, 7, 5], I), gt4, A.fill(10, A.constant(0)),
+                                 np.array([1, 9, 6, 4, 4, 2, 5], I)),                                 # Prelude.hs:1774-1778
+        "reverseOn_1": A.reverseOn(1, mat5x10), "reverseOn_2": A.reverseOn(2, mat5x10),               # Prelude.hs:1815-1838
+        "transposeOn_mat": A.transposeOn(1, 2, mat5x10),                                              # Prelude.hs:1868
+        "transposeOn_box_12": A.transposeOn(1, 2, box), "transposeOn_box_23": A.transposeOn(2, 3, box),
+        "transposeOn_box_13": A.transposeOn(1, 3, box),                                               # Prelude.hs:1881-1892
+        "take_5": A.take(5, mat5x10), "drop_7": A.drop(7, mat5x10),                                   # Prelude.hs:1925, 1952
+        "init_mat": A.init(mat5x10), "tail_mat": A.tail(mat5x10),                                     # Prelude.hs:1978, 2004
+    }
+
+
 def expected(key, got):
     """The reference's expected value in the layout `got` has (ndarray or tuple of leaves)."""
     v = VECTORS[key]

@@ -27,5 +27,25 @@ def test_oracle_matches_reference_closed_form(key):
     similar(got, want, **tol)
 
 
+PRELUDE = G.prelude_cases()
+
+
+@pytest.mark.parametrize("key", sorted(PRELUDE))
+def test_oracle_matches_reference_prelude_example(key):
+    got = oracle.run(PRELUDE[key])
+    if isinstance(got, tuple):          # nested tuples (an index paired with a value) are their leaves in order
+        got = tuple(got)
+    similar(got, G.expected(key, got))
+
+
+@pytest.mark.parametrize("key", ["replicate_two", "slice_sl1_cube", "indexed_mat", "all_even", "enumFromStepN_mat", "concatOn_2",
+                                 "filter_odd_mat_0", "gatherIf", "transposeOn_box_13", "postscanl_vec"])
+def test_prelude_examples_compile_for_the_gpu(key):
+    # (these programs are run on the oracle only; their kernels are the skeletons the GPU suite exercises)
+    import accelerate_b200 as A
+    from accelerate_b200 import backend
+    assert "ok" in backend.compile_check(A.build_program(PRELUDE[key]).text)
+
+
 def test_every_extracted_vector_is_used():
-    assert set(G.VECTORS) == set(CASES)
+    assert set(G.VECTORS) == set(CASES) | set(PRELUDE)
