@@ -1004,6 +1004,27 @@ def tail(a):
     return _drop_inner(1, a)
 
 
+def expand(f, g, xs):
+    """``expand`` (Prelude.hs:2519-2560): every element x becomes the ``f x`` elements ``g x 0 .. g x (f x - 1)``,
+    all in one vector (flattening by expansion: head flags from the sizes' offsets, a segmented iota and a
+    segmented copy of the source positions)."""
+    xs = compute(use(xs))
+    szs = compute(map_(f, xs))
+    offset, ln = scanl_prime(lambda x, y: x + y, constant(0), szs)
+    m = the(ln)
+    n = m + 1
+    put = lambda ix: Just_(index(offset[ix]))  # noqa: E731
+    head_flags = permute(lambda new, old: new, fill(index(n), constant(0)), put, fill(szs.shape, constant(1)))
+    plus = segmentedL(lambda x, y: x + y)
+    idxs = map_(lambda p: p[1] - 1, scanl1(plus, zip_(head_flags, fill(index(m), constant(1)))))
+    starts = permute(lambda new, old: new, fill(index(n), undef(INT)),
+                     lambda ix: cond(szs[ix] > 0, put(ix), Nothing_(1)), enumFromN(xs.shape, constant(0)))
+    iotas = map_(lambda p: p[1], scanl1(segmentedL(lambda x, y: x), zip_(head_flags, starts)))
+    full = zipWith(g, gather(iotas, xs), idxs)
+    empty = generate(index(0), lambda ix: undef(full.elt), full.elt)
+    return acond(lor(xs.size().eq(0), m.eq(0)), empty, full)
+
+
 def mkHeadFlags(seg):
     """Head flags of a segment descriptor for left scans: non-zero where a segment starts; a value
     above one stands for that many segments starting there (empty ones) (Prelude.hs:1364-1375)."""

@@ -172,6 +172,7 @@ def main(ref):
             ("drop_7", "run $ drop 7 (use mat)", 1),
             ("init_mat", "run $ init (use mat)", 1),
             ("tail_mat", "run $ tail (use mat)", 1),
+            ("primes_100", "run $ primes 100", 1),
         ],
     }
     for fname, cases in doc_cases.items():

@@ -123,6 +123,24 @@ def cases():
     return c
 
 
+def _primes(n):
+    # the sieve of Prelude.hs:2478-2508: awhile over (primes so far, upper bound), each trip expanding the
+    # known primes into their multiples, knocking those out with a permute, filtering what is left
+    n = A.constant(n)
+    limit = A.truncate(A.sqrt(A.from_integral(n + 1, "f32")))
+
+    def step(st):
+        old, c = st
+        c1 = A.the(c)
+        c2 = A.cond(c1 < limit, c1 * c1, n + 1)
+        sieves = A.compute(A.map(lambda v: v - c1, A.expand(lambda p: A.quot(c2 - p, p), lambda p, i: (2 + i) * p, old)))
+        m = c2 - c1
+        put = lambda ix: A.let_(sieves[ix], lambda s: A.cond(A.land(s >= 0, s < m), A.Just_(A.index(s)), A.Nothing_(1)))  # noqa: E731
+        left = A.permute(lambda a, b: a, A.enumFromN(A.index(m), c1), put, A.fill(sieves.shape, A.constant(0)))
+        return (A.append(old, A.filter_(lambda v: v > 0, left)[0]), A.unit(c2))
+    return A.awhile(lambda st: A.map(lambda c: c < n + 1, st[1]), step, (A.use(np.zeros(0, I)), A.unit(A.constant(2))))[0]
+
+
 def prelude_cases():
     """Further haddock examples of Language.hs and Prelude.hs: combinators the reference builds from
     the operations of the hot path (backpermute, generate, fold, scanl', permute), restated through the
@@ -183,6 +201,7 @@ def prelude_cases():
         "transposeOn_box_13": A.transposeOn(1, 3, box),                                               # Prelude.hs:1881-1892
         "take_5": A.take(5, mat5x10), "drop_7": A.drop(7, mat5x10),                                   # Prelude.hs:1925, 1952
         "init_mat": A.init(mat5x10), "tail_mat": A.tail(mat5x10),                                     # Prelude.hs:1978, 2004
+        "primes_100": _primes(100),                                                                   # Prelude.hs:2478-2512
     }
 
 

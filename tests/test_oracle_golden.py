@@ -39,7 +39,7 @@ def test_oracle_matches_reference_prelude_example(key):
 
 
 @pytest.mark.parametrize("key", ["replicate_two", "slice_sl1_cube", "indexed_mat", "all_even", "enumFromStepN_mat", "concatOn_2",
-                                 "filter_odd_mat_0", "gatherIf", "transposeOn_box_13", "postscanl_vec"])
+                                 "filter_odd_mat_0", "gatherIf", "transposeOn_box_13", "postscanl_vec", "primes_100"])
 def test_prelude_examples_compile_for_the_gpu(key):
     # (these programs are run on the oracle only; their kernels are the skeletons the GPU suite exercises)
     import accelerate_b200 as A
