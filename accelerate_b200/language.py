@@ -260,6 +260,13 @@ for _n in ("sin cos tan asin acos atan sinh cosh tanh asinh acosh atanh exp sqrt
 signum = _prim1("sig")
 
 
+def iterate(n, f, z):
+    """``iterate n f z`` (Prelude.hs:2320-2328): ``f`` applied ``n`` times, as a ``while`` over (count, value)."""
+    z = z if isinstance(z, Exp) else constant(z)
+    n = lift(n, INT)
+    return while_(lambda v: v[0] < n, lambda v: tup(v[0] + 1, f(v[1])), tup(constant(0), z))[1]
+
+
 def is_nan(x): return x._un("isnan", BOOL)
 def is_infinite(x): return x._un("isinf", BOOL)
 def pop_count(x): return x._un("popcount", INT)
@@ -290,6 +297,17 @@ def min_(a, b):
 def land(a, b): return Exp(BOOL, f"(prim land u8 {a.sx} {b.sx})", a.deps | b.deps)
 def lor(a, b): return Exp(BOOL, f"(prim lor u8 {a.sx} {b.sx})", a.deps | b.deps)
 def lnot(a): return Exp(BOOL, f"(prim lnot u8 {a.sx})", a.deps)
+
+
+def and_(a, b):
+    """``(&&)`` (Classes/Eq.hs:57-62): a conditional, so the second operand is evaluated only when the
+    first holds (``land`` is the strict ``(&&!)``)."""
+    return cond(a, b, Exp(BOOL, "(const u8 0)"))
+
+
+def or_(a, b):
+    """``(||)`` (Classes/Eq.hs:78-83): the second operand is evaluated only when the first fails."""
+    return cond(a, Exp(BOOL, "(const u8 1)"), b)
 
 
 def _conv(op, x, to):
@@ -426,11 +444,11 @@ def use(a, elt=None):
     if isinstance(a, Acc):
         return a
     if isinstance(a, (tuple, list)):
-        leaves = [np.ascontiguousarray(x) for x in a]
+        leaves = [np.asarray(x, order="C") for x in a]          # (keeps a 0-d array a Scalar)
         if elt is None:
             elt = tuple(TY_OF_NP[x.dtype] for x in leaves)
     else:
-        a = np.ascontiguousarray(a)
+        a = np.asarray(a, order="C")
         leaves = [a.view(np.uint8) if a.dtype == np.bool_ else a]
         elt = elt or TY_OF_NP[a.dtype]
     sh = tuple(int(d) for d in leaves[0].shape)
@@ -838,6 +856,12 @@ def slice(a, slix):  # noqa: A001
     return backpermute(index(*[ash[d] for d in kept]), src, a)
 
 
+def imap(f, a):
+    """``imap`` (Prelude.hs:177-181): map with the element's index."""
+    a = use(a)
+    return generate(a.shape, lambda ix: f(ix, a[ix]))
+
+
 def indexed(a):
     """``indexed`` (Prelude.hs:172-173: ``imap T2``): each element paired with its index."""
     a = use(a)
@@ -861,12 +885,12 @@ def fold1All(f, a):
 
 def all_(p, a):
     """``all`` (Prelude.hs:780-784, 807-810): ``and . map p``, ``and = fold (&&) True``."""
-    return fold(land, Exp(BOOL, "(const u8 1)"), map_(p, a))
+    return fold(and_, Exp(BOOL, "(const u8 1)"), map_(p, a))
 
 
 def any_(p, a):
     """``any`` (Prelude.hs:799-803, 814-817): ``or . map p``."""
-    return fold(lor, Exp(BOOL, "(const u8 0)"), map_(p, a))
+    return fold(or_, Exp(BOOL, "(const u8 0)"), map_(p, a))
 
 
 def prescanl(f, e, a):
@@ -1022,7 +1046,7 @@ def expand(f, g, xs):
     iotas = map_(lambda p: p[1], scanl1(segmentedL(lambda x, y: x), zip_(head_flags, starts)))
     full = zipWith(g, gather(iotas, xs), idxs)
     empty = generate(index(0), lambda ix: undef(full.elt), full.elt)
-    return acond(lor(xs.size().eq(0), m.eq(0)), empty, full)
+    return acond(or_(xs.size().eq(0), m.eq(0)), empty, full)
 
 
 def mkHeadFlags(seg):

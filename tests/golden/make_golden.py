@@ -191,6 +191,29 @@ def main(ref):
             line, shape, vals = issue_list(lines, nm)
             add(f"{fname[:-3].lower()}_{nm}", path, line, shape, vals)
 
+    # Issue102: one expected array.  Issue119: eleven folds and segmented scans whose inputs, segment
+    # descriptors and expected results are all literals of the test (every `fromList`, in file order,
+    # under the name it is bound to, numbered per test).
+    path = os.path.join(issues, "Issue102.hs")
+    line, shape, vals = issue_list(open(path, encoding="utf-8").read().splitlines(), "ref1")
+    add("issue102_ref1", path, line, shape, vals)
+    path = os.path.join(issues, "Issue119.hs")
+    big = {}
+    current = None
+    for i, l in enumerate(open(path, encoding="utf-8").read().splitlines()):
+        m = re.match(r"(ref|test)(\d+)\s*=", l)
+        if m:
+            current = m.group(2)
+        m = re.match(r"\s*(ref\d+|xs|seg|ps|rs)\s*=.*fromList\s*(\(Z[^)]*\)|Z)\s*\[([^\]]*)\]", l)
+        if m and current:
+            name = m.group(1) if not m.group(1).startswith("ref") else "ref"
+            big[f"{current}_{name}"] = {"source": f"{os.path.relpath(path, ref)}:{i + 1}",
+                                        "shape": [int(x) for x in re.findall(r"\d+", m.group(2))],
+                                        "values": [int(v) for v in NUM.findall(m.group(3))]}
+    dst119 = os.path.join(os.path.dirname(os.path.abspath(__file__)), "issue119.json")
+    json.dump(big, open(dst119, "w"), sort_keys=True)
+    print(f"wrote {len(big)} arrays to {dst119}")
+
     dst = os.path.join(os.path.dirname(os.path.abspath(__file__)), "reference_vectors.json")
     json.dump(out, open(dst, "w"), indent=1, sort_keys=True)
     print(f"wrote {len(out)} cases to {dst}")

@@ -205,6 +205,107 @@ def prelude_cases():
     }
 
 
+ISSUE119 = json.load(open(os.path.join(HERE, "golden", "issue119.json")))
+
+
+def _i119(key, dtype):
+    v = ISSUE119[key]
+    return np.array(v["values"], dtype=dtype).reshape(tuple(v["shape"]))
+
+
+def _issue102():
+    # Test/NoFib/Issues/Issue102.hs:36-63: a DFT written with reshape, replicate and fold
+    p, lts, rts, rustride = 3, 1, 1, 1
+    v = A.fill(A.index(p - 1), A.constant(2))
+    ru = A.fill(A.index(p - 1), A.constant(1))
+    x1 = A.reshape(A.index(lts, p - 1, rts), v)
+    y = A.generate(A.index(lts, p, rts), lambda ix: A.cond(ix[1].eq(0), A.constant(0), x1[A.index(ix[0], ix[1] - 1, ix[2])]))
+    y1 = A.reshape(A.index(lts, p, rts), A.flatten(y))
+    dftrus = A.generate(A.index(p, p), lambda ix: ru[A.index((ix[0] * ix[1] * rustride) % p)])
+    coeffs = A.compute(A.replicate((lts, A.All, rts, A.All), dftrus))
+    inputs = A.generate(coeffs.shape, lambda ix: y1[A.index(ix[0], ix[3], ix[2])])
+    ans = A.flatten(A.fold(add, A.constant(0), A.zipWith(lambda a, b: a * b, coeffs, inputs)))
+    return A.reshape(A.use(y).shape, ans)
+
+
+def _issue287_f(x, y):
+    # Test/NoFib/Issues/Issue287.hs:52-64
+    return A.tup(A.max_(x[0], x[5] + y[1]), x[1], x[2], y[3] * x[3], x[4], y[5])
+
+
+def issue_cases():
+    """More of the reference's regression tests (Test/NoFib/Issues/): `(term, expected)` with the expected
+    value as the test states it (the literals of Issue102 and Issue119 come from the fixture files)."""
+    out = {}
+    out["issue102"] = (_issue102(), np.array(VECTORS["issue102_ref1"]["values"], I).reshape(1, 3, 1))
+    # Issue119.hs:48-98: foldAll / fold of Int32 and Int64 matrices (sums that wrap in Int32)
+    for k, dt in (("1", np.int32), ("2", np.int32), ("3", np.int64), ("4", np.int64)):
+        out[f"issue119_{k}"] = (A.foldAll(add, dt(0), _i119(f"{k}_xs", dt)), _i119(f"{k}_ref", dt))
+    out["issue119_5"] = (A.fold(add, np.int32(0), _i119("5_xs", np.int32)), _i119("5_ref", np.int32))
+    # Issue119.hs:100-186: the six segmented scans over Int64 with Int32 segment descriptors
+    seg = lambda k: _i119(f"{k}_seg", np.int32)  # noqa: E731
+    xs = lambda k: _i119(f"{k}_xs", np.int64)  # noqa: E731
+    out["issue119_6"] = (A.scanl1Seg(add, xs(6), seg(6)), _i119("6_ref", np.int64))
+    out["issue119_7"] = (A.scanr1Seg(add, xs(7), seg(7)), _i119("7_ref", np.int64))
+    out["issue119_8"] = (A.scanlSeg(add, np.int64(0), xs(8), seg(8)), _i119("8_ref", np.int64))
+    out["issue119_9"] = (A.scanrSeg(add, np.int64(0), xs(9), seg(9)), _i119("9_ref", np.int64))
+    p10, r10 = A.scanl_primeSeg(add, np.int64(0), xs(10), seg(10))
+    out["issue119_10_ps"], out["issue119_10_rs"] = (p10, _i119("10_ps", np.int64)), (r10, _i119("10_rs", np.int64))
+    p11, r11 = A.scanr_primeSeg(add, np.int64(0), xs(11), seg(11))
+    out["issue119_11_ps"], out["issue119_11_rs"] = (p11, _i119("11_ps", np.int64)), (r11, _i119("11_rs", np.int64))
+    out["issue123"] = (A.fold(add, 0, A.fill(A.index(100), A.constant(1))), np.array(100, I))        # Issue123.hs:30-41
+    # Issue168.hs:29-58: iterate on tuples
+    q1 = lambda t: A.tup(A.constant(np.float32(3)), t[0])  # noqa: E731
+    d1 = A.tup(A.constant(np.float32(2)), A.constant(np.float32(1)))
+    out["issue168_A"] = (A.fill(A.index(1), q1(d1)), (np.array([3], np.float32), np.array([2], np.float32)))
+    out["issue168_B"] = (A.fill(A.index(1), A.iterate(1, q1, d1)), (np.array([3], np.float32), np.array([2], np.float32)))
+    d3 = A.tup(*[A.constant(np.float32(v)) for v in (6, 5, 4, 3, 2, 1)])
+    out["issue168_C"] = (A.fill(A.index(1), A.iterate(1, lambda t: A.tup(*[t[5 - k] for k in range(6)]), d3)),
+                         tuple(np.array([v], np.float32) for v in (1, 2, 3, 4, 5, 6)))
+    # Issue184.hs:36-63, Issue187.hs:31-52: what a conditional does not choose is not evaluated, so the
+    # read at linear index -1 never happens
+    v5 = A.use(np.array([1, 2, 3, 4, 5], I))
+    want184 = np.zeros(1000, I)
+    want184[:5] = [1, 4, 9, 16, 25]
+    out["issue184_A"] = (A.generate(A.index(1000), lambda ix: A.cond(ix[0] < 5, A.let_(v5.linear(ix[0]), lambda y: y * y), A.constant(0))), want184)
+    one = A.constant(1)
+    out["issue184_B"] = (A.unit(A.or_(one.eq(1), v5.linear(-1).eq(1))), np.array(1, np.uint8))
+    out["issue184_C"] = (A.unit(A.and_(one.ne(1), v5.linear(-1).eq(1))), np.array(0, np.uint8))
+    out["issue187_A"] = (A.generate(A.index(), lambda ix: A.or_(one.eq(1), v5.linear(-1).eq(1))), np.array(1, np.uint8))
+    x1 = A.unit(one)
+    out["issue187_B"] = (A.generate(A.index(), lambda ix: A.or_(one.eq(A.the(x1)), A.let_(v5.linear(-1), lambda y: (y * y).eq(1)))),
+                         np.array(1, np.uint8))
+    # Issue287.hs:34-50: scans of six-component tuples of zeros stay zeros
+    z6 = tuple(np.zeros(4, I) for _ in range(6))
+    s22 = np.array([2, 2], I)
+    out["issue287_A"] = (A.scanl1(_issue287_f, z6), z6)
+    out["issue287_B"] = (A.scanl1Seg(lambda a, b: b, z6, s22), z6)
+    out["issue287_C"] = (A.scanl1Seg(_issue287_f, z6, s22), z6)
+    # Issue288.hs:29-37: a while whose condition is False from the start is the identity
+    t10 = (np.arange(1, 11, dtype=I), np.arange(1, 11, dtype=I))
+    out["issue288"] = (A.map(lambda e: A.while_(lambda _: A.constant(False), lambda v: v, e), t10), t10)
+    # Issue407.hs:29-47
+    for ty, dt in (("f32", np.float32), ("f64", np.float64)):
+        with np.errstate(all="ignore"):
+            fl = np.array([np.nan, -np.inf, np.nan, 0.1, np.inf, 0.5, np.inf], dt)
+        out[f"issue407_isnan_{ty}"] = (A.map(A.is_nan, fl), np.array([1, 0, 1, 0, 0, 0, 0], np.uint8))
+        out[f"issue407_isinf_{ty}"] = (A.map(A.is_infinite, fl), np.array([0, 1, 0, 0, 1, 0, 1], np.uint8))
+        # Issue409.hs:29-50: y + tanh ((-y) * y) with y = recip x shared, at x = 1
+        f409 = lambda x: A.let_(A.recip(x), lambda y: y + A.tanh((-y) * y))  # noqa: E731
+        out[f"issue409_{ty}"] = (A.map(f409, np.array(1, dt)), np.array(dt(1) + np.tanh(dt(-1)), dt))
+    # Issue436.hs:31-56: filter (const True) of take 3
+    b5 = np.array([1, 0, 1, 0, 1], np.uint8)
+    r1, n1 = A.filter_(lambda _: A.constant(True), A.take(3, b5))
+    out["issue436_A_0"], out["issue436_A_1"] = (r1, np.array([1, 0, 1], np.uint8)), (n1, np.array(3, I))
+    b55 = np.resize(np.array([1, 0], np.uint8), 25).reshape(5, 5)
+    r2, n2 = A.filter_(lambda _: A.constant(True), A.take(3, b55))
+    out["issue436_B_0"] = (r2, np.array([1, 0, 1, 0, 1, 0, 1, 0, 1, 0, 1, 0, 1, 0, 1], np.uint8))
+    out["issue436_B_1"] = (n2, np.full(5, 3, I))
+    # Issue439.hs:28-37
+    out["issue439"] = (A.compute(A.map(lambda v: v * 2, A.compute(A.fill(A.index(), A.constant(np.float32(1)))))), np.array(2, np.float32))
+    return out
+
+
 def expected(key, got):
     """The reference's expected value in the layout `got` has (ndarray or tuple of leaves)."""
     v = VECTORS[key]

@@ -47,5 +47,22 @@ def test_prelude_examples_compile_for_the_gpu(key):
     assert "ok" in backend.compile_check(A.build_program(PRELUDE[key]).text)
 
 
+ISSUES = G.issue_cases()
+
+
+@pytest.mark.parametrize("key", sorted(ISSUES))
+def test_oracle_matches_reference_regression_test(key):
+    term, want = ISSUES[key]
+    tol = dict(rtol=5e-3, atol=5e-5) if key.startswith("issue409") else {}     # Test/Similar.hs:90-93
+    similar(oracle.run(term), want, **tol)
+
+
+@pytest.mark.parametrize("key", ["issue102", "issue119_2", "issue119_10_ps", "issue168_C", "issue184_B", "issue287_C", "issue436_B_0"])
+def test_regression_tests_compile_for_the_gpu(key):
+    import accelerate_b200 as A
+    from accelerate_b200 import backend
+    assert "ok" in backend.compile_check(A.build_program(ISSUES[key][0]).text)
+
+
 def test_every_extracted_vector_is_used():
-    assert set(G.VECTORS) == set(CASES) | set(PRELUDE)
+    assert set(G.VECTORS) == set(CASES) | set(PRELUDE) | {"issue102_ref1"}

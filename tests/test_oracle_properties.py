@@ -198,3 +198,33 @@ def test_segmented_scans_match_list_references(seed):
     body, sums = oracle.run(list(A.scanr_primeSeg(f, z, m, sg)))
     assert np.array_equal(body, rows_of(lambda p: rscan(p, True)[1:]))
     assert np.array_equal(sums, rows_of(lambda p: rscan(p, True)[:1]))
+
+
+@settings(max_examples=25, deadline=None)
+@given(st.integers(0, 40), st.integers(0, 1 << 30))
+def test_issue264_negations(n, seed):
+    # Test/NoFib/Issues/Issue264.hs: not.not, not (&&), not (||), their double negations, neg.neg
+    g = np.random.default_rng(seed)
+    x, y = g.integers(0, 2, n).astype(np.uint8), g.integers(0, 2, n).astype(np.uint8)
+    bx, by = x.astype(bool), y.astype(bool)
+    nn = lambda f: (lambda u, v: A.lnot(f(u, v)))  # noqa: E731
+    assert np.array_equal(oracle.run(A.map(A.lnot, A.map(A.lnot, x))), x)
+    assert np.array_equal(oracle.run(A.zipWith(nn(A.and_), x, y)), (~(bx & by)).astype(np.uint8))
+    assert np.array_equal(oracle.run(A.zipWith(nn(A.or_), x, y)), (~(bx | by)).astype(np.uint8))
+    assert np.array_equal(oracle.run(A.zipWith(lambda u, v: A.lnot(nn(A.and_)(u, v)), x, y)), (bx & by).astype(np.uint8))
+    assert np.array_equal(oracle.run(A.zipWith(lambda u, v: A.lnot(nn(A.or_)(u, v)), x, y)), (bx | by).astype(np.uint8))
+    for dt in (np.int8, np.int32, np.uint16, np.uint64, np.float32, np.float64):
+        v = (g.normal(size=n) * 100).astype(dt)
+        assert np.array_equal(oracle.run(A.map(lambda e: -(-e), v)), v)
+
+
+@settings(max_examples=25, deadline=None)
+@given(st.tuples(st.integers(0, 30), st.sampled_from([8, 64, 3, 17])), st.integers(0, 1 << 30))
+def test_issue427_indices_of_truth(shape, seed):
+    # Test/NoFib/Issues/Issue427.hs:52-83: filter over (row, column, flag) triples, the flag dropped afterwards
+    xs = np.random.default_rng(seed).integers(0, 2, size=shape).astype(np.uint8)
+    with_inds = A.imap(lambda ix, b: A.tup(ix[0], ix[1], b), xs)
+    kept = A.filter_(lambda t: t[2].ne(0), with_inds)[0]
+    got = oracle.run(A.map(lambda t: A.tup(t[0], t[1]), kept))
+    want = np.argwhere(xs != 0)
+    assert np.array_equal(got[0], want[:, 0]) and np.array_equal(got[1], want[:, 1])
