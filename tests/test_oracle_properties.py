@@ -228,3 +228,65 @@ def test_issue427_indices_of_truth(shape, seed):
     got = oracle.run(A.map(lambda t: A.tup(t[0], t[1]), kept))
     want = np.argwhere(xs != 0)
     assert np.array_equal(got[0], want[:, 0]) and np.array_equal(got[1], want[:, 1])
+
+
+def _black_scholes(lib, price, strike, years, one, c):
+    """Call and put prices the way Test/NoFib/Spectral/BlackScholes.hs:72-100 writes them; `lib` supplies
+    sqrt/log/exp/abs and the choice `where_(cond, a, b)`, `c` turns a Python number into the element type."""
+    r, v = c(0.02), c(0.30)
+    v_sqrt_t = v * lib.sqrt(years)
+    d1 = (lib.log(price / strike) + (r + c(0.5) * v * v) * years) / v_sqrt_t
+    d2 = d1 - v_sqrt_t
+
+    def cnd(d):
+        k = one / (one + c(0.2316419) * lib.abs(d))
+        coeff = [0.31938153, -0.356563782, 1.781477937, -1.821255978, 1.330274429]
+        acc = c(coeff[-1])
+        for a in coeff[-2::-1]:                      # horner: x * foldr1 (\a b -> a + x*b) coeff
+            acc = c(a) + k * acc
+        p = c(0.39894228040143267793994605993438) * lib.exp(c(-0.5) * d * d) * (k * acc)
+        return lib.where_(d > 0, one - p, p)
+    n1, n2 = cnd(d1), cnd(d2)
+    x_exp_rt = strike * lib.exp(-r * years)
+    return price * n1 - x_exp_rt * n2, x_exp_rt * (one - n2) - price * (one - n1)
+
+
+class _NumpyLib:
+    sqrt, log, exp, abs = np.sqrt, np.log, np.exp, np.abs
+    where_ = staticmethod(np.where)
+
+
+class _AccLib:
+    sqrt, log, exp = A.sqrt, A.log, A.exp
+    abs = staticmethod(abs)
+    where_ = staticmethod(A.cond)
+
+
+@settings(max_examples=10, deadline=None)
+@given(st.integers(0, 300), st.sampled_from(["f32", "f64"]), st.integers(0, 1 << 30))
+def test_black_scholes_matches_numpy(n, ty, seed):
+    dt = A.NP_OF[ty]
+    g = np.random.default_rng(seed)
+    price, strike, years = (g.uniform(5, 30, n).astype(dt), g.uniform(1, 100, n).astype(dt), g.uniform(0.25, 10, n).astype(dt))
+    psy = A.use((price, strike, years))
+    got = oracle.run(A.map(lambda t: A.tup(*_black_scholes(_AccLib, t[0], t[1], t[2], A.constant(dt(1)), lambda x: A.constant(dt(x)))), psy))
+    want = _black_scholes(_NumpyLib, price, strike, years, dt(1), dt)
+    for gv, wv in zip(got, want):                    # Test/Similar.hs:90-93: Float 5e-5 / 5e-3, Double 5e-9 / 5e-7
+        tol = (5e-5, 5e-3) if ty == "f32" else (5e-9, 5e-7)
+        assert np.all((np.abs(gv - wv) <= tol[0]) | (np.abs(gv - wv) <= tol[1] * np.maximum(np.abs(gv), np.abs(wv))))
+
+
+@settings(max_examples=15, deadline=None)
+@given(st.integers(0, 400), st.integers(0, 1 << 30))
+def test_saxpy_and_sasum_match_numpy(n, seed):
+    # Test/NoFib/Imaginary/SAXPY.hs:77-81 (zipWith (\x y -> alpha * x + y)) and SASUM.hs:74-78 (fold (+) 0 . map abs)
+    g = np.random.default_rng(seed)
+    x, y = g.normal(size=n).astype(np.float32), g.normal(size=n).astype(np.float32)
+    alpha = np.float32(g.normal())
+    assert np.array_equal(oracle.run(A.zipWith(lambda u, v: A.constant(alpha) * u + v, x, y)), alpha * x + y)
+    acc = np.float32(0)
+    for v in np.abs(x):
+        acc = np.float32(acc + v)
+    assert oracle.run(A.fold(add, np.float32(0), A.map(abs, x))) == acc
+    xi = g.integers(-1000, 1000, n).astype(np.int32)
+    assert oracle.run(A.fold(add, np.int32(0), A.map(abs, xi))) == np.abs(xi).sum(dtype=np.int32)
