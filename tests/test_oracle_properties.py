@@ -290,3 +290,22 @@ def test_saxpy_and_sasum_match_numpy(n, seed):
     assert oracle.run(A.fold(add, np.float32(0), A.map(abs, x))) == acc
     xi = g.integers(-1000, 1000, n).astype(np.int32)
     assert oracle.run(A.fold(add, np.int32(0), A.map(abs, xi))) == np.abs(xi).sum(dtype=np.int32)
+
+
+@settings(max_examples=30, deadline=None)
+@given(st.integers(1, 3), st.sampled_from(["i8", "i32", "u16", "u64", "f16", "f32", "f64"]), st.integers(0, 1 << 30))
+def test_filter_matches_list_reference(rank, ty, seed):
+    # Test/NoFib/Prelude/Filter.hs:96-124: `filter even` on integral and `filter (> 0)` on floating elements,
+    # ranks 1 to 3: the kept elements in row-major order, and how many every innermost row kept
+    g = np.random.default_rng(seed)
+    shape = tuple(int(d) for d in g.integers(0, 9, size=rank))
+    dt = A.NP_OF[ty]
+    if np.issubdtype(dt, np.integer):
+        xs = g.integers(0, 100, size=shape).astype(dt)
+        keep, pred = xs % 2 == 0, (lambda v: (v % 2).eq(0))
+    else:
+        xs = g.normal(size=shape).astype(dt)
+        keep, pred = xs > 0, (lambda v: v > 0)
+    vals, counts = oracle.run(list(A.filter_(pred, xs)))
+    assert np.array_equal(vals, xs[keep]) and vals.dtype == dt
+    assert np.array_equal(counts, keep.sum(axis=-1)) and counts.shape == shape[:-1]
