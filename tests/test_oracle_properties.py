@@ -309,3 +309,49 @@ def test_filter_matches_list_reference(rank, ty, seed):
     vals, counts = oracle.run(list(A.filter_(pred, xs)))
     assert np.array_equal(vals, xs[keep]) and vals.dtype == dt
     assert np.array_equal(counts, keep.sum(axis=-1)) and counts.shape == shape[:-1]
+
+
+def _shape(g, rank, lo):
+    return tuple(int(d) for d in g.integers(lo, 6, size=rank))
+
+
+@settings(max_examples=40, deadline=None)
+@given(st.integers(1, 3), st.integers(1, 3), st.integers(0, 1 << 30))
+def test_gather_scatter_accumulate_between_ranks(rank, rank2, seed):
+    # Test/NoFib/Prelude/Backpermute.hs:131-153 (gather->DIMn) and Permute.hs:96-160 (scatter->DIMn with
+    # unique or absent targets, accumulate->DIMn with Maybe targets): arrays of indices of another rank
+    g = np.random.default_rng(seed)
+    sh, sh2 = _shape(g, rank, 1), _shape(g, rank2, 0)
+    xs = g.integers(-50, 50, size=sh).astype(np.int64)
+    # gather: an array of shape sh2 of indices into xs
+    lin = g.integers(0, xs.size, size=sh2)
+    ixs = tuple(np.ascontiguousarray(c).astype(np.int64) for c in np.unravel_index(lin, sh))
+    iu = A.use(ixs)
+    got = oracle.run(A.backpermute(iu.shape, lambda j: iu[j], xs))
+    assert np.array_equal(got, xs.reshape(-1)[lin])
+    # scatter / accumulate: an array of shape sh of Maybe indices into a target of shape sh3 (not empty)
+    sh3 = _shape(g, rank2, 1)
+    n3 = int(np.prod(sh3))
+    tgt = g.integers(0, n3, size=sh)
+    absent = g.random(sh) < 0.4
+    comps = tuple(np.ascontiguousarray(c).astype(np.int64) for c in np.unravel_index(tgt, sh3))
+    mu = A.use((np.where(absent, 0, 1).astype(np.uint8),) + comps)
+    dest = lambda j: A.let_(mu[j], lambda m: A.tup(m[0], A.index(*[m[1 + d] for d in range(rank2)])))  # noqa: E731
+    want = np.zeros(n3, np.int64)
+    np.add.at(want, tgt[~absent], xs[~absent])
+    got = oracle.run(A.permute(add, A.fill(A.index(*sh3), A.constant(0)), dest, xs))
+    assert np.array_equal(got, want.reshape(sh3))
+    # `permute const` where no two sources share a target (the reference draws them that way)
+    first = np.zeros(tgt.shape, bool)
+    seen = set()
+    for pos in np.ndindex(*sh):
+        if not absent[pos] and int(tgt[pos]) not in seen:
+            seen.add(int(tgt[pos]))
+            first[pos] = True
+    mu2 = A.use((first.astype(np.uint8),) + comps)
+    dest2 = lambda j: A.let_(mu2[j], lambda m: A.tup(m[0], A.index(*[m[1 + d] for d in range(rank2)])))  # noqa: E731
+    defaults = g.integers(-9, 9, size=sh3).astype(np.int64)
+    want2 = defaults.reshape(-1).copy()
+    want2[tgt[first]] = xs[first]
+    got = oracle.run(A.permute(lambda new, old: new, defaults, dest2, xs))
+    assert np.array_equal(got, want2.reshape(sh3))
