@@ -55,3 +55,18 @@ def test_simd_type_errors():
 @pytest.mark.parametrize("key", ["extract_v3_f16_2", "inject_v4_u8", "fold_sum_v3_i32", "scanl1_sum_v3_i32", "complex_square_v2_f64"])
 def test_simd_programs_compile(key):
     assert "ok" in backend.compile_check(A.build_program(CASES[key][0]).text)
+
+
+def test_vectors_through_control_nodes_and_as_scalars():
+    x = simd_cases.data("f32", (4, 3), 2)
+    xs = A.use(x, elt=A.vec(3, "f32"))
+    rot = lambda v: A.vec_pack(*[A.vec_unpack(v)[(k + 1) % 3] for k in range(3)])  # noqa: E731
+    assert np.array_equal(oracle.run(A.compute(xs)), x)                              # in and straight out again
+    st = A.awhile(lambda s: A.map(lambda c: c < 2, s[1]), lambda s: (A.map(rot, s[0]), A.map(lambda c: c + 1, s[1])),
+                  (xs, A.unit(A.constant(0))))
+    assert np.array_equal(oracle.run(st[0]), np.roll(x, -2, axis=1))
+    assert "ok" in backend.compile_check(A.build_program(st[0]).text)
+    pick = A.acond(A.the(A.unit(A.constant(1))).eq(1), A.map(rot, xs), xs)
+    assert np.array_equal(oracle.run(pick), np.roll(x, -1, axis=1))
+    one = A.use(np.array([1, 2], np.int32), elt=A.vec(2, "i32"))                     # a Scalar of a vector
+    assert one.rank == 0 and int(oracle.run(A.map(lambda v: A.vec_unpack(v)[0] + A.vec_unpack(v)[1], one))) == 3
